@@ -1,0 +1,379 @@
+#!/usr/bin/env python
+"""Benchmark of the uneven-collective hot path (the reference's collective micro-benchmark
+configuration: a (256, C) tensor split on dim 0 by ratios [.22,.18,.15,.13,.11,.09,.07,.05]).
+
+    python bench.py --gpus 1 --steps K --warmup W            # 8 virtual ranks on one GPU (HBM bound)
+    torchrun --nproc-per-node N ... bench.py --gpus N ...    # one rank per GPU over NVLink (N = 2, 4, 8)
+    python bench.py --impl reference ...                     # the CPU port of the reference on gloo ranks
+
+A step = one uneven all_gather + one reduce_scatter + one all_reduce of a tensor of
+``--size-mib`` MiB.  ``value`` is the nccl-tests style bus bandwidth of the step
+(bus bytes = S(W-1)/W + S(W-1)/W + 2S(W-1)/W), summed over the GPUs of the job.
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+R8 = [.22, .18, .15, .13, .11, .09, .07, .05]
+ROWS = 256
+NVLINK_NOMINAL_GBS = 900.0      # per direction per GPU
+NVLINK_MEASURED_GBS = 770.0     # peer copy measured on this pool
+
+
+def ratios_for(world):
+    r = R8[:world]
+    s = sum(r)
+    return [x / s for x in r]
+
+
+def bus_bytes(S, W):
+    return 4.0 * S * (W - 1) / W
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f), "measured"
+    except OSError:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU arm: the gloo port of the reference's collectives on the host cores
+# ----------------------------------------------------------------------------------------------
+def _cpu_worker(rank, world, store, size_bytes, steps, warmup, threads, out_path):
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    from oracle import gloo_port as gp
+    from oracle.sharding_round import sharding_round
+    torch.set_num_threads(max(1, threads))
+    dist.init_process_group("gloo", rank=rank, world_size=world, init_method=f"file://{store}")
+    cols = size_bytes // (ROWS * 4)
+    L = sharding_round(ROWS, ratios_for(world))
+    g = torch.Generator().manual_seed(1000 + rank)
+    shard = torch.randn(L[rank], cols, generator=g)
+    full = torch.randn(ROWS, cols, generator=g)
+    times = []
+    for it in range(warmup + steps):
+        dist.barrier()
+        t0 = time.perf_counter()
+        gp.all_gather(shard, 0, L, rank)
+        gp.reduce_scatter(full, 0, L, rank)
+        gp.all_reduce(full)
+        dist.barrier()
+        if it >= warmup:
+            times.append(time.perf_counter() - t0)
+    if rank == 0:
+        with open(out_path, "w") as f:
+            json.dump(times, f)
+    dist.destroy_process_group()
+
+
+def run_cpu_arm(world, size_bytes, steps, warmup):
+    import torch.multiprocessing as mp
+    cores = os.cpu_count() or 1
+    threads = max(1, cores // world)
+    with tempfile.TemporaryDirectory() as d:
+        out = os.path.join(d, "times.json")
+        mp.spawn(_cpu_worker, args=(world, os.path.join(d, "store"), size_bytes, steps, warmup, threads, out),
+                 nprocs=world, join=True)
+        times = json.load(open(out))
+    mean = sum(times) / len(times)
+    return {"value": bus_bytes(size_bytes, world) / mean / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+            "sample": f"{world} gloo ranks x {threads} threads, fp32 tensor of {size_bytes >> 20} MiB, "
+                      f"{steps} steps after {warmup} warm-ups (padding-mode all_gather + reduce_scatter + all_reduce)",
+            "ms_per_step": mean * 1e3}
+
+
+# ----------------------------------------------------------------------------------------------
+# clocks during the timed region (read-only NVML)
+# ----------------------------------------------------------------------------------------------
+class ClockSampler(threading.Thread):
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_evt = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                mask = self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop_evt.wait(0.1)
+
+    def finish(self):
+        self._stop_evt.set()
+        self.join(timeout=2)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------
+def run_gpu_arm(args):
+    import torch
+    import hap_b200
+    from hap_b200 import _native as N
+
+    n_gpus = args.gpus
+    rank = int(os.environ.get("RANK", 0))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    world_env = int(os.environ.get("WORLD_SIZE", 1))
+    if n_gpus > 1 and world_env != n_gpus:
+        raise SystemExit(f"--gpus {n_gpus} needs a launcher with WORLD_SIZE={n_gpus} (torchrun); got {world_env}")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    S = args.size_mib << 20
+    dtype = torch.float32
+    es = 4
+    cols = S // (ROWS * es)
+    emulated = n_gpus == 1
+    W = 8 if emulated else n_gpus
+    L = hap_b200.sharding_round(ROWS, ratios_for(W))
+    stage = (int(S * 1.25) + (64 << 20) + 255) // 256 * 256
+    heap = stage + int(S * 1.3) + (64 << 20)
+
+    if emulated:
+        comm = hap_b200.local_comm(W, dev, heap_bytes=heap, stage_bytes=stage)
+        dist = None
+    else:
+        import torch.distributed as dist
+        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=n_gpus)
+        comm = hap_b200.init_process_comm(heap_bytes=heap, stage_bytes=stage)
+        hap_b200.collectives.set_default_comm(comm)
+    ranks = comm.ranks()
+    nl = comm.n_local
+
+    # inputs resident in the peer-visible heap (read in place by the kernels)
+    shards, fulls = [], []
+    for i, r in enumerate(ranks):
+        g = torch.Generator(dev).manual_seed(1000 + r)
+        sh = comm.symm_empty((L[r], cols), dtype, i)
+        sh.copy_(torch.randn(L[r], cols, device=dev, generator=g))
+        fu = comm.symm_empty((ROWS, cols), dtype, i)
+        fu.copy_(torch.randn(ROWS, cols, device=dev, generator=g))
+        shards.append(sh)
+        fulls.append(fu)
+    ag_out = [torch.empty(ROWS, cols, dtype=dtype, device=dev) for _ in ranks]
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def step(events=None):
+        marks = [ev() for _ in range(4)] if events is not None else None
+        if marks: marks[0].record()
+        comm.all_gather(shards, 0, L, out=ag_out)
+        if marks: marks[1].record()
+        rs = comm.reduce_scatter(fulls, 0, L)
+        if marks: marks[2].record()
+        ar = comm.all_reduce(fulls, scale=1.0 / W)
+        if marks:
+            marks[3].record()
+            events.append(marks)
+        return rs, ar
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    comm.check()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = N.lib.hapx_launch_count()
+    events = []
+    t_begin, t_end = ev(), ev()
+    barrier()
+    t_begin.record()
+    for _ in range(args.steps):
+        step(events)
+    t_end.record()
+    barrier()
+    launches = N.lib.hapx_launch_count() - launches0
+    clocks = sampler.finish()
+    comm.check()
+    total_ms = t_begin.elapsed_time(t_end)
+    op_ms = [sum(m[k].elapsed_time(m[k + 1]) for m in events) / len(events) for k in range(3)]
+
+    def max_over_ranks(x):
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    total_ms = max_over_ranks(total_ms)
+    op_ms = [max_over_ranks(x) for x in op_ms]
+    ms_per_step = total_ms / args.steps
+    busbw = bus_bytes(S, W) / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through the public API with host buffers --------------------------------------
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    host_shards = [torch.randn(L[r], cols).pin_memory() for r in ranks]
+    host_full = torch.randn(ROWS, cols).pin_memory()
+    host_out = [torch.empty(L[r], cols).pin_memory() for r in ranks]
+    lc = hap_b200.LocalCollectives(comm) if emulated else None
+
+    def e2e_step():
+        d_sh = [torch.empty(L[r], cols, device=dev).copy_(h, non_blocking=True) for r, h in zip(ranks, host_shards)]
+        d_fu = [torch.empty(ROWS, cols, device=dev).copy_(host_full, non_blocking=True) for _ in ranks]
+        if emulated:
+            lc.all_gather(d_sh, 0, L)
+            rs = lc.reduce_scatter(d_fu, 0, L)
+            lc.all_reduce(d_fu)
+        else:
+            col = hap_b200.collectives
+            col.all_gather(d_sh[0], 0, L, rank)
+            rs = [col.reduce_scatter(d_fu[0], 0, L, rank)]
+            col.all_reduce(d_fu[0])
+        for o, h in zip(rs, host_out):
+            h.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    b0, b1 = ev(), ev()
+    b0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    b1.record()
+    barrier()
+    e2e_ms = max_over_ranks(b0.elapsed_time(b1)) / e2e_steps
+    comm.check()
+    h2d = sum(h.numel() * 4 for h in host_shards) + nl * host_full.numel() * 4
+    d2h = sum(h.numel() * 4 for h in host_out)
+    if dist is not None:
+        h2d, d2h = h2d * n_gpus, d2h * n_gpus   # whole job (every rank copies its own)
+    e2e = {"value": bus_bytes(S, W) / (e2e_ms * 1e-3) / 1e9 * n_gpus, "unit": "GB/s", "h2d_bytes_per_step": int(h2d),
+           "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms, "steps": e2e_steps,
+           "api": "hap_b200.LocalCollectives" if emulated else "hap_b200.collectives (drop-in)"}
+
+    # ---- roofline of the dominant kernel -----------------------------------------------------------
+    peaks, peak_kind = measured_peaks()
+    ag_ms, rs_ms, ar_ms = op_ms
+    if emulated:
+        # one launch serves all 8 virtual ranks: every output byte written once, every input byte read once
+        # (all_gather: S in + W*S out; reduce_scatter: W*S in + S out)
+        alg = (W + 1) * S
+        dom = ("pull_reduce_kernel<float,float> (reduce_scatter)", rs_ms) if rs_ms >= ag_ms else ("pull_copy_kernel (all_gather)", ag_ms)
+        achieved = alg / (dom[1] * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": dom[0], "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / peaks["hbm_gbs"], "peak_kind": peak_kind, "traffic": None,
+                    "algorithmic_bytes_per_launch": alg, "launch_ms": dom[1]}
+    else:
+        s = [L[r] * cols * es for r in range(W)]
+        alg = max(max(s[r] * (W - 1), S - s[r]) for r in range(W))      # busiest NVLink port, busier direction
+        dom = ("pull_reduce_kernel<float,float> (reduce_scatter)", rs_ms) if rs_ms >= ag_ms else ("pull_copy_kernel (all_gather)", ag_ms)
+        achieved = alg / (dom[1] * 1e-3) / 1e9
+        roofline = {"bound": "nvlink", "kernel": dom[0], "achieved": achieved, "peak": NVLINK_NOMINAL_GBS, "unit": "GB/s",
+                    "frac": achieved / NVLINK_NOMINAL_GBS, "peak_kind": "nominal per direction per GPU",
+                    "frac_of_measured_peer_copy": achieved / NVLINK_MEASURED_GBS, "traffic": None,
+                    "algorithmic_bytes_per_launch": alg, "launch_ms": dom[1]}
+
+    ops = {}
+    for name, ms, bb in (("all_gather", ag_ms, S * (W - 1) / W), ("reduce_scatter", rs_ms, S * (W - 1) / W),
+                         ("all_reduce", ar_ms, 2 * S * (W - 1) / W)):
+        ops[name] = {"ms": ms, "busbw_GBps": bb / (ms * 1e-3) / 1e9}
+
+    result = None
+    if rank == 0:
+        result = {
+            "metric": "uneven_collective_bus_bandwidth", "value": busbw * n_gpus, "unit": "GB/s", "n_gpus": n_gpus,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"uneven collective micro-benchmark: all_gather + reduce_scatter + all_reduce of a "
+                                   f"({ROWS}, {cols}) fp32 tensor ({args.size_mib} MiB) split on dim 0",
+                       "world": W, "sharding_lengths": L, "ratios": "r8 (first W renormalised)",
+                       "ranks": "8 virtual ranks on one GPU, one cooperative launch per collective" if emulated
+                                else "one process per GPU, peer loads over NVLink",
+                       "inputs": "resident in the peer-visible heap", "l2": "inputs larger than L2 (126 MB)"},
+            "ops": ops, "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+        }
+    # release device memory before the CPU baseline runs
+    del shards, fulls, ag_out
+    comm.destroy()
+    if rank == 0 and emulated and not args.no_cpu_baseline:
+        result["cpu_baseline"] = run_cpu_arm(8, args.cpu_size_mib << 20, args.cpu_steps, 2)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(result), flush=True)
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", 0))
+    if rank != 0:
+        return
+    W = 8 if args.gpus == 1 else args.gpus
+    size = args.cpu_size_mib << 20
+    base = run_cpu_arm(W, size, max(1, args.steps), max(1, args.warmup))
+    cols = size // (ROWS * 4)
+    line = {
+        "impl": "reference", "metric": "uneven_collective_bus_bandwidth", "value": base["value"], "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"uneven collective micro-benchmark: all_gather + reduce_scatter + all_reduce of a "
+                               f"({ROWS}, {cols}) fp32 tensor split on dim 0; CPU sample of {args.cpu_size_mib} MiB per step",
+                   "world": W, "ranks": "gloo ranks on the host cores"},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="hapx", choices=["hapx", "reference"])
+    ap.add_argument("--size-mib", type=int, default=1024, help="tensor size S of the GPU arm")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--cpu-size-mib", type=int, default=64, help="tensor size of the bounded CPU sample")
+    ap.add_argument("--cpu-steps", type=int, default=5)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

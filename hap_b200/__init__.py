@@ -1,0 +1,14 @@
+"""hap_b200 - B200-native (sm_100a) executor for the hot path of HAP's synthesized SPMD programs.
+
+The package holds the uneven collectives (drop-in for the reference's ``collectives.py``),
+the shard-extent rounding, and the CUDA sources behind them (``csrc/``, C ABI in
+``include/hapx.h``).  Importing it requires the built ``libhapx.so``; there is no CPU path.
+"""
+from . import _native
+from .sharding import sharding_round, sharding_round_
+from .comm import Comm, init_process_comm, local_comm
+from . import collectives
+from .local import LocalCollectives
+
+__all__ = ["Comm", "init_process_comm", "local_comm", "collectives", "LocalCollectives",
+           "sharding_round", "sharding_round_"]

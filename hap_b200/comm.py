@@ -1,0 +1,314 @@
+"""Communicators and the tensor-level operations on them (no autograd here).
+
+A :class:`Comm` wraps one ``hapx_comm``:
+
+* :func:`init_process_comm` - one process per GPU (what ``worker.py:14-18`` of the
+  reference sets up with ``init_process_group('nccl')``): every rank allocates a
+  peer-visible heap, the CUDA IPC handles travel through the already initialised
+  ``torch.distributed`` group, every rank maps every peer's heap.
+* :func:`local_comm` - ``world`` virtual ranks on one device in one process.  Every
+  collective is then a single cooperative launch over all ranks' data; the kernels and
+  the flag protocol are the ones the multi-GPU path runs.  Meant for single-GPU tests.
+
+All methods take and return LISTS with one tensor per local rank (length 1 for a
+process communicator).  PyTorch supplies device memory and the current stream; all
+data movement and arithmetic happens in the library's kernels.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import _native as N
+
+_DTYPES = {
+    torch.float32: N.F32, torch.bfloat16: N.BF16, torch.float16: N.F16, torch.float64: N.F64,
+    torch.int8: N.B8, torch.uint8: N.B8, torch.bool: N.B8, torch.int16: N.B16,
+    torch.int32: N.B32, torch.int64: N.B64,
+}
+_REDUCIBLE = (torch.float32, torch.bfloat16, torch.float16)
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise TypeError(f"hap_b200: unsupported dtype {dtype}") from None
+
+
+def _prod(xs) -> int:
+    out = 1
+    for x in xs:
+        out *= int(x)
+    return out
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+class _RawDeviceMemory:
+    """Exposes a raw device range through ``__cuda_array_interface__`` so torch can view it."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {
+            "shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2, "strides": None,
+        }
+
+
+class Comm:
+    def __init__(self, handle: int, device: torch.device):
+        self._h = C.c_void_p(handle)
+        self.device = device
+        w, nl, fr = C.c_int(), C.c_int(), C.c_int()
+        N.check(N.lib.hapx_comm_world(self._h, C.byref(w), C.byref(nl), C.byref(fr)))
+        self.world, self.n_local, self.first_rank = w.value, nl.value, fr.value
+        self._heap_views: List[Optional[torch.Tensor]] = [None] * self.n_local
+        self._heap_cursor = [0] * self.n_local
+        self.debug_sync = os.environ.get("HAPX_DEBUG_SYNC", "0") == "1"
+
+    # ---- lifecycle -------------------------------------------------------------------
+    def destroy(self) -> None:
+        if self._h:
+            self._heap_views = [None] * self.n_local
+            N.check(N.lib.hapx_comm_destroy(self._h))
+            self._h = None
+
+    def check(self) -> None:
+        """Synchronise and raise if a kernel recorded an error (e.g. a peer that never arrived)."""
+        N.check(N.lib.hapx_comm_check(self._h))
+
+    def set_timeout_ms(self, ms: int) -> None:
+        N.check(N.lib.hapx_comm_set_timeout_ms(self._h, int(ms)))
+
+    def set_max_ctas(self, ctas: int) -> None:
+        N.check(N.lib.hapx_comm_set_max_ctas(self._h, int(ctas)))
+
+    def ranks(self) -> List[int]:
+        return list(range(self.first_rank, self.first_rank + self.n_local))
+
+    # ---- peer-visible tensors --------------------------------------------------------
+    def _heap(self, i: int) -> torch.Tensor:
+        if self._heap_views[i] is None:
+            base, nbytes = C.c_void_p(), C.c_size_t()
+            N.check(N.lib.hapx_comm_heap(self._h, i, C.byref(base), C.byref(nbytes)))
+            self._heap_views[i] = torch.as_tensor(_RawDeviceMemory(base.value, nbytes.value), device=self.device)
+        return self._heap_views[i]
+
+    def symm_empty(self, shape, dtype=torch.float32, local_index: int = 0) -> torch.Tensor:
+        """A tensor inside local rank ``local_index``'s peer-visible heap (bump allocation, 256-byte
+        aligned, never freed individually; :meth:`symm_reset` releases everything).  Collectives
+        read such inputs in place instead of staging them."""
+        heap = self._heap(local_index)
+        nbytes = _prod(shape) * torch.empty((), dtype=dtype).element_size()
+        start = (self._heap_cursor[local_index] + 255) // 256 * 256
+        if start + nbytes > heap.numel():
+            raise MemoryError(f"hap_b200: heap exhausted ({start + nbytes} > {heap.numel()} bytes)")
+        self._heap_cursor[local_index] = start + nbytes
+        return heap[start:start + nbytes].view(dtype).view(*shape)
+
+    def symm_reset(self) -> None:
+        self._heap_cursor = [0] * self.n_local
+
+    # ---- helpers ---------------------------------------------------------------------------
+    def _lists(self, tensors: Sequence[torch.Tensor], what: str) -> List[torch.Tensor]:
+        if len(tensors) != self.n_local:
+            raise ValueError(f"{what}: expected {self.n_local} tensor(s), one per local rank, got {len(tensors)}")
+        out = []
+        for t in tensors:
+            if not t.is_cuda:
+                raise RuntimeError(f"{what}: hap_b200 has no CPU path; tensor is on {t.device}")
+            out.append(t.contiguous())
+        return out
+
+    def _lengths(self, lengths: Sequence[int], what: str) -> List[int]:
+        lengths = [int(x) for x in lengths]
+        if len(lengths) != self.world:
+            raise ValueError(f"{what}: {len(lengths)} sharding lengths for world size {self.world}")
+        return lengths
+
+    def _after(self) -> None:
+        if self.debug_sync:
+            self.check()
+
+    # ---- collectives ----------------------------------------------------------------------------
+    def all_gather(self, shards: Sequence[torch.Tensor], dim: int, lengths: Sequence[int],
+                   mode: int = N.MODE_PADDING, out: Optional[Sequence[torch.Tensor]] = None) -> List[torch.Tensor]:
+        shards = self._lists(shards, "all_gather")
+        lengths = self._lengths(lengths, "all_gather")
+        ref = shards[0]
+        dim = dim % ref.dim()
+        for i, (r, t) in enumerate(zip(self.ranks(), shards)):
+            if t.shape[dim] != lengths[r]:
+                raise ValueError(f"all_gather: rank {r} holds extent {t.shape[dim]} on dim {dim}, sharding length is {lengths[r]}")
+            if t.dtype != ref.dtype or t.shape[:dim] != ref.shape[:dim] or t.shape[dim + 1:] != ref.shape[dim + 1:]:
+                raise ValueError("all_gather: shards disagree in dtype or non-sharded extents")
+        full = list(ref.shape)
+        full[dim] = sum(lengths)
+        outs = list(out) if out is not None else [torch.empty(full, dtype=ref.dtype, device=t.device) for t in shards]
+        N.check(N.lib.hapx_all_gather(self._h, N.ptr_array([o.data_ptr() for o in outs]),
+                                      N.ptr_array([t.data_ptr() for t in shards]), dtype_code(ref.dtype),
+                                      _prod(ref.shape[:dim]), _prod(ref.shape[dim + 1:]), N.i64_array(lengths),
+                                      mode, _stream(self.device)))
+        self._after()
+        return outs
+
+    def reduce_scatter(self, inputs: Sequence[torch.Tensor], dim: int, lengths: Sequence[int],
+                       mode: int = N.MODE_PADDING, scale: float = 1.0,
+                       out_dtype: Optional[torch.dtype] = None) -> List[torch.Tensor]:
+        inputs = self._lists(inputs, "reduce_scatter")
+        lengths = self._lengths(lengths, "reduce_scatter")
+        ref = inputs[0]
+        dim = dim % ref.dim()
+        if ref.dtype not in _REDUCIBLE:
+            raise TypeError(f"reduce_scatter: unsupported dtype {ref.dtype}")
+        if ref.shape[dim] != sum(lengths):
+            raise ValueError(f"reduce_scatter: extent {ref.shape[dim]} on dim {dim} != sum of sharding lengths {sum(lengths)}")
+        for t in inputs:
+            if t.shape != ref.shape or t.dtype != ref.dtype:
+                raise ValueError("reduce_scatter: inputs disagree in shape or dtype")
+        out_dtype = out_dtype or ref.dtype
+        outs = []
+        for r in self.ranks():
+            shape = list(ref.shape)
+            shape[dim] = lengths[r]
+            outs.append(torch.empty(shape, dtype=out_dtype, device=ref.device))
+        N.check(N.lib.hapx_reduce_scatter(self._h, N.ptr_array([o.data_ptr() for o in outs]),
+                                          N.ptr_array([t.data_ptr() for t in inputs]), dtype_code(ref.dtype),
+                                          dtype_code(out_dtype), float(scale), _prod(ref.shape[:dim]),
+                                          _prod(ref.shape[dim + 1:]), N.i64_array(lengths), mode, _stream(self.device)))
+        self._after()
+        return outs
+
+    def all_reduce(self, inputs: Sequence[torch.Tensor], scale: float = 1.0, out_dtype: Optional[torch.dtype] = None,
+                   inplace: bool = False) -> List[torch.Tensor]:
+        inputs = self._lists(inputs, "all_reduce")
+        ref = inputs[0]
+        if ref.dtype not in _REDUCIBLE:
+            raise TypeError(f"all_reduce: unsupported dtype {ref.dtype}")
+        for t in inputs:
+            if t.shape != ref.shape or t.dtype != ref.dtype:
+                raise ValueError("all_reduce: inputs disagree in shape or dtype")
+        out_dtype = out_dtype or ref.dtype
+        if inplace:
+            if out_dtype != ref.dtype:
+                raise ValueError("all_reduce: in-place needs out_dtype == input dtype")
+            outs = inputs
+        else:
+            outs = [torch.empty(t.shape, dtype=out_dtype, device=t.device) for t in inputs]
+        N.check(N.lib.hapx_all_reduce(self._h, N.ptr_array([o.data_ptr() for o in outs]),
+                                      N.ptr_array([t.data_ptr() for t in inputs]), dtype_code(ref.dtype),
+                                      dtype_code(out_dtype), float(scale), ref.numel(), _stream(self.device)))
+        self._after()
+        return outs
+
+    def all_to_all(self, inputs: Sequence[torch.Tensor], split_dim: int, cat_dim: int,
+                   split_lengths: Sequence[int], cat_lengths: Sequence[int]) -> List[torch.Tensor]:
+        inputs = self._lists(inputs, "all_to_all")
+        split_lengths = self._lengths(split_lengths, "all_to_all")
+        cat_lengths = self._lengths(cat_lengths, "all_to_all")
+        ref = inputs[0]
+        nd = ref.dim()
+        split_dim, cat_dim = split_dim % nd, cat_dim % nd
+        if split_dim == cat_dim:
+            raise ValueError("all_to_all: split_dim and cat_dim must differ")
+        d1, d2 = min(split_dim, cat_dim), max(split_dim, cat_dim)
+        outs = []
+        for r, t in zip(self.ranks(), inputs):
+            if t.shape[split_dim] != sum(split_lengths):
+                raise ValueError(f"all_to_all: extent {t.shape[split_dim]} on split dim != sum of split lengths {sum(split_lengths)}")
+            if t.shape[cat_dim] != cat_lengths[r]:
+                raise ValueError(f"all_to_all: rank {r} holds extent {t.shape[cat_dim]} on cat dim, sharding length is {cat_lengths[r]}")
+            shape = list(t.shape)
+            shape[split_dim] = split_lengths[r]
+            shape[cat_dim] = sum(cat_lengths)
+            outs.append(torch.empty(shape, dtype=t.dtype, device=t.device))
+        a, b, c = _prod(ref.shape[:d1]), _prod(ref.shape[d1 + 1:d2]), _prod(ref.shape[d2 + 1:])
+        N.check(N.lib.hapx_all_to_all(self._h, N.ptr_array([o.data_ptr() for o in outs]),
+                                      N.ptr_array([t.data_ptr() for t in inputs]), dtype_code(ref.dtype),
+                                      a, b, c, 1 if split_dim < cat_dim else 0, N.i64_array(split_lengths),
+                                      N.i64_array(cat_lengths), _stream(self.device)))
+        self._after()
+        return outs
+
+
+# ---- purely local re-sharding (no communicator needed) ------------------------------------------
+def dynamic_slice(tensor: torch.Tensor, dim: int, lengths: Sequence[int], rank: int) -> torch.Tensor:
+    if not tensor.is_cuda:
+        raise RuntimeError(f"dynamic_slice: hap_b200 has no CPU path; tensor is on {tensor.device}")
+    t = tensor.contiguous()
+    dim = dim % t.dim()
+    lengths = [int(x) for x in lengths]
+    if t.shape[dim] != sum(lengths):
+        raise ValueError(f"dynamic_slice: extent {t.shape[dim]} on dim {dim} != sum of sharding lengths {sum(lengths)}")
+    shape = list(t.shape)
+    shape[dim] = lengths[rank]
+    out = torch.empty(shape, dtype=t.dtype, device=t.device)
+    with torch.cuda.device(t.device):
+        N.check(N.lib.hapx_dynamic_slice(out.data_ptr(), t.data_ptr(), dtype_code(t.dtype), _prod(t.shape[:dim]),
+                                         _prod(t.shape[dim + 1:]), N.i64_array(lengths), len(lengths), int(rank),
+                                         _stream(t.device)))
+    return out
+
+
+def dynamic_slice_backward(grad: torch.Tensor, dim: int, lengths: Sequence[int], rank: int) -> torch.Tensor:
+    g = grad.contiguous()
+    dim = dim % g.dim()
+    lengths = [int(x) for x in lengths]
+    shape = list(g.shape)
+    shape[dim] = sum(lengths)
+    out = torch.empty(shape, dtype=g.dtype, device=g.device)
+    with torch.cuda.device(g.device):
+        N.check(N.lib.hapx_dynamic_slice_backward(out.data_ptr(), g.data_ptr(), dtype_code(g.dtype), _prod(g.shape[:dim]),
+                                                  _prod(g.shape[dim + 1:]), N.i64_array(lengths), len(lengths), int(rank),
+                                                  _stream(g.device)))
+    return out
+
+
+# ---- construction ---------------------------------------------------------------------------------
+def _sizes(heap_bytes: Optional[int], stage_bytes: Optional[int]):
+    stage = int(stage_bytes if stage_bytes is not None else os.environ.get("HAPX_STAGE_BYTES", 512 << 20))
+    stage = (stage + 255) // 256 * 256
+    heap = int(heap_bytes if heap_bytes is not None else os.environ.get("HAPX_HEAP_BYTES", 0)) or (stage + (64 << 20))
+    heap = max(heap, stage + (1 << 20))
+    return heap, stage
+
+
+def local_comm(world: int, device=None, heap_bytes: Optional[int] = None, stage_bytes: Optional[int] = None) -> Comm:
+    """``world`` virtual ranks on one device (single-GPU emulation of the multi-GPU path)."""
+    if not torch.cuda.is_available():
+        raise RuntimeError("hap_b200 needs a CUDA device (there is no CPU fallback)")
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    heap, stage = _sizes(heap_bytes, stage_bytes)
+    h = C.c_void_p()
+    torch.cuda.init()
+    N.check(N.lib.hapx_comm_create_local(C.byref(h), int(world), device.index or 0, heap, stage))
+    return Comm(h.value, device)
+
+
+def init_process_comm(group=None, device=None, heap_bytes: Optional[int] = None,
+                      stage_bytes: Optional[int] = None) -> Comm:
+    """One rank per process.  ``torch.distributed`` must be initialised; it only carries the
+    64-byte IPC handles and a barrier."""
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise RuntimeError("hap_b200 needs a CUDA device (there is no CPU fallback)")
+    if not dist.is_initialized():
+        raise RuntimeError("hap_b200: call torch.distributed.init_process_group first")
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    heap, stage = _sizes(heap_bytes, stage_bytes)
+    torch.cuda.init()
+    h = C.c_void_p()
+    N.check(N.lib.hapx_comm_create(C.byref(h), world, rank, device.index or 0, heap, stage))
+    mine = C.create_string_buffer(N.IPC_HANDLE_BYTES)
+    N.check(N.lib.hapx_comm_ipc_handle(h, mine))
+    handles = [None] * world
+    with torch.cuda.device(device):
+        dist.all_gather_object(handles, bytes(mine.raw), group=group)
+        N.check(N.lib.hapx_comm_open_peers(h, b"".join(handles)))
+        dist.barrier(group=group)  # nobody launches before every rank has mapped everyone
+    return Comm(h.value, device)

@@ -1,0 +1,64 @@
+// Internal declarations shared by the hapx translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string>
+
+#include "hapx.h"
+
+namespace hapx {
+
+// ---- error reporting ---------------------------------------------------------
+void set_error(const std::string& msg);
+int fail(int code, const std::string& msg);
+#define HAPX_CUDA(expr)                                                                      \
+  do {                                                                                       \
+    cudaError_t _e = (expr);                                                                 \
+    if (_e != cudaSuccess)                                                                   \
+      return ::hapx::fail(HAPX_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e)); \
+  } while (0)
+
+void count_launch(int n = 1);
+
+// ---- heap layout -----------------------------------------------------------------
+// [0, kCtrlBytes)                  control block (flags written by peers, counters, status)
+// [kCtrlBytes, +stage_bytes)       staging area for inputs that live outside the heap
+// [.., heap_bytes)                 user area
+constexpr size_t kCtrlBytes = 4096;
+
+struct Ctrl {
+  unsigned long long start[HAPX_MAX_WORLD];  // peer p writes (seq<<40 | offset of its input in its heap)
+  unsigned long long done[HAPX_MAX_WORLD];   // peer p writes seq when it has finished reading this rank
+  unsigned int cta_done;                     // CTAs of the running kernel that have finished
+  unsigned int status;                       // 0, or a hapx_status code left by a kernel (as a positive number)
+  unsigned long long status_info;            // (seq<<32 | peer) of the wait that ran out
+};
+static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
+
+inline int dtype_size(int dtype) {
+  switch (dtype) {
+    case HAPX_F32: case HAPX_B32: return 4;
+    case HAPX_BF16: case HAPX_F16: case HAPX_B16: return 2;
+    case HAPX_F64: case HAPX_B64: return 8;
+    case HAPX_B8: return 1;
+    default: return 0;
+  }
+}
+
+}  // namespace hapx
+
+struct hapx_comm {
+  int world = 0, n_local = 0, first_rank = 0, device = 0;
+  bool local_mode = false;
+  size_t heap_bytes = 0, stage_bytes = 0;
+  char* heap[HAPX_MAX_WORLD] = {};  // this process's mapping of every rank's heap
+  bool mapped[HAPX_MAX_WORLD] = {};
+  bool ipc_opened[HAPX_MAX_WORLD] = {};
+  unsigned seq = 0;                 // sequence number of the last collective launched
+  int timeout_ms = 10000;
+  int max_ctas = 0;
+  int sm_count = 0;
+  cudaEvent_t last_done = nullptr;
+  cudaStream_t last_stream = nullptr;
+  bool any_launched = false;
+};

@@ -1,0 +1,163 @@
+/*
+ * hapx - C ABI of the B200-native executor for HAP's uneven collectives and
+ * ratio-sharded tensor ops.
+ *
+ * Every entry point takes plain pointers and sizes (no torch types) so that the
+ * reference's Python layer (collectives.py) can bind it with ctypes, and any
+ * other host language with its own FFI.  Each declaration cites the reference
+ * interface it stands in for, by path inside the reference project.
+ *
+ * Conventions
+ *  - All functions return 0 on success or a negative hapx_status code;
+ *    hapx_last_error() returns a thread-local message for the last failure.
+ *  - A tensor of shape S sharded on dimension `dim` is described as
+ *    (outer, extent, inner): outer = prod(S[:dim]), inner = prod(S[dim+1:]);
+ *    rank r holds extent lengths[r].  All tensors are contiguous.
+ *  - Pointer-array arguments (`dst`, `src`) have one entry per LOCAL rank of the
+ *    communicator: exactly one for a one-process-per-GPU communicator, `world`
+ *    for a local (single-device emulation) communicator.
+ *  - Work is enqueued on `stream` (a cudaStream_t); results are usable on that
+ *    stream without further synchronisation, as with the NCCL calls the
+ *    reference makes (comment at collectives.py:47).
+ *  - All ranks must issue the same sequence of collective calls.
+ *  - No entry point falls back to the CPU.
+ */
+#ifndef HAPX_H
+#define HAPX_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HAPX_MAX_WORLD 16
+#define HAPX_IPC_HANDLE_BYTES 64
+
+typedef struct hapx_comm hapx_comm;
+typedef void* hapx_stream; /* cudaStream_t */
+
+enum hapx_status {
+  HAPX_OK = 0,
+  HAPX_ERR_ARGUMENT = -1,    /* bad pointer, world size, dimension ...            */
+  HAPX_ERR_EXTENT = -2,      /* sharding lengths inconsistent with the geometry  */
+  HAPX_ERR_DTYPE = -3,       /* dtype not supported by this operation            */
+  HAPX_ERR_CUDA = -4,        /* a CUDA runtime call failed                       */
+  HAPX_ERR_PEER_TIMEOUT = -5,/* a bounded device-side wait on a peer ran out     */
+  HAPX_ERR_STAGING = -6,     /* input is outside the peer-visible heap and does
+                                not fit the staging area                         */
+  HAPX_ERR_STATE = -7        /* communicator not ready (peers not opened, ...)   */
+};
+
+enum hapx_dtype {
+  HAPX_F32 = 0, HAPX_BF16 = 1, HAPX_F16 = 2, HAPX_F64 = 3,
+  /* copy-only element types (gather / slice / all-to-all) */
+  HAPX_B8 = 4, HAPX_B16 = 5, HAPX_B32 = 6, HAPX_B64 = 7
+};
+
+/* Entry point selection that mirrors the reference's two strategies.  Both
+ * return identical values. */
+enum hapx_mode {
+  HAPX_MODE_PADDING = 0,   /* collectives.py:14-29, 88-103  (all_gather / reduce_scatter)              */
+  HAPX_MODE_GROUP_CALL = 1 /* collectives.py:31-66, 105-140 (all_gather_by_group_call / reduce_scatter_by_group_call) */
+};
+
+const char* hapx_last_error(void);
+int hapx_version(void);
+
+/* Number of kernels this library has launched in this process (all communicators). */
+int64_t hapx_launch_count(void);
+
+/* ---- extents ---------------------------------------------------------------
+ * Replaces hap.rs:3536-3559 (fn sharding_round; Python export hap.rs:211-218).
+ * Writes `world` integer extents that sum to full_length. */
+int hapx_sharding_round(int64_t full_length, const double* ratios, int world, int64_t* out_lengths);
+
+/* ---- communicator ------------------------------------------------------------
+ * Replaces dist.init_process_group('nccl', rank=...) at worker.py:18 as far as
+ * the collectives below are concerned: one peer-visible heap per rank, mapped
+ * into every other rank's address space, plus the flag words the kernels use to
+ * synchronise over NVLink.  The heap's first bytes are a control block, followed
+ * by a staging area of `stage_bytes` (for inputs that live outside the heap) and
+ * the user area (hapx_comm_heap) from which callers may carve zero-copy tensors.
+ */
+int hapx_comm_create(hapx_comm** out, int world, int rank, int device, size_t heap_bytes, size_t stage_bytes);
+/* `world` virtual ranks on ONE device, driven by one process: every collective
+ * is a single cooperative launch over all ranks' data.  For single-GPU testing. */
+int hapx_comm_create_local(hapx_comm** out, int world, int device, size_t heap_bytes, size_t stage_bytes);
+/* Exchange step of a one-process-per-GPU communicator: get this rank's 64-byte
+ * handle, all-gather the handles with any host transport, open the peers. */
+int hapx_comm_ipc_handle(hapx_comm* c, void* out_handle);
+int hapx_comm_open_peers(hapx_comm* c, const void* handles /* world * 64 bytes, rank order */);
+/* Alternative to open_peers when the caller maps peer heaps itself. */
+int hapx_comm_attach_peer(hapx_comm* c, int peer, void* mapped_base);
+int hapx_comm_destroy(hapx_comm* c);
+int hapx_comm_world(hapx_comm* c, int* world, int* n_local, int* first_rank);
+/* User area of local rank `local_index`'s heap. */
+int hapx_comm_heap(hapx_comm* c, int local_index, void** base, size_t* bytes);
+/* Upper bound for device-side waits on peers, in milliseconds (default 10000). */
+int hapx_comm_set_timeout_ms(hapx_comm* c, int ms);
+/* Cap the CTAs per rank that a collective launches (0 = one full wave). */
+int hapx_comm_set_max_ctas(hapx_comm* c, int ctas);
+/* Synchronises the device and reports (then clears) the status words the kernels
+ * leave behind: 0, or HAPX_ERR_PEER_TIMEOUT with details in hapx_last_error(). */
+int hapx_comm_check(hapx_comm* c);
+
+/* ---- collectives ---------------------------------------------------------------
+ * all_gather: replaces AllGather.forward (collectives.py:14-20),
+ * AllGatherByGroupCall.forward (:31-50), ReduceScatter.backward (:98-103) and
+ * ReduceScatterByGroupCall.backward (:123-140).
+ * src[i]: (outer, lengths[rank_i], inner); dst[i]: (outer, sum(lengths), inner). */
+int hapx_all_gather(hapx_comm* c, void* const* dst, const void* const* src, int dtype,
+                    int64_t outer, int64_t inner, const int64_t* lengths, int mode, hapx_stream stream);
+
+/* reduce_scatter: replaces ReduceScatter.forward (collectives.py:88-96),
+ * ReduceScatterByGroupCall.forward (:105-121), AllGather.backward (:22-29) and
+ * AllGatherByGroupCall.backward (:52-66).
+ * src[i]: (outer, sum(lengths), inner) partial; dst[i]: (outer, lengths[rank_i], inner)
+ * = out_dtype(scale * sum over ranks), accumulated in fp32 in rank order.
+ * The input is never modified (the group-call reference overwrites it). */
+int hapx_reduce_scatter(hapx_comm* c, void* const* dst, const void* const* src, int in_dtype, int out_dtype,
+                        double scale, int64_t outer, int64_t inner, const int64_t* lengths, int mode,
+                        hapx_stream stream);
+
+/* all_reduce: replaces AllReduce.forward/backward (collectives.py:73-84) and
+ * Replicate.backward (:176-180).  dst[i] = out_dtype(scale * sum_r src_r), n elements.
+ * dst[i] may equal src[i] when in_dtype == out_dtype. */
+int hapx_all_reduce(hapx_comm* c, void* const* dst, const void* const* src, int in_dtype, int out_dtype,
+                    double scale, int64_t n, hapx_stream stream);
+
+/* all_to_all: replaces AllToAll.forward/backward (collectives.py:152-166).
+ * The tensor is viewed as (a, X1, b, X2, c) where X1/X2 are the lower/higher of
+ * (split_dim, cat_dim); split_is_first != 0 when split_dim < cat_dim.
+ * src[i] has extent sum(split_lengths) on the split dim and cat_lengths[rank_i]
+ * on the cat dim; dst[i] has split_lengths[rank_i] and sum(cat_lengths). */
+int hapx_all_to_all(hapx_comm* c, void* const* dst, const void* const* src, int dtype,
+                    int64_t a, int64_t b, int64_t cc, int split_is_first,
+                    const int64_t* split_lengths, const int64_t* cat_lengths, hapx_stream stream);
+
+/* dynamic_slice: replaces collectives.py:146-148 (split + getitem + contiguous)
+ * and the placeholder sharding emitted at hap.rs:2511-2515.  Purely local.
+ * src: (outer, sum(lengths), inner); dst: (outer, lengths[rank], inner). */
+int hapx_dynamic_slice(void* dst, const void* src, int dtype, int64_t outer, int64_t inner,
+                       const int64_t* lengths, int world, int rank, hapx_stream stream);
+/* Its autograd dual: dst (outer, sum(lengths), inner) = zeros with slice `rank` = src. */
+int hapx_dynamic_slice_backward(void* dst, const void* src, int dtype, int64_t outer, int64_t inner,
+                                const int64_t* lengths, int world, int rank, hapx_stream stream);
+
+/* ---- diagnostics ----------------------------------------------------------------
+ * No counterpart in the reference.  Walks the kernels' tiling of ONE rank's pull over
+ * HOST buffers (op: 0 gather, 1 all-to-all, 2 slice, 3 slice-backward), bounds-checking
+ * every byte range and counting in `cover` (optional, dst_bytes long) how often each
+ * output byte is written.  It exists so that CPU-only tests can validate the index
+ * arithmetic of a geometry; it is not a compute path and takes no device pointers. */
+int hapx_debug_host_walk(int op, int world, int rank, int elem_size, int64_t a, int64_t b, int64_t cc,
+                         int split_is_first, const int64_t* l1, const int64_t* l2,
+                         const void* const* src_per_rank, const size_t* src_bytes, void* dst, size_t dst_bytes,
+                         unsigned char* cover);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HAPX_H */

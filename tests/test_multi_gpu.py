@@ -1,0 +1,111 @@
+"""The one-process-per-GPU path: real peer access over NVLink through CUDA IPC, the drop-in
+``collectives`` functions with autograd, against the oracle.  Needs >= 2 GPUs (skipped
+otherwise); each rank is a child process, torch.distributed (gloo) only carries the IPC
+handles and the comparison data."""
+import os
+import sys
+import tempfile
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, store):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    import hap_b200
+    from hap_b200 import collectives as col
+    from oracle import collectives_math as cm
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world, init_method=f"file://{store}")
+    comm = hap_b200.init_process_comm(stage_bytes=96 << 20, heap_bytes=(96 << 20) + (160 << 20))
+    col.set_default_comm(comm)
+    dev = f"cuda:{rank}"
+    ratios = [.22, .18, .15, .13, .11, .09, .07, .05][:world]
+    ratios = [x / sum(ratios) for x in ratios]
+
+    def gen(shape, seed, dtype):
+        return torch.randn(*shape, generator=torch.Generator().manual_seed(seed)).to(dtype)
+
+    def everyone(t):
+        got = [None] * world
+        dist.all_gather_object(got, t.cpu())
+        return got
+
+    tol = {torch.float32: dict(rtol=1e-5, atol=1e-5), torch.bfloat16: dict(rtol=1e-2, atol=1e-2)}
+    for dtype in (torch.float32, torch.bfloat16):
+        for total, other, dim in ((256, 1000, 0), (256, 1000, 1), (33, 7, 1), (4096, 64, 0)):
+            L = hap_b200.sharding_round(total, ratios)
+            shape = [other, other]
+            shape[dim] = L[rank]
+            # all_gather forward + reduce_scatter backward
+            x = gen(shape, 1000 + rank, dtype).to(dev).requires_grad_(True)
+            for fn in (col.all_gather, col.all_gather_by_group_call):
+                x.grad = None
+                out = fn(x, dim, L, rank)
+                w = gen(out.shape, 2000 + rank, dtype).to(dev)
+                (out * w).sum().backward()
+                xs, ws = everyone(x.detach()), everyone(w)
+                assert torch.equal(out.detach().cpu(), cm.all_gather(xs, dim, L)[rank])
+                torch.testing.assert_close(x.grad.cpu(), cm.all_gather_backward(ws, dim, L)[rank], **tol[dtype])
+            # reduce_scatter forward + all_gather backward
+            shape[dim] = total
+            y = gen(shape, 3000 + rank, dtype).to(dev).requires_grad_(True)
+            for fn in (col.reduce_scatter, col.reduce_scatter_by_group_call):
+                y.grad = None
+                out = fn(y, dim, L, rank)
+                w = gen(out.shape, 4000 + rank, dtype).to(dev)
+                (out * w).sum().backward()
+                ys, ws = everyone(y.detach()), everyone(w)
+                torch.testing.assert_close(out.detach().cpu(), cm.reduce_scatter(ys, dim, L)[rank], **tol[dtype])
+                assert torch.equal(y.grad.cpu(), cm.reduce_scatter_backward(ws, dim, L)[rank])
+            # all_reduce / replicate
+            z = gen(shape, 5000 + rank, dtype).to(dev).requires_grad_(True)
+            out = col.all_reduce(z)
+            out.sum().backward()
+            torch.testing.assert_close(out.detach().cpu(), cm.all_reduce(everyone(z.detach()))[rank], **tol[dtype])
+            assert torch.equal(z.grad.cpu(), torch.full(shape, float(world)).to(dtype))
+            p = gen(shape, 6000, dtype).to(dev).requires_grad_(True)
+            (col.replicate(p) * (rank + 1)).sum().backward()
+            assert torch.equal(p.grad.cpu(), torch.full(shape, world * (world + 1) / 2).to(dtype))
+            # dynamic_slice
+            assert torch.equal(col.dynamic_slice(y.detach(), dim, L, rank).cpu(), cm.dynamic_slice(y.detach().cpu(), dim, L, rank))
+        # all_to_all forward + backward
+        sl = hap_b200.sharding_round(32, ratios)
+        cl = hap_b200.sharding_round(40, ratios)
+        for sd, cd in ((0, 1), (1, 0), (2, 1)):
+            shape = [6, 6, 6]
+            shape[sd] = sum(sl)
+            shape[cd] = cl[rank]
+            x = gen(shape, 7000 + rank, dtype).to(dev).requires_grad_(True)
+            out = col.all_to_all(x, sd, cd, sl, cl, rank)
+            w = gen(out.shape, 8000 + rank, dtype).to(dev)
+            (out * w).sum().backward()
+            xs, ws = everyone(x.detach()), everyone(w)
+            assert torch.equal(out.detach().cpu(), cm.all_to_all(xs, sd, cd, sl, cl)[rank])
+            assert torch.equal(x.grad.cpu(), cm.all_to_all_backward(ws, sd, cd, sl, cl)[rank])
+    # heap-resident (zero-copy) input, 64 MiB, round trip
+    L = hap_b200.sharding_round(256, ratios)
+    cols = (64 << 20) // (256 * 4)
+    shard = comm.symm_empty((L[rank], cols), torch.float32)
+    shard.copy_(torch.randn(L[rank], cols, device=dev, generator=torch.Generator(dev).manual_seed(rank)))
+    full = comm.all_gather([shard], 0, L)[0]
+    assert torch.equal(hap_b200.comm.dynamic_slice(full, 0, L, rank), shard)
+    back = comm.reduce_scatter([full], 0, L, scale=1.0 / world)[0]
+    torch.testing.assert_close(back, shard, rtol=1e-6, atol=1e-6)
+    comm.check()
+    dist.barrier()
+    comm.destroy()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_drop_in_collectives_across_gpus(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_worker, args=(world, os.path.join(d, "store")), nprocs=world, join=True)
