@@ -130,7 +130,7 @@ class ClockSampler(threading.Thread):
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._stop_evt.wait(0.1)
+            self._stop_evt.wait(0.02)
 
     def finish(self):
         self._stop_evt.set()
@@ -162,8 +162,8 @@ def run_gpu_arm(args):
     emulated = n_gpus == 1
     W = 8 if emulated else n_gpus
     L = hap_b200.sharding_round(ROWS, ratios_for(W))
-    stage = (int(S * 1.25) + (64 << 20) + 255) // 256 * 256
-    heap = stage + int(S * 1.3) + (64 << 20)
+    stage = (S + S // W + (64 << 20) + 255) // 256 * 256     # staged input + the reduced slice of all_reduce
+    heap = stage + S + (max(L) * cols * es) + (64 << 20)
 
     if emulated:
         comm = hap_b200.local_comm(W, dev, heap_bytes=heap, stage_bytes=stage)

@@ -308,13 +308,19 @@ def test_large_round_trips(dtype):
     for r in range(world):
         assert torch.equal(hap_b200.comm.dynamic_slice(full[r], 0, lengths, r), shards[r])
         assert torch.equal(full[r], full[0])
-    # reduce_scatter of W copies of the same tensor = W * slice (exact in fp32 for W=8: multiplying by 8 is exact)
+    # reduce_scatter of W copies of the same tensor: the kernel adds in rank order in fp32, so the
+    # result must equal the same chain of fp32 additions done with plain tensor ops, bit for bit
+    def chain(x, scale=None):
+        acc = x.float().clone()
+        for _ in range(world - 1):
+            acc += x.float()
+        return (acc if scale is None else acc * scale).to(dtype)
     rs = comm.reduce_scatter([full[0]] * world, 0, lengths)
     for r in range(world):
-        assert torch.equal(rs[r], (shards[r].float() * world).to(dtype))
-    # all_reduce(scale=1/W) of identical inputs is the identity; linearity: AR(x + y) == AR(x) + AR(y) in fp32
+        assert torch.equal(rs[r], chain(shards[r]))
     ar = comm.all_reduce([full[0]] * world, scale=1.0 / world)
-    assert all(torch.equal(a, full[0]) for a in ar)
+    want = chain(full[0], 1.0 / world)
+    assert all(torch.equal(a, want) for a in ar)
     comm.check()
     # checksum of checksums: sum over ranks of reduce_scatter outputs == sum of all inputs
     if dtype == torch.float32:
