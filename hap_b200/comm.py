@@ -312,3 +312,32 @@ def init_process_comm(group=None, device=None, heap_bytes: Optional[int] = None,
         N.check(N.lib.hapx_comm_open_peers(h, b"".join(handles)))
         dist.barrier(group=group)  # nobody launches before every rank has mapped everyone
     return Comm(h.value, device)
+
+
+def local_all_reduce_noalloc(inputs: Sequence[torch.Tensor], outputs: Sequence[torch.Tensor], scale: float = 1.0) -> None:
+    """Sum ``inputs`` (one tensor per virtual rank, all on the current device) into every tensor of
+    ``outputs`` without allocating anything: no communicator, no ``cudaMalloc``, no torch allocation.
+
+    For callers that cannot obtain device memory at the moment the collective is due - the whole
+    card already belongs to another allocator, or the calling thread must not take the device-wide
+    synchronisation an allocation implies.  The caller provides inputs AND outputs (contiguous;
+    ``outputs[r]`` may be ``inputs[r]``); all scratch is a fixed 16 MiB array inside the library,
+    which limits the call to 8 ranks and roughly 460 000 float32 elements at 8 ranks (a larger call
+    raises ``HapxError`` with code ``ERR_STAGING``).  The first call on a device should happen
+    outside stream capture.  Calls share the scratch: do not let two of them overlap on the GPU.
+    """
+    if len(inputs) != len(outputs) or not inputs:
+        raise ValueError("local_all_reduce_noalloc: need one output per input")
+    ref = inputs[0]
+    for t in list(inputs) + list(outputs):
+        if not t.is_cuda:
+            raise RuntimeError(f"local_all_reduce_noalloc: hap_b200 has no CPU path; tensor is on {t.device}")
+        if not t.is_contiguous() or t.numel() != ref.numel() or t.device != ref.device:
+            raise ValueError("local_all_reduce_noalloc: tensors must be contiguous, equally sized and on one device")
+    if any(t.dtype != ref.dtype for t in inputs) or any(o.dtype != outputs[0].dtype for o in outputs):
+        raise ValueError("local_all_reduce_noalloc: mixed dtypes")
+    with torch.cuda.device(ref.device):
+        N.check(N.lib.hapx_local_all_reduce_noalloc(len(inputs), N.ptr_array([o.data_ptr() for o in outputs]),
+                                                    N.ptr_array([t.data_ptr() for t in inputs]), dtype_code(ref.dtype),
+                                                    dtype_code(outputs[0].dtype), float(scale), ref.numel(),
+                                                    _stream(ref.device)))

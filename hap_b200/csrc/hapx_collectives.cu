@@ -25,6 +25,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <mutex>
 #include <type_traits>
 #include <string>
 
@@ -846,6 +847,125 @@ int hapx_dynamic_slice_backward(void* dst, const void* src, int dtype, int64_t o
   return slice_impl(OP_UNSLICE, dst, src, dtype, outer, inner, lengths, world, rank, static_cast<cudaStream_t>(stream));
 }
 
+
+/* ---- all_reduce for callers that must not allocate ------------------------------------------
+ * Same result as hapx_all_reduce on a local (single-device, `world` virtual ranks)
+ * communicator, but with no communicator and no allocation of any kind: the control blocks,
+ * the staged copies of the inputs and the reduced slices live in the file-scope device array
+ * below (16 MiB per GPU that loads the library, held until the process exits), and the same
+ * pull_reduce / pull_copy kernels run over it.  It exists for hosts that cannot call cudaMalloc
+ * when a collective is due: a process that has already handed all device memory to another
+ * allocator (a caching allocator with the whole card reserved, a fixed memory budget), or a
+ * latency-critical thread on which the device-wide synchronisation of cudaMalloc / cudaFree
+ * would stall every stream.
+ *
+ * Limits: world <= 8 and 4096 + round256(n * in_size) + round256(ceil(n / world) rounded up to
+ * 16 bytes * out_size) <= 2 MiB per rank (about 460 000 float32 elements at world 8); larger
+ * calls are rejected with HAPX_ERR_STAGING.
+ * The first call on a device looks the array's device address up (cudaGetSymbolAddress); make
+ * that first call outside any stream capture.  All calls share the one array: each call
+ * clears the control blocks it uses before launching, and two calls whose kernels overlap on
+ * the GPU (different streams without ordering between them, or two host threads) race. */
+constexpr int kNoAllocMaxWorld = 8;
+constexpr size_t kNoAllocRankBytes = 2u << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocMaxWorld * kNoAllocRankBytes];
+
+namespace {
+struct NoAllocDevice {
+  bool ready = false;
+  char* base = nullptr;   // DEVICE address of g_noalloc_scratch on that device (never the host-side symbol)
+  int sm_count = 0;
+  unsigned seq = 0;
+};
+NoAllocDevice g_noalloc_dev[64];
+std::mutex g_noalloc_mutex;
+}  // namespace
+
+int hapx_local_all_reduce_noalloc(int world, void* const* dst, const void* const* src, int in_dtype, int out_dtype,
+                                  double scale, int64_t n, hapx_stream stream_) {
+  if (world < 1 || world > kNoAllocMaxWorld)
+    return fail(HAPX_ERR_ARGUMENT, "all_reduce_noalloc: world must be in [1, " + std::to_string(kNoAllocMaxWorld) + "]");
+  if (!dst || !src) return fail(HAPX_ERR_ARGUMENT, "all_reduce_noalloc: null pointer array");
+  if (n < 0) return fail(HAPX_ERR_EXTENT, "all_reduce_noalloc: negative size");
+  PullKernel reduce_kernel = reduce_kernel_for(in_dtype, out_dtype);
+  if (!reduce_kernel) return fail(HAPX_ERR_DTYPE, "all_reduce_noalloc: reductions support float32, bfloat16 and float16");
+  if (n == 0) return HAPX_OK;
+  const int es_in = dtype_size(in_dtype), es_out = dtype_size(out_dtype);
+  const long long vec = 16 / es_in;
+  const long long per = ((n + world - 1) / world + vec - 1) / vec * vec;   // even split on 16-byte boundaries
+  const size_t in_bytes = (size_t)n * es_in;
+  const size_t in_room = (in_bytes + 255) / 256 * 256;
+  const size_t mid_bytes = ((size_t)per * es_out + 255) / 256 * 256;
+  if (kCtrlBytes + in_room + mid_bytes > kNoAllocRankBytes)
+    return fail(HAPX_ERR_STAGING, "all_reduce_noalloc: " + std::to_string(n) + " elements need " +
+                                      std::to_string(kCtrlBytes + in_room + mid_bytes) + " bytes of scratch per rank; the built-in array holds " +
+                                      std::to_string(kNoAllocRankBytes) + " (use hapx_all_reduce on a communicator for larger tensors)");
+  for (int r = 0; r < world; ++r)
+    if (!dst[r] || !src[r]) return fail(HAPX_ERR_ARGUMENT, "all_reduce_noalloc: null tensor pointer");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  int device = 0;
+  HAPX_CUDA(cudaGetDevice(&device));
+  if (device < 0 || device >= 64) return fail(HAPX_ERR_ARGUMENT, "all_reduce_noalloc: device index out of range");
+  NoAllocDevice& nd = g_noalloc_dev[device];
+  if (!nd.ready) {  // once per device, with that device current
+    void* p = nullptr;
+    HAPX_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    HAPX_CUDA(cudaDeviceGetAttribute(&nd.sm_count, cudaDevAttrMultiProcessorCount, device));
+    nd.base = static_cast<char*>(p);
+    nd.ready = true;
+  }
+
+  // A communicator-shaped view of the array (host struct only; nothing is allocated).
+  hapx_comm view;
+  view.world = world; view.n_local = world; view.first_rank = 0; view.device = device; view.local_mode = true;
+  view.heap_bytes = kNoAllocRankBytes; view.stage_bytes = kNoAllocRankBytes - kCtrlBytes;
+  view.sm_count = nd.sm_count;
+  for (int r = 0; r < world; ++r) { view.heap[r] = nd.base + (size_t)r * kNoAllocRankBytes; view.mapped[r] = true; }
+  // the control blocks keep the previous call's flags and counters: start from zero
+  for (int r = 0; r < world; ++r) HAPX_CUDA(cudaMemsetAsync(view.heap[r], 0, kCtrlBytes, stream));
+
+  int64_t lengths[HAPX_MAX_WORLD];
+  long long L[HAPX_MAX_WORLD], Pfx[HAPX_MAX_WORLD], total;
+  long long left = n;
+  for (int r = 0; r < HAPX_MAX_WORLD; ++r) { lengths[r] = (r < world) ? std::min(per, left) : 0; left -= lengths[r]; }
+  fill_prefix(lengths, world, L, Pfx, &total);
+  const size_t mid_pos = view.stage_bytes - mid_bytes;
+
+  // 1st launch: rank r sums slice r of every (staged) input into the tail of its staging area
+  PullParams P;
+  init_params(&view, P, OP_REDUCE, es_in, es_out);
+  P.A = 1; P.C = 1; P.scale = (float)scale;
+  for (int i = 0; i < HAPX_MAX_WORLD; ++i) { P.L1[i] = L[i]; P.P1[i] = Pfx[i]; }
+  P.tot1 = total;
+  for (int r = 0; r < world; ++r) {
+    P.lr[r].rank = r;
+    P.lr[r].src = static_cast<const char*>(src[r]);
+    P.lr[r].dst = view.heap[r] + kCtrlBytes + mid_pos;
+    if (int e = publish_input(&view, r, src[r], in_bytes, true, 0, stream, &P.lr[r].src_off)) return e;
+  }
+  nd.seq = (nd.seq + 1) & 0xffffffu;
+  if (nd.seq == 0) nd.seq = 1;
+  P.seq = nd.seq;
+  if (int e = launch_pull(&view, reduce_kernel, P, kRedTile, stream)) return e;
+
+  // 2nd launch: every rank gathers the reduced slices into its output
+  PullParams G;
+  init_params(&view, G, OP_GATHER, es_out, es_out);
+  G.A = 1; G.C = 1;
+  fill_prefix(lengths, world, G.L1, G.P1, &G.tot1);
+  for (int r = 0; r < world; ++r) {
+    G.lr[r].rank = r;
+    G.lr[r].src = view.heap[r] + kCtrlBytes + mid_pos;
+    G.lr[r].dst = static_cast<char*>(dst[r]);
+    G.lr[r].src_off = kCtrlBytes + mid_pos;
+  }
+  nd.seq = (nd.seq + 1) & 0xffffffu;
+  if (nd.seq == 0) nd.seq = 1;
+  G.seq = nd.seq;
+  return launch_pull(&view, pull_copy_kernel, G, kCopyTile, stream);
+}
 
 /* Diagnostic, host memory only: walks the warp tiling of one rank's pull (the same
  * build_seg / locate code the kernels run) over HOST buffers, checking every byte range

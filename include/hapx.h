@@ -146,6 +146,23 @@ int hapx_dynamic_slice(void* dst, const void* src, int dtype, int64_t outer, int
 int hapx_dynamic_slice_backward(void* dst, const void* src, int dtype, int64_t outer, int64_t inner,
                                 const int64_t* lengths, int world, int rank, hapx_stream stream);
 
+/* all_reduce that allocates nothing.  No counterpart in the reference.
+ * Same values as hapx_all_reduce on a local (single-device) communicator of `world` virtual
+ * ranks, but without a communicator: all scratch (control blocks, staged inputs, reduced
+ * slices) is a 16 MiB device array built into the library, so the call performs no cudaMalloc /
+ * cudaFree and needs none to have happened.  For hosts that cannot allocate when the
+ * collective is due (all device memory already owned by another allocator, or a thread that
+ * must not take cudaMalloc's device-wide synchronisation).
+ * dst[r], src[r]: n elements each, r = 0..world-1, src 16-byte aligned or not (inputs are
+ * copied into the scratch first); dst[r] may equal src[r].
+ * Limits: world <= 8; 4096 + round256(n*in_size) + round256(slice*out_size) <= 2 MiB, where
+ * slice = ceil(n/world) rounded up to 16 bytes (about 460 000 float32 elements at world 8);
+ * beyond that the call returns HAPX_ERR_STAGING.
+ * The first call on a device resolves the array's device address; make it outside any stream
+ * capture.  Calls share the array: calls whose kernels overlap on the GPU race. */
+int hapx_local_all_reduce_noalloc(int world, void* const* dst, const void* const* src, int in_dtype, int out_dtype,
+                                  double scale, int64_t n, hapx_stream stream);
+
 /* ---- diagnostics ----------------------------------------------------------------
  * No counterpart in the reference.  Walks the kernels' tiling of ONE rank's pull over
  * HOST buffers (op: 0 gather, 1 all-to-all, 2 slice, 3 slice-backward), bounds-checking
