@@ -336,6 +336,132 @@ def run_gpu_arm(args):
         print(json.dumps(result), flush=True)
 
 
+
+# ----------------------------------------------------------------------------------------------
+# size sweep of the collective micro-benchmark (1 KiB ... 1 GiB in powers of 4, fp32 and bf16,
+# both entry points), next to the reference's algorithm run on NCCL on the same GPUs
+# ----------------------------------------------------------------------------------------------
+def run_sweep(args):
+    import torch
+    import hap_b200
+    from hap_b200 import _native as N
+
+    n_gpus = args.gpus
+    rank = int(os.environ.get("RANK", 0))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    emulated = n_gpus == 1
+    W = 8 if emulated else n_gpus
+    L = hap_b200.sharding_round(ROWS, ratios_for(W))
+    max_bytes = args.sweep_max_mib << 20
+    stage = (max_bytes // W + (64 << 20) + 255) // 256 * 256      # all_reduce keeps its reduced slice there
+    heap = stage + max_bytes + max(L) * (max_bytes // ROWS) + (64 << 20)
+    if emulated:
+        comm = hap_b200.local_comm(W, dev, heap_bytes=heap, stage_bytes=stage)
+        dist = None
+        gp = None
+    else:
+        import torch.distributed as dist
+        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=n_gpus)
+        comm = hap_b200.init_process_comm(heap_bytes=heap, stage_bytes=stage)
+        from oracle import gloo_port as gp      # the reference's algorithm; here it runs on NCCL as the on-box bar
+    ranks = comm.ranks()
+
+    def sync():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, reps, warm=5):
+        for _ in range(warm):
+            fn()
+        sync()
+        ts = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if dist is not None:
+                dist.barrier()
+            a.record()
+            fn()
+            b.record()
+            b.synchronize()
+            ts.append(a.elapsed_time(b))
+        if dist is not None:
+            t = torch.tensor(ts, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ts = t.tolist()
+        return statistics.median(ts), min(ts)
+
+    rows = []
+    sizes = [1 << k for k in range(10, 31, 2) if (1 << k) <= max_bytes]
+    for dtype, dname, es in ((torch.float32, "f32", 4), (torch.bfloat16, "bf16", 2)):
+        for S in sizes:
+            cols = S // (ROWS * es)
+            if cols < 1:
+                continue
+            comm.symm_reset()
+            shards, fulls = [], []
+            for i, r in enumerate(ranks):
+                g = torch.Generator(dev).manual_seed(1000 + r)
+                sh = comm.symm_empty((L[r], cols), dtype, i)
+                sh.copy_(torch.randn(L[r], cols, device=dev, generator=g).to(dtype))
+                fu = comm.symm_empty((ROWS, cols), dtype, i)
+                fu.copy_(torch.randn(ROWS, cols, device=dev, generator=g).to(dtype))
+                shards.append(sh)
+                fulls.append(fu)
+            out = [torch.empty(ROWS, cols, dtype=dtype, device=dev) for _ in ranks]
+            reps = 20 if S <= (256 << 20) else 5
+            s_r = [L[r] * cols * es for r in range(W)]
+            alg_ag = max(max(s_r[r] * (W - 1), S - s_r[r]) for r in range(W))
+            cases = [
+                ("all_gather", lambda: comm.all_gather(shards, 0, L, N.MODE_PADDING, out=out), S * (W - 1) / W, alg_ag),
+                ("all_gather_by_group_call", lambda: comm.all_gather(shards, 0, L, N.MODE_GROUP_CALL, out=out), S * (W - 1) / W, alg_ag),
+                ("reduce_scatter", lambda: comm.reduce_scatter(fulls, 0, L, N.MODE_PADDING), S * (W - 1) / W, alg_ag),
+                ("reduce_scatter_by_group_call", lambda: comm.reduce_scatter(fulls, 0, L, N.MODE_GROUP_CALL), S * (W - 1) / W, alg_ag),
+                ("all_reduce", lambda: comm.all_reduce(fulls, scale=1.0 / W), 2 * S * (W - 1) / W, 2 * S * (W - 1) / W),
+            ]
+            for name, fn, bus, alg in cases:
+                med, best = timed(fn, reps)
+                row = {"op": name, "dtype": dname, "bytes": S, "world": W, "ms_median": med, "ms_min": best,
+                       "busbw_GBps": bus / (med * 1e-3) / 1e9, "alg_GBps": alg / (med * 1e-3) / 1e9}
+                if not emulated:
+                    row["frac_nvlink_900"] = row["alg_GBps"] / NVLINK_NOMINAL_GBS
+                    if dtype == torch.float32 or name == "all_reduce":      # the reference's buffers are fp32-only
+                        ref = {"all_gather": lambda: gp.all_gather(shards[0], 0, L, rank),
+                               "all_gather_by_group_call": lambda: gp.all_gather_by_group_call(shards[0], 0, L, rank),
+                               "reduce_scatter": lambda: gp.reduce_scatter(fulls[0], 0, L, rank),
+                               "reduce_scatter_by_group_call": lambda: gp.reduce_scatter_by_group_call(fulls[0], 0, L, rank),
+                               "all_reduce": lambda: gp.all_reduce(fulls[0])}[name]
+                        rmed, rbest = timed(ref, max(3, reps // 2), warm=2)
+                        row["reference_on_nccl_ms_median"] = rmed
+                        row["speedup_vs_reference_on_nccl"] = rmed / med
+                rows.append(row)
+                if rank == 0:
+                    _print_sweep_row(row)
+            del out, shards, fulls
+            torch.cuda.empty_cache()
+    comm.check()
+    comm.destroy()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
+        with open(os.path.join(ROOT, "gpurun_out", f"sweep_{n_gpus}gpu.json"), "w") as f:
+            json.dump(rows, f, indent=1)
+
+
+def _print_sweep_row(r):
+    extra = ""
+    if "frac_nvlink_900" in r:
+        extra = f" nvlink {100 * r['frac_nvlink_900']:5.1f}%"
+    if "speedup_vs_reference_on_nccl" in r:
+        extra += f"  ref/NCCL {r['reference_on_nccl_ms_median']:9.4f} ms (x{r['speedup_vs_reference_on_nccl']:.2f})"
+    print(f"{r['op']:30s} {r['dtype']:4s} {r['bytes']:>11d} B  {r['ms_median']:9.4f} ms  bus {r['busbw_GBps']:8.2f} GB/s"
+          f"  alg {r['alg_GBps']:8.2f} GB/s{extra}", flush=True)
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
@@ -368,9 +494,13 @@ def main():
     ap.add_argument("--cpu-size-mib", type=int, default=64, help="tensor size of the bounded CPU sample")
     ap.add_argument("--cpu-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep", action="store_true", help="size sweep instead of the single JSON line")
+    ap.add_argument("--sweep-max-mib", type=int, default=1024)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.sweep:
+        run_sweep(args)
     else:
         run_gpu_arm(args)
 

@@ -54,6 +54,7 @@ struct PullParams {
   int op, world, n_local, es_in, es_out;
   int self_only;    // no peers involved: skip the flag protocol
   int split_first;  // OP_EXCHANGE: split dim comes before cat dim
+  int order_log2;   // copy kernels visit tiles in 2^order_log2 interleaved streams (0 = in order)
   unsigned seq;
   unsigned long long timeout_ns;
   float scale;
@@ -297,7 +298,17 @@ __global__ void __launch_bounds__(kThreads) pull_copy_kernel(const __grid_consta
   const unsigned gw = blockIdx.x * kWarps + (threadIdx.x >> 5);
   const unsigned nw = gridDim.x * kWarps;
   const unsigned total = sh.total_tiles;
-  for (unsigned t = gw; t < total; t += nw) {
+  // Tiles are numbered source after source.  Walking them in that order would make every
+  // rank read the same peer at the same time (one NVLink port saturated, the others idle),
+  // so the walk is split into G = 2^order_log2 streams that start G equally spaced places
+  // apart: at any moment all sources are being read, each in proportion to its size.
+  const unsigned lg = (unsigned)P.order_log2;
+  const unsigned G = 1u << lg;
+  const unsigned Q = (total + G - 1) >> lg;
+  const unsigned long long walk = (unsigned long long)Q << lg;
+  for (unsigned long long t0 = gw; t0 < walk; t0 += nw) {
+    const unsigned t = ((unsigned)t0 & (G - 1)) * Q + (unsigned)(t0 >> lg);
+    if (t >= total) continue;
     const TilePos tp = locate(sh.segs, sh.nseg, t);
     const Seg& s = sh.segs[tp.si];
     const char* srow = sh.base[s.peer] + tp.src_row_b;
@@ -614,6 +625,7 @@ static void init_params(hapx_comm* c, PullParams& P, int op, int es_in, int es_o
   P.op = op; P.world = c->world; P.n_local = c->n_local; P.es_in = es_in; P.es_out = es_out;
   P.scale = 1.f;
   P.timeout_ns = (unsigned long long)c->timeout_ms * 1000000ull;
+  P.order_log2 = c->order_log2;
   for (int p = 0; p < c->world; ++p) P.heap[p] = c->heap[p];
 }
 

@@ -5,6 +5,7 @@
 // device pointer to every other rank's heap, so the collective kernels can load peers'
 // inputs directly over NVLink.
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 
@@ -32,6 +33,10 @@ static int check_sizes(int world, size_t heap_bytes, size_t stage_bytes) {
 }
 
 static int common_init(hapx_comm* c) {
+  if (const char* e = std::getenv("HAPX_TILE_STREAMS_LOG2")) {  // tuning knob, 0..10
+    int v = std::atoi(e);
+    if (v >= 0 && v <= 10) c->order_log2 = v;
+  }
   HAPX_CUDA(cudaSetDevice(c->device));
   HAPX_CUDA(cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, c->device));
   HAPX_CUDA(cudaEventCreateWithFlags(&c->last_done, cudaEventDisableTiming));

@@ -57,6 +57,7 @@ struct hapx_comm {
   unsigned seq = 0;                 // sequence number of the last collective launched
   int timeout_ms = 10000;
   int max_ctas = 0;
+  int order_log2 = 6;               // copy kernels interleave 64 tile streams (see pull_copy_kernel)
   int sm_count = 0;
   cudaEvent_t last_done = nullptr;
   cudaStream_t last_stream = nullptr;
