@@ -373,7 +373,9 @@ def run_sweep(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, reps, warm=5):
+    def timed(fn, reps, warm=5, inner=1):
+        """Median / min device time of one call; `inner` calls are queued back to back between the
+        two events (as nccl-tests does), so the host's launch overhead overlaps with the previous call."""
         for _ in range(warm):
             fn()
         sync()
@@ -383,10 +385,11 @@ def run_sweep(args):
             if dist is not None:
                 dist.barrier()
             a.record()
-            fn()
+            for _ in range(inner):
+                fn()
             b.record()
             b.synchronize()
-            ts.append(a.elapsed_time(b))
+            ts.append(a.elapsed_time(b) / inner)
         if dist is not None:
             t = torch.tensor(ts, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -412,6 +415,7 @@ def run_sweep(args):
                 fulls.append(fu)
             out = [torch.empty(ROWS, cols, dtype=dtype, device=dev) for _ in ranks]
             reps = 20 if S <= (256 << 20) else 5
+            inner = 10 if S <= (64 << 20) else 2
             s_r = [L[r] * cols * es for r in range(W)]
             alg_ag = max(max(s_r[r] * (W - 1), S - s_r[r]) for r in range(W))
             cases = [
@@ -422,8 +426,8 @@ def run_sweep(args):
                 ("all_reduce", lambda: comm.all_reduce(fulls, scale=1.0 / W), 2 * S * (W - 1) / W, 2 * S * (W - 1) / W),
             ]
             for name, fn, bus, alg in cases:
-                med, best = timed(fn, reps)
-                row = {"op": name, "dtype": dname, "bytes": S, "world": W, "ms_median": med, "ms_min": best,
+                med, best = timed(fn, reps, inner=inner)
+                row = {"op": name, "dtype": dname, "bytes": S, "world": W, "ms_median": med, "ms_min": best, "calls_per_timing": inner,
                        "busbw_GBps": bus / (med * 1e-3) / 1e9, "alg_GBps": alg / (med * 1e-3) / 1e9}
                 if not emulated:
                     row["frac_nvlink_900"] = row["alg_GBps"] / NVLINK_NOMINAL_GBS
@@ -433,7 +437,7 @@ def run_sweep(args):
                                "reduce_scatter": lambda: gp.reduce_scatter(fulls[0], 0, L, rank),
                                "reduce_scatter_by_group_call": lambda: gp.reduce_scatter_by_group_call(fulls[0], 0, L, rank),
                                "all_reduce": lambda: gp.all_reduce(fulls[0])}[name]
-                        rmed, rbest = timed(ref, max(3, reps // 2), warm=2)
+                        rmed, rbest = timed(ref, max(3, reps // 2), warm=2, inner=inner)
                         row["reference_on_nccl_ms_median"] = rmed
                         row["speedup_vs_reference_on_nccl"] = rmed / med
                 rows.append(row)

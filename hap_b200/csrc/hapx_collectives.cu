@@ -25,6 +25,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <map>
 #include <mutex>
 #include <type_traits>
 #include <string>
@@ -585,7 +586,18 @@ static int launch_pull(hapx_comm* c, PullKernel kernel, PullParams& P, int tile_
     max_tiles = std::max(max_tiles, tiles);
   }
   int per_sm = 0;
-  HAPX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0));
+  {  // the occupancy query costs microseconds: ask once per kernel
+    static std::mutex mu;
+    static std::map<const void*, int> cache;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(reinterpret_cast<const void*>(kernel));
+    if (it == cache.end()) {
+      HAPX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0));
+      cache[reinterpret_cast<const void*>(kernel)] = per_sm;
+    } else {
+      per_sm = it->second;
+    }
+  }
   if (per_sm < 1) return fail(HAPX_ERR_CUDA, "kernel does not fit on an SM");
   long long cap = (long long)c->sm_count * per_sm;
   if (c->local_mode && !P.self_only) cap = std::max<long long>(1, cap / c->world);
