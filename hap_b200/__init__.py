@@ -9,6 +9,8 @@ from .sharding import sharding_round, sharding_round_
 from .comm import Comm, init_process_comm, local_comm
 from . import collectives
 from .local import LocalCollectives
+from . import linear as linear_ops
+from .linear import linear
 
 __all__ = ["Comm", "init_process_comm", "local_comm", "collectives", "LocalCollectives",
-           "sharding_round", "sharding_round_"]
+           "sharding_round", "sharding_round_", "linear", "linear_ops"]

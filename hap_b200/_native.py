@@ -45,6 +45,10 @@ SIGNATURES = {
     "hapx_all_to_all": (_int, [_vp, _pp, _pp, _int, _i64, _i64, _i64, _int, _pi64, _pi64, _vp]),
     "hapx_dynamic_slice": (_int, [_vp, _vp, _int, _i64, _i64, _pi64, _int, _int, _vp]),
     "hapx_dynamic_slice_backward": (_int, [_vp, _vp, _int, _i64, _i64, _pi64, _int, _int, _vp]),
+    "hapx_linear_forward": (_int, [_vp, _vp, _vp, _vp, _int, _int, _i64, _i64, _i64, _int, _vp]),
+    "hapx_linear_dgrad": (_int, [_vp, _vp, _vp, _int, _int, _i64, _i64, _i64, _vp]),
+    "hapx_linear_wgrad": (_int, [_vp, _vp, _vp, _vp, _int, _int, _i64, _i64, _i64, _vp]),
+    "hapx_gemm_status": (_int, []),
     "hapx_local_all_reduce_noalloc": (_int, [_int, _pp, _pp, _int, _int, _dbl, _i64, _vp]),
     "hapx_debug_host_walk": (_int, [_int, _int, _int, _int, _i64, _i64, _i64, _int, _pi64, _pi64, _pp,
                                      C.POINTER(_sz), _vp, _sz, _vp]),

@@ -1,0 +1,557 @@
+// Uneven-shard GEMMs for F.linear (forward, dgrad, wgrad) on Blackwell tensor cores.
+//
+// One persistent, warp-specialised kernel: D[M,N] = A[M,Kc] * B[N,Kc]^T (+ bias, activation)
+// with bf16 operands and fp32 accumulation in tensor memory.
+//
+//   warp 0      : TMA producer (cp.async.bulk.tensor, 128-byte swizzle) into a ring of stages
+//   warp 1      : allocates TMEM, one elected thread issues tcgen05.mma (cta_group::1, 128 x BN x 16)
+//   warps 2..5  : epilogue - tcgen05.ld the accumulator, bias / activation / cast, global stores
+//
+// Two accumulator buffers in TMEM let the epilogue of tile i run under the main loop of tile
+// i+1.  Either operand may be "K-major" (contraction index contiguous in memory) or "MN-major"
+// (output index contiguous), which is what dgrad (B = W as stored) and wgrad (A = g^T, B = x^T
+// as stored) need: no transposed copies are ever made.  Ragged shard extents (M = 38, N = 2458,
+// ...) are handled by TMA's zero fill on loads and by predicated stores, so no operand is padded.
+//
+// Every mbarrier wait is bounded; on expiry the kernel raises an error word, leaves its loops,
+// frees its TMEM and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <mutex>
+#include <string>
+
+#include "hapx_internal.h"
+
+namespace hapx {
+namespace gemm {
+
+constexpr int BM = 128;
+constexpr int BK = 64;                 // bf16 elements: one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr int kEpilogueThreads = 128;
+constexpr unsigned long long kWaitNs = 2000000000ull;  // upper bound of any single wait
+
+enum Epilogue { EPI_NONE = 0, EPI_RELU = 1, EPI_GELU = 2, EPI_SIGMOID = 3 };
+
+struct Params {
+  int M, N, Kc;           // D is M x N, contraction length Kc
+  long long ldd;          // elements between rows of D
+  void* D;
+  const void* bias;       // N values of the input dtype, or null
+  int epilogue;
+  int out_f32;            // D is fp32 instead of bf16
+  int m_tiles, n_tiles, k_blocks;
+  unsigned* error;        // device word: 0 or a code left by a wait that ran out
+};
+
+// ---- PTX wrappers -------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: false when the phase did not complete within kWaitNs.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (unsigned it = 0; it < 0x7fffffffu; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 63u && global_ns() - t0 > kWaitNs) return false;
+  }
+  return false;
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(unsigned dst_smem, unsigned cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned idesc,
+                                          unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on an mbarrier once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32(unsigned taddr, unsigned (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+// AND-reduction of a predicate over the 128 epilogue threads (named barrier 2), so that they
+// take the same branch after a bounded wait.
+__device__ __forceinline__ bool epilogue_all(bool mine) {
+  unsigned out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "bar.red.and.pred q, 2, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out)
+      : "r"((unsigned)mine)
+      : "memory");
+  return out != 0;
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (version 1 = Blackwell, 128-byte swizzle).  Offsets in bytes.
+__device__ __forceinline__ unsigned long long make_desc(unsigned smem_addr, unsigned lbo_bytes, unsigned sbo_bytes) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_addr & 0x3ffffu) >> 4);
+  d |= (unsigned long long)((lbo_bytes >> 4) & 0x3fffu) << 16;
+  d |= (unsigned long long)((sbo_bytes >> 4) & 0x3fffu) << 32;
+  d |= 1ull << 46;   // descriptor version
+  d |= 2ull << 61;   // SWIZZLE_128B
+  return d;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+struct Cfg {
+  static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr unsigned A_BYTES = BM * BK * 2;
+  static constexpr unsigned B_BYTES = BN * BK * 2;
+  static constexpr unsigned STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr unsigned TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
+  // dynamic shared memory: stages (1024-byte aligned) + bias tile + barriers
+  static constexpr unsigned SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + BN * 4 + 256;
+  // instruction descriptor: fp32 accumulate, bf16 x bf16, majors, N >> 3, M >> 4
+  static constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                                    ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+};
+
+__device__ __forceinline__ float apply_epilogue(float v, int epi) {
+  switch (epi) {
+    case EPI_RELU: return v > 0.f ? v : 0.f;
+    case EPI_GELU: return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+    case EPI_SIGMOID: return 1.f / (1.f + __expf(-v));
+    default: return v;
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+  using C = Cfg<BN, A_MN, B_MN>;
+  extern __shared__ unsigned char smem_raw[];
+  const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  float* bias_tile = reinterpret_cast<float*>(gen_base + C::STAGES * C::STAGE_BYTES);
+  const unsigned bars = base + C::STAGES * C::STAGE_BYTES + BN * 4;
+  // barrier map (8 bytes each): full[s], empty[s], tmem_full[2], tmem_empty[2]; then the TMEM address slot
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + 2 + a); };
+  const unsigned tmem_slot = bars + 8u * (2 * C::STAGES + 4);
+  volatile unsigned* tmem_slot_gen = reinterpret_cast<volatile unsigned*>(gen_base + C::STAGES * C::STAGE_BYTES + BN * 4 + 8 * (2 * C::STAGES + 4));
+  volatile unsigned* abort_flag = tmem_slot_gen + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = p.m_tiles * p.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), kEpilogueThreads); }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = *tmem_slot_gen;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      unsigned phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u)) { ok = false; break; }
+          const unsigned sa = base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+          mbar_expect_tx(full_bar(stage), C::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d(sa, &tmA, k0, m0, full_bar(stage));                 // box {64 k, 128 m}
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i)                                // boxes {64 m, 64 k}
+              tma_load_2d(sa + i * 8192u, &tmA, m0 + 64 * i, k0, full_bar(stage));
+          }
+          if (!B_MN) {
+            tma_load_2d(sb, &tmB, k0, n0, full_bar(stage));                 // box {64 k, BN n}
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i)                                // boxes {64 n, 64 k}
+              tma_load_2d(sb + i * 8192u, &tmB, n0 + 64 * i, k0, full_bar(stage));
+          }
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) { *abort_flag = 1; atomicCAS(p.error, 0u, 1u); }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int stage = 0, acc = 0;
+      unsigned phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u)) { ok = false; break; }
+        tc_fence_after();
+        const unsigned d_tmem = tmem_base + (unsigned)(acc * BN);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase)) { ok = false; break; }
+          tc_fence_after();
+          const unsigned sa = base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // K-major: 16 elements = 32 bytes further inside the 128-byte swizzle row;
+            // MN-major: 16 contraction rows of 128 bytes further
+            const unsigned long long da = A_MN ? make_desc(sa + k * 2048u, 8192u, 1024u) : make_desc(sa + k * 32u, 16u, 1024u);
+            const unsigned long long db = B_MN ? make_desc(sb + k * 2048u, 8192u, 1024u) : make_desc(sb + k * 32u, 16u, 1024u);
+            umma_bf16(d_tmem, da, db, C::IDESC, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));   // frees the stage once these MMAs have read it
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(tfull_bar(acc));       // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (!ok) { *abort_flag = 1; atomicCAS(p.error, 0u, 2u); }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int q = warp & 3;                       // TMEM lane quarter this warp may read
+    const int et = threadIdx.x - 64;              // 0..127
+    int acc = 0;
+    unsigned acc_phase = 0;
+    bool ok = true;
+    const bool vec_ok = p.out_f32 ? ((p.ldd & 3) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15u) == 0)
+                                  : ((p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15u) == 0);
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * BN;
+      // bias tile -> shared (fp32)
+      asm volatile("bar.sync 1, 128;" ::: "memory");   // previous tile's readers are done with bias_tile
+      for (int j = et; j < BN; j += kEpilogueThreads) {
+        float b = 0.f;
+        if (p.bias != nullptr && n0 + j < p.N) b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n0 + j]);
+        bias_tile[j] = b;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      ok = epilogue_all(mbar_wait(tfull_bar(acc), acc_phase));
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const unsigned t_row = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(acc * BN);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        unsigned r[32];
+        tmem_ld_32x32(t_row + (unsigned)c0, r);
+        tmem_ld_wait();
+        if (row < p.M && n0 + c0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = apply_epilogue(__uint_as_float(r[j]) + bias_tile[c0 + j], p.epilogue);
+          const int ncols = min(32, p.N - (n0 + c0));
+          if (p.out_f32) {
+            float* out = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + n0 + c0;
+            if (vec_ok && ncols == 32) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = v[j];
+            }
+          } else {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd + n0 + c0;
+            if (vec_ok && ncols == 32) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 pk;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
+                pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
+                *reinterpret_cast<uint4*>(out + j) = pk;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = __float2bfloat16_rn(v[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(tempty_bar(acc));     // this thread has drained its part of the accumulator
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (!ok) { *abort_flag = 1; atomicCAS(p.error, 0u, 3u); }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row pitch `ld` elements.
+static int make_map(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long ld, int box_inner, int box_outer) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(HAPX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0) return fail(HAPX_ERR_ARGUMENT, "gemm: operand base must be 16-byte aligned");
+  if ((ld * 2) % 16 != 0) return fail(HAPX_ERR_EXTENT, "gemm: operand row pitch must be a multiple of 16 bytes (8 bf16 elements)");
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(HAPX_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  return HAPX_OK;
+}
+
+struct DeviceState {
+  bool ready = false;
+  int sm_count = 0;
+  unsigned* error = nullptr;  // one device word per device for the kernels' error reports
+};
+static DeviceState g_dev[64];
+static std::mutex g_dev_mutex;
+
+static int device_state(DeviceState** out) {
+  int device = 0;
+  HAPX_CUDA(cudaGetDevice(&device));
+  if (device < 0 || device >= 64) return fail(HAPX_ERR_ARGUMENT, "gemm: device index out of range");
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  DeviceState& d = g_dev[device];
+  if (!d.ready) {
+    HAPX_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device));
+    HAPX_CUDA(cudaMalloc(&d.error, sizeof(unsigned)));
+    HAPX_CUDA(cudaMemset(d.error, 0, sizeof(unsigned)));
+    d.ready = true;
+  }
+  *out = &d;
+  return HAPX_OK;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch(const void* A, long long lda, const void* B, long long ldb, Params& p, cudaStream_t stream, int sm_count) {
+  using C = Cfg<BN, A_MN, B_MN>;
+  CUtensorMap tmA, tmB;
+  // K-major operand [rows = M or N][Kc contiguous]: inner = Kc, box {64, rows per tile}
+  // MN-major operand [rows = Kc][M or N contiguous]: inner = M or N, box {64, 64}
+  if (int e = A_MN ? make_map(&tmA, A, p.M, p.Kc, lda, 64, 64) : make_map(&tmA, A, p.Kc, p.M, lda, BK, BM)) return e;
+  if (int e = B_MN ? make_map(&tmB, B, p.N, p.Kc, ldb, 64, 64) : make_map(&tmB, B, p.Kc, p.N, ldb, BK, BN)) return e;
+  p.m_tiles = (p.M + BM - 1) / BM;
+  p.n_tiles = (p.N + BN - 1) / BN;
+  p.k_blocks = (p.Kc + BK - 1) / BK;
+  auto kernel = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    HAPX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES));
+    attr_set = true;
+  }
+  const int grid = std::max(1, std::min(p.m_tiles * p.n_tiles, sm_count));
+  kernel<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  HAPX_CUDA(cudaGetLastError());
+  count_launch();
+  return HAPX_OK;
+}
+
+// D[M,N] = A * B^T with the given operand majors.  lda/ldb/ldd in elements.
+static int gemm_bf16(void* D, int out_f32, long long ldd, const void* A, bool a_mn, long long lda, const void* B, bool b_mn,
+                     long long ldb, const void* bias, int epilogue, long long M, long long N, long long Kc, cudaStream_t stream) {
+  if (M < 0 || N < 0 || Kc < 0) return fail(HAPX_ERR_EXTENT, "gemm: negative extent");
+  if (M == 0 || N == 0) return HAPX_OK;
+  if (Kc == 0) return fail(HAPX_ERR_EXTENT, "gemm: empty contraction");
+  if (M > 0x7fffffff || N > 0x7fffffff || Kc > 0x7fffffff) return fail(HAPX_ERR_EXTENT, "gemm: extent exceeds 2^31");
+  if (!D || !A || !B) return fail(HAPX_ERR_ARGUMENT, "gemm: null pointer");
+  DeviceState* dev = nullptr;
+  if (int e = device_state(&dev)) return e;
+  Params p = Params();
+  p.M = (int)M; p.N = (int)N; p.Kc = (int)Kc; p.ldd = ldd; p.D = D; p.bias = bias; p.epilogue = epilogue; p.out_f32 = out_f32;
+  p.error = dev->error;
+  // tile width: fewest waves first, then the wider tile
+  auto waves = [&](int bn) {
+    const long long tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+    return (double)((tiles + dev->sm_count - 1) / dev->sm_count) * bn;
+  };
+  const int bn = (waves(256) <= waves(128)) ? 256 : 128;
+#define HAPX_GEMM_CASE(BN_, AMN_, BMN_) \
+  if (bn == BN_ && a_mn == AMN_ && b_mn == BMN_) return launch<BN_, AMN_, BMN_>(A, lda, B, ldb, p, stream, dev->sm_count);
+  HAPX_GEMM_CASE(256, false, false)
+  HAPX_GEMM_CASE(128, false, false)
+  HAPX_GEMM_CASE(256, false, true)
+  HAPX_GEMM_CASE(128, false, true)
+  HAPX_GEMM_CASE(256, true, true)
+  HAPX_GEMM_CASE(128, true, true)
+#undef HAPX_GEMM_CASE
+  return fail(HAPX_ERR_ARGUMENT, "gemm: unsupported operand layout");
+}
+
+// Column sums of g[M,N] (the bias gradient), fp32 accumulation.
+__global__ void __launch_bounds__(256) colsum_bf16_kernel(const __nv_bfloat16* __restrict__ g, long long ldg, int M, int N,
+                                                          void* out, int out_f32) {
+  // one thread per column pair, grid.y slices of rows combined with atomics into an fp32 scratch-free path:
+  // each block owns 64 columns and ALL rows, so no atomics are needed
+  __shared__ float part[4][64];
+  const int c = blockIdx.x * 64 + (threadIdx.x & 63);
+  const int rg = threadIdx.x >> 6;
+  float acc = 0.f;
+  if (c < N)
+    for (int r = rg; r < M; r += 4) acc += __bfloat162float(g[(long long)r * ldg + c]);
+  part[rg][threadIdx.x & 63] = acc;
+  __syncthreads();
+  if (rg == 0 && c < N) {
+    const float s = part[0][threadIdx.x] + part[1][threadIdx.x] + part[2][threadIdx.x] + part[3][threadIdx.x];
+    if (out_f32) reinterpret_cast<float*>(out)[c] = s;
+    else reinterpret_cast<__nv_bfloat16*>(out)[c] = __float2bfloat16_rn(s);
+  }
+}
+
+}  // namespace gemm
+}  // namespace hapx
+
+using namespace hapx;
+
+extern "C" {
+
+int hapx_linear_forward(void* y, const void* x, const void* w, const void* bias, int dtype, int out_dtype, int64_t m,
+                        int64_t n, int64_t k, int epilogue, hapx_stream stream) {
+  if (dtype != HAPX_BF16) return fail(HAPX_ERR_DTYPE, "linear_forward: the tensor-core path takes bfloat16 operands");
+  if (out_dtype != HAPX_BF16 && out_dtype != HAPX_F32) return fail(HAPX_ERR_DTYPE, "linear_forward: output must be bfloat16 or float32");
+  if (epilogue < 0 || epilogue > 3) return fail(HAPX_ERR_ARGUMENT, "linear_forward: unknown epilogue");
+  // y[m,n] = x[m,k] * w[n,k]^T : both operands K-major
+  return gemm::gemm_bf16(y, out_dtype == HAPX_F32, n, x, false, k, w, false, k, bias, epilogue, m, n, k, static_cast<cudaStream_t>(stream));
+}
+
+int hapx_linear_dgrad(void* dx, const void* g, const void* w, int dtype, int out_dtype, int64_t m, int64_t n, int64_t k,
+                      hapx_stream stream) {
+  if (dtype != HAPX_BF16) return fail(HAPX_ERR_DTYPE, "linear_dgrad: the tensor-core path takes bfloat16 operands");
+  if (out_dtype != HAPX_BF16 && out_dtype != HAPX_F32) return fail(HAPX_ERR_DTYPE, "linear_dgrad: output must be bfloat16 or float32");
+  // dx[m,k] = g[m,n] * w[n,k] : contraction over n; A = g is K-major, B[k][n] = w[n][k] is MN-major as stored
+  return gemm::gemm_bf16(dx, out_dtype == HAPX_F32, k, g, false, n, w, true, k, nullptr, 0, m, k, n, static_cast<cudaStream_t>(stream));
+}
+
+int hapx_linear_wgrad(void* dw, void* dbias, const void* g, const void* x, int dtype, int out_dtype, int64_t m, int64_t n,
+                      int64_t k, hapx_stream stream_) {
+  if (dtype != HAPX_BF16) return fail(HAPX_ERR_DTYPE, "linear_wgrad: the tensor-core path takes bfloat16 operands");
+  if (out_dtype != HAPX_BF16 && out_dtype != HAPX_F32) return fail(HAPX_ERR_DTYPE, "linear_wgrad: output must be bfloat16 or float32");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  // dw[n,k] = g[m,n]^T * x[m,k] : contraction over m; A[n][m] = g[m][n] and B[k][m] = x[m][k] are both MN-major as stored
+  if (dw) {
+    if (int e = gemm::gemm_bf16(dw, out_dtype == HAPX_F32, k, g, true, n, x, true, k, nullptr, 0, n, k, m, stream)) return e;
+  }
+  if (dbias && n > 0) {
+    if (m < 0 || m > 0x7fffffff || n > 0x7fffffff) return fail(HAPX_ERR_EXTENT, "linear_wgrad: extent out of range");
+    gemm::colsum_bf16_kernel<<<(unsigned)((n + 63) / 64), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(g), n, (int)m, (int)n,
+                                                                             dbias, out_dtype == HAPX_F32);
+    HAPX_CUDA(cudaGetLastError());
+    count_launch();
+  }
+  return HAPX_OK;
+}
+
+int hapx_gemm_status(void) {
+  gemm::DeviceState* dev = nullptr;
+  if (int e = gemm::device_state(&dev)) return e;
+  HAPX_CUDA(cudaDeviceSynchronize());
+  unsigned code = 0;
+  HAPX_CUDA(cudaMemcpy(&code, dev->error, sizeof(code), cudaMemcpyDeviceToHost));
+  if (code != 0) {
+    HAPX_CUDA(cudaMemset(dev->error, 0, sizeof(unsigned)));
+    return fail(HAPX_ERR_PEER_TIMEOUT, "a GEMM kernel gave up waiting on a barrier (role " + std::to_string(code) +
+                                           ": 1 = TMA producer, 2 = MMA issuer, 3 = epilogue)");
+  }
+  return HAPX_OK;
+}
+
+}  // extern "C"

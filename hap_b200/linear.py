@@ -1,0 +1,115 @@
+"""``F.linear`` on ratio-sharded tensors, through the C ABI into the tcgen05 GEMM kernels.
+
+Stands in for the ``torch.nn.functional.linear`` nodes of the synthesized program
+(``hap.rs:1030-1037``, sharding variants ``hap.rs:2787-2816``): same signature, same autograd
+results (``dx = g W``, ``dW = g^T x``, ``db = sum g``), bfloat16 operands with fp32 accumulation.
+There is no fallback to cuBLAS: unsupported inputs raise.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _native as N
+from .comm import _stream
+
+_EPILOGUES = {"none": 0, "relu": 1, "gelu": 2, "sigmoid": 3}
+
+
+def _check(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{what}: hap_b200 has no CPU path; tensor is on {t.device}")
+    if t.dtype != torch.bfloat16:
+        raise TypeError(f"{what}: the tensor-core path takes bfloat16, got {t.dtype}")
+
+
+def _out_code(dtype: torch.dtype) -> int:
+    if dtype == torch.bfloat16:
+        return N.BF16
+    if dtype == torch.float32:
+        return N.F32
+    raise TypeError(f"linear: output dtype must be bfloat16 or float32, got {dtype}")
+
+
+def linear_forward(x2: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], epilogue: str = "none",
+                   out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """y[m,n] = act(x2[m,k] @ w[n,k]^T + b[n]) for contiguous 2-D bf16 operands."""
+    _check(x2, "linear"), _check(w, "linear")
+    m, k = x2.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise ValueError(f"linear: input features {k} != weight in_features {w.shape[1]}")
+    if b is not None:
+        _check(b, "linear")
+        if b.numel() != n:
+            raise ValueError("linear: bias size does not match out_features")
+    if k % 8:
+        raise ValueError(f"linear: in_features must be a multiple of 8 (got {k})")
+    y = torch.empty((m, n), dtype=out_dtype, device=x2.device)
+    with torch.cuda.device(x2.device):
+        N.check(N.lib.hapx_linear_forward(y.data_ptr(), x2.data_ptr(), w.data_ptr(), b.data_ptr() if b is not None else None,
+                                          N.BF16, _out_code(out_dtype), m, n, k, _EPILOGUES[epilogue], _stream(x2.device)))
+    return y
+
+
+def linear_dgrad(g2: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    _check(g2, "linear backward"), _check(w, "linear backward")
+    m, n = g2.shape
+    k = w.shape[1]
+    if n % 8 or k % 8:
+        raise ValueError(f"linear backward: features must be multiples of 8 (got n={n}, k={k})")
+    dx = torch.empty((m, k), dtype=out_dtype, device=g2.device)
+    with torch.cuda.device(g2.device):
+        N.check(N.lib.hapx_linear_dgrad(dx.data_ptr(), g2.data_ptr(), w.data_ptr(), N.BF16, _out_code(out_dtype), m, n, k,
+                                        _stream(g2.device)))
+    return dx
+
+
+def linear_wgrad(g2: torch.Tensor, x2: torch.Tensor, need_weight: bool = True, need_bias: bool = True,
+                 out_dtype: torch.dtype = torch.bfloat16):
+    _check(g2, "linear backward"), _check(x2, "linear backward")
+    m, n = g2.shape
+    k = x2.shape[1]
+    if n % 8 or k % 8:
+        raise ValueError(f"linear backward: features must be multiples of 8 (got n={n}, k={k})")
+    dw = torch.empty((n, k), dtype=out_dtype, device=g2.device) if need_weight else None
+    db = torch.empty((n,), dtype=out_dtype, device=g2.device) if need_bias else None
+    with torch.cuda.device(g2.device):
+        N.check(N.lib.hapx_linear_wgrad(dw.data_ptr() if need_weight else None, db.data_ptr() if need_bias else None,
+                                        g2.data_ptr(), x2.data_ptr(), N.BF16, _out_code(out_dtype), m, n, k, _stream(g2.device)))
+    return dw, db
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        wc = w.contiguous()
+        ctx.save_for_backward(x2, wc)
+        ctx.has_bias = b is not None
+        ctx.x_shape = x.shape
+        y = linear_forward(x2, wc, b.contiguous() if b is not None else None)
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, g):
+        x2, w = ctx.saved_tensors
+        g2 = g.reshape(-1, g.shape[-1]).contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = linear_dgrad(g2, w).view(ctx.x_shape)
+        need_w, need_b = ctx.needs_input_grad[1], ctx.has_bias and ctx.needs_input_grad[2]
+        if need_w or need_b:
+            dw, db = linear_wgrad(g2, x2, need_w, need_b)
+        return dx, dw, db
+
+
+def linear(input: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Drop-in for ``torch.nn.functional.linear`` on CUDA bfloat16 tensors."""
+    return _Linear.apply(input, weight, bias)
+
+
+def gemm_status() -> None:
+    """Synchronise and raise if a GEMM kernel reported a barrier wait that ran out."""
+    N.check(N.lib.hapx_gemm_status())

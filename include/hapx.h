@@ -146,6 +146,26 @@ int hapx_dynamic_slice(void* dst, const void* src, int dtype, int64_t outer, int
 int hapx_dynamic_slice_backward(void* dst, const void* src, int dtype, int64_t outer, int64_t inner,
                                 const int64_t* lengths, int world, int rank, hapx_stream stream);
 
+/* ---- ratio-sharded F.linear on the tensor cores --------------------------------------------
+ * Replace the F.linear nodes the planner emits (hap.rs:1030-1037; sharding variants
+ * hap.rs:2787-2816: data parallel = uneven m, column parallel = uneven n) and their autograd
+ * backward.  bfloat16 operands, fp32 accumulation; m, n, k are the extents of THIS rank's
+ * shard and may be any positive numbers (rows of every operand must be 16-byte multiples:
+ * k % 8 == 0 for forward, n % 8 == 0 and k % 8 == 0 for dgrad / wgrad).  All tensors
+ * contiguous row-major.  out_dtype: HAPX_BF16 or HAPX_F32.
+ *   forward: y[m,n] = act(x[m,k] * w[n,k]^T + bias[n])     epilogue: 0 none, 1 relu, 2 gelu(erf), 3 sigmoid
+ *   dgrad  : dx[m,k] = g[m,n] * w[n,k]
+ *   wgrad  : dw[n,k] = g[m,n]^T * x[m,k];  dbias[n] = column sums of g (either output may be null) */
+int hapx_linear_forward(void* y, const void* x, const void* w, const void* bias, int dtype, int out_dtype,
+                        int64_t m, int64_t n, int64_t k, int epilogue, hapx_stream stream);
+int hapx_linear_dgrad(void* dx, const void* g, const void* w, int dtype, int out_dtype,
+                      int64_t m, int64_t n, int64_t k, hapx_stream stream);
+int hapx_linear_wgrad(void* dw, void* dbias, const void* g, const void* x, int dtype, int out_dtype,
+                      int64_t m, int64_t n, int64_t k, hapx_stream stream);
+/* Synchronises the device and reports (then clears) an error left by a GEMM kernel whose
+ * bounded barrier wait ran out. */
+int hapx_gemm_status(void);
+
 /* all_reduce that allocates nothing.  No counterpart in the reference.
  * Same values as hapx_all_reduce on a local (single-device) communicator of `world` virtual
  * ranks, but without a communicator: all scratch (control blocks, staged inputs, reduced
