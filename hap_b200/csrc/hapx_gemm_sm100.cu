@@ -410,6 +410,9 @@ static int device_state(DeviceState** out) {
   int device = 0;
   HAPX_CUDA(cudaGetDevice(&device));
   if (device < 0 || device >= 64) return fail(HAPX_ERR_ARGUMENT, "gemm: device index out of range");
+  // cuTensorMapEncodeTiled is a driver call: make sure the primary context is current on this
+  // thread (autograd's backward threads have selected the device but may not have bound it yet)
+  HAPX_CUDA(cudaSetDevice(device));
   std::lock_guard<std::mutex> lock(g_dev_mutex);
   DeviceState& d = g_dev[device];
   if (!d.ready) {
