@@ -466,6 +466,79 @@ def _print_sweep_row(r):
           f"  alg {r['alg_GBps']:8.2f} GB/s{extra}", flush=True)
 
 
+
+# ----------------------------------------------------------------------------------------------
+# sharded F.linear GEMMs of the Transformer-LM configuration (per-GPU token count 32 x 256 = 8192),
+# forward + dgrad + wgrad, next to cuBLAS (torch.matmul) on the same GPU
+# ----------------------------------------------------------------------------------------------
+LM_LAYERS = [("attn in-proj", 2304, 768), ("attn out-proj", 768, 768), ("ffn up", 3072, 768), ("ffn down", 768, 3072),
+             ("lm head", 33280, 768)]
+
+
+def run_gemm(args):
+    import torch
+    import hap_b200
+    from hap_b200 import linear_ops as LO
+    from hap_b200 import _native as N
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    peaks, peak_kind = measured_peaks()
+    M = args.gemm_tokens
+    rows, tot_flops, tot_ms, tot_ms_ref = [], 0.0, 0.0, 0.0
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)       # > L2, written between timed iterations
+
+    def timeit(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(args.steps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            b.synchronize()
+            ts.append(a.elapsed_time(b))
+        return statistics.median(ts)
+
+    launches0 = N.lib.hapx_launch_count()
+    for name, n, k in LM_LAYERS:
+        g = torch.Generator(dev).manual_seed(39)
+        x = torch.randn(M, k, device=dev, generator=g).to(torch.bfloat16)
+        w = (torch.randn(n, k, device=dev, generator=g) * k ** -0.5).to(torch.bfloat16)
+        b = torch.randn(n, device=dev, generator=g).to(torch.bfloat16)
+        gy = torch.randn(M, n, device=dev, generator=g).to(torch.bfloat16)
+        flops = 2.0 * M * n * k
+        cases = [("fwd", lambda: LO.linear_forward(x, w, b), lambda: torch.nn.functional.linear(x, w, b)),
+                 ("dgrad", lambda: LO.linear_dgrad(gy, w), lambda: gy @ w),
+                 ("wgrad", lambda: LO.linear_wgrad(gy, x, True, False), lambda: gy.t() @ x)]
+        for what, ours, ref in cases:
+            ms, ms_ref = timeit(ours), timeit(ref)
+            rows.append({"layer": name, "op": what, "m": M, "n": n, "k": k, "ms": ms, "tflops": flops / ms / 1e9,
+                         "frac_of_peak": flops / ms / 1e9 / peaks["bf16_tflops"], "cublas_ms": ms_ref,
+                         "cublas_tflops": flops / ms_ref / 1e9})
+            tot_flops += flops
+            tot_ms += ms
+            tot_ms_ref += ms_ref
+    LO.gemm_status()
+    launches = N.lib.hapx_launch_count() - launches0
+    for r in rows:
+        print(f"{r['layer']:14s} {r['op']:6s} m={r['m']} n={r['n']:6d} k={r['k']:5d}  {r['ms']:8.4f} ms {r['tflops']:8.1f} TF/s "
+              f"({100 * r['frac_of_peak']:5.1f}% of {peaks['bf16_tflops']:.0f})   cuBLAS {r['cublas_ms']:8.4f} ms {r['cublas_tflops']:8.1f} TF/s",
+              file=sys.stderr, flush=True)
+    best = max(rows, key=lambda r: r["ms"])
+    print(json.dumps({
+        "metric": "sharded_linear_tflops", "value": tot_flops / tot_ms / 1e9, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": tot_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"forward + dgrad + wgrad of the 5 linear layers of the Transformer-LM configuration at {M} tokens per GPU",
+                   "l2": "256 MiB flush buffer written between timed iterations"},
+        "roofline": {"bound": "tensor", "kernel": f"gemm_bf16_kernel ({best['layer']} {best['op']})", "achieved": best["tflops"],
+                     "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": best["frac_of_peak"], "peak_kind": peak_kind, "traffic": None},
+        "cublas_tflops": tot_flops / tot_ms_ref / 1e9, "gpu_launches": int(launches), "layers": rows}), flush=True)
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
@@ -500,9 +573,13 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="size sweep instead of the single JSON line")
     ap.add_argument("--sweep-max-mib", type=int, default=1024)
+    ap.add_argument("--workload", default="collectives", choices=["collectives", "gemm"])
+    ap.add_argument("--gemm-tokens", type=int, default=8192)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "gemm":
+        run_gemm(args)
     elif args.sweep:
         run_sweep(args)
     else:

@@ -503,22 +503,38 @@ __global__ void __launch_bounds__(256) colsum_bf16_kernel(const __nv_bfloat16* _
 }  // namespace gemm
 }  // namespace hapx
 
+namespace hapx { namespace sgemm {
+int run(const float* A, long long a_i, long long a_k, const float* B, long long b_j, long long b_k, const float* bias, float* D,
+        long long ldd, long long M, long long N, long long K, int epilogue, cudaStream_t stream);
+int colsum(const float* g, long long m, long long n, float* out, cudaStream_t stream);
+} }
+
 using namespace hapx;
 
 extern "C" {
 
 int hapx_linear_forward(void* y, const void* x, const void* w, const void* bias, int dtype, int out_dtype, int64_t m,
                         int64_t n, int64_t k, int epilogue, hapx_stream stream) {
-  if (dtype != HAPX_BF16) return fail(HAPX_ERR_DTYPE, "linear_forward: the tensor-core path takes bfloat16 operands");
-  if (out_dtype != HAPX_BF16 && out_dtype != HAPX_F32) return fail(HAPX_ERR_DTYPE, "linear_forward: output must be bfloat16 or float32");
   if (epilogue < 0 || epilogue > 3) return fail(HAPX_ERR_ARGUMENT, "linear_forward: unknown epilogue");
+  if (dtype == HAPX_F32) {  // fp32 operands: CUDA-core path (tcgen05 has no fp32 multiply)
+    if (out_dtype != HAPX_F32) return fail(HAPX_ERR_DTYPE, "linear_forward: float32 operands give a float32 result");
+    return sgemm::run(static_cast<const float*>(x), k, 1, static_cast<const float*>(w), k, 1, static_cast<const float*>(bias),
+                      static_cast<float*>(y), n, m, n, k, epilogue, static_cast<cudaStream_t>(stream));
+  }
+  if (dtype != HAPX_BF16) return fail(HAPX_ERR_DTYPE, "linear_forward: operands must be bfloat16 or float32");
+  if (out_dtype != HAPX_BF16 && out_dtype != HAPX_F32) return fail(HAPX_ERR_DTYPE, "linear_forward: output must be bfloat16 or float32");
   // y[m,n] = x[m,k] * w[n,k]^T : both operands K-major
   return gemm::gemm_bf16(y, out_dtype == HAPX_F32, n, x, false, k, w, false, k, bias, epilogue, m, n, k, static_cast<cudaStream_t>(stream));
 }
 
 int hapx_linear_dgrad(void* dx, const void* g, const void* w, int dtype, int out_dtype, int64_t m, int64_t n, int64_t k,
                       hapx_stream stream) {
-  if (dtype != HAPX_BF16) return fail(HAPX_ERR_DTYPE, "linear_dgrad: the tensor-core path takes bfloat16 operands");
+  if (dtype == HAPX_F32) {  // dx[m,k] = sum_n g[m,n] w[n,k]
+    if (out_dtype != HAPX_F32) return fail(HAPX_ERR_DTYPE, "linear_dgrad: float32 operands give a float32 result");
+    return sgemm::run(static_cast<const float*>(g), n, 1, static_cast<const float*>(w), 1, k, nullptr, static_cast<float*>(dx), k,
+                      m, k, n, 0, static_cast<cudaStream_t>(stream));
+  }
+  if (dtype != HAPX_BF16) return fail(HAPX_ERR_DTYPE, "linear_dgrad: operands must be bfloat16 or float32");
   if (out_dtype != HAPX_BF16 && out_dtype != HAPX_F32) return fail(HAPX_ERR_DTYPE, "linear_dgrad: output must be bfloat16 or float32");
   // dx[m,k] = g[m,n] * w[n,k] : contraction over n; A = g is K-major, B[k][n] = w[n][k] is MN-major as stored
   return gemm::gemm_bf16(dx, out_dtype == HAPX_F32, k, g, false, n, w, true, k, nullptr, 0, m, k, n, static_cast<cudaStream_t>(stream));
@@ -526,7 +542,16 @@ int hapx_linear_dgrad(void* dx, const void* g, const void* w, int dtype, int out
 
 int hapx_linear_wgrad(void* dw, void* dbias, const void* g, const void* x, int dtype, int out_dtype, int64_t m, int64_t n,
                       int64_t k, hapx_stream stream_) {
-  if (dtype != HAPX_BF16) return fail(HAPX_ERR_DTYPE, "linear_wgrad: the tensor-core path takes bfloat16 operands");
+  if (dtype == HAPX_F32) {  // dw[n,k] = sum_m g[m,n] x[m,k]
+    if (out_dtype != HAPX_F32) return fail(HAPX_ERR_DTYPE, "linear_wgrad: float32 operands give a float32 result");
+    cudaStream_t st = static_cast<cudaStream_t>(stream_);
+    if (dw)
+      if (int e = sgemm::run(static_cast<const float*>(g), 1, n, static_cast<const float*>(x), 1, k, nullptr, static_cast<float*>(dw), k,
+                             n, k, m, 0, st)) return e;
+    if (dbias) return sgemm::colsum(static_cast<const float*>(g), m, n, static_cast<float*>(dbias), st);
+    return HAPX_OK;
+  }
+  if (dtype != HAPX_BF16) return fail(HAPX_ERR_DTYPE, "linear_wgrad: operands must be bfloat16 or float32");
   if (out_dtype != HAPX_BF16 && out_dtype != HAPX_F32) return fail(HAPX_ERR_DTYPE, "linear_wgrad: output must be bfloat16 or float32");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   // dw[n,k] = g[m,n]^T * x[m,k] : contraction over m; A[n][m] = g[m][n] and B[k][m] = x[m][k] are both MN-major as stored

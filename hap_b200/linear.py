@@ -2,7 +2,8 @@
 
 Stands in for the ``torch.nn.functional.linear`` nodes of the synthesized program
 (``hap.rs:1030-1037``, sharding variants ``hap.rs:2787-2816``): same signature, same autograd
-results (``dx = g W``, ``dW = g^T x``, ``db = sum g``), bfloat16 operands with fp32 accumulation.
+results (``dx = g W``, ``dW = g^T x``, ``db = sum g``).  bfloat16 operands run on the tensor cores
+with fp32 accumulation; float32 operands (the 1e-5 parity configuration) run an fp32 FFMA kernel.
 There is no fallback to cuBLAS: unsupported inputs raise.
 """
 from __future__ import annotations
@@ -20,8 +21,18 @@ _EPILOGUES = {"none": 0, "relu": 1, "gelu": 2, "sigmoid": 3}
 def _check(t: torch.Tensor, what: str) -> None:
     if not t.is_cuda:
         raise RuntimeError(f"{what}: hap_b200 has no CPU path; tensor is on {t.device}")
-    if t.dtype != torch.bfloat16:
-        raise TypeError(f"{what}: the tensor-core path takes bfloat16, got {t.dtype}")
+    if t.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError(f"{what}: operands must be bfloat16 or float32, got {t.dtype}")
+
+
+def _same(ref: torch.Tensor, *others) -> None:
+    for t in others:
+        if t is not None and t.dtype != ref.dtype:
+            raise TypeError(f"linear: mixed operand dtypes {ref.dtype} and {t.dtype}")
+
+
+def _default_out(t: torch.Tensor, out_dtype):
+    return out_dtype if out_dtype is not None else t.dtype
 
 
 def _out_code(dtype: torch.dtype) -> int:
@@ -33,9 +44,10 @@ def _out_code(dtype: torch.dtype) -> int:
 
 
 def linear_forward(x2: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], epilogue: str = "none",
-                   out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-    """y[m,n] = act(x2[m,k] @ w[n,k]^T + b[n]) for contiguous 2-D bf16 operands."""
-    _check(x2, "linear"), _check(w, "linear")
+                   out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """y[m,n] = act(x2[m,k] @ w[n,k]^T + b[n]) for contiguous 2-D operands (bf16 or fp32)."""
+    _check(x2, "linear"), _check(w, "linear"), _same(x2, w, b)
+    out_dtype = _default_out(x2, out_dtype)
     m, k = x2.shape
     n = w.shape[0]
     if w.shape[1] != k:
@@ -44,40 +56,44 @@ def linear_forward(x2: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor],
         _check(b, "linear")
         if b.numel() != n:
             raise ValueError("linear: bias size does not match out_features")
-    if k % 8:
-        raise ValueError(f"linear: in_features must be a multiple of 8 (got {k})")
+    if x2.dtype == torch.bfloat16 and k % 8:
+        raise ValueError(f"linear: bfloat16 in_features must be a multiple of 8 (got {k})")
     y = torch.empty((m, n), dtype=out_dtype, device=x2.device)
     with torch.cuda.device(x2.device):
         N.check(N.lib.hapx_linear_forward(y.data_ptr(), x2.data_ptr(), w.data_ptr(), b.data_ptr() if b is not None else None,
-                                          N.BF16, _out_code(out_dtype), m, n, k, _EPILOGUES[epilogue], _stream(x2.device)))
+                                          _out_code(x2.dtype), _out_code(out_dtype), m, n, k, _EPILOGUES[epilogue],
+                                          _stream(x2.device)))
     return y
 
 
-def linear_dgrad(g2: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-    _check(g2, "linear backward"), _check(w, "linear backward")
+def linear_dgrad(g2: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    _check(g2, "linear backward"), _check(w, "linear backward"), _same(g2, w)
+    out_dtype = _default_out(g2, out_dtype)
     m, n = g2.shape
     k = w.shape[1]
-    if n % 8 or k % 8:
-        raise ValueError(f"linear backward: features must be multiples of 8 (got n={n}, k={k})")
+    if g2.dtype == torch.bfloat16 and (n % 8 or k % 8):
+        raise ValueError(f"linear backward: bfloat16 features must be multiples of 8 (got n={n}, k={k})")
     dx = torch.empty((m, k), dtype=out_dtype, device=g2.device)
     with torch.cuda.device(g2.device):
-        N.check(N.lib.hapx_linear_dgrad(dx.data_ptr(), g2.data_ptr(), w.data_ptr(), N.BF16, _out_code(out_dtype), m, n, k,
-                                        _stream(g2.device)))
+        N.check(N.lib.hapx_linear_dgrad(dx.data_ptr(), g2.data_ptr(), w.data_ptr(), _out_code(g2.dtype), _out_code(out_dtype),
+                                        m, n, k, _stream(g2.device)))
     return dx
 
 
 def linear_wgrad(g2: torch.Tensor, x2: torch.Tensor, need_weight: bool = True, need_bias: bool = True,
-                 out_dtype: torch.dtype = torch.bfloat16):
-    _check(g2, "linear backward"), _check(x2, "linear backward")
+                 out_dtype: Optional[torch.dtype] = None):
+    _check(g2, "linear backward"), _check(x2, "linear backward"), _same(g2, x2)
+    out_dtype = _default_out(g2, out_dtype)
     m, n = g2.shape
     k = x2.shape[1]
-    if n % 8 or k % 8:
-        raise ValueError(f"linear backward: features must be multiples of 8 (got n={n}, k={k})")
+    if g2.dtype == torch.bfloat16 and (n % 8 or k % 8):
+        raise ValueError(f"linear backward: bfloat16 features must be multiples of 8 (got n={n}, k={k})")
     dw = torch.empty((n, k), dtype=out_dtype, device=g2.device) if need_weight else None
     db = torch.empty((n,), dtype=out_dtype, device=g2.device) if need_bias else None
     with torch.cuda.device(g2.device):
         N.check(N.lib.hapx_linear_wgrad(dw.data_ptr() if need_weight else None, db.data_ptr() if need_bias else None,
-                                        g2.data_ptr(), x2.data_ptr(), N.BF16, _out_code(out_dtype), m, n, k, _stream(g2.device)))
+                                        g2.data_ptr(), x2.data_ptr(), _out_code(g2.dtype), _out_code(out_dtype), m, n, k,
+                                        _stream(g2.device)))
     return dw, db
 
 
@@ -106,7 +122,7 @@ class _Linear(torch.autograd.Function):
 
 
 def linear(input: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Drop-in for ``torch.nn.functional.linear`` on CUDA bfloat16 tensors."""
+    """Drop-in for ``torch.nn.functional.linear`` on CUDA bfloat16 or float32 tensors."""
     return _Linear.apply(input, weight, bias)
 
 

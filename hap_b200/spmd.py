@@ -1,0 +1,115 @@
+"""Run a synthesized SPMD program: the training step of the reference's ``worker.py``.
+
+Two executors for the same ``torch.fx`` programs:
+
+* :class:`ProcessWorker` - one rank per process (``worker.py:44, 58-83``): the program is an
+  ordinary ``torch.fx.GraphModule`` whose collective nodes call :mod:`hap_b200.collectives`.
+* :class:`LockstepWorld` - all ``world`` ranks of the program inside one process on one device.
+  The ranks' graphs are walked node by node in lockstep; at a collective node the inputs of
+  all ranks go to the list-based backend (:class:`hap_b200.LocalCollectives`, i.e. one
+  cooperative kernel over all virtual ranks), every other node runs per rank.  This is how the
+  whole step is exercised on a single GPU.
+
+Both follow the reference's step: ``zero_grad`` -> forward -> partial losses summed
+(``dist.reduce`` at ``worker.py:63-64``) -> backward -> ``clip_grad_norm_(params, 0.5)`` over the
+LOCAL shards only (``worker.py:74``) -> Adam (``worker.py:47, 76``).
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Sequence
+
+import torch
+from torch.fx.node import map_arg
+
+from .collectives import NAMES as _COLLECTIVE_NAMES
+
+
+def _is_collective(target) -> bool:
+    module = (getattr(target, "__module__", "") or "").split(".")[-1]
+    return getattr(target, "__name__", None) in _COLLECTIVE_NAMES and module in ("collectives", "gloo_port")
+
+
+class LockstepWorld:
+    def __init__(self, modules: Sequence[torch.fx.GraphModule], backend, lr: float = 5e-4, clip: float = 0.5):
+        self.modules = list(modules)
+        self.world = len(self.modules)
+        self.backend = backend
+        self.clip = clip
+        self.optimizers = [torch.optim.Adam(m.parameters(), lr=lr) for m in self.modules]
+        self._nodes = [list(m.graph.nodes) for m in self.modules]
+        if len({len(n) for n in self._nodes}) != 1:
+            raise ValueError("SPMD ranks must run the same node sequence")
+
+    def forward(self, inputs_per_rank: Sequence[Sequence[torch.Tensor]]) -> List[torch.Tensor]:
+        envs = [dict() for _ in range(self.world)]
+        feeds = [iter(inp) for inp in inputs_per_rank]
+        results = [None] * self.world
+        load = lambda r: (lambda n: envs[r][n])
+        for step in zip(*self._nodes):
+            n0 = step[0]
+            if n0.op == "placeholder":
+                for r, n in enumerate(step):
+                    envs[r][n] = next(feeds[r])
+            elif n0.op == "get_attr":
+                for r, n in enumerate(step):
+                    obj = self.modules[r]
+                    for part in n.target.split("."):
+                        obj = getattr(obj, part)
+                    envs[r][n] = obj
+            elif n0.op == "call_function" and _is_collective(n0.target):
+                name = n0.target.__name__
+                per_rank = [map_arg(n.args, load(r)) for r, n in enumerate(step)]
+                tensors = [a[0] for a in per_rank]
+                if name in ("all_reduce", "replicate"):
+                    outs = getattr(self.backend, name)(tensors)
+                elif name == "all_to_all":
+                    outs = self.backend.all_to_all(tensors, *per_rank[0][1:5])
+                else:  # (tensor, dim, sharding_lengths, rank)
+                    outs = getattr(self.backend, name)(tensors, per_rank[0][1], per_rank[0][2])
+                for r, n in enumerate(step):
+                    envs[r][n] = outs[r]
+            elif n0.op == "call_function":
+                for r, n in enumerate(step):
+                    envs[r][n] = n.target(*map_arg(n.args, load(r)), **map_arg(n.kwargs, load(r)))
+            elif n0.op == "call_method":
+                for r, n in enumerate(step):
+                    args = map_arg(n.args, load(r))
+                    envs[r][n] = getattr(args[0], n.target)(*args[1:], **map_arg(n.kwargs, load(r)))
+            elif n0.op == "output":
+                for r, n in enumerate(step):
+                    results[r] = map_arg(n.args[0], load(r))
+            else:
+                raise NotImplementedError(n0.op)
+        return results
+
+    def step(self, inputs_per_rank) -> float:
+        """One training iteration for all ranks; returns the global loss (sum of the partial losses)."""
+        for opt in self.optimizers:
+            opt.zero_grad()
+        losses = self.forward(inputs_per_rank)
+        total = torch.stack([l.detach() for l in losses]).sum()
+        torch.stack(losses).sum().backward()
+        for m, opt in zip(self.modules, self.optimizers):
+            torch.nn.utils.clip_grad_norm_(m.parameters(), self.clip)
+            opt.step()
+        return total
+
+
+class ProcessWorker:
+    def __init__(self, module: torch.fx.GraphModule, lr: float = 5e-4, clip: float = 0.5,
+                 reduce_loss: Callable[[torch.Tensor], torch.Tensor] = None):
+        self.module = module
+        self.clip = clip
+        self.optimizer = torch.optim.Adam(module.parameters(), lr=lr)
+        self.reduce_loss = reduce_loss
+
+    def step(self, *inputs) -> torch.Tensor:
+        self.optimizer.zero_grad()
+        loss = self.module(*inputs)
+        total = loss.detach().clone()
+        if self.reduce_loss is not None:
+            total = self.reduce_loss(total)
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_(self.module.parameters(), self.clip)
+        self.optimizer.step()
+        return total

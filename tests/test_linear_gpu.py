@@ -88,11 +88,33 @@ def test_leading_dims_are_flattened():
     close(wd.grad, dw)
 
 
+FP32_SHAPES = [(38, 4096, 1024), (26, 1024, 4096), (64, 2458, 1024), (64, 410, 4096), (7, 5, 3), (130, 67, 33)]
+
+
+@pytest.mark.parametrize("m,n,k", FP32_SHAPES)
+def test_fp32_forward_and_backward_within_1e5(m, n, k):
+    """The fp32 configuration (2-layer MLP, ratios [.6,.4]) must match to 1e-5 relative."""
+    g = torch.Generator().manual_seed(39)
+    x, w, b = torch.randn(m, k, generator=g), torch.randn(n, k, generator=g) * k ** -0.5, torch.randn(n, generator=g)
+    gy = torch.randn(m, n, generator=g)
+    xd, wd, bd = (t.to(DEV).requires_grad_(True) for t in (x, w, b))
+    y = hap_b200.linear(xd, wd, bd)
+    y.backward(gy.to(DEV))
+    assert y.dtype == torch.float32
+    dx, dw, db = lm.linear_backward(gy, x, w)
+    for got, want in ((y, lm.linear_forward(x, w, b)), (xd.grad, dx), (wd.grad, dw), (bd.grad, db)):
+        rms = float(want.pow(2).mean().sqrt())
+        err = (got.detach().double().cpu() - want).abs()
+        assert float((err - 1e-5 * want.abs()).max()) <= 1e-5 * rms
+
+
 def test_unsupported_inputs_raise():
     x, w = gen((8, 12), 1).to(DEV), gen((8, 12), 2).to(DEV)
     with pytest.raises(ValueError):
-        L.linear_forward(x, w, None)                       # k % 8 != 0
+        L.linear_forward(x, w, None)                       # bf16 with k % 8 != 0
     with pytest.raises(TypeError):
-        L.linear_forward(x.float(), w.float(), None)
+        L.linear_forward(x.half(), w.half(), None)
+    with pytest.raises(TypeError):
+        L.linear_forward(x.float(), w, None)                # mixed dtypes
     with pytest.raises(RuntimeError):
         L.linear_forward(x.cpu(), w.cpu(), None)

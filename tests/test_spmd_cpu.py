@@ -1,0 +1,85 @@
+"""Host logic of the SPMD path on the CPU: the plan emitter and the lockstep executor replay the
+synthesized MLP programs (data parallel and column parallel, ratios [.6,.4]) with the CPU oracle
+backend and must reproduce the unsharded model; the same programs run as 2 gloo processes with
+the port of the reference's collectives (the N>1 host path)."""
+import os
+import sys
+import tempfile
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from hap_b200.spmd import LockstepWorld, ProcessWorker
+from oracle.lockstep_backend import OracleCollectives
+from tests import spmd_common as C
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("plan", ["dp", "tp"])
+def test_lockstep_program_reproduces_the_unsharded_model(plan):
+    model, dims = C.reference_model(small=True)
+    x, y = C.batch(dims)
+    want_loss, want_grads = C.full_gradients(model, x, y)
+    world = LockstepWorld(C.rank_modules(model, plan, C.cpu_namespace()), OracleCollectives())
+    losses = world.forward([(x, y), (x, y)])
+    assert abs(float(sum(losses)) - want_loss) <= 1e-5 * abs(want_loss)
+    torch.stack(losses).sum().backward()
+    for r, m in enumerate(world.modules):
+        for name, p in m.named_parameters():
+            want = C.expected_shard(want_grads[name], name, plan, r, dims)
+            assert p.grad.shape == want.shape, (plan, r, name)
+            torch.testing.assert_close(p.grad.double(), want, rtol=1e-4, atol=1e-4 * float(want.abs().max()))
+
+
+def test_emitted_programs_have_the_planner_node_sequence():
+    model, dims = C.reference_model(small=True)
+    ns = C.cpu_namespace()
+    import copy
+    dp = C.P.emit_mlp(copy.deepcopy(model), "dp", C.RATIOS, 1, C.BATCH, ns)
+    names = [n.target.__name__ if callable(n.target) else n.target for n in dp.nodes if n.op in ("call_function", "call_method")]
+    assert names == ["split", "getitem", "split", "getitem", "replicate", "replicate", "replicate", "replicate",
+                     "linear", "gelu", "linear", "mse_loss"]
+    m = copy.deepcopy(model)
+    tp = C.P.emit_mlp(m, "tp", C.RATIOS, 1, C.BATCH, ns)
+    names = [n.target.__name__ if callable(n.target) else n.target for n in tp.nodes if n.op in ("call_function", "call_method")]
+    assert names == ["linear", "all_gather", "gelu", "linear", "split", "getitem", "mse_loss"]
+    # parameters were cut in place: rank 1 holds the second shard (hap.rs:929-944)
+    assert tuple(m.fc1.weight.shape) == (136 - 82, 64) and tuple(m.fc2.bias.shape) == (72 - 43,)
+    gather = next(n for n in tp.nodes if n.op == "call_function" and n.target.__name__ == "all_gather")
+    assert gather.args[1:] == (1, [82, 54], 1)
+
+
+def _gloo_worker(rank, world, store, plan, out_dir):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    from tests import spmd_common as C2
+    dist.init_process_group("gloo", rank=rank, world_size=world, init_method=f"file://{store}")
+    model, dims = C2.reference_model(small=True)
+    x, y = C2.batch(dims)
+    import copy
+    m = copy.deepcopy(model)
+    graph = C2.P.emit_mlp(m, plan, C2.RATIOS, rank, C2.BATCH, C2.cpu_namespace())
+    worker = ProcessWorker(torch.fx.GraphModule(m, graph), reduce_loss=lambda t: (dist.all_reduce(t), t)[1])
+    totals = [float(worker.step(x, y)) for _ in range(2)]
+    torch.save({"totals": totals, "params": {n: p.detach().clone() for n, p in worker.module.named_parameters()}},
+               os.path.join(out_dir, f"rank{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("plan", ["dp", "tp"])
+def test_two_gloo_processes_match_the_lockstep_replay(plan):
+    model, dims = C.reference_model(small=True)
+    x, y = C.batch(dims)
+    world = LockstepWorld(C.rank_modules(model, plan, C.cpu_namespace()), OracleCollectives())
+    want_totals = [float(world.step([(x, y), (x, y)])) for _ in range(2)]
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_gloo_worker, args=(2, os.path.join(d, "store"), plan, d), nprocs=2, join=True)
+        for r in range(2):
+            got = torch.load(os.path.join(d, f"rank{r}.pt"), weights_only=False)
+            for a, b in zip(got["totals"], want_totals):
+                assert abs(a - b) <= 1e-5 * abs(b)
+            for name, p in world.modules[r].named_parameters():
+                torch.testing.assert_close(got["params"][name], p.detach(), rtol=1e-5, atol=1e-6)
