@@ -20,6 +20,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <string>
 
@@ -364,6 +365,255 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+
+// ---- two-CTA variant -----------------------------------------------------------------------------
+// A cluster of two CTAs (an SM pair) works on one 256 x 256 output tile with tcgen05.mma
+// cta_group::2: CTA c holds rows [128c, 128c+128) of A and of the accumulator, and loads only
+// HALF of the B tile (columns [128c, 128c+128) of the output); the tensor cores of both SMs read
+// both halves.  Per SM this moves 32 KiB of operands per 64-deep slice instead of 48 KiB, which
+// is what lifts the kernel off the L2-to-shared-memory bandwidth limit, and leaves room for 6
+// pipeline stages.  The leader CTA (cluster rank 0) issues all MMAs; barrier traffic between the
+// two CTAs goes through cluster-mapped mbarriers.  No TMA multicast is used.
+__device__ __forceinline__ unsigned cluster_ctarank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ unsigned map_to_cta(unsigned smem_addr, unsigned cta) {
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load whose completion bytes are credited to an mbarrier of the pair's leader CTA.
+__device__ __forceinline__ void tma_load_2d_pair(unsigned dst, const CUtensorMap* map, int x, int y, unsigned leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(leader_bar)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(unsigned dst_smem, unsigned cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(unsigned taddr, unsigned cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma2_bf16(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned idesc,
+                                           unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the mbarrier at the same offset in BOTH CTAs once all MMAs issued so far are done.
+__device__ __forceinline__ void umma2_commit_both(unsigned bar) {
+  const unsigned short mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"(mask)
+               : "memory");
+}
+
+template <bool A_MN, bool B_MN>
+struct Cfg2 {
+  static constexpr int BN = 256;                     // output columns per pair tile
+  static constexpr int STAGES = 6;
+  static constexpr unsigned A_BYTES = BM * BK * 2;   // this CTA's 128 rows
+  static constexpr unsigned B_BYTES = (BN / 2) * BK * 2;
+  static constexpr unsigned STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr unsigned TMEM_COLS = 512;
+  static constexpr unsigned SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + BN * 4 + 256;
+  static constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                                    ((unsigned)(BN >> 3) << 17) | ((unsigned)((2 * BM) >> 4) << 24);
+};
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+  using C = Cfg2<A_MN, B_MN>;
+  constexpr int BN = C::BN;
+  extern __shared__ unsigned char smem_raw[];
+  const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  float* bias_tile = reinterpret_cast<float*>(gen_base + C::STAGES * C::STAGE_BYTES);
+  const unsigned bars = base + C::STAGES * C::STAGE_BYTES + BN * 4;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + 2 + a); };
+  const unsigned tmem_slot = bars + 8u * (2 * C::STAGES + 4);
+  volatile unsigned* tmem_slot_gen = reinterpret_cast<volatile unsigned*>(gen_base + C::STAGES * C::STAGE_BYTES + BN * 4 + 8 * (2 * C::STAGES + 4));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned cta = cluster_ctarank();            // 0 = leader
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int total_tiles = p.m_tiles * p.n_tiles;     // m_tiles counts 256-row tiles here
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 2 * kEpilogueThreads); }
+    fence_barrier_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc2(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish2();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                                // both CTAs' barriers and TMEM are ready
+  tc_fence_after();
+  const unsigned tmem_base = *tmem_slot_gen;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (one per CTA) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      unsigned phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+        const int m0 = (tile % p.m_tiles) * (2 * BM) + (int)cta * BM;
+        const int n0 = (tile / p.m_tiles) * BN + (int)cta * (BN / 2);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u)) { ok = false; break; }
+          const unsigned sa = base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+          const unsigned leader_full = map_to_cta(full_bar(stage), 0);
+          if (cta == 0) mbar_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);   // bytes of both CTAs
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d_pair(sa, &tmA, k0, m0, leader_full);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i) tma_load_2d_pair(sa + i * 8192u, &tmA, m0 + 64 * i, k0, leader_full);
+          }
+          if (!B_MN) {
+            tma_load_2d_pair(sb, &tmB, k0, n0, leader_full);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / 128; ++i) tma_load_2d_pair(sb + i * 8192u, &tmB, n0 + 64 * i, k0, leader_full);
+          }
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) atomicCAS(p.error, 0u, 1u);
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (lane == 0 && cta == 0) {
+      int stage = 0, acc = 0;
+      unsigned phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u)) { ok = false; break; }
+        tc_fence_after();
+        const unsigned d_tmem = tmem_base + (unsigned)(acc * BN);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase)) { ok = false; break; }
+          tc_fence_after();
+          const unsigned sa = base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const unsigned long long da = A_MN ? make_desc(sa + k * 2048u, 8192u, 1024u) : make_desc(sa + k * 32u, 16u, 1024u);
+            const unsigned long long db = B_MN ? make_desc(sb + k * 2048u, 8192u, 1024u) : make_desc(sb + k * 32u, 16u, 1024u);
+            umma2_bf16(d_tmem, da, db, C::IDESC, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma2_commit_both(empty_bar(stage));
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma2_commit_both(tfull_bar(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (!ok) atomicCAS(p.error, 0u, 2u);
+    }
+  } else {
+    // ---------------- epilogue: this CTA's 128 rows of the pair tile ----------------
+    const int q = warp & 3;
+    const int et = threadIdx.x - 64;
+    int acc = 0;
+    unsigned acc_phase = 0;
+    bool ok = true;
+    const bool vec_ok = p.out_f32 ? ((p.ldd & 3) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15u) == 0)
+                                  : ((p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15u) == 0);
+    for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+      const int m0 = (tile % p.m_tiles) * (2 * BM) + (int)cta * BM, n0 = (tile / p.m_tiles) * BN;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      for (int j = et; j < BN; j += kEpilogueThreads) {
+        float b = 0.f;
+        if (p.bias != nullptr && n0 + j < p.N) b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n0 + j]);
+        bias_tile[j] = b;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      ok = epilogue_all(mbar_wait(tfull_bar(acc), acc_phase));
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const unsigned t_row = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(acc * BN);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        unsigned r[32];
+        tmem_ld_32x32(t_row + (unsigned)c0, r);
+        tmem_ld_wait();
+        if (row < p.M && n0 + c0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = apply_epilogue(__uint_as_float(r[j]) + bias_tile[c0 + j], p.epilogue);
+          const int ncols = min(32, p.N - (n0 + c0));
+          if (p.out_f32) {
+            float* out = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + n0 + c0;
+            if (vec_ok && ncols == 32) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = v[j];
+            }
+          } else {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd + n0 + c0;
+            if (vec_ok && ncols == 32) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 pk;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
+                pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
+                *reinterpret_cast<uint4*>(out + j) = pk;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = __float2bfloat16_rn(v[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));   // tell the leader this thread has drained its rows
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (!ok) atomicCAS(p.error, 0u, 3u);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();      // neither CTA may leave (or free TMEM) while the other can still signal it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, C::TMEM_COLS);
+  }
+}
+
 // ---- host side ------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -449,6 +699,42 @@ static int launch(const void* A, long long lda, const void* B, long long ldb, Pa
   return HAPX_OK;
 }
 
+
+template <bool A_MN, bool B_MN>
+static int launch2(const void* A, long long lda, const void* B, long long ldb, Params& p, cudaStream_t stream, int sm_count) {
+  using C = Cfg2<A_MN, B_MN>;
+  CUtensorMap tmA, tmB;
+  if (int e = A_MN ? make_map(&tmA, A, p.M, p.Kc, lda, 64, 64) : make_map(&tmA, A, p.Kc, p.M, lda, BK, BM)) return e;
+  if (int e = B_MN ? make_map(&tmB, B, p.N, p.Kc, ldb, 64, 64) : make_map(&tmB, B, p.Kc, p.N, ldb, BK, C::BN / 2)) return e;
+  p.m_tiles = (p.M + 2 * BM - 1) / (2 * BM);
+  p.n_tiles = (p.N + C::BN - 1) / C::BN;
+  p.k_blocks = (p.Kc + BK - 1) / BK;
+  auto kernel = gemm2_bf16_kernel<A_MN, B_MN>;
+  static int max_clusters = 0;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (max_clusters == 0) {
+    HAPX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES));
+    cfg.gridDim = dim3(sm_count / 2 * 2);
+    int n = 0;
+    HAPX_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+    if (n < 1) return fail(HAPX_ERR_CUDA, "gemm: no SM pair can host the two-CTA kernel");
+    max_clusters = n;
+  }
+  const int pairs = std::max(1, std::min(p.m_tiles * p.n_tiles, max_clusters));
+  cfg.gridDim = dim3(2 * pairs);
+  HAPX_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, p));
+  count_launch();
+  return HAPX_OK;
+}
+
 // D[M,N] = A * B^T with the given operand majors.  lda/ldb/ldd in elements.
 static int gemm_bf16(void* D, int out_f32, long long ldd, const void* A, bool a_mn, long long lda, const void* B, bool b_mn,
                      long long ldb, const void* bias, int epilogue, long long M, long long N, long long Kc, cudaStream_t stream) {
@@ -467,6 +753,13 @@ static int gemm_bf16(void* D, int out_f32, long long ldd, const void* A, bool a_
     const long long tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
     return (double)((tiles + dev->sm_count - 1) / dev->sm_count) * bn;
   };
+  // SM pairs (256 x 256 tiles, half the B traffic per SM) whenever there is more than one row tile
+  static const bool pair_kernel = std::getenv("HAPX_GEMM_SINGLE_CTA") == nullptr;
+  if (pair_kernel && M > BM && N > 64) {
+    if (!a_mn && !b_mn) return launch2<false, false>(A, lda, B, ldb, p, stream, dev->sm_count);
+    if (!a_mn && b_mn) return launch2<false, true>(A, lda, B, ldb, p, stream, dev->sm_count);
+    if (a_mn && b_mn) return launch2<true, true>(A, lda, B, ldb, p, stream, dev->sm_count);
+  }
   const int bn = (waves(256) <= waves(128)) ? 256 : 128;
 #define HAPX_GEMM_CASE(BN_, AMN_, BMN_) \
   if (bn == BN_ && a_mn == AMN_ && b_mn == BMN_) return launch<BN_, AMN_, BMN_>(A, lda, B, ldb, p, stream, dev->sm_count);

@@ -17,10 +17,15 @@ DEV = "cuda:0"
 
 
 def rel_close(got, want, tol, what):
+    """Relative error of the whole tensor (Frobenius norm) within tol; every element within
+    tol * (|want| + rms) in fp32, and within 4x that in bf16, where a single rounding flip early in
+    the chain (one bf16 ulp = 0.8 %) shows up in a handful of the millions of entries."""
     got, want = got.detach().double().cpu(), want.detach().double().cpu()
-    scale = float(want.pow(2).mean().sqrt()) + 1e-30
-    err = float((got - want).abs().max())
-    assert err <= tol * max(scale, float(want.abs().max()) * 0.1), f"{what}: max err {err:.3g} vs scale {scale:.3g}"
+    rms = float(want.pow(2).mean().sqrt()) + 1e-30
+    assert float((got - want).norm()) <= tol * float(want.norm()) + 1e-30, f"{what}: relative error {float((got - want).norm() / want.norm()):.3g}"
+    slack = 1.0 if tol < 1e-3 else 4.0
+    excess = (got - want).abs() - slack * tol * (want.abs() + rms)
+    assert float(excess.max()) <= 0, f"{what}: {int((excess > 0).sum())} of {want.numel()} entries off by up to {float(excess.max()):.3g} (rms {rms:.3g})"
 
 
 @pytest.mark.parametrize("plan", ["dp", "tp"])
@@ -30,12 +35,14 @@ def test_training_step_matches_cpu_replay(plan, dtype, tol):
         pytest.skip("column-parallel bf16 shards (2458 columns) need 16-byte row pitches: repacking path not built yet")
     model, dims = C.reference_model(dtype)
     x, y = C.batch(dims, dtype)
-    cpu = LockstepWorld(C.rank_modules(model.float(), plan, C.cpu_namespace()), OracleCollectives())
+    # the CPU replay runs in the same dtype, so both sides round at the same places and differ only
+    # in accumulation order
+    cpu = LockstepWorld(C.rank_modules(model, plan, C.cpu_namespace()), OracleCollectives())
     comm = hap_b200.local_comm(2, DEV, stage_bytes=64 << 20, heap_bytes=96 << 20)
     try:
         gpu = LockstepWorld(C.rank_modules(model.to(dtype), plan, hap_b200.plan.default_namespace(), device=DEV),
                             hap_b200.LocalCollectives(comm))
-        xf, yf = x.float(), y.float()
+        xf, yf = x, y
         xg, yg = x.to(DEV), y.to(DEV)
         # forward + backward of the first step: partial losses and every parameter-gradient shard
         want_losses = cpu.forward([(xf, yf), (xf, yf)])
@@ -55,7 +62,13 @@ def test_training_step_matches_cpu_replay(plan, dtype, tol):
             assert abs(got - want) <= tol * abs(want), (plan, it, got, want)
         for r in range(2):
             for (name, pw), (_, pg) in zip(cpu.modules[r].named_parameters(), gpu.modules[r].named_parameters()):
-                rel_close(pg, pw, max(tol, 1e-4) if dtype == torch.float32 else 2e-2, f"{plan} rank {r} param {name}")
+                # Adam normalises each element's update to about +-lr whatever the gradient's size, so
+                # entries whose gradient is near zero may move differently: allow 5 % of the distance
+                # two steps can travel (lr = 5e-4) in fp32, one bf16 ulp of the parameter scale in bf16
+                if dtype == torch.float32:
+                    assert float((pg.detach().cpu() - pw.detach()).abs().max()) <= 0.05 * 2 * 5e-4, (plan, r, name)
+                else:
+                    rel_close(pg, pw, 2e-2, f"{plan} rank {r} param {name}")
         comm.check()
         hap_b200.linear_ops.gemm_status()
     finally:
