@@ -21,6 +21,7 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <string>
 
@@ -47,6 +48,7 @@ struct Params {
   int out_f32;            // D is fp32 instead of bf16
   int m_tiles, n_tiles, k_blocks;
   unsigned* error;        // device word: 0 or a code left by a wait that ran out
+  int tma_store;          // D's pitch and base allow bulk tensor stores
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -164,19 +166,17 @@ __device__ __forceinline__ unsigned long long make_desc(unsigned smem_addr, unsi
   return d;
 }
 
-template <int BN, bool A_MN, bool B_MN>
-struct Cfg {
-  static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
-  static constexpr unsigned A_BYTES = BM * BK * 2;
-  static constexpr unsigned B_BYTES = BN * BK * 2;
-  static constexpr unsigned STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr unsigned TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
-  // dynamic shared memory: stages (1024-byte aligned) + bias tile + barriers
-  static constexpr unsigned SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + BN * 4 + 256;
-  // instruction descriptor: fp32 accumulate, bf16 x bf16, majors, N >> 3, M >> 4
-  static constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
-                                    ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
-};
+
+// ---- epilogue -------------------------------------------------------------------------------------
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, unsigned src_smem, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src_smem), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+constexpr unsigned kStoreTileBytes = 128 * 128;   // 128 rows x 128 bytes (64 bf16 or 32 fp32 columns)
 
 __device__ __forceinline__ float apply_epilogue(float v, int epi) {
   switch (epi) {
@@ -187,22 +187,142 @@ __device__ __forceinline__ float apply_epilogue(float v, int epi) {
   }
 }
 
+// Drain one 128 x BN accumulator tile: this thread owns row (q*32 + lane) of it.
+// With `use_tma` the rows go through a 128-byte-swizzled staging tile in shared memory and leave
+// as bulk tensor stores (fully coalesced, clipped at the matrix edge by the tensor map); otherwise
+// each thread stores its own row segments directly (any row pitch, any alignment).
+template <int BN>
+__device__ __forceinline__ void drain_tile(const Params& p, const CUtensorMap* tmD, bool use_tma, unsigned char* stage_gen,
+                                           unsigned stage_u32, const float* bias_tile, unsigned t_row, int m0, int n0, int q,
+                                           int lane, int et, int& buf) {
+  const int row_in_tile = q * 32 + lane;
+  const int row = m0 + row_in_tile;
+  if (use_tma) {
+    constexpr int CH = 32;   // accumulator columns per tcgen05.ld
+    const int cols_per_store = p.out_f32 ? 32 : 64;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += cols_per_store) {
+      if (n0 + c0 >= p.N) break;                       // same decision in every thread
+      unsigned r0[32], r1[32];
+      tmem_ld_32x32(t_row + (unsigned)c0, r0);
+      if (!p.out_f32) tmem_ld_32x32(t_row + (unsigned)(c0 + CH), r1);
+      tmem_ld_wait();
+      if (et == 0) bulk_wait_read_1();                 // the store issued two chunks ago has left this buffer
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      unsigned char* tile = stage_gen + buf * kStoreTileBytes + row_in_tile * 128;
+      const int sw = row_in_tile & 7;
+      if (p.out_f32) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float4 o;
+          o.x = apply_epilogue(__uint_as_float(r0[4 * j]) + bias_tile[c0 + 4 * j], p.epilogue);
+          o.y = apply_epilogue(__uint_as_float(r0[4 * j + 1]) + bias_tile[c0 + 4 * j + 1], p.epilogue);
+          o.z = apply_epilogue(__uint_as_float(r0[4 * j + 2]) + bias_tile[c0 + 4 * j + 2], p.epilogue);
+          o.w = apply_epilogue(__uint_as_float(r0[4 * j + 3]) + bias_tile[c0 + 4 * j + 3], p.epilogue);
+          *reinterpret_cast<float4*>(tile + ((j ^ sw) << 4)) = o;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const unsigned* src = (j < 4) ? r0 : r1;
+          const int b = (j & 3) * 8, cb = c0 + j * 8;
+          float v[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = apply_epilogue(__uint_as_float(src[b + e]) + bias_tile[cb + e], p.epilogue);
+          __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
+          __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]), h3 = __floats2bfloat162_rn(v[6], v[7]);
+          uint4 pk;
+          pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
+          pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
+          *reinterpret_cast<uint4*>(tile + ((j ^ sw) << 4)) = pk;
+        }
+      }
+      fence_proxy_async();                             // make the tile visible to the bulk-copy engine
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (et == 0) {
+        tma_store_2d(tmD, stage_u32 + buf * kStoreTileBytes, n0 + c0, m0);
+        bulk_commit_group();
+      }
+      buf ^= 1;
+    }
+    return;
+  }
+  const bool vec_ok = p.out_f32 ? ((p.ldd & 3) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15u) == 0)
+                                : ((p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15u) == 0);
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += 32) {
+    unsigned r[32];
+    tmem_ld_32x32(t_row + (unsigned)c0, r);
+    tmem_ld_wait();
+    if (row < p.M && n0 + c0 < p.N) {
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = apply_epilogue(__uint_as_float(r[j]) + bias_tile[c0 + j], p.epilogue);
+      const int ncols = min(32, p.N - (n0 + c0));
+      if (p.out_f32) {
+        float* out = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + n0 + c0;
+        if (vec_ok && ncols == 32) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = v[j];
+        }
+      } else {
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd + n0 + c0;
+        if (vec_ok && ncols == 32) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 pk;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+            pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
+            pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
+            *reinterpret_cast<uint4*>(out + j) = pk;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = __float2bfloat16_rn(v[j]);
+        }
+      }
+    }
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN>
+struct Cfg {
+  static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr unsigned A_BYTES = BM * BK * 2;
+  static constexpr unsigned B_BYTES = BN * BK * 2;
+  static constexpr unsigned STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr unsigned TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
+  // dynamic shared memory: stages (1024-byte aligned) + bias tile + barriers
+  static constexpr unsigned SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 2 * kStoreTileBytes + BN * 4 + 256;
+  // instruction descriptor: fp32 accumulate, bf16 x bf16, majors, N >> 3, M >> 4
+  static constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                                    ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+};
+
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmD, const Params p) {
   using C = Cfg<BN, A_MN, B_MN>;
   extern __shared__ unsigned char smem_raw[];
   const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
-  float* bias_tile = reinterpret_cast<float*>(gen_base + C::STAGES * C::STAGE_BYTES);
-  const unsigned bars = base + C::STAGES * C::STAGE_BYTES + BN * 4;
+  constexpr unsigned kOff = C::STAGES * C::STAGE_BYTES + 2 * kStoreTileBytes;   // stages, then the two store tiles
+  unsigned char* store_gen = gen_base + C::STAGES * C::STAGE_BYTES;
+  const unsigned store_u32 = base + C::STAGES * C::STAGE_BYTES;
+  float* bias_tile = reinterpret_cast<float*>(gen_base + kOff);
+  const unsigned bars = base + kOff + BN * 4;
   // barrier map (8 bytes each): full[s], empty[s], tmem_full[2], tmem_empty[2]; then the TMEM address slot
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
   auto tfull_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + a); };
   auto tempty_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + 2 + a); };
   const unsigned tmem_slot = bars + 8u * (2 * C::STAGES + 4);
-  volatile unsigned* tmem_slot_gen = reinterpret_cast<volatile unsigned*>(gen_base + C::STAGES * C::STAGE_BYTES + BN * 4 + 8 * (2 * C::STAGES + 4));
+  volatile unsigned* tmem_slot_gen = reinterpret_cast<volatile unsigned*>(gen_base + kOff + BN * 4 + 8 * (2 * C::STAGES + 4));
   volatile unsigned* abort_flag = tmem_slot_gen + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -295,8 +415,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int acc = 0;
     unsigned acc_phase = 0;
     bool ok = true;
-    const bool vec_ok = p.out_f32 ? ((p.ldd & 3) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15u) == 0)
-                                  : ((p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15u) == 0);
+    int store_buf = 0;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * BN;
       // bias tile -> shared (fp32)
@@ -310,50 +429,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       ok = epilogue_all(mbar_wait(tfull_bar(acc), acc_phase));
       if (!ok) break;
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
       const unsigned t_row = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(acc * BN);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        unsigned r[32];
-        tmem_ld_32x32(t_row + (unsigned)c0, r);
-        tmem_ld_wait();
-        if (row < p.M && n0 + c0 < p.N) {
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = apply_epilogue(__uint_as_float(r[j]) + bias_tile[c0 + j], p.epilogue);
-          const int ncols = min(32, p.N - (n0 + c0));
-          if (p.out_f32) {
-            float* out = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + n0 + c0;
-            if (vec_ok && ncols == 32) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = v[j];
-            }
-          } else {
-            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd + n0 + c0;
-            if (vec_ok && ncols == 32) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 pk;
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
-                pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
-                *reinterpret_cast<uint4*>(out + j) = pk;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = __float2bfloat16_rn(v[j]);
-            }
-          }
-        }
-      }
+      drain_tile<BN>(p, &tmD, p.tma_store != 0, store_gen, store_u32, bias_tile, t_row, m0, n0, q, lane, et, store_buf);
       tc_fence_before();
       mbar_arrive(tempty_bar(acc));     // this thread has drained its part of the accumulator
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
+    if (et == 0) bulk_wait_all();   // bulk stores still read the staging tiles
     if (!ok) { *abort_flag = 1; atomicCAS(p.error, 0u, 3u); }
   }
 
@@ -432,27 +514,31 @@ struct Cfg2 {
   static constexpr unsigned B_BYTES = (BN / 2) * BK * 2;
   static constexpr unsigned STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr unsigned TMEM_COLS = 512;
-  static constexpr unsigned SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + BN * 4 + 256;
+  static constexpr unsigned SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 2 * kStoreTileBytes + BN * 4 + 256;
   static constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
                                     ((unsigned)(BN >> 3) << 17) | ((unsigned)((2 * BM) >> 4) << 24);
 };
 
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmD, const Params p) {
   using C = Cfg2<A_MN, B_MN>;
   constexpr int BN = C::BN;
   extern __shared__ unsigned char smem_raw[];
   const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
-  float* bias_tile = reinterpret_cast<float*>(gen_base + C::STAGES * C::STAGE_BYTES);
-  const unsigned bars = base + C::STAGES * C::STAGE_BYTES + BN * 4;
+  constexpr unsigned kOff = C::STAGES * C::STAGE_BYTES + 2 * kStoreTileBytes;   // stages, then the two store tiles
+  unsigned char* store_gen = gen_base + C::STAGES * C::STAGE_BYTES;
+  const unsigned store_u32 = base + C::STAGES * C::STAGE_BYTES;
+  float* bias_tile = reinterpret_cast<float*>(gen_base + kOff);
+  const unsigned bars = base + kOff + BN * 4;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
   auto tfull_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + a); };
   auto tempty_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + 2 + a); };
   const unsigned tmem_slot = bars + 8u * (2 * C::STAGES + 4);
-  volatile unsigned* tmem_slot_gen = reinterpret_cast<volatile unsigned*>(gen_base + C::STAGES * C::STAGE_BYTES + BN * 4 + 8 * (2 * C::STAGES + 4));
+  volatile unsigned* tmem_slot_gen = reinterpret_cast<volatile unsigned*>(gen_base + kOff + BN * 4 + 8 * (2 * C::STAGES + 4));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned cta = cluster_ctarank();            // 0 = leader
@@ -544,8 +630,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     int acc = 0;
     unsigned acc_phase = 0;
     bool ok = true;
-    const bool vec_ok = p.out_f32 ? ((p.ldd & 3) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15u) == 0)
-                                  : ((p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15u) == 0);
+    int store_buf = 0;
     for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
       const int m0 = (tile % p.m_tiles) * (2 * BM) + (int)cta * BM, n0 = (tile / p.m_tiles) * BN;
       asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -558,50 +643,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       ok = epilogue_all(mbar_wait(tfull_bar(acc), acc_phase));
       if (!ok) break;
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
       const unsigned t_row = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(acc * BN);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        unsigned r[32];
-        tmem_ld_32x32(t_row + (unsigned)c0, r);
-        tmem_ld_wait();
-        if (row < p.M && n0 + c0 < p.N) {
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = apply_epilogue(__uint_as_float(r[j]) + bias_tile[c0 + j], p.epilogue);
-          const int ncols = min(32, p.N - (n0 + c0));
-          if (p.out_f32) {
-            float* out = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + n0 + c0;
-            if (vec_ok && ncols == 32) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = v[j];
-            }
-          } else {
-            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd + n0 + c0;
-            if (vec_ok && ncols == 32) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 pk;
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
-                pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
-                *reinterpret_cast<uint4*>(out + j) = pk;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = __float2bfloat16_rn(v[j]);
-            }
-          }
-        }
-      }
+      drain_tile<BN>(p, &tmD, p.tma_store != 0, store_gen, store_u32, bias_tile, t_row, m0, n0, q, lane, et, store_buf);
       tc_fence_before();
       mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));   // tell the leader this thread has drained its rows
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
+    if (et == 0) bulk_wait_all();   // bulk stores still read the staging tiles
     if (!ok) atomicCAS(p.error, 0u, 3u);
   }
 
@@ -629,6 +677,28 @@ static EncodeTiledFn encode_fn() {
       fn = reinterpret_cast<EncodeTiledFn>(sym);
   });
   return fn;
+}
+
+// Tensor map of the output for bulk stores: boxes of 128 rows x 128 bytes.  Returns with *ok = 0
+// (and a zeroed map) when D's base or row pitch is not a multiple of 16 bytes; the kernel then
+// stores directly.
+static int make_out_map(CUtensorMap* map, int* ok, void* ptr, long long cols, long long rows, long long ld, int out_f32) {
+  std::memset(map, 0, sizeof(*map));
+  *ok = 0;
+  const int es = out_f32 ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0 || (ld * es) % 16 != 0) return HAPX_OK;
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(HAPX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * es};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / es), 128};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, out_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(HAPX_ERR_CUDA, "cuTensorMapEncodeTiled(output) failed with code " + std::to_string((int)r));
+  *ok = 1;
+  return HAPX_OK;
 }
 
 // 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row pitch `ld` elements.
@@ -678,7 +748,8 @@ static int device_state(DeviceState** out) {
 template <int BN, bool A_MN, bool B_MN>
 static int launch(const void* A, long long lda, const void* B, long long ldb, Params& p, cudaStream_t stream, int sm_count) {
   using C = Cfg<BN, A_MN, B_MN>;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmD;
+  if (int e = make_out_map(&tmD, &p.tma_store, p.D, p.N, p.M, p.ldd, p.out_f32)) return e;
   // K-major operand [rows = M or N][Kc contiguous]: inner = Kc, box {64, rows per tile}
   // MN-major operand [rows = Kc][M or N contiguous]: inner = M or N, box {64, 64}
   if (int e = A_MN ? make_map(&tmA, A, p.M, p.Kc, lda, 64, 64) : make_map(&tmA, A, p.Kc, p.M, lda, BK, BM)) return e;
@@ -693,7 +764,7 @@ static int launch(const void* A, long long lda, const void* B, long long ldb, Pa
     attr_set = true;
   }
   const int grid = std::max(1, std::min(p.m_tiles * p.n_tiles, sm_count));
-  kernel<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  kernel<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmA, tmB, tmD, p);
   HAPX_CUDA(cudaGetLastError());
   count_launch();
   return HAPX_OK;
@@ -703,7 +774,8 @@ static int launch(const void* A, long long lda, const void* B, long long ldb, Pa
 template <bool A_MN, bool B_MN>
 static int launch2(const void* A, long long lda, const void* B, long long ldb, Params& p, cudaStream_t stream, int sm_count) {
   using C = Cfg2<A_MN, B_MN>;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmD;
+  if (int e = make_out_map(&tmD, &p.tma_store, p.D, p.N, p.M, p.ldd, p.out_f32)) return e;
   if (int e = A_MN ? make_map(&tmA, A, p.M, p.Kc, lda, 64, 64) : make_map(&tmA, A, p.Kc, p.M, lda, BK, BM)) return e;
   if (int e = B_MN ? make_map(&tmB, B, p.N, p.Kc, ldb, 64, 64) : make_map(&tmB, B, p.Kc, p.N, ldb, BK, C::BN / 2)) return e;
   p.m_tiles = (p.M + 2 * BM - 1) / (2 * BM);
@@ -730,7 +802,7 @@ static int launch2(const void* A, long long lda, const void* B, long long ldb, P
   }
   const int pairs = std::max(1, std::min(p.m_tiles * p.n_tiles, max_clusters));
   cfg.gridDim = dim3(2 * pairs);
-  HAPX_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, p));
+  HAPX_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmD, p));
   count_launch();
   return HAPX_OK;
 }

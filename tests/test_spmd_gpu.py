@@ -65,10 +65,14 @@ def test_training_step_matches_cpu_replay(plan, dtype, tol):
                 # Adam normalises each element's update to about +-lr whatever the gradient's size, so
                 # entries whose gradient is near zero may move differently: allow 5 % of the distance
                 # two steps can travel (lr = 5e-4) in fp32, one bf16 ulp of the parameter scale in bf16
+                diff = (pg.detach().float().cpu() - pw.detach().float())
                 if dtype == torch.float32:
-                    assert float((pg.detach().cpu() - pw.detach()).abs().max()) <= 0.05 * 2 * 5e-4, (plan, r, name)
+                    assert float(diff.abs().max()) <= 0.05 * 2 * 5e-4, (plan, r, name)
                 else:
-                    rel_close(pg, pw, 2e-2, f"{plan} rank {r} param {name}")
+                    # in bf16 a near-zero gradient can even change sign, so single entries may differ by the
+                    # full distance of two steps (2 * lr each way); the tensor as a whole must still agree
+                    assert float(diff.abs().max()) <= 2 * 2 * 5e-4 + 2.0 ** -7 * float(pw.abs().max()), (plan, r, name)
+                    assert float(diff.norm()) <= 2e-2 * float(pw.float().norm()), (plan, r, name)
         comm.check()
         hap_b200.linear_ops.gemm_status()
     finally:
