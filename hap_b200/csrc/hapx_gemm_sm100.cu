@@ -49,6 +49,9 @@ struct Params {
   int m_tiles, n_tiles, k_blocks;
   unsigned* error;        // device word: 0 or a code left by a wait that ran out
   int tma_store;          // D's pitch and base allow bulk tensor stores
+  int splits;             // > 1: the contraction is cut into `splits` ranges of kb_per_split slices, each
+  int kb_per_split;       //      writing an fp32 partial tile to rows [split * m_pad, ...) of the workspace
+  int m_pad;
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -176,7 +179,8 @@ __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bul
 __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
-constexpr unsigned kStoreTileBytes = 128 * 128;   // 128 rows x 128 bytes (64 bf16 or 32 fp32 columns)
+constexpr unsigned kStoreTileBytes = 128 * 128;   // staging: 128 rows x 128 bytes (64 bf16 or 32 fp32 columns), two of them
+constexpr unsigned kWarpTileBytes = 32 * 128;     // the 32 rows one epilogue warp owns
 
 __device__ __forceinline__ float apply_epilogue(float v, int epi) {
   switch (epi) {
@@ -188,9 +192,11 @@ __device__ __forceinline__ float apply_epilogue(float v, int epi) {
 }
 
 // Drain one 128 x BN accumulator tile: this thread owns row (q*32 + lane) of it.
-// With `use_tma` the rows go through a 128-byte-swizzled staging tile in shared memory and leave
-// as bulk tensor stores (fully coalesced, clipped at the matrix edge by the tensor map); otherwise
-// each thread stores its own row segments directly (any row pitch, any alignment).
+// With `use_tma` every warp works on its own: it converts 128 bytes per row into a private,
+// 128-byte-swizzled 32-row staging tile (two of them, used alternately) and its lane 0 sends the
+// tile off as one bulk tensor store (coalesced, clipped at the matrix edge by the tensor map).
+// No barrier between warps is involved.  Otherwise each thread stores its own row segments
+// directly (any row pitch, any alignment).
 template <int BN>
 __device__ __forceinline__ void drain_tile(const Params& p, const CUtensorMap* tmD, bool use_tma, unsigned char* stage_gen,
                                            unsigned stage_u32, const float* bias_tile, unsigned t_row, int m0, int n0, int q,
@@ -200,6 +206,9 @@ __device__ __forceinline__ void drain_tile(const Params& p, const CUtensorMap* t
   if (use_tma) {
     constexpr int CH = 32;   // accumulator columns per tcgen05.ld
     const int cols_per_store = p.out_f32 ? 32 : 64;
+    unsigned char* warp_gen = stage_gen + q * (2 * kWarpTileBytes);
+    const unsigned warp_u32 = stage_u32 + q * (2 * kWarpTileBytes);
+    const int sw = lane & 7;
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += cols_per_store) {
       if (n0 + c0 >= p.N) break;                       // same decision in every thread
@@ -207,10 +216,9 @@ __device__ __forceinline__ void drain_tile(const Params& p, const CUtensorMap* t
       tmem_ld_32x32(t_row + (unsigned)c0, r0);
       if (!p.out_f32) tmem_ld_32x32(t_row + (unsigned)(c0 + CH), r1);
       tmem_ld_wait();
-      if (et == 0) bulk_wait_read_1();                 // the store issued two chunks ago has left this buffer
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      unsigned char* tile = stage_gen + buf * kStoreTileBytes + row_in_tile * 128;
-      const int sw = row_in_tile & 7;
+      if (lane == 0) bulk_wait_read_1();               // the store this warp issued two chunks ago has left the buffer
+      __syncwarp();
+      unsigned char* tile = warp_gen + buf * kWarpTileBytes + lane * 128;
       if (p.out_f32) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -237,10 +245,10 @@ __device__ __forceinline__ void drain_tile(const Params& p, const CUtensorMap* t
           *reinterpret_cast<uint4*>(tile + ((j ^ sw) << 4)) = pk;
         }
       }
-      fence_proxy_async();                             // make the tile visible to the bulk-copy engine
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (et == 0) {
-        tma_store_2d(tmD, stage_u32 + buf * kStoreTileBytes, n0 + c0, m0);
+      fence_proxy_async();                             // make the rows visible to the bulk-copy engine
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(tmD, warp_u32 + buf * kWarpTileBytes, n0 + c0, m0 + q * 32);
         bulk_commit_group();
       }
       buf ^= 1;
@@ -435,7 +443,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_arrive(tempty_bar(acc));     // this thread has drained its part of the accumulator
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
-    if (et == 0) bulk_wait_all();   // bulk stores still read the staging tiles
+    if (lane == 0) bulk_wait_all();   // this warp's bulk stores still read its staging tiles
     if (!ok) { *abort_flag = 1; atomicCAS(p.error, 0u, 3u); }
   }
 
@@ -543,7 +551,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned cta = cluster_ctarank();            // 0 = leader
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-  const int total_tiles = p.m_tiles * p.n_tiles;     // m_tiles counts 256-row tiles here
+  const int total_tiles = p.m_tiles * p.n_tiles * p.splits;   // work units: (256-row tile, column tile, contraction range)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -568,10 +576,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int stage = 0;
       unsigned phase = 0;
       bool ok = true;
-      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+      for (int unit = pair; unit < total_tiles && ok; unit += n_pairs) {
+        const int tile = unit / p.splits, sp = unit - tile * p.splits;
         const int m0 = (tile % p.m_tiles) * (2 * BM) + (int)cta * BM;
         const int n0 = (tile / p.m_tiles) * BN + (int)cta * (BN / 2);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        const int kb_begin = sp * p.kb_per_split, kb_end = min(kb_begin + p.kb_per_split, p.k_blocks);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u)) { ok = false; break; }
           const unsigned sa = base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
           const unsigned leader_full = map_to_cta(full_bar(stage), 0);
@@ -600,11 +610,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int stage = 0, acc = 0;
       unsigned phase = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+      for (int unit = pair; unit < total_tiles && ok; unit += n_pairs) {
+        const int sp = unit % p.splits;
+        const int kb_begin = sp * p.kb_per_split, kb_end = min(kb_begin + p.kb_per_split, p.k_blocks);
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u)) { ok = false; break; }
         tc_fence_after();
         const unsigned d_tmem = tmem_base + (unsigned)(acc * BN);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(full_bar(stage), phase)) { ok = false; break; }
           tc_fence_after();
           const unsigned sa = base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
@@ -612,7 +624,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const unsigned long long da = A_MN ? make_desc(sa + k * 2048u, 8192u, 1024u) : make_desc(sa + k * 32u, 16u, 1024u);
             const unsigned long long db = B_MN ? make_desc(sb + k * 2048u, 8192u, 1024u) : make_desc(sb + k * 32u, 16u, 1024u);
-            umma2_bf16(d_tmem, da, db, C::IDESC, (kb | k) != 0 ? 1u : 0u);
+            umma2_bf16(d_tmem, da, db, C::IDESC, (kb != kb_begin || k != 0) ? 1u : 0u);
           }
           umma2_commit_both(empty_bar(stage));
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
@@ -631,8 +643,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     unsigned acc_phase = 0;
     bool ok = true;
     int store_buf = 0;
-    for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
-      const int m0 = (tile % p.m_tiles) * (2 * BM) + (int)cta * BM, n0 = (tile / p.m_tiles) * BN;
+    for (int unit = pair; unit < total_tiles && ok; unit += n_pairs) {
+      const int tile = unit / p.splits, sp = unit - tile * p.splits;
+      // with split-K the partial tile goes to the workspace, whose rows are [split][m_pad]
+      const int m0 = (tile % p.m_tiles) * (2 * BM) + (int)cta * BM + sp * p.m_pad, n0 = (tile / p.m_tiles) * BN;
       asm volatile("bar.sync 1, 128;" ::: "memory");
       for (int j = et; j < BN; j += kEpilogueThreads) {
         float b = 0.f;
@@ -649,7 +663,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));   // tell the leader this thread has drained its rows
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
-    if (et == 0) bulk_wait_all();   // bulk stores still read the staging tiles
+    if (lane == 0) bulk_wait_all();   // this warp's bulk stores still read its staging tiles
     if (!ok) atomicCAS(p.error, 0u, 3u);
   }
 
@@ -679,7 +693,7 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// Tensor map of the output for bulk stores: boxes of 128 rows x 128 bytes.  Returns with *ok = 0
+// Tensor map of the output for bulk stores: boxes of 32 rows x 128 bytes.  Returns with *ok = 0
 // (and a zeroed map) when D's base or row pitch is not a multiple of 16 bytes; the kernel then
 // stores directly.
 static int make_out_map(CUtensorMap* map, int* ok, void* ptr, long long cols, long long rows, long long ld, int out_f32) {
@@ -691,7 +705,7 @@ static int make_out_map(CUtensorMap* map, int* ok, void* ptr, long long cols, lo
   if (!fn) return fail(HAPX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * es};
-  cuuint32_t box[2] = {(cuuint32_t)(128 / es), 128};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / es), 32};     // one epilogue warp's rows
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, out_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
@@ -755,6 +769,7 @@ static int launch(const void* A, long long lda, const void* B, long long ldb, Pa
   if (int e = A_MN ? make_map(&tmA, A, p.M, p.Kc, lda, 64, 64) : make_map(&tmA, A, p.Kc, p.M, lda, BK, BM)) return e;
   if (int e = B_MN ? make_map(&tmB, B, p.N, p.Kc, ldb, 64, 64) : make_map(&tmB, B, p.Kc, p.N, ldb, BK, BN)) return e;
   p.m_tiles = (p.M + BM - 1) / BM;
+  p.splits = 1; p.kb_per_split = 0; p.m_pad = 0;
   p.n_tiles = (p.N + BN - 1) / BN;
   p.k_blocks = (p.Kc + BK - 1) / BK;
   auto kernel = gemm_bf16_kernel<BN, A_MN, B_MN>;
@@ -771,16 +786,50 @@ static int launch(const void* A, long long lda, const void* B, long long ldb, Pa
 }
 
 
+// Sum the fp32 partial tiles of a split-K GEMM in split order (deterministic), then bias,
+// activation and cast.  ws rows: [split][m_pad], N columns.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ ws, int splits, int M, int N, long long m_pad,
+                                                            const void* bias, int epilogue, void* out, int out_f32, long long ldd) {
+  // N is a multiple of 4 (checked by the launcher): one thread sums 4 adjacent columns of one row
+  const int n4 = N >> 2;
+  const long long total = (long long)M * n4;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(e / n4), c = (int)(e - (long long)r * n4) << 2;
+    float4 acc = *reinterpret_cast<const float4*>(ws + (long long)r * N + c);
+    for (int s = 1; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(ws + ((long long)s * m_pad + r) * N + c);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    float o[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (bias) o[j] += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[c + j]);
+      o[j] = apply_epilogue(o[j], epilogue);
+      if (out_f32) reinterpret_cast<float*>(out)[(long long)r * ldd + c + j] = o[j];
+      else reinterpret_cast<__nv_bfloat16*>(out)[(long long)r * ldd + c + j] = __float2bfloat16_rn(o[j]);
+    }
+  }
+}
+
+struct Workspace { float* ptr = nullptr; size_t bytes = 0; };
+static Workspace g_ws[64];
+
+// Grows the per-device split-K workspace (the only allocation on this path; it happens when a
+// larger problem is seen for the first time, never in steady state).
+static int workspace(int device, size_t bytes, float** out) {
+  Workspace& w = g_ws[device];
+  if (w.bytes < bytes) {
+    if (w.ptr) { HAPX_CUDA(cudaDeviceSynchronize()); HAPX_CUDA(cudaFree(w.ptr)); w.ptr = nullptr; w.bytes = 0; }
+    HAPX_CUDA(cudaMalloc(&w.ptr, bytes));
+    w.bytes = bytes;
+  }
+  *out = w.ptr;
+  return HAPX_OK;
+}
+
 template <bool A_MN, bool B_MN>
 static int launch2(const void* A, long long lda, const void* B, long long ldb, Params& p, cudaStream_t stream, int sm_count) {
   using C = Cfg2<A_MN, B_MN>;
-  CUtensorMap tmA, tmB, tmD;
-  if (int e = make_out_map(&tmD, &p.tma_store, p.D, p.N, p.M, p.ldd, p.out_f32)) return e;
-  if (int e = A_MN ? make_map(&tmA, A, p.M, p.Kc, lda, 64, 64) : make_map(&tmA, A, p.Kc, p.M, lda, BK, BM)) return e;
-  if (int e = B_MN ? make_map(&tmB, B, p.N, p.Kc, ldb, 64, 64) : make_map(&tmB, B, p.Kc, p.N, ldb, BK, C::BN / 2)) return e;
-  p.m_tiles = (p.M + 2 * BM - 1) / (2 * BM);
-  p.n_tiles = (p.N + C::BN - 1) / C::BN;
-  p.k_blocks = (p.Kc + BK - 1) / BK;
   auto kernel = gemm2_bf16_kernel<A_MN, B_MN>;
   static int max_clusters = 0;
   cudaLaunchConfig_t cfg = {};
@@ -800,10 +849,52 @@ static int launch2(const void* A, long long lda, const void* B, long long ldb, P
     if (n < 1) return fail(HAPX_ERR_CUDA, "gemm: no SM pair can host the two-CTA kernel");
     max_clusters = n;
   }
-  const int pairs = std::max(1, std::min(p.m_tiles * p.n_tiles, max_clusters));
+  p.m_tiles = (p.M + 2 * BM - 1) / (2 * BM);
+  p.n_tiles = (p.N + C::BN - 1) / C::BN;
+  p.k_blocks = (p.Kc + BK - 1) / BK;
+  p.splits = 1; p.kb_per_split = p.k_blocks; p.m_pad = 0;
+  // Few output tiles but a long contraction (weight gradients): cut the contraction so that all SM
+  // pairs have work.  Take the smallest split count that fills >= 85 % of the waves it needs.
+  const int tiles = p.m_tiles * p.n_tiles;
+  if (tiles * 2 <= max_clusters && p.k_blocks >= 16) {
+    int best = 1;
+    double best_eff = (double)tiles / (((tiles + max_clusters - 1) / max_clusters) * (double)max_clusters);
+    for (int sp = 2; sp <= 32 && sp * 4 <= p.k_blocks; ++sp) {
+      const int per = (p.k_blocks + sp - 1) / sp;
+      if ((sp - 1) * per >= p.k_blocks) continue;            // an empty last range
+      const int units = tiles * sp;
+      const double eff = (double)units / (((units + max_clusters - 1) / max_clusters) * (double)max_clusters);
+      if (eff > best_eff + 1e-9) { best = sp; best_eff = eff; }
+      if (eff >= 0.85) break;
+    }
+    if (best > 1) { p.splits = best; p.kb_per_split = (p.k_blocks + best - 1) / best; p.m_pad = p.m_tiles * 2 * BM; }
+  }
+  Params user = p;   // what the caller asked for (output, bias, activation)
+  float* ws = nullptr;
+  if (p.splits > 1) {
+    int device = 0;
+    HAPX_CUDA(cudaGetDevice(&device));
+    if (int e = workspace(device, (size_t)p.splits * p.m_pad * p.N * sizeof(float), &ws)) return e;
+    p.D = ws; p.ldd = p.N; p.out_f32 = 1; p.bias = nullptr; p.epilogue = EPI_NONE;
+  }
+  CUtensorMap tmA, tmB, tmD;
+  const long long out_rows = p.splits > 1 ? (long long)p.splits * p.m_pad : p.M;
+  if (int e = make_out_map(&tmD, &p.tma_store, p.D, p.N, out_rows, p.ldd, p.out_f32)) return e;
+  if (p.splits > 1 && !p.tma_store) return fail(HAPX_ERR_EXTENT, "gemm: split-K needs an output width that is a multiple of 4");
+  if (int e = A_MN ? make_map(&tmA, A, p.M, p.Kc, lda, 64, 64) : make_map(&tmA, A, p.Kc, p.M, lda, BK, BM)) return e;
+  if (int e = B_MN ? make_map(&tmB, B, p.N, p.Kc, ldb, 64, 64) : make_map(&tmB, B, p.Kc, p.N, ldb, BK, C::BN / 2)) return e;
+  const int pairs = std::max(1, std::min(tiles * p.splits, max_clusters));
   cfg.gridDim = dim3(2 * pairs);
   HAPX_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmD, p));
   count_launch();
+  if (p.splits > 1) {
+    const long long total = (long long)user.M * (user.N / 4);
+    const int grid = (int)std::min<long long>((total + 255) / 256, (long long)sm_count * 8);
+    splitk_reduce_kernel<<<grid, 256, 0, stream>>>(ws, p.splits, user.M, user.N, p.m_pad, user.bias, user.epilogue, user.D,
+                                                   user.out_f32, user.ldd);
+    HAPX_CUDA(cudaGetLastError());
+    count_launch();
+  }
   return HAPX_OK;
 }
 
