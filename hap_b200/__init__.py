@@ -11,7 +11,7 @@ from . import collectives
 from .local import LocalCollectives
 from . import linear as linear_ops
 from .linear import linear
-from . import plan, spmd
+from . import plan, spmd, attention
 
 __all__ = ["Comm", "init_process_comm", "local_comm", "collectives", "LocalCollectives",
-           "sharding_round", "sharding_round_", "linear", "linear_ops", "plan", "spmd"]
+           "sharding_round", "sharding_round_", "linear", "linear_ops", "plan", "spmd", "attention"]

@@ -49,6 +49,8 @@ SIGNATURES = {
     "hapx_linear_dgrad": (_int, [_vp, _vp, _vp, _int, _int, _i64, _i64, _i64, _vp]),
     "hapx_linear_wgrad": (_int, [_vp, _vp, _vp, _vp, _int, _int, _i64, _i64, _i64, _vp]),
     "hapx_gemm_status": (_int, []),
+    "hapx_attention_forward": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp]),
+    "hapx_attention_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "hapx_local_all_reduce_noalloc": (_int, [_int, _pp, _pp, _int, _int, _dbl, _i64, _vp]),
     "hapx_debug_host_walk": (_int, [_int, _int, _int, _int, _i64, _i64, _i64, _int, _pi64, _pi64, _pp,
                                      C.POINTER(_sz), _vp, _sz, _vp]),

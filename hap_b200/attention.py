@@ -1,0 +1,101 @@
+"""``F.multi_head_attention_forward`` on a batch shard, through the C ABI.
+
+The planner emits self-attention as one call of
+``torch.nn.functional.multi_head_attention_forward(query=x, key=x, value=x, in_proj_weight=...,
+in_proj_bias=..., out_proj_weight=..., out_proj_bias=..., attn_mask=..., embed_dim_to_check=E,
+num_heads=H, bias_k=None, bias_v=None, add_zero_attn=False, dropout_p=p)`` on (L, N, E) tensors
+(``hap.rs:1297-1329``); only N is ever sharded (``hap.rs:2903-2926``).  :func:`multi_head_attention_forward`
+takes the same keyword arguments and returns ``(output, None)``; the two projections run on the
+package's linear kernels and the attention core on the batched tensor-core GEMMs plus softmax kernels.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from . import _native as N
+from .comm import _stream
+from .linear import linear
+
+
+def _classify_mask(mask: Optional[torch.Tensor], L: int):
+    """(causal flag, additive fp32 mask or None).  The LM's mask (-inf strictly above the diagonal,
+    0 elsewhere, ``models.py:72``) is recognised and handled without reading a mask tensor."""
+    if mask is None:
+        return 0, None
+    if mask.dtype == torch.bool:
+        add = torch.zeros(mask.shape, dtype=torch.float32, device=mask.device).masked_fill_(mask, float("-inf"))
+    else:
+        add = mask.float()
+    if add.shape != (L, L):
+        raise ValueError(f"attention: attn_mask must be ({L}, {L}), got {tuple(add.shape)}")
+    causal = torch.full((L, L), float("-inf"), device=add.device).triu_(1)
+    if torch.equal(add, causal):
+        return 1, None
+    return 0, add.contiguous()
+
+
+class _Attention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, num_heads, causal, mask):
+        L, n, e3 = qkv.shape
+        E = e3 // 3
+        D = E // num_heads
+        Lp = (L + 7) // 8 * 8
+        qkv = qkv.contiguous()
+        out = torch.empty((L, n, E), dtype=torch.bfloat16, device=qkv.device)
+        probs = torch.empty((n * num_heads, L, Lp), dtype=torch.bfloat16, device=qkv.device)
+        scores = torch.empty((n * num_heads, L, Lp), dtype=torch.float32, device=qkv.device)
+        with torch.cuda.device(qkv.device):
+            N.check(N.lib.hapx_attention_forward(out.data_ptr(), probs.data_ptr(), scores.data_ptr(), qkv.data_ptr(), L, n,
+                                                 num_heads, D, int(causal), mask.data_ptr() if mask is not None else None,
+                                                 _stream(qkv.device)))
+        ctx.save_for_backward(qkv, probs)
+        ctx.meta = (L, n, num_heads, D)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, probs = ctx.saved_tensors
+        L, n, H, D = ctx.meta
+        dout = dout.contiguous()
+        dqkv = torch.empty_like(qkv)
+        dscores = torch.empty(probs.shape, dtype=torch.float32, device=qkv.device)
+        ds = torch.empty_like(probs)
+        with torch.cuda.device(qkv.device):
+            N.check(N.lib.hapx_attention_backward(dqkv.data_ptr(), dscores.data_ptr(), ds.data_ptr(), dout.data_ptr(),
+                                                  probs.data_ptr(), qkv.data_ptr(), L, n, H, D, _stream(qkv.device)))
+        return dqkv, None, None, None
+
+
+def attention(qkv: torch.Tensor, num_heads: int, attn_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """softmax(Q K^T / sqrt(d) + mask) V for packed ``qkv`` of shape (L, N, 3E), bfloat16, on CUDA."""
+    if not qkv.is_cuda:
+        raise RuntimeError(f"attention: hap_b200 has no CPU path; tensor is on {qkv.device}")
+    if qkv.dtype != torch.bfloat16:
+        raise TypeError(f"attention: bfloat16 only, got {qkv.dtype}")
+    if qkv.dim() != 3 or qkv.shape[2] % (3 * num_heads):
+        raise ValueError("attention: qkv must be (L, N, 3 * num_heads * head_dim)")
+    causal, mask = _classify_mask(attn_mask, qkv.shape[0])
+    return _Attention.apply(qkv, num_heads, causal, mask)
+
+
+def multi_head_attention_forward(query, key, value, embed_dim_to_check, num_heads, in_proj_weight, in_proj_bias,
+                                 bias_k=None, bias_v=None, add_zero_attn=False, dropout_p=0.0, out_proj_weight=None,
+                                 out_proj_bias=None, training=True, key_padding_mask=None, need_weights=True, attn_mask=None,
+                                 use_separate_proj_weight=False, **unsupported):
+    """Same call surface as ``torch.nn.functional.multi_head_attention_forward`` for the case the planner
+    emits (self-attention, packed projection).  Returns ``(attn_output, None)``."""
+    if not (query is key and key is value):
+        raise NotImplementedError("attention: only self-attention (query is key is value) is emitted by the planner")
+    if bias_k is not None or bias_v is not None or add_zero_attn or key_padding_mask is not None or use_separate_proj_weight:
+        raise NotImplementedError("attention: bias_k / bias_v / add_zero_attn / key_padding_mask / separate weights are not emitted by the planner")
+    if dropout_p and training:
+        raise NotImplementedError("attention: dropout on the attention probabilities is not built yet (use dropout_p=0)")
+    if query.shape[-1] != embed_dim_to_check:
+        raise ValueError("attention: embedding dimension mismatch")
+    qkv = linear(query, in_proj_weight, in_proj_bias)
+    out = attention(qkv, num_heads, attn_mask)
+    return linear(out, out_proj_weight, out_proj_bias), None

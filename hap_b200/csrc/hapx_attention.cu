@@ -1,0 +1,168 @@
+// Multi-head self-attention on a batch shard: softmax(Q K^T / sqrt(d) + mask) V, forward and backward.
+//
+// Stands in for the attention core of F.multi_head_attention_forward as the planner emits it
+// (hap.rs:1297-1329; only the batch dimension is ever sharded, hap.rs:2903-2926), working directly
+// on the packed in-projection output qkv[L, N, 3E] and producing [L, N, E], i.e. in the (L, N, E)
+// layout of the reference with no transposed copies: heads and batch entries are batch coordinates
+// of the tensor maps.  The contractions run on the batched tcgen05 GEMM (hapx_gemm_sm100.cu):
+//
+//   forward : S = Q K^T (fp32)  ->  P = softmax(scale * S + mask) (bf16, kept for backward)  ->  O = P V
+//   backward: dV = P^T dO;  dP = dO V^T (fp32);  dS = scale * P * (dP - rowsum(dP * P));  dQ = dS K;  dK = dS^T Q
+//
+// The softmax kernels keep one row per warp in registers (L <= 1024).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <string>
+
+#include "hapx_internal.h"
+
+namespace hapx {
+namespace attn {
+
+constexpr int kMaxPerLane = 32;  // L <= 1024
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// rows = batch * L; row r is query (r % L).  S, P: [rows][Lp].  mask: additive [L][L] fp32 or null.
+__global__ void __launch_bounds__(256) softmax_fwd_kernel(const float* __restrict__ S, __nv_bfloat16* __restrict__ P, int L, int Lp,
+                                                          long long rows, float scale, int causal, const float* __restrict__ mask) {
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31, q = (int)(row % L);
+  const float* s = S + row * Lp;
+  float v[kMaxPerLane];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    const int j = lane + 32 * i;
+    float x = -INFINITY;
+    if (j < L && !(causal && j > q)) {
+      x = s[j] * scale;
+      if (mask) x += mask[(long long)q * L + j];
+    }
+    v[i] = x;
+    mx = fmaxf(mx, x);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    v[i] = (v[i] == -INFINITY) ? 0.f : __expf(v[i] - mx);
+    sum += v[i];
+  }
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+  __nv_bfloat16* p = P + row * Lp;
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    const int j = lane + 32 * i;
+    if (j < Lp) p[j] = __float2bfloat16_rn(j < L ? v[i] * inv : 0.f);
+  }
+}
+
+__global__ void __launch_bounds__(256) softmax_bwd_kernel(const __nv_bfloat16* __restrict__ P, const float* __restrict__ dP,
+                                                          __nv_bfloat16* __restrict__ dS, int L, int Lp, long long rows, float scale) {
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const __nv_bfloat16* p = P + row * Lp;
+  const float* g = dP + row * Lp;
+  float pv[kMaxPerLane], gv[kMaxPerLane];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    const int j = lane + 32 * i;
+    pv[i] = (j < L) ? __bfloat162float(p[j]) : 0.f;
+    gv[i] = (j < L) ? g[j] : 0.f;
+    dot += pv[i] * gv[i];
+  }
+  dot = warp_sum(dot);
+  __nv_bfloat16* o = dS + row * Lp;
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    const int j = lane + 32 * i;
+    if (j < Lp) o[j] = __float2bfloat16_rn(j < L ? scale * pv[i] * (gv[i] - dot) : 0.f);
+  }
+}
+
+static int check(long long L, long long N, long long H, long long D) {
+  if (L < 1 || N < 1 || H < 1 || D < 1) return fail(HAPX_ERR_EXTENT, "attention: extents must be positive");
+  if (L > 32 * kMaxPerLane) return fail(HAPX_ERR_EXTENT, "attention: sequence length above 1024 is not supported");
+  if (D % 8 != 0) return fail(HAPX_ERR_EXTENT, "attention: head dimension must be a multiple of 8");
+  if (N * H > 0x7fffffff) return fail(HAPX_ERR_EXTENT, "attention: too many (batch, head) pairs");
+  return HAPX_OK;
+}
+
+}  // namespace attn
+}  // namespace hapx
+
+using namespace hapx;
+using hapx::gemm::Operand;
+
+extern "C" {
+
+int hapx_attention_forward(void* out, void* probs, void* scores_ws, const void* qkv, int64_t L, int64_t N, int64_t H, int64_t D,
+                           int causal, const float* mask, hapx_stream stream_) {
+  if (int e = attn::check(L, N, H, D)) return e;
+  if (!out || !probs || !scores_ws || !qkv) return fail(HAPX_ERR_ARGUMENT, "attention_forward: null pointer");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const long long E = H * D, Lp = (L + 7) / 8 * 8, row_qkv = N * 3 * E;
+  const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(qkv);
+  const Operand Q{base, false, row_qkv, D, 3 * E}, K{base + E, false, row_qkv, D, 3 * E};
+  const Operand Vmn{base + 2 * E, true, row_qkv, D, 3 * E};
+  const Operand S{scores_ws, false, Lp, L * Lp, H * L * Lp}, P{probs, false, Lp, L * Lp, H * L * Lp};
+  const Operand O{out, false, N * E, D, E};
+  // S[b] = Q[b] K[b]^T   (fp32)
+  if (int e = gemm::gemm_bf16(S, 1, Q, K, nullptr, 0, L, L, D, (int)H, (int)N, stream)) return e;
+  const long long rows = N * H * L;
+  attn::softmax_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(static_cast<const float*>(scores_ws),
+                                                                           static_cast<__nv_bfloat16*>(probs), (int)L, (int)Lp, rows,
+                                                                           1.0f / sqrtf((float)D), causal, mask);
+  HAPX_CUDA(cudaGetLastError());
+  count_launch();
+  // O[b] = P[b] V[b]      (contraction over keys; V is MN-major as stored)
+  return gemm::gemm_bf16(O, 0, P, Vmn, nullptr, 0, L, D, L, (int)H, (int)N, stream);
+}
+
+int hapx_attention_backward(void* dqkv, void* dscores_ws, void* ds_ws, const void* dout, const void* probs, const void* qkv,
+                            int64_t L, int64_t N, int64_t H, int64_t D, hapx_stream stream_) {
+  if (int e = attn::check(L, N, H, D)) return e;
+  if (!dqkv || !dscores_ws || !ds_ws || !dout || !probs || !qkv) return fail(HAPX_ERR_ARGUMENT, "attention_backward: null pointer");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const long long E = H * D, Lp = (L + 7) / 8 * 8, row_qkv = N * 3 * E;
+  const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(qkv);
+  __nv_bfloat16* gbase = static_cast<__nv_bfloat16*>(dqkv);
+  const Operand Qmn{base, true, row_qkv, D, 3 * E}, Kmn{base + E, true, row_qkv, D, 3 * E};
+  const Operand V{base + 2 * E, false, row_qkv, D, 3 * E};
+  const Operand dO{dout, false, N * E, D, E}, dOmn{dout, true, N * E, D, E};
+  const Operand P_mn{probs, true, Lp, L * Lp, H * L * Lp};
+  const Operand dPf{dscores_ws, false, Lp, L * Lp, H * L * Lp};
+  const Operand dS{ds_ws, false, Lp, L * Lp, H * L * Lp}, dSmn{ds_ws, true, Lp, L * Lp, H * L * Lp};
+  const Operand dQ{gbase, false, row_qkv, D, 3 * E}, dK{gbase + E, false, row_qkv, D, 3 * E}, dV{gbase + 2 * E, false, row_qkv, D, 3 * E};
+  // dV[k, d] = sum_q P[q, k] dO[q, d]
+  if (int e = gemm::gemm_bf16(dV, 0, P_mn, dOmn, nullptr, 0, L, D, L, (int)H, (int)N, stream)) return e;
+  // dP[q, k] = sum_d dO[q, d] V[k, d]   (fp32)
+  if (int e = gemm::gemm_bf16(dPf, 1, dO, V, nullptr, 0, L, L, D, (int)H, (int)N, stream)) return e;
+  const long long rows = N * H * L;
+  attn::softmax_bwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(probs),
+                                                                           static_cast<const float*>(dscores_ws),
+                                                                           static_cast<__nv_bfloat16*>(ds_ws), (int)L, (int)Lp, rows,
+                                                                           1.0f / sqrtf((float)D));
+  HAPX_CUDA(cudaGetLastError());
+  count_launch();
+  // dQ[q, d] = sum_k dS[q, k] K[k, d];   dK[k, d] = sum_q dS[q, k] Q[q, d]
+  if (int e = gemm::gemm_bf16(dQ, 0, dS, Kmn, nullptr, 0, L, D, L, (int)H, (int)N, stream)) return e;
+  return gemm::gemm_bf16(dK, 0, dSmn, Qmn, nullptr, 0, L, D, L, (int)H, (int)N, stream);
+}
+
+}  // extern "C"

@@ -52,6 +52,11 @@ struct Params {
   int splits;             // > 1: the contraction is cut into `splits` ranges of kb_per_split slices, each
   int kb_per_split;       //      writing an fp32 partial tile to rows [split * m_pad, ...) of the workspace
   int m_pad;
+  // batched operation: `batch` independent GEMMs; batch index b = b_out * batch_in + b_in and every
+  // tensor map carries (b_in, b_out) as its 3rd and 4th coordinate.  Element strides of D for the
+  // direct-store path:
+  int batch, batch_in;
+  long long d_stride_in, d_stride_out;
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -95,10 +100,11 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+// All tensor maps are 4-D: (contiguous index, row, batch_in, batch_out).
+__device__ __forceinline__ void tma_load_4d(unsigned dst, const CUtensorMap* map, int x, int y, int bi, int bo, unsigned bar) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-      "l"(map), "r"(x), "r"(y), "r"(bar)
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bi), "r"(bo), "r"(bar)
       : "memory");
 }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
@@ -171,8 +177,9 @@ __device__ __forceinline__ unsigned long long make_desc(unsigned smem_addr, unsi
 
 
 // ---- epilogue -------------------------------------------------------------------------------------
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, unsigned src_smem, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src_smem), "r"(x), "r"(y)
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, unsigned src_smem, int x, int y, int bi, int bo) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map), "r"(src_smem), "r"(x),
+               "r"(y), "r"(bi), "r"(bo)
                : "memory");
 }
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
@@ -199,8 +206,8 @@ __device__ __forceinline__ float apply_epilogue(float v, int epi) {
 // directly (any row pitch, any alignment).
 template <int BN>
 __device__ __forceinline__ void drain_tile(const Params& p, const CUtensorMap* tmD, bool use_tma, unsigned char* stage_gen,
-                                           unsigned stage_u32, const float* bias_tile, unsigned t_row, int m0, int n0, int q,
-                                           int lane, int et, int& buf) {
+                                           unsigned stage_u32, const float* bias_tile, unsigned t_row, int m0, int n0, int bi, int bo,
+                                           int q, int lane, int et, int& buf) {
   const int row_in_tile = q * 32 + lane;
   const int row = m0 + row_in_tile;
   if (use_tma) {
@@ -248,7 +255,7 @@ __device__ __forceinline__ void drain_tile(const Params& p, const CUtensorMap* t
       fence_proxy_async();                             // make the rows visible to the bulk-copy engine
       __syncwarp();
       if (lane == 0) {
-        tma_store_2d(tmD, warp_u32 + buf * kWarpTileBytes, n0 + c0, m0 + q * 32);
+        tma_store_4d(tmD, warp_u32 + buf * kWarpTileBytes, n0 + c0, m0 + q * 32, bi, bo);
         bulk_commit_group();
       }
       buf ^= 1;
@@ -268,7 +275,7 @@ __device__ __forceinline__ void drain_tile(const Params& p, const CUtensorMap* t
       for (int j = 0; j < 32; ++j) v[j] = apply_epilogue(__uint_as_float(r[j]) + bias_tile[c0 + j], p.epilogue);
       const int ncols = min(32, p.N - (n0 + c0));
       if (p.out_f32) {
-        float* out = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + n0 + c0;
+        float* out = reinterpret_cast<float*>(p.D) + bo * p.d_stride_out + bi * p.d_stride_in + (long long)row * p.ldd + n0 + c0;
         if (vec_ok && ncols == 32) {
 #pragma unroll
           for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
@@ -277,7 +284,7 @@ __device__ __forceinline__ void drain_tile(const Params& p, const CUtensorMap* t
           for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = v[j];
         }
       } else {
-        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd + n0 + c0;
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.D) + bo * p.d_stride_out + bi * p.d_stride_in + (long long)row * p.ldd + n0 + c0;
         if (vec_ok && ncols == 32) {
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
@@ -334,7 +341,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   volatile unsigned* abort_flag = tmem_slot_gen + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total_tiles = p.m_tiles * p.n_tiles;
+  const int tiles_per_batch = p.m_tiles * p.n_tiles;
+  const int total_tiles = tiles_per_batch * p.batch;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -359,7 +367,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       unsigned phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < total_tiles && ok; unit += gridDim.x) {
+        const int b = unit / tiles_per_batch, tile = unit - b * tiles_per_batch;
+        const int bo = b / p.batch_in, bi = b - bo * p.batch_in;
         const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * BN;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u)) { ok = false; break; }
@@ -367,18 +377,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mbar_expect_tx(full_bar(stage), C::STAGE_BYTES);
           const int k0 = kb * BK;
           if (!A_MN) {
-            tma_load_2d(sa, &tmA, k0, m0, full_bar(stage));                 // box {64 k, 128 m}
+            tma_load_4d(sa, &tmA, k0, m0, bi, bo, full_bar(stage));         // box {64 k, 128 m}
           } else {
 #pragma unroll
             for (int i = 0; i < BM / 64; ++i)                                // boxes {64 m, 64 k}
-              tma_load_2d(sa + i * 8192u, &tmA, m0 + 64 * i, k0, full_bar(stage));
+              tma_load_4d(sa + i * 8192u, &tmA, m0 + 64 * i, k0, bi, bo, full_bar(stage));
           }
           if (!B_MN) {
-            tma_load_2d(sb, &tmB, k0, n0, full_bar(stage));                 // box {64 k, BN n}
+            tma_load_4d(sb, &tmB, k0, n0, bi, bo, full_bar(stage));         // box {64 k, BN n}
           } else {
 #pragma unroll
             for (int i = 0; i < BN / 64; ++i)                                // boxes {64 n, 64 k}
-              tma_load_2d(sb + i * 8192u, &tmB, n0 + 64 * i, k0, full_bar(stage));
+              tma_load_4d(sb + i * 8192u, &tmB, n0 + 64 * i, k0, bi, bo, full_bar(stage));
           }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -424,7 +434,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     unsigned acc_phase = 0;
     bool ok = true;
     int store_buf = 0;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+    for (int unit = blockIdx.x; unit < total_tiles && ok; unit += gridDim.x) {
+      const int b = unit / tiles_per_batch, tile = unit - b * tiles_per_batch;
+      const int bo = b / p.batch_in, bi = b - bo * p.batch_in;
       const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * BN;
       // bias tile -> shared (fp32)
       asm volatile("bar.sync 1, 128;" ::: "memory");   // previous tile's readers are done with bias_tile
@@ -438,7 +450,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       const unsigned t_row = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(acc * BN);
-      drain_tile<BN>(p, &tmD, p.tma_store != 0, store_gen, store_u32, bias_tile, t_row, m0, n0, q, lane, et, store_buf);
+      drain_tile<BN>(p, &tmD, p.tma_store != 0, store_gen, store_u32, bias_tile, t_row, m0, n0, bi, bo, q, lane, et, store_buf);
       tc_fence_before();
       mbar_arrive(tempty_bar(acc));     // this thread has drained its part of the accumulator
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
@@ -482,10 +494,10 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 // TMA load whose completion bytes are credited to an mbarrier of the pair's leader CTA.
-__device__ __forceinline__ void tma_load_2d_pair(unsigned dst, const CUtensorMap* map, int x, int y, unsigned leader_bar) {
+__device__ __forceinline__ void tma_load_4d_pair(unsigned dst, const CUtensorMap* map, int x, int y, int bi, int bo, unsigned leader_bar) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-      "l"(map), "r"(x), "r"(y), "r"(leader_bar)
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bi), "r"(bo), "r"(leader_bar)
       : "memory");
 }
 __device__ __forceinline__ void tmem_alloc2(unsigned dst_smem, unsigned cols) {
@@ -551,7 +563,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned cta = cluster_ctarank();            // 0 = leader
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-  const int total_tiles = p.m_tiles * p.n_tiles * p.splits;   // work units: (256-row tile, column tile, contraction range)
+  const int tiles_per_batch = p.m_tiles * p.n_tiles;
+  const int total_tiles = tiles_per_batch * p.splits * p.batch;   // work units: (batch, 256-row tile, column tile, contraction range); splits > 1 only without batching
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -577,7 +590,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       unsigned phase = 0;
       bool ok = true;
       for (int unit = pair; unit < total_tiles && ok; unit += n_pairs) {
-        const int tile = unit / p.splits, sp = unit - tile * p.splits;
+        const int bt = unit / p.splits, sp = unit - bt * p.splits;
+        const int b = bt / tiles_per_batch, tile = bt - b * tiles_per_batch;
+        const int bo = b / p.batch_in, bi = b - bo * p.batch_in;
         const int m0 = (tile % p.m_tiles) * (2 * BM) + (int)cta * BM;
         const int n0 = (tile / p.m_tiles) * BN + (int)cta * (BN / 2);
         const int kb_begin = sp * p.kb_per_split, kb_end = min(kb_begin + p.kb_per_split, p.k_blocks);
@@ -588,16 +603,16 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (cta == 0) mbar_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);   // bytes of both CTAs
           const int k0 = kb * BK;
           if (!A_MN) {
-            tma_load_2d_pair(sa, &tmA, k0, m0, leader_full);
+            tma_load_4d_pair(sa, &tmA, k0, m0, bi, bo, leader_full);
           } else {
 #pragma unroll
-            for (int i = 0; i < BM / 64; ++i) tma_load_2d_pair(sa + i * 8192u, &tmA, m0 + 64 * i, k0, leader_full);
+            for (int i = 0; i < BM / 64; ++i) tma_load_4d_pair(sa + i * 8192u, &tmA, m0 + 64 * i, k0, bi, bo, leader_full);
           }
           if (!B_MN) {
-            tma_load_2d_pair(sb, &tmB, k0, n0, leader_full);
+            tma_load_4d_pair(sb, &tmB, k0, n0, bi, bo, leader_full);
           } else {
 #pragma unroll
-            for (int i = 0; i < BN / 128; ++i) tma_load_2d_pair(sb + i * 8192u, &tmB, n0 + 64 * i, k0, leader_full);
+            for (int i = 0; i < BN / 128; ++i) tma_load_4d_pair(sb + i * 8192u, &tmB, n0 + 64 * i, k0, bi, bo, leader_full);
           }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -644,7 +659,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     bool ok = true;
     int store_buf = 0;
     for (int unit = pair; unit < total_tiles && ok; unit += n_pairs) {
-      const int tile = unit / p.splits, sp = unit - tile * p.splits;
+      const int bt = unit / p.splits, sp = unit - bt * p.splits;
+      const int b = bt / tiles_per_batch, tile = bt - b * tiles_per_batch;
+      const int bo = b / p.batch_in, bi = b - bo * p.batch_in;
       // with split-K the partial tile goes to the workspace, whose rows are [split][m_pad]
       const int m0 = (tile % p.m_tiles) * (2 * BM) + (int)cta * BM + sp * p.m_pad, n0 = (tile / p.m_tiles) * BN;
       asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -658,7 +675,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (!ok) break;
       tc_fence_after();
       const unsigned t_row = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(acc * BN);
-      drain_tile<BN>(p, &tmD, p.tma_store != 0, store_gen, store_u32, bias_tile, t_row, m0, n0, q, lane, et, store_buf);
+      drain_tile<BN>(p, &tmD, p.tma_store != 0, store_gen, store_u32, bias_tile, t_row, m0, n0, bi, bo, q, lane, et, store_buf);
       tc_fence_before();
       mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));   // tell the leader this thread has drained its rows
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
@@ -693,43 +710,56 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// 4-D tensor map (contiguous index, row, batch_in, batch_out) with 128-byte swizzle.
+static int encode_map(CUtensorMap* map, const void* ptr, CUtensorMapDataType type, int es, long long inner, long long rows,
+                      long long ld, int batch_in, long long s_in, int batch_out, long long s_out, int box_inner, int box_rows,
+                      CUtensorMapL2promotion promo) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(HAPX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  // a batch dimension of extent 1 still needs a legal stride
+  const long long bs_in = (batch_in > 1 ? s_in : ld) * es, bs_out = (batch_out > 1 ? s_out : ld) * es;
+  cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)batch_in, (cuuint64_t)batch_out};
+  cuuint64_t strides[3] = {(cuuint64_t)(ld * es), (cuuint64_t)bs_in, (cuuint64_t)bs_out};
+  cuuint32_t box[4] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, type, 4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(HAPX_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  return HAPX_OK;
+}
+
+static bool strides_ok(const void* ptr, int es, long long ld, int batch_in, long long s_in, int batch_out, long long s_out) {
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0 || (ld * es) % 16 != 0) return false;
+  if (batch_in > 1 && (s_in * es) % 16 != 0) return false;
+  if (batch_out > 1 && (s_out * es) % 16 != 0) return false;
+  return true;
+}
+
 // Tensor map of the output for bulk stores: boxes of 32 rows x 128 bytes.  Returns with *ok = 0
-// (and a zeroed map) when D's base or row pitch is not a multiple of 16 bytes; the kernel then
-// stores directly.
-static int make_out_map(CUtensorMap* map, int* ok, void* ptr, long long cols, long long rows, long long ld, int out_f32) {
+// (and a zeroed map) when D's base, row pitch or batch strides are not multiples of 16 bytes; the
+// kernel then stores directly.
+static int make_out_map(CUtensorMap* map, int* ok, void* ptr, long long cols, long long rows, long long ld, int out_f32,
+                        int batch_in, long long s_in, int batch_out, long long s_out) {
   std::memset(map, 0, sizeof(*map));
   *ok = 0;
   const int es = out_f32 ? 4 : 2;
-  if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0 || (ld * es) % 16 != 0) return HAPX_OK;
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return fail(HAPX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * es};
-  cuuint32_t box[2] = {(cuuint32_t)(128 / es), 32};     // one epilogue warp's rows
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, out_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(HAPX_ERR_CUDA, "cuTensorMapEncodeTiled(output) failed with code " + std::to_string((int)r));
+  if (!strides_ok(ptr, es, ld, batch_in, s_in, batch_out, s_out)) return HAPX_OK;
+  if (int e = encode_map(map, ptr, out_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, es, cols, rows, ld,
+                         batch_in, s_in, batch_out, s_out, 128 / es, 32, CU_TENSOR_MAP_L2_PROMOTION_NONE)) return e;
   *ok = 1;
   return HAPX_OK;
 }
 
-// 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row pitch `ld` elements.
-static int make_map(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long ld, int box_inner, int box_outer) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return fail(HAPX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0) return fail(HAPX_ERR_ARGUMENT, "gemm: operand base must be 16-byte aligned");
-  if ((ld * 2) % 16 != 0) return fail(HAPX_ERR_EXTENT, "gemm: operand row pitch must be a multiple of 16 bytes (8 bf16 elements)");
-  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(HAPX_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
-  return HAPX_OK;
+// bf16 operand map.  K-major operand [rows][contraction contiguous]: box {64, tile rows};
+// MN-major operand [contraction rows][M or N contiguous]: box {64, 64}.
+static int make_map(CUtensorMap* map, const Operand& op, long long mn_extent, long long kc, int tile_rows, int batch_in, int batch_out) {
+  if (!strides_ok(op.ptr, 2, op.ld, batch_in, op.s_in, batch_out, op.s_out))
+    return fail(HAPX_ERR_EXTENT, "gemm: operand base, row pitch and batch strides must be multiples of 16 bytes (8 bf16 elements)");
+  if (op.mn_major)
+    return encode_map(map, op.ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, mn_extent, kc, op.ld, batch_in, op.s_in, batch_out, op.s_out, 64, 64,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+  return encode_map(map, op.ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, kc, mn_extent, op.ld, batch_in, op.s_in, batch_out, op.s_out, BK, tile_rows,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
 }
 
 struct DeviceState {
@@ -760,14 +790,13 @@ static int device_state(DeviceState** out) {
 }
 
 template <int BN, bool A_MN, bool B_MN>
-static int launch(const void* A, long long lda, const void* B, long long ldb, Params& p, cudaStream_t stream, int sm_count) {
+static int launch(const Operand& A, const Operand& B, const Operand& Dop, Params& p, cudaStream_t stream, int sm_count) {
   using C = Cfg<BN, A_MN, B_MN>;
+  const int batch_out = p.batch / p.batch_in;
   CUtensorMap tmA, tmB, tmD;
-  if (int e = make_out_map(&tmD, &p.tma_store, p.D, p.N, p.M, p.ldd, p.out_f32)) return e;
-  // K-major operand [rows = M or N][Kc contiguous]: inner = Kc, box {64, rows per tile}
-  // MN-major operand [rows = Kc][M or N contiguous]: inner = M or N, box {64, 64}
-  if (int e = A_MN ? make_map(&tmA, A, p.M, p.Kc, lda, 64, 64) : make_map(&tmA, A, p.Kc, p.M, lda, BK, BM)) return e;
-  if (int e = B_MN ? make_map(&tmB, B, p.N, p.Kc, ldb, 64, 64) : make_map(&tmB, B, p.Kc, p.N, ldb, BK, BN)) return e;
+  if (int e = make_out_map(&tmD, &p.tma_store, p.D, p.N, p.M, p.ldd, p.out_f32, p.batch_in, Dop.s_in, batch_out, Dop.s_out)) return e;
+  if (int e = make_map(&tmA, A, p.M, p.Kc, BM, p.batch_in, batch_out)) return e;
+  if (int e = make_map(&tmB, B, p.N, p.Kc, BN, p.batch_in, batch_out)) return e;
   p.m_tiles = (p.M + BM - 1) / BM;
   p.splits = 1; p.kb_per_split = 0; p.m_pad = 0;
   p.n_tiles = (p.N + BN - 1) / BN;
@@ -778,7 +807,9 @@ static int launch(const void* A, long long lda, const void* B, long long ldb, Pa
     HAPX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES));
     attr_set = true;
   }
-  const int grid = std::max(1, std::min(p.m_tiles * p.n_tiles, sm_count));
+  const long long units = (long long)p.m_tiles * p.n_tiles * p.batch;
+  if (units > 0x7fffffff) return fail(HAPX_ERR_EXTENT, "gemm: too many tiles");
+  const int grid = (int)std::max<long long>(1, std::min<long long>(units, sm_count));
   kernel<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmA, tmB, tmD, p);
   HAPX_CUDA(cudaGetLastError());
   count_launch();
@@ -828,7 +859,7 @@ static int workspace(int device, size_t bytes, float** out) {
 }
 
 template <bool A_MN, bool B_MN>
-static int launch2(const void* A, long long lda, const void* B, long long ldb, Params& p, cudaStream_t stream, int sm_count) {
+static int launch2(const Operand& A, const Operand& B, const Operand& Dop, Params& p, cudaStream_t stream, int sm_count) {
   using C = Cfg2<A_MN, B_MN>;
   auto kernel = gemm2_bf16_kernel<A_MN, B_MN>;
   static int max_clusters = 0;
@@ -856,7 +887,7 @@ static int launch2(const void* A, long long lda, const void* B, long long ldb, P
   // Few output tiles but a long contraction (weight gradients): cut the contraction so that all SM
   // pairs have work.  Take the smallest split count that fills >= 85 % of the waves it needs.
   const int tiles = p.m_tiles * p.n_tiles;
-  if (tiles * 2 <= max_clusters && p.k_blocks >= 16) {
+  if (p.batch == 1 && tiles * 2 <= max_clusters && p.k_blocks >= 16) {
     int best = 1;
     double best_eff = (double)tiles / (((tiles + max_clusters - 1) / max_clusters) * (double)max_clusters);
     for (int sp = 2; sp <= 32 && sp * 4 <= p.k_blocks; ++sp) {
@@ -878,12 +909,15 @@ static int launch2(const void* A, long long lda, const void* B, long long ldb, P
     p.D = ws; p.ldd = p.N; p.out_f32 = 1; p.bias = nullptr; p.epilogue = EPI_NONE;
   }
   CUtensorMap tmA, tmB, tmD;
+  const int batch_out = p.batch / p.batch_in;
   const long long out_rows = p.splits > 1 ? (long long)p.splits * p.m_pad : p.M;
-  if (int e = make_out_map(&tmD, &p.tma_store, p.D, p.N, out_rows, p.ldd, p.out_f32)) return e;
+  if (int e = make_out_map(&tmD, &p.tma_store, p.D, p.N, out_rows, p.ldd, p.out_f32, p.batch_in, Dop.s_in, batch_out, Dop.s_out)) return e;
   if (p.splits > 1 && !p.tma_store) return fail(HAPX_ERR_EXTENT, "gemm: split-K needs an output width that is a multiple of 4");
-  if (int e = A_MN ? make_map(&tmA, A, p.M, p.Kc, lda, 64, 64) : make_map(&tmA, A, p.Kc, p.M, lda, BK, BM)) return e;
-  if (int e = B_MN ? make_map(&tmB, B, p.N, p.Kc, ldb, 64, 64) : make_map(&tmB, B, p.Kc, p.N, ldb, BK, C::BN / 2)) return e;
-  const int pairs = std::max(1, std::min(tiles * p.splits, max_clusters));
+  if (int e = make_map(&tmA, A, p.M, p.Kc, BM, p.batch_in, batch_out)) return e;
+  if (int e = make_map(&tmB, B, p.N, p.Kc, C::BN / 2, p.batch_in, batch_out)) return e;
+  const long long units = (long long)tiles * p.splits * p.batch;
+  if (units > 0x7fffffff) return fail(HAPX_ERR_EXTENT, "gemm: too many tiles");
+  const int pairs = (int)std::max<long long>(1, std::min<long long>(units, max_clusters));
   cfg.gridDim = dim3(2 * pairs);
   HAPX_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmD, p));
   count_launch();
@@ -898,34 +932,37 @@ static int launch2(const void* A, long long lda, const void* B, long long ldb, P
   return HAPX_OK;
 }
 
-// D[M,N] = A * B^T with the given operand majors.  lda/ldb/ldd in elements.
-static int gemm_bf16(void* D, int out_f32, long long ldd, const void* A, bool a_mn, long long lda, const void* B, bool b_mn,
-                     long long ldb, const void* bias, int epilogue, long long M, long long N, long long Kc, cudaStream_t stream) {
-  if (M < 0 || N < 0 || Kc < 0) return fail(HAPX_ERR_EXTENT, "gemm: negative extent");
+// D[b] = A[b] * B[b]^T for b in [0, batch): M x N outputs, contraction length Kc.
+int gemm_bf16(const Operand& Dop, int out_f32, const Operand& A, const Operand& B, const void* bias, int epilogue,
+                     long long M, long long N, long long Kc, int batch_in, int batch_out, cudaStream_t stream) {
+  if (M < 0 || N < 0 || Kc < 0 || batch_in < 1 || batch_out < 1) return fail(HAPX_ERR_EXTENT, "gemm: bad extent");
   if (M == 0 || N == 0) return HAPX_OK;
   if (Kc == 0) return fail(HAPX_ERR_EXTENT, "gemm: empty contraction");
   if (M > 0x7fffffff || N > 0x7fffffff || Kc > 0x7fffffff) return fail(HAPX_ERR_EXTENT, "gemm: extent exceeds 2^31");
-  if (!D || !A || !B) return fail(HAPX_ERR_ARGUMENT, "gemm: null pointer");
+  if (!Dop.ptr || !A.ptr || !B.ptr) return fail(HAPX_ERR_ARGUMENT, "gemm: null pointer");
   DeviceState* dev = nullptr;
   if (int e = device_state(&dev)) return e;
   Params p = Params();
-  p.M = (int)M; p.N = (int)N; p.Kc = (int)Kc; p.ldd = ldd; p.D = D; p.bias = bias; p.epilogue = epilogue; p.out_f32 = out_f32;
+  p.M = (int)M; p.N = (int)N; p.Kc = (int)Kc; p.ldd = Dop.ld; p.D = const_cast<void*>(Dop.ptr); p.bias = bias; p.epilogue = epilogue;
+  p.out_f32 = out_f32;
   p.error = dev->error;
-  // tile width: fewest waves first, then the wider tile
-  auto waves = [&](int bn) {
-    const long long tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
-    return (double)((tiles + dev->sm_count - 1) / dev->sm_count) * bn;
-  };
+  p.batch = batch_in * batch_out; p.batch_in = batch_in; p.d_stride_in = Dop.s_in; p.d_stride_out = Dop.s_out;
+  const bool a_mn = A.mn_major, b_mn = B.mn_major;
   // SM pairs (256 x 256 tiles, half the B traffic per SM) whenever there is more than one row tile
   static const bool pair_kernel = std::getenv("HAPX_GEMM_SINGLE_CTA") == nullptr;
   if (pair_kernel && M > BM && N > 64) {
-    if (!a_mn && !b_mn) return launch2<false, false>(A, lda, B, ldb, p, stream, dev->sm_count);
-    if (!a_mn && b_mn) return launch2<false, true>(A, lda, B, ldb, p, stream, dev->sm_count);
-    if (a_mn && b_mn) return launch2<true, true>(A, lda, B, ldb, p, stream, dev->sm_count);
+    if (!a_mn && !b_mn) return launch2<false, false>(A, B, Dop, p, stream, dev->sm_count);
+    if (!a_mn && b_mn) return launch2<false, true>(A, B, Dop, p, stream, dev->sm_count);
+    if (a_mn && b_mn) return launch2<true, true>(A, B, Dop, p, stream, dev->sm_count);
   }
+  // single-CTA tiles: fewest waves first, then the wider tile
+  auto waves = [&](int bn) {
+    const long long tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn) * p.batch;
+    return (double)((tiles + dev->sm_count - 1) / dev->sm_count) * bn;
+  };
   const int bn = (waves(256) <= waves(128)) ? 256 : 128;
 #define HAPX_GEMM_CASE(BN_, AMN_, BMN_) \
-  if (bn == BN_ && a_mn == AMN_ && b_mn == BMN_) return launch<BN_, AMN_, BMN_>(A, lda, B, ldb, p, stream, dev->sm_count);
+  if (bn == BN_ && a_mn == AMN_ && b_mn == BMN_) return launch<BN_, AMN_, BMN_>(A, B, Dop, p, stream, dev->sm_count);
   HAPX_GEMM_CASE(256, false, false)
   HAPX_GEMM_CASE(128, false, false)
   HAPX_GEMM_CASE(256, false, true)
@@ -980,7 +1017,8 @@ int hapx_linear_forward(void* y, const void* x, const void* w, const void* bias,
   if (dtype != HAPX_BF16) return fail(HAPX_ERR_DTYPE, "linear_forward: operands must be bfloat16 or float32");
   if (out_dtype != HAPX_BF16 && out_dtype != HAPX_F32) return fail(HAPX_ERR_DTYPE, "linear_forward: output must be bfloat16 or float32");
   // y[m,n] = x[m,k] * w[n,k]^T : both operands K-major
-  return gemm::gemm_bf16(y, out_dtype == HAPX_F32, n, x, false, k, w, false, k, bias, epilogue, m, n, k, static_cast<cudaStream_t>(stream));
+  return gemm::gemm_bf16({y, false, n, 0, 0}, out_dtype == HAPX_F32, {x, false, k, 0, 0}, {w, false, k, 0, 0}, bias, epilogue, m, n, k, 1, 1,
+                         static_cast<cudaStream_t>(stream));
 }
 
 int hapx_linear_dgrad(void* dx, const void* g, const void* w, int dtype, int out_dtype, int64_t m, int64_t n, int64_t k,
@@ -993,7 +1031,8 @@ int hapx_linear_dgrad(void* dx, const void* g, const void* w, int dtype, int out
   if (dtype != HAPX_BF16) return fail(HAPX_ERR_DTYPE, "linear_dgrad: operands must be bfloat16 or float32");
   if (out_dtype != HAPX_BF16 && out_dtype != HAPX_F32) return fail(HAPX_ERR_DTYPE, "linear_dgrad: output must be bfloat16 or float32");
   // dx[m,k] = g[m,n] * w[n,k] : contraction over n; A = g is K-major, B[k][n] = w[n][k] is MN-major as stored
-  return gemm::gemm_bf16(dx, out_dtype == HAPX_F32, k, g, false, n, w, true, k, nullptr, 0, m, k, n, static_cast<cudaStream_t>(stream));
+  return gemm::gemm_bf16({dx, false, k, 0, 0}, out_dtype == HAPX_F32, {g, false, n, 0, 0}, {w, true, k, 0, 0}, nullptr, 0, m, k, n, 1, 1,
+                         static_cast<cudaStream_t>(stream));
 }
 
 int hapx_linear_wgrad(void* dw, void* dbias, const void* g, const void* x, int dtype, int out_dtype, int64_t m, int64_t n,
@@ -1012,7 +1051,8 @@ int hapx_linear_wgrad(void* dw, void* dbias, const void* g, const void* x, int d
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   // dw[n,k] = g[m,n]^T * x[m,k] : contraction over m; A[n][m] = g[m][n] and B[k][m] = x[m][k] are both MN-major as stored
   if (dw) {
-    if (int e = gemm::gemm_bf16(dw, out_dtype == HAPX_F32, k, g, true, n, x, true, k, nullptr, 0, n, k, m, stream)) return e;
+    if (int e = gemm::gemm_bf16({dw, false, k, 0, 0}, out_dtype == HAPX_F32, {g, true, n, 0, 0}, {x, true, k, 0, 0}, nullptr, 0, n, k, m, 1, 1, stream))
+      return e;
   }
   if (dbias && n > 0) {
     if (m < 0 || m > 0x7fffffff || n > 0x7fffffff) return fail(HAPX_ERR_EXTENT, "linear_wgrad: extent out of range");

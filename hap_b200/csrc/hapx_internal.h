@@ -45,6 +45,20 @@ inline int dtype_size(int dtype) {
   }
 }
 
+namespace gemm {
+// One matrix operand (or the output) of a possibly batched bf16 GEMM.  ld and the batch strides
+// are in elements; batch index b = b_out * batch_in + b_in addresses ptr + b_out * s_out + b_in * s_in.
+// mn_major: the output index (not the contraction index) is the contiguous one in memory.
+struct Operand {
+  const void* ptr;
+  bool mn_major;
+  long long ld, s_in, s_out;
+};
+// D[b] = A[b] * B[b]^T (+ bias, activation) on the tensor cores; see hapx_gemm_sm100.cu.
+int gemm_bf16(const Operand& D, int out_f32, const Operand& A, const Operand& B, const void* bias, int epilogue,
+              long long M, long long N, long long Kc, int batch_in, int batch_out, cudaStream_t stream);
+}  // namespace gemm
+
 }  // namespace hapx
 
 struct hapx_comm {

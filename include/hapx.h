@@ -166,6 +166,22 @@ int hapx_linear_wgrad(void* dw, void* dbias, const void* g, const void* x, int d
  * bounded barrier wait ran out. */
 int hapx_gemm_status(void);
 
+/* ---- multi-head self-attention on a batch shard ---------------------------------------------
+ * Replace the attention core of F.multi_head_attention_forward as emitted at hap.rs:1297-1329
+ * (query = key = value, packed in-projection, no bias_k/bias_v, no key padding mask; only the
+ * batch dimension N is sharded, hap.rs:2903-2926).  All tensors bfloat16, (L, N, E) layout:
+ *   qkv  [L, N, 3E]  output of the packed in-projection (E = H * D);   out [L, N, E]
+ *   probs      [N*H, L, Lp] bf16, Lp = L rounded up to 8: softmax output, kept for backward
+ *   scores_ws  [N*H, L, Lp] fp32 scratch;   ds_ws [N*H, L, Lp] bf16 scratch (backward)
+ * forward : out = softmax(Q K^T / sqrt(D) + mask) V.  causal != 0 masks keys after the query
+ *           (the -inf upper-triangular mask of models.py:72); mask = optional additive [L, L] fp32.
+ * backward: dqkv [L, N, 3E] from dout [L, N, E].  Attention dropout is not applied (p = 0).
+ * Limits: L <= 1024, D % 8 == 0. */
+int hapx_attention_forward(void* out, void* probs, void* scores_ws, const void* qkv, int64_t L, int64_t N, int64_t H,
+                           int64_t D, int causal, const float* mask, hapx_stream stream);
+int hapx_attention_backward(void* dqkv, void* dscores_ws, void* ds_ws, const void* dout, const void* probs,
+                            const void* qkv, int64_t L, int64_t N, int64_t H, int64_t D, hapx_stream stream);
+
 /* all_reduce that allocates nothing.  No counterpart in the reference.
  * Same values as hapx_all_reduce on a local (single-device) communicator of `world` virtual
  * ranks, but without a communicator: all scratch (control blocks, staged inputs, reduced
