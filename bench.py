@@ -544,6 +544,167 @@ def run_gemm(args):
                      "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": best["frac_of_peak"], "peak_kind": peak_kind, "traffic": None},
         "cublas_tflops": tot_flops / tot_ms_ref / 1e9, "gpu_launches": int(launches), "layers": rows}), flush=True)
 
+
+# ----------------------------------------------------------------------------------------------
+# SPMD training step of the Transformer-LM configuration: samples/s at N GPUs
+# (12 layers, d_model 768, 12 heads, FFN 3072, pre-LN, vocab 33278 padded to 33280, seq 256, bf16,
+#  batch 32 per GPU of uniform token ids; data parallel with ratio-sharded FFN/attention weights)
+# ----------------------------------------------------------------------------------------------
+def _lm_cpu_worker(rank, world, store, batch_per_rank, out_path, layers):
+    import copy
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    from types import SimpleNamespace
+    sys.path.insert(0, ROOT)
+    from hap_b200 import plan as P
+    from hap_b200.spmd import ProcessWorker
+    from oracle import gloo_port
+    torch.set_num_threads(max(1, (os.cpu_count() or 1) // world))
+    dist.init_process_group("gloo", rank=rank, world_size=world, init_method=f"file://{store}")
+    torch.manual_seed(39)
+    model = P.TransformerLM(nlayers=layers).to(torch.bfloat16)
+    ns = SimpleNamespace(collectives=gloo_port, linear=F.linear, mha=F.multi_head_attention_forward)
+    B = batch_per_rank * world
+    graph = P.emit_lm(model, "dp_zero", ratios_for(world), rank, B, ns)
+    worker = ProcessWorker(torch.fx.GraphModule(model, graph))
+    g = torch.Generator().manual_seed(2024)
+    tok = torch.randint(0, 33278, (B, 256), generator=g)
+    tgt = torch.randint(0, 33278, (B, 256), generator=g)
+    worker.step(tok, tgt)
+    dist.barrier()
+    t0 = time.perf_counter()
+    worker.step(tok, tgt)
+    dist.barrier()
+    if rank == 0:
+        json.dump({"s": time.perf_counter() - t0, "batch": B}, open(out_path, "w"))
+    dist.destroy_process_group()
+
+
+def run_lm_cpu(world, batch_per_rank, layers):
+    import torch.multiprocessing as mp
+    with tempfile.TemporaryDirectory() as d:
+        out = os.path.join(d, "t.json")
+        mp.spawn(_lm_cpu_worker, args=(world, os.path.join(d, "store"), batch_per_rank, out, layers), nprocs=world, join=True)
+        r = json.load(open(out))
+    cores = os.cpu_count() or 1
+    # a step's cost is proportional to the layer count (the embedding/decoder part is counted once too often, in the CPU's favour)
+    return {"value": r["batch"] / r["s"] * layers / 12.0, "unit": "samples/s", "cores": cores, "kind": "port",
+            "sample": f"{world} gloo ranks x {max(1, cores // world)} threads, same fx program (dp_zero) with the CPU port of the collectives "
+                      f"and torch CPU ops, {layers} of 12 layers, batch {batch_per_rank} per rank, 1 step after 1 warm-up; "
+                      f"value scaled by {layers}/12",
+            "step_s": r["s"]}
+
+
+def run_lm(args):
+    import copy
+    import torch
+    import hap_b200
+    from hap_b200 import plan as P
+    from hap_b200 import _native as N
+    from hap_b200.spmd import LockstepWorld, ProcessWorker
+    n_gpus = args.gpus
+    rank = int(os.environ.get("RANK", 0))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    W = n_gpus
+    B = args.lm_batch * W
+    ratios = ratios_for(W)
+    torch.manual_seed(39)
+    model = P.TransformerLM(nlayers=args.lm_layers).to(torch.bfloat16).to(dev)
+    n_params = sum(p.numel() for p in model.parameters())
+    if W == 1:
+        dist = None
+        comm = hap_b200.local_comm(1, dev, stage_bytes=256 << 20, heap_bytes=320 << 20)
+        graph = P.emit_lm(model, args.lm_plan, ratios, 0, B)
+        world = LockstepWorld([torch.fx.GraphModule(model, graph)], hap_b200.LocalCollectives(comm))
+        step = lambda tok, tgt: world.step([(tok, tgt)])
+    else:
+        import torch.distributed as dist
+        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=W)
+        comm = hap_b200.init_process_comm(stage_bytes=256 << 20, heap_bytes=320 << 20)
+        hap_b200.collectives.set_default_comm(comm)
+        graph = P.emit_lm(model, args.lm_plan, ratios, rank, B)
+        # the reference sums the partial losses with dist.reduce (worker.py:63-64); here through the package's all_reduce
+        worker = ProcessWorker(torch.fx.GraphModule(model, graph),
+                               reduce_loss=lambda t: comm.all_reduce([t.reshape(1).float()])[0])
+        step = worker.step
+    g = torch.Generator().manual_seed(2024)
+    tok_h = torch.randint(0, 33278, (B, 256), generator=g).pin_memory()
+    tgt_h = torch.randint(0, 33278, (B, 256), generator=g).pin_memory()
+    tok, tgt = tok_h.to(dev), tgt_h.to(dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step(tok, tgt)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    l0 = N.lib.hapx_launch_count()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    a.record()
+    for _ in range(args.steps):
+        loss = step(tok, tgt)
+    b.record()
+    barrier()
+    launches = N.lib.hapx_launch_count() - l0
+    clocks = sampler.finish()
+    ms = a.elapsed_time(b) / args.steps
+    # end to end: tokens come from pinned host memory every step, the loss goes back to the host
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    c, d = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    c.record()
+    for _ in range(e2e_steps):
+        loss = step(tok_h.to(dev, non_blocking=True), tgt_h.to(dev, non_blocking=True))
+        loss_host = float(loss)
+    d.record()
+    barrier()
+    e2e_ms = c.elapsed_time(d) / e2e_steps
+    if dist is not None:
+        t = torch.tensor([ms, e2e_ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    comm.check()
+    hap_b200.linear_ops.gemm_status()
+    peaks, peak_kind = measured_peaks()
+    # GEMM flops of one step on the busiest rank (largest batch share): 3 x forward, 2*M*N*K each
+    lb = hap_b200.sharding_round(B, ratios)
+    M = max(lb) * 256
+    L = args.lm_layers
+    fwd = L * (2.0 * M * 768 * (2304 + 768 + 3072 + 3072) + 2 * 2.0 * max(lb) * 12 * 256 * 256 * 64) + 2.0 * M * 768 * 33280
+    achieved = 3 * fwd / (ms * 1e-3) / 1e12
+    result = {
+        "metric": "spmd_step_samples_per_s", "value": B / (ms * 1e-3), "unit": "samples/s", "n_gpus": n_gpus, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"Transformer LM training step ({L} layers, d_model 768, 12 heads, FFN 3072, pre-LN, vocab 33280, seq 256), "
+                               f"plan {args.lm_plan}, global batch {B} split {lb}", "parameters": n_params,
+                   "l2": "activations and weights of a step exceed L2 by far", "loss": loss_host},
+        "roofline": {"bound": "tensor", "kernel": "gemm2_bf16_kernel (all linear / attention contractions of the busiest rank)",
+                     "achieved": achieved, "peak": peaks["bf16_tflops_sustained"] if "bf16_tflops_sustained" in peaks else peaks["bf16_tflops"],
+                     "unit": "TFLOP/s", "frac": achieved / (peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]),
+                     "peak_kind": peak_kind + " (sustained: the kernels run inside a long step)", "traffic": None,
+                     "note": "whole-step time, so this fraction also pays for every non-GEMM op of the step"},
+        "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": int(2 * B * 256 * 8) * (1 if dist is None else 1),
+                "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms, "steps": e2e_steps},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+    comm.destroy()
+    if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
+        result["cpu_baseline"] = run_lm_cpu(2, 2, 2)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(result), flush=True)
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
@@ -578,13 +739,18 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="size sweep instead of the single JSON line")
     ap.add_argument("--sweep-max-mib", type=int, default=1024)
-    ap.add_argument("--workload", default="collectives", choices=["collectives", "gemm"])
+    ap.add_argument("--workload", default="collectives", choices=["collectives", "gemm", "lm"])
+    ap.add_argument("--lm-batch", type=int, default=32, help="samples per GPU")
+    ap.add_argument("--lm-layers", type=int, default=12)
+    ap.add_argument("--lm-plan", default="dp_zero", choices=["dp", "dp_zero"])
     ap.add_argument("--gemm-tokens", type=int, default=8192)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
     elif args.workload == "gemm":
         run_gemm(args)
+    elif args.workload == "lm":
+        run_lm(args)
     elif args.sweep:
         run_sweep(args)
     else:

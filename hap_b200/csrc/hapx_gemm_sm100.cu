@@ -887,7 +887,7 @@ static int launch2(const Operand& A, const Operand& B, const Operand& Dop, Param
   // Few output tiles but a long contraction (weight gradients): cut the contraction so that all SM
   // pairs have work.  Take the smallest split count that fills >= 85 % of the waves it needs.
   const int tiles = p.m_tiles * p.n_tiles;
-  if (p.batch == 1 && tiles * 2 <= max_clusters && p.k_blocks >= 16) {
+  if (p.batch == 1 && tiles * 4 <= max_clusters && p.k_blocks >= 16) {
     int best = 1;
     double best_eff = (double)tiles / (((tiles + max_clusters - 1) / max_clusters) * (double)max_clusters);
     for (int sp = 2; sp <= 32 && sp * 4 <= p.k_blocks; ++sp) {

@@ -44,8 +44,9 @@ class MLP(torch.nn.Module):
 
 def default_namespace() -> SimpleNamespace:
     from . import collectives
+    from .attention import multi_head_attention_forward
     from .linear import linear
-    return SimpleNamespace(collectives=collectives, linear=linear)
+    return SimpleNamespace(collectives=collectives, linear=linear, mha=multi_head_attention_forward)
 
 
 def shard_parameter_(module: torch.nn.Module, name: str, lengths: Sequence[int], dim: int, rank: int) -> None:
@@ -101,6 +102,127 @@ def emit_mlp(model: MLP, plan: str, ratios: Sequence[float], rank: int, batch: i
         loss = g.call_function(F.mse_loss, (o_r, y_r), {"reduction": "sum"})
     else:
         raise ValueError(f"unknown plan {plan!r}")
+    g.output(loss)
+    g.lint()
+    return g
+
+
+# ---------------------------------------------------------------------------------------------
+# Transformer language model (the bf16 throughput configuration)
+# ---------------------------------------------------------------------------------------------
+class TransformerLM(torch.nn.Module):
+    """Parameters of a pre-LN Transformer language model in the (L, N, E) layout the planner's
+    attention handler expects (``hap.rs:1284-1287``): token + positional embedding, ``nlayers`` blocks
+    of x + MHA(LN(x)) and x + W2 relu(W1 LN(x)), final LN, tied-size decoder, summed NLL loss
+    (``log_softmax`` + ``nll_loss``, the ops of ``hap.rs:1808, 1858``).  The vocabulary is padded to
+    a multiple of 8 (the reference pads it to a multiple of the world size, ``config.py:116``)."""
+
+    def __init__(self, vocab=33280, d_model=768, nheads=12, d_ffn=3072, nlayers=12, seqlen=256):
+        super().__init__()
+        self.vocab, self.d_model, self.nheads, self.nlayers, self.seqlen = vocab, d_model, nheads, nlayers, seqlen
+        self.embed = torch.nn.Embedding(vocab, d_model)
+        self.pos = torch.nn.Parameter(torch.randn(seqlen, 1, d_model) * 0.02)
+        for i in range(nlayers):
+            self.register_parameter(f"l{i}_ln1_w", torch.nn.Parameter(torch.ones(d_model)))
+            self.register_parameter(f"l{i}_ln1_b", torch.nn.Parameter(torch.zeros(d_model)))
+            self.register_parameter(f"l{i}_in_w", torch.nn.Parameter(torch.randn(3 * d_model, d_model) * d_model ** -0.5))
+            self.register_parameter(f"l{i}_in_b", torch.nn.Parameter(torch.zeros(3 * d_model)))
+            self.register_parameter(f"l{i}_out_w", torch.nn.Parameter(torch.randn(d_model, d_model) * d_model ** -0.5))
+            self.register_parameter(f"l{i}_out_b", torch.nn.Parameter(torch.zeros(d_model)))
+            self.register_parameter(f"l{i}_ln2_w", torch.nn.Parameter(torch.ones(d_model)))
+            self.register_parameter(f"l{i}_ln2_b", torch.nn.Parameter(torch.zeros(d_model)))
+            self.register_parameter(f"l{i}_w1", torch.nn.Parameter(torch.randn(d_ffn, d_model) * d_model ** -0.5))
+            self.register_parameter(f"l{i}_b1", torch.nn.Parameter(torch.zeros(d_ffn)))
+            self.register_parameter(f"l{i}_w2", torch.nn.Parameter(torch.randn(d_model, d_ffn) * d_ffn ** -0.5))
+            self.register_parameter(f"l{i}_b2", torch.nn.Parameter(torch.zeros(d_model)))
+        self.lnf_w = torch.nn.Parameter(torch.ones(d_model))
+        self.lnf_b = torch.nn.Parameter(torch.zeros(d_model))
+        self.dec_w = torch.nn.Parameter(torch.randn(vocab, d_model) * d_model ** -0.5)
+        self.dec_b = torch.nn.Parameter(torch.zeros(vocab))
+
+    def forward(self, tokens, targets):
+        """Unsharded reference forward: tokens, targets (B, S) int64 -> summed NLL."""
+        ns = SimpleNamespace(collectives=None, linear=F.linear, mha=F.multi_head_attention_forward)
+        return _lm_forward(self, tokens, targets, ns, None, None, None, "none")
+
+
+def _lm_forward(m, tokens, targets, ns, emit, ratios, rank, plan):
+    """The model's forward written once; `emit` (an fx graph) turns parameter reads and collectives
+    into nodes, otherwise it runs eagerly on the unsharded module."""
+    col, linear, mha = ns.collectives, ns.linear, ns.mha
+    E, H = m.d_model, m.nheads
+
+    def param(name, shardable=False):
+        if emit is None:
+            obj = m
+            for part in name.split("."):
+                obj = getattr(obj, part)
+            return obj
+        node = emit.get_attr(name)
+        if plan == "dp_zero" and shardable:
+            # ZeRO-style: the parameter lives sharded on dim 0 and is gathered where it is used
+            # (hap.rs:2527-2555); backward of the gather is the uneven reduce_scatter of its gradient
+            full = m._full_extent[name]
+            return emit.call_function(col.all_gather, (node, 0, sharding_round(full, ratios), rank))
+        return emit.call_function(col.replicate, (node,))
+
+    call = (lambda fn, *a, **k: fn(*a, **k)) if emit is None else (lambda fn, *a, **k: emit.call_function(fn, a, k))
+    method = (lambda obj, name, *a: getattr(obj, name)(*a)) if emit is None else (lambda obj, name, *a: emit.call_method(name, (obj, *a)))
+
+    x = call(F.embedding, tokens, param("embed.weight"))                  # (B, S, E)
+    x = method(x, "transpose", 0, 1)                                       # (S, B, E): the (L, N, E) layout
+    x = call(operator.add, x, param("pos"))
+    S = m.seqlen
+    mask = call(torch.triu, call(torch.full, (S, S), float("-inf"), device=_device_of(m)), 1)
+    for i in range(m.nlayers):
+        h = call(F.layer_norm, x, (E,), param(f"l{i}_ln1_w"), param(f"l{i}_ln1_b"))
+        att = call(mha, query=h, key=h, value=h, embed_dim_to_check=E, num_heads=H,
+                   in_proj_weight=param(f"l{i}_in_w", True), in_proj_bias=param(f"l{i}_in_b", True), bias_k=None, bias_v=None,
+                   add_zero_attn=False, dropout_p=0.0, out_proj_weight=param(f"l{i}_out_w", True),
+                   out_proj_bias=param(f"l{i}_out_b"), attn_mask=mask)
+        x = call(operator.add, x, call(operator.getitem, att, 0))
+        h = call(F.layer_norm, x, (E,), param(f"l{i}_ln2_w"), param(f"l{i}_ln2_b"))
+        h = call(linear, h, param(f"l{i}_w1", True), param(f"l{i}_b1", True))
+        h = call(F.relu, h)
+        h = call(linear, h, param(f"l{i}_w2", True), param(f"l{i}_b2"))
+        x = call(operator.add, x, h)
+    x = call(F.layer_norm, x, (E,), param("lnf_w"), param("lnf_b"))
+    logits = call(linear, x, param("dec_w", True), param("dec_b", True))  # (S, B, V)
+    logp = call(F.log_softmax, method(logits, "float"), -1)
+    logp = method(logp, "reshape", -1, m.vocab)
+    tgt = method(method(targets, "transpose", 0, 1), "reshape", -1)
+    return call(F.nll_loss, logp, tgt, reduction="sum")
+
+
+def _device_of(m):
+    return next(m.parameters()).device
+
+
+def emit_lm(model: TransformerLM, plan: str, ratios: Sequence[float], rank: int, batch: int, ns=None) -> torch.fx.Graph:
+    """fx graph of the language model's training forward for one rank.
+
+    ``"dp"``      - batch-sharded tokens/targets, every parameter replicated (gradient all-reduce);
+    ``"dp_zero"`` - as above, but attention and FFN weights, the first FFN bias and the decoder live
+                    sharded on dim 0 by ``ratios`` (cut in place on the module) and are all-gathered
+                    at their use; their gradients come back through the uneven reduce_scatter.
+    """
+    ns = ns or default_namespace()
+    if plan not in ("dp", "dp_zero"):
+        raise ValueError(f"unknown plan {plan!r}")
+    g = torch.fx.Graph()
+    tokens, targets = g.placeholder("tokens"), g.placeholder("targets")
+    lb = sharding_round(batch, ratios)
+    tok_r = g.call_function(operator.getitem, (g.call_method("split", (tokens, lb, 0)), rank))
+    tgt_r = g.call_function(operator.getitem, (g.call_method("split", (targets, lb, 0)), rank))
+    model._full_extent = {}
+    if plan == "dp_zero":
+        names = [n for i in range(model.nlayers) for n in (f"l{i}_in_w", f"l{i}_in_b", f"l{i}_out_w", f"l{i}_w1", f"l{i}_b1", f"l{i}_w2")]
+        names += ["dec_w", "dec_b"]
+        for n in names:
+            full = getattr(model, n).shape[0]
+            model._full_extent[n] = full
+            shard_parameter_(model, n, sharding_round(full, ratios), 0, rank)
+    loss = _lm_forward(model, tok_r, tgt_r, ns, g, list(ratios), rank, plan)
     g.output(loss)
     g.lint()
     return g

@@ -50,3 +50,33 @@ def expected_shard(full, name, plan, rank, dims):
     from hap_b200 import sharding_round
     extent = dims[1] if name.startswith("fc1") else dims[2]
     return torch.split(full, sharding_round(extent, RATIOS), dim=0)[rank]
+
+
+# ---- Transformer language model ------------------------------------------------------------------
+LM_SMALL = dict(vocab=64, d_model=64, nheads=2, d_ffn=128, nlayers=2, seqlen=16)
+LM_BATCH = 8
+
+
+def lm_model(dtype=torch.float32):
+    torch.manual_seed(39)
+    return P.TransformerLM(**LM_SMALL).to(dtype)
+
+
+def lm_batch():
+    g = torch.Generator().manual_seed(2024)
+    return (torch.randint(0, LM_SMALL["vocab"], (LM_BATCH, LM_SMALL["seqlen"]), generator=g),
+            torch.randint(0, LM_SMALL["vocab"], (LM_BATCH, LM_SMALL["seqlen"]), generator=g))
+
+
+def lm_rank_modules(model, plan, ns, world=2, device="cpu"):
+    mods = []
+    for r in range(world):
+        m = copy.deepcopy(model).to(device)
+        graph = P.emit_lm(m, plan, RATIOS, r, LM_BATCH, ns)
+        mods.append(torch.fx.GraphModule(m, graph))
+    return mods
+
+
+def lm_cpu_namespace():
+    from oracle import gloo_port
+    return SimpleNamespace(collectives=gloo_port, linear=F.linear, mha=F.multi_head_attention_forward)

@@ -83,3 +83,30 @@ def test_two_gloo_processes_match_the_lockstep_replay(plan):
                 assert abs(a - b) <= 1e-5 * abs(b)
             for name, p in world.modules[r].named_parameters():
                 torch.testing.assert_close(got["params"][name], p.detach(), rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("plan", ["dp", "dp_zero"])
+def test_language_model_programs_reproduce_the_unsharded_model(plan):
+    """Transformer LM (pre-LN, causal MHA, summed NLL): data parallel, and data parallel with
+    ZeRO-style dim-0 sharded weights gathered at use (hap.rs:2527-2555)."""
+    import copy
+    from hap_b200 import sharding_round
+    model = C.lm_model()
+    tok, tgt = C.lm_batch()
+    ref = copy.deepcopy(model)
+    want = ref(tok, tgt)
+    want.backward()
+    world = LockstepWorld(C.lm_rank_modules(model, plan, C.lm_cpu_namespace()), OracleCollectives())
+    losses = world.forward([(tok, tgt), (tok, tgt)])
+    assert abs(float(sum(losses)) - float(want)) <= 1e-5 * abs(float(want))
+    torch.stack(losses).sum().backward()
+    full = dict(ref.named_parameters())
+    n_sharded = 0
+    for r, m in enumerate(world.modules):
+        for name, p in m.named_parameters():
+            g = full[name].grad
+            if p.shape != g.shape:
+                g = torch.split(g, sharding_round(g.shape[0], C.RATIOS), dim=0)[r]
+                n_sharded += 1
+            torch.testing.assert_close(p.grad, g, rtol=1e-3, atol=1e-4)
+    assert (n_sharded > 0) == (plan == "dp_zero")

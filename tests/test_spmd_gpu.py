@@ -77,3 +77,32 @@ def test_training_step_matches_cpu_replay(plan, dtype, tol):
         hap_b200.linear_ops.gemm_status()
     finally:
         comm.destroy()
+
+
+@pytest.mark.parametrize("plan", ["dp", "dp_zero"])
+def test_language_model_step_matches_cpu_replay(plan):
+    """Transformer LM step in bf16: package linear + attention + collectives on the GPU (2 virtual
+    ranks) against the same fx programs replayed on the CPU in bf16 with torch's own ops."""
+    dtype = torch.bfloat16
+    model = C.lm_model(dtype)
+    tok, tgt = C.lm_batch()
+    cpu = LockstepWorld(C.lm_rank_modules(model, plan, C.lm_cpu_namespace()), OracleCollectives())
+    comm = hap_b200.local_comm(2, DEV, stage_bytes=16 << 20, heap_bytes=32 << 20)
+    try:
+        gpu = LockstepWorld(C.lm_rank_modules(model, plan, hap_b200.plan.default_namespace(), device=DEV),
+                            hap_b200.LocalCollectives(comm))
+        want = cpu.forward([(tok, tgt), (tok, tgt)])
+        got = gpu.forward([(tok.to(DEV), tgt.to(DEV)), (tok.to(DEV), tgt.to(DEV))])
+        for r in range(2):
+            assert abs(float(got[r]) - float(want[r])) <= 1e-2 * abs(float(want[r])), (plan, r, float(got[r]), float(want[r]))
+        torch.stack(want).sum().backward()
+        torch.stack(got).sum().backward()
+        for r in range(2):
+            for (name, pw), (_, pg) in zip(cpu.modules[r].named_parameters(), gpu.modules[r].named_parameters()):
+                assert pg.grad.shape == pw.grad.shape, name
+                d = (pg.grad.detach().float().cpu() - pw.grad.detach().float())
+                assert float(d.norm()) <= 5e-2 * float(pw.grad.float().norm()) + 1e-3, (plan, r, name, float(d.norm()), float(pw.grad.float().norm()))
+        comm.check()
+        hap_b200.linear_ops.gemm_status()
+    finally:
+        comm.destroy()
