@@ -616,10 +616,11 @@ def run_lm(args):
     n_params = sum(p.numel() for p in model.parameters())
     if W == 1:
         dist = None
-        comm = hap_b200.local_comm(1, dev, stage_bytes=256 << 20, heap_bytes=320 << 20)
+        comm = hap_b200.single_comm(dev, stage_bytes=256 << 20, heap_bytes=320 << 20)
+        hap_b200.collectives.set_default_comm(comm)
         graph = P.emit_lm(model, args.lm_plan, ratios, 0, B)
-        world = LockstepWorld([torch.fx.GraphModule(model, graph)], hap_b200.LocalCollectives(comm))
-        step = lambda tok, tgt: world.step([(tok, tgt)])
+        worker = ProcessWorker(torch.fx.GraphModule(model, graph))
+        step = worker.step
     else:
         import torch.distributed as dist
         dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=W)

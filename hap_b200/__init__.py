@@ -6,12 +6,13 @@ the shard-extent rounding, and the CUDA sources behind them (``csrc/``, C ABI in
 """
 from . import _native
 from .sharding import sharding_round, sharding_round_
-from .comm import Comm, init_process_comm, local_comm
+from .comm import Comm, init_process_comm, local_comm, single_comm
 from . import collectives
 from .local import LocalCollectives
 from . import linear as linear_ops
 from .linear import linear
 from . import plan, spmd, attention
+from .einsum import einsum
 
-__all__ = ["Comm", "init_process_comm", "local_comm", "collectives", "LocalCollectives",
-           "sharding_round", "sharding_round_", "linear", "linear_ops", "plan", "spmd", "attention"]
+__all__ = ["Comm", "init_process_comm", "local_comm", "single_comm", "collectives", "LocalCollectives",
+           "sharding_round", "sharding_round_", "linear", "linear_ops", "plan", "spmd", "attention", "einsum"]

@@ -48,6 +48,7 @@ SIGNATURES = {
     "hapx_linear_forward": (_int, [_vp, _vp, _vp, _vp, _int, _int, _i64, _i64, _i64, _int, _vp]),
     "hapx_linear_dgrad": (_int, [_vp, _vp, _vp, _int, _int, _i64, _i64, _i64, _vp]),
     "hapx_linear_wgrad": (_int, [_vp, _vp, _vp, _vp, _int, _int, _i64, _i64, _i64, _vp]),
+    "hapx_gemm_batched": (_int, [_vp, _vp, _vp, _int, _int, _int] + [_i64] * 14 + [_vp]),
     "hapx_gemm_status": (_int, []),
     "hapx_attention_forward": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp]),
     "hapx_attention_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),

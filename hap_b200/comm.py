@@ -289,6 +289,20 @@ def local_comm(world: int, device=None, heap_bytes: Optional[int] = None, stage_
     return Comm(h.value, device)
 
 
+def single_comm(device=None, heap_bytes: Optional[int] = None, stage_bytes: Optional[int] = None) -> Comm:
+    """A one-rank-per-process communicator for a world of ONE process: no peers, no
+    ``torch.distributed``.  Every collective degenerates to local kernels (the 1-GPU point of the
+    scaling curve) while the program still runs through the same drop-in functions."""
+    if not torch.cuda.is_available():
+        raise RuntimeError("hap_b200 needs a CUDA device (there is no CPU fallback)")
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    heap, stage = _sizes(heap_bytes, stage_bytes)
+    torch.cuda.init()
+    h = C.c_void_p()
+    N.check(N.lib.hapx_comm_create(C.byref(h), 1, 0, device.index or 0, heap, stage))
+    return Comm(h.value, device)
+
+
 def init_process_comm(group=None, device=None, heap_bytes: Optional[int] = None,
                       stage_bytes: Optional[int] = None) -> Comm:
     """One rank per process.  ``torch.distributed`` must be initialised; it only carries the

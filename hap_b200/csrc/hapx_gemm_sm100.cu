@@ -57,6 +57,7 @@ struct Params {
   // direct-store path:
   int batch, batch_in;
   long long d_stride_in, d_stride_out;
+  int a_shared_out, b_shared_out;   // operand does not depend on b_out (e.g. expert weights): its maps get coordinate 0
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -370,6 +371,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int unit = blockIdx.x; unit < total_tiles && ok; unit += gridDim.x) {
         const int b = unit / tiles_per_batch, tile = unit - b * tiles_per_batch;
         const int bo = b / p.batch_in, bi = b - bo * p.batch_in;
+        const int boA = p.a_shared_out ? 0 : bo, boB = p.b_shared_out ? 0 : bo;
         const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * BN;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u)) { ok = false; break; }
@@ -377,18 +379,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mbar_expect_tx(full_bar(stage), C::STAGE_BYTES);
           const int k0 = kb * BK;
           if (!A_MN) {
-            tma_load_4d(sa, &tmA, k0, m0, bi, bo, full_bar(stage));         // box {64 k, 128 m}
+            tma_load_4d(sa, &tmA, k0, m0, bi, boA, full_bar(stage));        // box {64 k, 128 m}
           } else {
 #pragma unroll
             for (int i = 0; i < BM / 64; ++i)                                // boxes {64 m, 64 k}
-              tma_load_4d(sa + i * 8192u, &tmA, m0 + 64 * i, k0, bi, bo, full_bar(stage));
+              tma_load_4d(sa + i * 8192u, &tmA, m0 + 64 * i, k0, bi, boA, full_bar(stage));
           }
           if (!B_MN) {
-            tma_load_4d(sb, &tmB, k0, n0, bi, bo, full_bar(stage));         // box {64 k, BN n}
+            tma_load_4d(sb, &tmB, k0, n0, bi, boB, full_bar(stage));        // box {64 k, BN n}
           } else {
 #pragma unroll
             for (int i = 0; i < BN / 64; ++i)                                // boxes {64 n, 64 k}
-              tma_load_4d(sb + i * 8192u, &tmB, n0 + 64 * i, k0, bi, bo, full_bar(stage));
+              tma_load_4d(sb + i * 8192u, &tmB, n0 + 64 * i, k0, bi, boB, full_bar(stage));
           }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -593,6 +595,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int bt = unit / p.splits, sp = unit - bt * p.splits;
         const int b = bt / tiles_per_batch, tile = bt - b * tiles_per_batch;
         const int bo = b / p.batch_in, bi = b - bo * p.batch_in;
+        const int boA = p.a_shared_out ? 0 : bo, boB = p.b_shared_out ? 0 : bo;
         const int m0 = (tile % p.m_tiles) * (2 * BM) + (int)cta * BM;
         const int n0 = (tile / p.m_tiles) * BN + (int)cta * (BN / 2);
         const int kb_begin = sp * p.kb_per_split, kb_end = min(kb_begin + p.kb_per_split, p.k_blocks);
@@ -603,16 +606,16 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (cta == 0) mbar_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);   // bytes of both CTAs
           const int k0 = kb * BK;
           if (!A_MN) {
-            tma_load_4d_pair(sa, &tmA, k0, m0, bi, bo, leader_full);
+            tma_load_4d_pair(sa, &tmA, k0, m0, bi, boA, leader_full);
           } else {
 #pragma unroll
-            for (int i = 0; i < BM / 64; ++i) tma_load_4d_pair(sa + i * 8192u, &tmA, m0 + 64 * i, k0, bi, bo, leader_full);
+            for (int i = 0; i < BM / 64; ++i) tma_load_4d_pair(sa + i * 8192u, &tmA, m0 + 64 * i, k0, bi, boA, leader_full);
           }
           if (!B_MN) {
-            tma_load_4d_pair(sb, &tmB, k0, n0, bi, bo, leader_full);
+            tma_load_4d_pair(sb, &tmB, k0, n0, bi, boB, leader_full);
           } else {
 #pragma unroll
-            for (int i = 0; i < BN / 128; ++i) tma_load_4d_pair(sb + i * 8192u, &tmB, n0 + 64 * i, k0, bi, bo, leader_full);
+            for (int i = 0; i < BN / 128; ++i) tma_load_4d_pair(sb + i * 8192u, &tmB, n0 + 64 * i, k0, bi, boB, leader_full);
           }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -795,8 +798,8 @@ static int launch(const Operand& A, const Operand& B, const Operand& Dop, Params
   const int batch_out = p.batch / p.batch_in;
   CUtensorMap tmA, tmB, tmD;
   if (int e = make_out_map(&tmD, &p.tma_store, p.D, p.N, p.M, p.ldd, p.out_f32, p.batch_in, Dop.s_in, batch_out, Dop.s_out)) return e;
-  if (int e = make_map(&tmA, A, p.M, p.Kc, BM, p.batch_in, batch_out)) return e;
-  if (int e = make_map(&tmB, B, p.N, p.Kc, BN, p.batch_in, batch_out)) return e;
+  if (int e = make_map(&tmA, A, p.M, p.Kc, BM, p.batch_in, p.a_shared_out ? 1 : batch_out)) return e;
+  if (int e = make_map(&tmB, B, p.N, p.Kc, BN, p.batch_in, p.b_shared_out ? 1 : batch_out)) return e;
   p.m_tiles = (p.M + BM - 1) / BM;
   p.splits = 1; p.kb_per_split = 0; p.m_pad = 0;
   p.n_tiles = (p.N + BN - 1) / BN;
@@ -913,8 +916,8 @@ static int launch2(const Operand& A, const Operand& B, const Operand& Dop, Param
   const long long out_rows = p.splits > 1 ? (long long)p.splits * p.m_pad : p.M;
   if (int e = make_out_map(&tmD, &p.tma_store, p.D, p.N, out_rows, p.ldd, p.out_f32, p.batch_in, Dop.s_in, batch_out, Dop.s_out)) return e;
   if (p.splits > 1 && !p.tma_store) return fail(HAPX_ERR_EXTENT, "gemm: split-K needs an output width that is a multiple of 4");
-  if (int e = make_map(&tmA, A, p.M, p.Kc, BM, p.batch_in, batch_out)) return e;
-  if (int e = make_map(&tmB, B, p.N, p.Kc, C::BN / 2, p.batch_in, batch_out)) return e;
+  if (int e = make_map(&tmA, A, p.M, p.Kc, BM, p.batch_in, p.a_shared_out ? 1 : batch_out)) return e;
+  if (int e = make_map(&tmB, B, p.N, p.Kc, C::BN / 2, p.batch_in, p.b_shared_out ? 1 : batch_out)) return e;
   const long long units = (long long)tiles * p.splits * p.batch;
   if (units > 0x7fffffff) return fail(HAPX_ERR_EXTENT, "gemm: too many tiles");
   const int pairs = (int)std::max<long long>(1, std::min<long long>(units, max_clusters));
@@ -947,6 +950,8 @@ int gemm_bf16(const Operand& Dop, int out_f32, const Operand& A, const Operand& 
   p.out_f32 = out_f32;
   p.error = dev->error;
   p.batch = batch_in * batch_out; p.batch_in = batch_in; p.d_stride_in = Dop.s_in; p.d_stride_out = Dop.s_out;
+  p.a_shared_out = (batch_out > 1 && A.s_out == 0) ? 1 : 0;
+  p.b_shared_out = (batch_out > 1 && B.s_out == 0) ? 1 : 0;
   const bool a_mn = A.mn_major, b_mn = B.mn_major;
   // SM pairs (256 x 256 tiles, half the B traffic per SM) whenever there is more than one row tile
   static const bool pair_kernel = std::getenv("HAPX_GEMM_SINGLE_CTA") == nullptr;
@@ -973,24 +978,48 @@ int gemm_bf16(const Operand& Dop, int out_f32, const Operand& A, const Operand& 
   return fail(HAPX_ERR_ARGUMENT, "gemm: unsupported operand layout");
 }
 
-// Column sums of g[M,N] (the bias gradient), fp32 accumulation.
-__global__ void __launch_bounds__(256) colsum_bf16_kernel(const __nv_bfloat16* __restrict__ g, long long ldg, int M, int N,
-                                                          void* out, int out_f32) {
-  // one thread per column pair, grid.y slices of rows combined with atomics into an fp32 scratch-free path:
-  // each block owns 64 columns and ALL rows, so no atomics are needed
+// Column sums of g[M,N] (the bias gradient), fp32 accumulation, in two deterministic passes:
+// blocks of 64 columns x one slice of the rows write partial sums, a second kernel adds the
+// slices in order and casts.
+__global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16* __restrict__ g, long long ldg, int M, int N,
+                                                             int rows_per_slice, float* __restrict__ partial) {
   __shared__ float part[4][64];
   const int c = blockIdx.x * 64 + (threadIdx.x & 63);
   const int rg = threadIdx.x >> 6;
+  const int r0 = blockIdx.y * rows_per_slice, r1 = min(M, r0 + rows_per_slice);
   float acc = 0.f;
   if (c < N)
-    for (int r = rg; r < M; r += 4) acc += __bfloat162float(g[(long long)r * ldg + c]);
+    for (int r = r0 + rg; r < r1; r += 4) acc += __bfloat162float(g[(long long)r * ldg + c]);
   part[rg][threadIdx.x & 63] = acc;
   __syncthreads();
-  if (rg == 0 && c < N) {
-    const float s = part[0][threadIdx.x] + part[1][threadIdx.x] + part[2][threadIdx.x] + part[3][threadIdx.x];
-    if (out_f32) reinterpret_cast<float*>(out)[c] = s;
-    else reinterpret_cast<__nv_bfloat16*>(out)[c] = __float2bfloat16_rn(s);
-  }
+  if (rg == 0 && c < N)
+    partial[(long long)blockIdx.y * N + c] = (part[0][threadIdx.x] + part[1][threadIdx.x]) + (part[2][threadIdx.x] + part[3][threadIdx.x]);
+}
+__global__ void __launch_bounds__(256) colsum_final_kernel(const float* __restrict__ partial, int slices, int N, void* out, int out_f32) {
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= N) return;
+  float s = 0.f;
+  for (int i = 0; i < slices; ++i) s += partial[(long long)i * N + c];
+  if (out_f32) reinterpret_cast<float*>(out)[c] = s;
+  else reinterpret_cast<__nv_bfloat16*>(out)[c] = __float2bfloat16_rn(s);
+}
+
+int colsum_bf16(const void* g, long long m, long long n, void* out, int out_f32, cudaStream_t stream) {
+  if (n <= 0) return HAPX_OK;
+  if (m < 0 || m > 0x7fffffff || n > 0x7fffffff) return fail(HAPX_ERR_EXTENT, "linear_wgrad: extent out of range");
+  int device = 0;
+  HAPX_CUDA(cudaGetDevice(&device));
+  const int rows_per_slice = (int)std::max<long long>(128, (m + 65534) / 65535);
+  const int slices = (int)std::max<long long>(1, (m + rows_per_slice - 1) / rows_per_slice);
+  float* ws = nullptr;
+  if (int e = workspace(device, (size_t)slices * n * sizeof(float), &ws)) return e;
+  dim3 grid((unsigned)((n + 63) / 64), (unsigned)slices);
+  colsum_partial_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(g), n, (int)m, (int)n, rows_per_slice, ws);
+  HAPX_CUDA(cudaGetLastError());
+  colsum_final_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(ws, slices, (int)n, out, out_f32);
+  HAPX_CUDA(cudaGetLastError());
+  count_launch(2);
+  return HAPX_OK;
 }
 
 }  // namespace gemm
@@ -1054,14 +1083,20 @@ int hapx_linear_wgrad(void* dw, void* dbias, const void* g, const void* x, int d
     if (int e = gemm::gemm_bf16({dw, false, k, 0, 0}, out_dtype == HAPX_F32, {g, true, n, 0, 0}, {x, true, k, 0, 0}, nullptr, 0, n, k, m, 1, 1, stream))
       return e;
   }
-  if (dbias && n > 0) {
-    if (m < 0 || m > 0x7fffffff || n > 0x7fffffff) return fail(HAPX_ERR_EXTENT, "linear_wgrad: extent out of range");
-    gemm::colsum_bf16_kernel<<<(unsigned)((n + 63) / 64), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(g), n, (int)m, (int)n,
-                                                                             dbias, out_dtype == HAPX_F32);
-    HAPX_CUDA(cudaGetLastError());
-    count_launch();
-  }
+  if (dbias && n > 0) return gemm::colsum_bf16(g, m, n, dbias, out_dtype == HAPX_F32, stream);
   return HAPX_OK;
+}
+
+int hapx_gemm_batched(void* d, const void* a, const void* b, int out_dtype, int a_mn_major, int b_mn_major, int64_t m, int64_t n,
+                      int64_t kc, int64_t lda, int64_t ldb, int64_t ldd, int64_t batch_in, int64_t batch_out, int64_t a_stride_in,
+                      int64_t a_stride_out, int64_t b_stride_in, int64_t b_stride_out, int64_t d_stride_in, int64_t d_stride_out,
+                      hapx_stream stream) {
+  if (out_dtype != HAPX_BF16 && out_dtype != HAPX_F32) return fail(HAPX_ERR_DTYPE, "gemm_batched: output must be bfloat16 or float32");
+  if (batch_in < 1 || batch_out < 1 || batch_in * batch_out > 0x7fffffff) return fail(HAPX_ERR_EXTENT, "gemm_batched: bad batch counts");
+  if (a_mn_major && !b_mn_major) return fail(HAPX_ERR_ARGUMENT, "gemm_batched: A MN-major with B K-major is not built (swap the operands and transpose the result)");
+  return gemm::gemm_bf16({d, false, ldd, d_stride_in, d_stride_out}, out_dtype == HAPX_F32, {a, a_mn_major != 0, lda, a_stride_in, a_stride_out},
+                         {b, b_mn_major != 0, ldb, b_stride_in, b_stride_out}, nullptr, 0, m, n, kc, (int)batch_in, (int)batch_out,
+                         static_cast<cudaStream_t>(stream));
 }
 
 int hapx_gemm_status(void) {

@@ -1,0 +1,160 @@
+"""The four ``torch.einsum`` contractions of the reference's MoE layers on the batched tensor-core GEMM.
+
+The planner emits ``torch.einsum(code, a, b)`` nodes for exactly four codes (``hap.rs:2255-2260,
+2266-2276``; model side ``models.py:356-364``):
+
+    "bsd,bsec->becd"   dispatch : expert_inputs = x (x) dispatch_tensor
+    "edh,becd->bech"   expert FFN 1 (per-expert weights w1[e, d, h])
+    "ehd,bech->becd"   expert FFN 2 (per-expert weights w2[e, h, d])
+    "becd,bsec->bsd"   combine  : output = expert_outputs (x) combine_tensor
+
+:func:`einsum` has ``torch.einsum``'s call surface for these codes (bfloat16, CUDA) with autograd.
+Every contraction - forward and backward - is one call of ``hapx_gemm_batched``; operands are passed
+as strided views (an index is allowed to be the contiguous one on either side of the contraction),
+so the only copies are the (b, e) <-> (e, b) re-orderings that give the expert GEMMs b*c rows.
+The two expert contractions return a (b, e, c, .) VIEW of (e, b, c, .) memory; values are identical.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _native as N
+from .comm import _stream
+
+CODES = ("bsd,bsec->becd", "edh,becd->bech", "ehd,bech->becd", "becd,bsec->bsd")
+
+
+def _major(t: torch.Tensor, what: str):
+    """(mn_major, ld) of a [..., R, K] view: K-major when the last stride is 1, MN-major when the
+    second-to-last is."""
+    r, k = t.stride(-2), t.stride(-1)
+    if k == 1 and (t.shape[-2] == 1 or r >= t.shape[-1]):
+        return False, r if t.shape[-2] > 1 else max(r, t.shape[-1])
+    if r == 1 and (t.shape[-1] == 1 or k >= t.shape[-2]):
+        return True, k if t.shape[-1] > 1 else max(k, t.shape[-2])
+    raise ValueError(f"einsum: {what} has no unit stride in its last two dimensions (strides {t.stride()})")
+
+
+def bmm_nt(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """out[bo, bi, m, n] = sum_k a[bo, bi, m, k] * b[bo, bi, n, k] for 4-D bf16 views with arbitrary
+    (8-element aligned) strides; ``b`` may be expanded (stride 0) along ``bo``."""
+    if a.dim() != 4 or b.dim() != 4 or a.shape[:2] != b.shape[:2] or a.shape[3] != b.shape[3]:
+        raise ValueError(f"bmm_nt: incompatible shapes {tuple(a.shape)} and {tuple(b.shape)}")
+    for t in (a, b):
+        if not t.is_cuda:
+            raise RuntimeError(f"einsum: hap_b200 has no CPU path; tensor is on {t.device}")
+        if t.dtype != torch.bfloat16:
+            raise TypeError(f"einsum: bfloat16 only, got {t.dtype}")
+    bo, bi, m, k = a.shape
+    n = b.shape[2]
+    a_mn, lda = _major(a, "first operand")
+    b_mn, ldb = _major(b, "second operand")
+    for v, what in ((lda, "row pitch"), (ldb, "row pitch"), (a.stride(1) if bi > 1 else 0, "batch stride"),
+                    (a.stride(0) if bo > 1 else 0, "batch stride"), (b.stride(1) if bi > 1 else 0, "batch stride"),
+                    (b.stride(0) if bo > 1 else 0, "batch stride")):
+        if v % 8:
+            raise ValueError(f"einsum: operand {what} {v} is not a multiple of 8 elements")
+    out = torch.empty((bo, bi, m, n), dtype=out_dtype, device=a.device)
+    with torch.cuda.device(a.device):
+        N.check(N.lib.hapx_gemm_batched(out.data_ptr(), a.data_ptr(), b.data_ptr(), N.BF16 if out_dtype == torch.bfloat16 else N.F32,
+                                        int(a_mn), int(b_mn), m, n, k, lda, ldb, n, bi, bo,
+                                        a.stride(1) if bi > 1 else 0, a.stride(0) if bo > 1 else 0,
+                                        b.stride(1) if bi > 1 else 0, b.stride(0) if bo > 1 else 0,
+                                        m * n, bi * m * n, _stream(a.device)))
+    return out
+
+
+def _T(t):
+    return t.transpose(-1, -2)
+
+
+def _expert_major(t: torch.Tensor) -> torch.Tensor:
+    """(b, e, c, x) -> contiguous-in-memory (e, b*c, x); free when t is already a view of such memory."""
+    b, e, c, x = t.shape
+    return t.permute(1, 0, 2, 3).contiguous().view(e, b * c, x)
+
+
+class _Dispatch(torch.autograd.Function):          # "bsd,bsec->becd"
+    @staticmethod
+    def forward(ctx, x, disp):
+        b, s, d = x.shape
+        e, c = disp.shape[2], disp.shape[3]
+        x, disp = x.contiguous(), disp.contiguous()
+        ctx.save_for_backward(x, disp)
+        out = bmm_nt(_T(disp.view(b, 1, s, e * c)), _T(x.view(b, 1, s, d)))
+        return out.view(b, e, c, d)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, disp = ctx.saved_tensors
+        b, s, d = x.shape
+        e, c = disp.shape[2], disp.shape[3]
+        g2 = g.contiguous().view(b, 1, e * c, d)
+        dx = ddisp = None
+        if ctx.needs_input_grad[0]:
+            dx = bmm_nt(disp.view(b, 1, s, e * c), _T(g2)).view(b, s, d)
+        if ctx.needs_input_grad[1]:
+            ddisp = bmm_nt(x.view(b, 1, s, d), g2).view(b, s, e, c)
+        return dx, ddisp
+
+
+class _ExpertLinear(torch.autograd.Function):      # "edh,becd->bech" and "ehd,bech->becd"
+    @staticmethod
+    def forward(ctx, w, inp):
+        e, kin, kout = w.shape
+        b, _, c, _ = inp.shape
+        w = w.contiguous()
+        ie = _expert_major(inp)                                       # (e, b*c, kin)
+        ctx.save_for_backward(w, ie)
+        ctx.bc = (b, c)
+        out = bmm_nt(ie.view(1, e, b * c, kin), _T(w).unsqueeze(0))  # B(n = kout, k = kin) = w[e, kin, kout]^T
+        return out.view(e, b, c, kout).permute(1, 0, 2, 3)
+
+    @staticmethod
+    def backward(ctx, g):
+        w, ie = ctx.saved_tensors
+        e, kin, kout = w.shape
+        b, c = ctx.bc
+        ge = _expert_major(g)                                         # (e, b*c, kout)
+        dw = dinp = None
+        if ctx.needs_input_grad[0]:
+            dw = bmm_nt(_T(ie).unsqueeze(0), _T(ge).unsqueeze(0)).view(e, kin, kout)
+        if ctx.needs_input_grad[1]:
+            dinp = bmm_nt(ge.view(1, e, b * c, kout), w.unsqueeze(0)).view(e, b, c, kin).permute(1, 0, 2, 3)
+        return dw, dinp
+
+
+class _Combine(torch.autograd.Function):           # "becd,bsec->bsd"
+    @staticmethod
+    def forward(ctx, eo, comb):
+        b, e, c, d = eo.shape
+        s = comb.shape[1]
+        eo, comb = eo.contiguous(), comb.contiguous()
+        ctx.save_for_backward(eo, comb)
+        out = bmm_nt(comb.view(b, 1, s, e * c), _T(eo.view(b, 1, e * c, d)))
+        return out.view(b, s, d)
+
+    @staticmethod
+    def backward(ctx, g):
+        eo, comb = ctx.saved_tensors
+        b, e, c, d = eo.shape
+        s = comb.shape[1]
+        g2 = g.contiguous().view(b, 1, s, d)
+        deo = dcomb = None
+        if ctx.needs_input_grad[0]:
+            deo = bmm_nt(_T(comb.view(b, 1, s, e * c)), _T(g2)).view(b, e, c, d)
+        if ctx.needs_input_grad[1]:
+            dcomb = bmm_nt(g2, eo.view(b, 1, e * c, d)).view(b, s, e, c)
+        return deo, dcomb
+
+
+def einsum(code: str, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``torch.einsum(code, a, b)`` for the four MoE contractions of the reference."""
+    code = code.replace(" ", "")
+    if code == "bsd,bsec->becd":
+        return _Dispatch.apply(a, b)
+    if code in ("edh,becd->bech", "ehd,bech->becd"):
+        return _ExpertLinear.apply(a, b)
+    if code == "becd,bsec->bsd":
+        return _Combine.apply(a, b)
+    raise NotImplementedError(f"einsum: the planner only emits {CODES}; got {code!r}")

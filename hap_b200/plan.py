@@ -173,7 +173,7 @@ def _lm_forward(m, tokens, targets, ns, emit, ratios, rank, plan):
     x = method(x, "transpose", 0, 1)                                       # (S, B, E): the (L, N, E) layout
     x = call(operator.add, x, param("pos"))
     S = m.seqlen
-    mask = call(torch.triu, call(torch.full, (S, S), float("-inf"), device=_device_of(m)), 1)
+    mask = call(torch.triu, call(torch.full, (S, S), float("-inf"), device=_device_of(m), dtype=m.pos.dtype), 1)
     for i in range(m.nlayers):
         h = call(F.layer_norm, x, (E,), param(f"l{i}_ln1_w"), param(f"l{i}_ln1_b"))
         att = call(mha, query=h, key=h, value=h, embed_dim_to_check=E, num_heads=H,

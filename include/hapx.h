@@ -162,6 +162,19 @@ int hapx_linear_dgrad(void* dx, const void* g, const void* w, int dtype, int out
                       int64_t m, int64_t n, int64_t k, hapx_stream stream);
 int hapx_linear_wgrad(void* dw, void* dbias, const void* g, const void* x, int dtype, int out_dtype,
                       int64_t m, int64_t n, int64_t k, hapx_stream stream);
+/* Batched contraction behind the expert einsums the planner emits for MoE layers (torch.einsum
+ * codes "bsd,bsec->becd", "edh,becd->bech", "ehd,bech->becd", "becd,bsec->bsd": hap.rs:2255-2276,
+ * models.py:356-364) and their backward.  For every batch entry (b_out, b_in):
+ *     D[m, n] = sum_k A(m, k) * B(n, k)          bfloat16 operands, fp32 accumulation
+ * An operand is "K-major" when k is its contiguous index (element (r, k) at r * ld + k) or
+ * "MN-major" when m / n is (element (r, k) at k * ld + r); ld and the batch strides are in elements
+ * and must be multiples of 8.  A batch_out stride of 0 shares the operand across b_out (expert
+ * weights).  D is row-major with pitch ldd.  A MN-major together with B K-major is not built. */
+int hapx_gemm_batched(void* d, const void* a, const void* b, int out_dtype, int a_mn_major, int b_mn_major,
+                      int64_t m, int64_t n, int64_t kc, int64_t lda, int64_t ldb, int64_t ldd,
+                      int64_t batch_in, int64_t batch_out, int64_t a_stride_in, int64_t a_stride_out,
+                      int64_t b_stride_in, int64_t b_stride_out, int64_t d_stride_in, int64_t d_stride_out,
+                      hapx_stream stream);
 /* Synchronises the device and reports (then clears) an error left by a GEMM kernel whose
  * bounded barrier wait ran out. */
 int hapx_gemm_status(void);

@@ -1,0 +1,85 @@
+"""MoE einsums (dispatch, two expert FFN contractions, combine) on the batched tensor-core GEMM
+against float64 torch.einsum, forward and backward; shapes follow the MoE configuration
+(capacity 20, d_model 1024, expert FFN 4096) at reduced batch / expert counts, including the
+uneven per-GPU expert counts [7, 3, 2]."""
+import pytest
+import torch
+
+import hap_b200
+from hap_b200.einsum import einsum
+from oracle.einsum_math import einsum as oracle_einsum
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def close(got, want, what, tol=1e-2):
+    got, want = got.detach().double().cpu(), want.detach().double().cpu()
+    assert got.shape == want.shape, (what, got.shape, want.shape)
+    rms = float(want.pow(2).mean().sqrt()) + 1e-30
+    assert float((got - want).norm()) <= tol * float(want.norm()) + 1e-30, f"{what}: relative error {float((got - want).norm() / want.norm()):.3g}"
+    excess = (got - want).abs() - 4 * tol * (want.abs() + rms)
+    assert float(excess.max()) <= 0, f"{what}: {int((excess > 0).sum())} entries off (rms {rms:.3g})"
+
+
+def run(code, a, b, grad_a=True, grad_b=True):
+    ra, rb = a.double().requires_grad_(grad_a), b.double().requires_grad_(grad_b)
+    want = oracle_einsum(code, ra, rb)
+    g = torch.randn(want.shape, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)
+    (want * g.double()).sum().backward()
+    da, db = a.to(DEV).requires_grad_(grad_a), b.to(DEV).requires_grad_(grad_b)
+    got = einsum(code, da, db)
+    (got * g.to(DEV)).sum().backward()
+    hap_b200.linear_ops.gemm_status()
+    close(got, want, code)
+    if grad_a:
+        close(da.grad, ra.grad, code + " grad a", 2e-2)
+    if grad_b:
+        close(db.grad, rb.grad, code + " grad b", 2e-2)
+
+
+def gen(shape, seed, scale=1.0):
+    return (torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("b,s,e,c,d", [(4, 64, 4, 8, 64), (3, 512, 32, 20, 128), (2, 128, 8, 20, 1024)])
+def test_dispatch_and_combine(b, s, e, c, d):
+    x = gen((b, s, d), 1)
+    disp = (torch.rand(b, s, e, c, generator=torch.Generator().manual_seed(2)) < 0.05).to(torch.bfloat16)
+    run("bsd,bsec->becd", x, disp, grad_b=False)
+    eo = gen((b, e, c, d), 3)
+    comb = (torch.rand(b, s, e, c, generator=torch.Generator().manual_seed(4)) * disp.float()).to(torch.bfloat16)
+    run("becd,bsec->bsd", eo, comb)
+
+
+@pytest.mark.parametrize("b,e,c,d,h", [(4, 4, 8, 64, 128), (16, 7, 20, 256, 512), (16, 3, 20, 1024, 4096), (8, 2, 20, 1024, 4096)])
+def test_expert_ffn(b, e, c, d, h):
+    w1 = gen((e, d, h), 5, d ** -0.5)
+    inp = gen((b, e, c, d), 6)
+    run("edh,becd->bech", w1, inp)
+    w2 = gen((e, h, d), 7, h ** -0.5)
+    hid = gen((b, e, c, h), 8)
+    run("ehd,bech->becd", w2, hid)
+
+
+def test_moe_block_chain_matches_oracle():
+    """dispatch -> FFN1 -> relu -> FFN2 -> combine, as in models.py:356-364, through views."""
+    b, s, e, c, d, h = 4, 128, 4, 20, 128, 256
+    x, w1, w2 = gen((b, s, d), 1), gen((e, d, h), 2, d ** -0.5), gen((e, h, d), 3, h ** -0.5)
+    disp = (torch.rand(b, s, e, c, generator=torch.Generator().manual_seed(4)) < 0.05).to(torch.bfloat16)
+    comb = (disp.float() * 0.5).to(torch.bfloat16)
+
+    def block(f, x, w1, w2, disp, comb):
+        ei = f("bsd,bsec->becd", x, disp)
+        hh = torch.relu(f("edh,becd->bech", w1, ei))
+        eo = f("ehd,bech->becd", w2, hh)
+        return f("becd,bsec->bsd", eo, comb)
+
+    want = block(oracle_einsum, x, w1, w2, disp, comb)
+    got = block(einsum, x.to(DEV), w1.to(DEV), w2.to(DEV), disp.to(DEV), comb.to(DEV))
+    close(got, want, "moe block", 3e-2)
+
+
+def test_unsupported_code_raises():
+    with pytest.raises(NotImplementedError):
+        einsum("ab,bc->ac", torch.ones(8, 8, device=DEV, dtype=torch.bfloat16), torch.ones(8, 8, device=DEV, dtype=torch.bfloat16))
