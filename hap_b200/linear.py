@@ -66,11 +66,27 @@ def linear_forward(x2: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor],
     return y
 
 
+def _pad_dim(t: torch.Tensor, dim: int, to: int) -> torch.Tensor:
+    """Zero-extend ``t`` on ``dim`` to extent ``to`` with the package's own re-sharding kernel
+    (the backward of dynamic_slice writes a shard into a zeroed larger tensor)."""
+    from .comm import dynamic_slice_backward
+    return dynamic_slice_backward(t, dim, [t.shape[dim], to - t.shape[dim]], 0)
+
+
+def _round8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
 def linear_dgrad(g2: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     _check(g2, "linear backward"), _check(w, "linear backward"), _same(g2, w)
     out_dtype = _default_out(g2, out_dtype)
     m, n = g2.shape
     k = w.shape[1]
+    if g2.dtype == torch.bfloat16 and n % 8 and k % 8 == 0:
+        # a column-parallel shard whose width is not a multiple of 8 (e.g. 2458 of 4096): the tensor
+        # maps need 16-byte row pitches, so contract over a zero-extended copy of g and w
+        n8 = _round8(n)
+        return linear_dgrad(_pad_dim(g2, 1, n8), _pad_dim(w, 0, n8), out_dtype)
     if g2.dtype == torch.bfloat16 and (n % 8 or k % 8):
         raise ValueError(f"linear backward: bfloat16 features must be multiples of 8 (got n={n}, k={k})")
     dx = torch.empty((m, k), dtype=out_dtype, device=g2.device)
@@ -86,6 +102,13 @@ def linear_wgrad(g2: torch.Tensor, x2: torch.Tensor, need_weight: bool = True, n
     out_dtype = _default_out(g2, out_dtype)
     m, n = g2.shape
     k = x2.shape[1]
+    if g2.dtype == torch.bfloat16 and n % 8 and k % 8 == 0:
+        # see linear_dgrad: compute the gradient of the zero-extended shard, then cut the extension off
+        from .comm import dynamic_slice
+        n8 = _round8(n)
+        dw8, db8 = linear_wgrad(_pad_dim(g2, 1, n8), x2, need_weight, need_bias, out_dtype)
+        cut = lambda t: dynamic_slice(t, 0, [n, n8 - n], 0) if t is not None else None
+        return cut(dw8), cut(db8)
     if g2.dtype == torch.bfloat16 and (n % 8 or k % 8):
         raise ValueError(f"linear backward: bfloat16 features must be multiples of 8 (got n={n}, k={k})")
     dw = torch.empty((n, k), dtype=out_dtype, device=g2.device) if need_weight else None

@@ -58,7 +58,8 @@ def test_fused_epilogues(act):
 
 
 BWD_SHAPES = [(38, 4096, 1024), (26, 1024, 4096), (300, 520, 72), (1000, 768, 3072), (2048, 2304, 768), (8, 8, 8),
-              (77, 1000, 768), (4096, 768, 768), (8192, 256, 520)]      # the last ones take the split-K path in wgrad
+              (77, 1000, 768), (4096, 768, 768), (8192, 256, 520),      # the last ones take the split-K path in wgrad
+              (64, 2458, 1024), (64, 410, 4096)]                       # column-parallel shards, width not a multiple of 8
 
 
 @pytest.mark.parametrize("m,n,k", BWD_SHAPES)

@@ -109,3 +109,61 @@ def test_drop_in_collectives_across_gpus(world):
         pytest.skip(f"needs {world} GPUs")
     with tempfile.TemporaryDirectory() as d:
         mp.spawn(_worker, args=(world, os.path.join(d, "store")), nprocs=world, join=True)
+
+
+def _spmd_worker(rank, world, store):
+    """The synthesized programs as real one-process-per-GPU runs (ProcessWorker, drop-in collectives
+    over NVLink) against their CPU lockstep replay, which every rank recomputes for itself."""
+    sys.path.insert(0, ROOT)
+    import copy
+    import torch.distributed as dist
+    import hap_b200
+    from hap_b200 import collectives as col
+    from hap_b200 import plan as P
+    from hap_b200.spmd import LockstepWorld, ProcessWorker
+    from oracle.lockstep_backend import OracleCollectives
+    from tests import spmd_common as C
+    torch.cuda.set_device(rank)
+    dev = f"cuda:{rank}"
+    dist.init_process_group("gloo", rank=rank, world_size=world, init_method=f"file://{store}")
+    comm = hap_b200.init_process_comm(stage_bytes=64 << 20, heap_bytes=96 << 20)
+    col.set_default_comm(comm)
+    ratios = [.22, .18, .15, .13, .11, .09, .07, .05][:world]
+    ratios = [x / sum(ratios) for x in ratios]
+    C.RATIOS = ratios
+    reduce = lambda t: comm.all_reduce([t.reshape(1).float()])[0]
+    # fp32 MLP, both plans
+    for plan in ("dp", "tp"):
+        model, dims = C.reference_model()
+        x, y = C.batch(dims)
+        cpu = LockstepWorld(C.rank_modules(model, plan, C.cpu_namespace(), world=world), OracleCollectives())
+        want = [float(cpu.step([(x, y)] * world)) for _ in range(2)]
+        m = copy.deepcopy(model).to(dev)
+        worker = ProcessWorker(torch.fx.GraphModule(m, P.emit_mlp(m, plan, ratios, rank, C.BATCH)), reduce_loss=reduce)
+        got = [float(worker.step(x.to(dev), y.to(dev))) for _ in range(2)]
+        for a, b in zip(got, want):
+            assert abs(a - b) <= 1e-5 * abs(b), (plan, got, want)
+        for (name, pw), (_, pg) in zip(cpu.modules[rank].named_parameters(), worker.module.named_parameters()):
+            assert float((pg.detach().cpu() - pw.detach()).abs().max()) <= 0.05 * 2 * 5e-4, (plan, name)
+    # bf16 Transformer LM, ZeRO-style sharded weights
+    model = C.lm_model(torch.bfloat16)
+    tok, tgt = C.lm_batch()
+    cpu = LockstepWorld(C.lm_rank_modules(model, "dp_zero", C.lm_cpu_namespace(), world=world), OracleCollectives())
+    want = float(cpu.step([(tok, tgt)] * world))
+    m = copy.deepcopy(model).to(dev)
+    worker = ProcessWorker(torch.fx.GraphModule(m, P.emit_lm(m, "dp_zero", ratios, rank, C.LM_BATCH)), reduce_loss=reduce)
+    got = float(worker.step(tok.to(dev), tgt.to(dev)))
+    assert abs(got - want) <= 1e-2 * abs(want), (got, want)
+    comm.check()
+    hap_b200.linear_ops.gemm_status()
+    dist.barrier()
+    comm.destroy()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_spmd_programs_across_gpus(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_spmd_worker, args=(world, os.path.join(d, "store")), nprocs=world, join=True)
