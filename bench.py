@@ -616,20 +616,20 @@ def run_lm(args):
     n_params = sum(p.numel() for p in model.parameters())
     if W == 1:
         dist = None
-        comm = hap_b200.single_comm(dev, stage_bytes=256 << 20, heap_bytes=320 << 20)
+        comm = hap_b200.single_comm(dev, stage_bytes=256 << 20, heap_bytes=(320 << 20) + 2 * n_params)
         hap_b200.collectives.set_default_comm(comm)
         graph = P.emit_lm(model, args.lm_plan, ratios, 0, B)
-        worker = ProcessWorker(torch.fx.GraphModule(model, graph))
+        worker = ProcessWorker(torch.fx.GraphModule(model, graph), comm=comm)
         step = worker.step
     else:
         import torch.distributed as dist
         dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=W)
-        comm = hap_b200.init_process_comm(stage_bytes=256 << 20, heap_bytes=320 << 20)
+        comm = hap_b200.init_process_comm(stage_bytes=256 << 20, heap_bytes=(320 << 20) + 2 * n_params)
         hap_b200.collectives.set_default_comm(comm)
         graph = P.emit_lm(model, args.lm_plan, ratios, rank, B)
         # the reference sums the partial losses with dist.reduce (worker.py:63-64); here through the package's all_reduce
         worker = ProcessWorker(torch.fx.GraphModule(model, graph),
-                               reduce_loss=lambda t: comm.all_reduce([t.reshape(1).float()])[0])
+                               reduce_loss=lambda t: comm.all_reduce([t.reshape(1).float()])[0], comm=comm)
         step = worker.step
     g = torch.Generator().manual_seed(2024)
     tok_h = torch.randint(0, 33278, (B, 256), generator=g).pin_memory()

@@ -16,7 +16,7 @@ from typing import Optional
 import torch
 
 from . import _native as N
-from .comm import _stream
+from .comm import _on_device, _stream
 from .linear import linear
 
 
@@ -48,7 +48,7 @@ class _Attention(torch.autograd.Function):
         out = torch.empty((L, n, E), dtype=torch.bfloat16, device=qkv.device)
         probs = torch.empty((n * num_heads, L, Lp), dtype=torch.bfloat16, device=qkv.device)
         scores = torch.empty((n * num_heads, L, Lp), dtype=torch.float32, device=qkv.device)
-        with torch.cuda.device(qkv.device):
+        with _on_device(qkv.device):
             N.check(N.lib.hapx_attention_forward(out.data_ptr(), probs.data_ptr(), scores.data_ptr(), qkv.data_ptr(), L, n,
                                                  num_heads, D, int(causal), mask.data_ptr() if mask is not None else None,
                                                  _stream(qkv.device)))
@@ -64,7 +64,7 @@ class _Attention(torch.autograd.Function):
         dqkv = torch.empty_like(qkv)
         dscores = torch.empty(probs.shape, dtype=torch.float32, device=qkv.device)
         ds = torch.empty_like(probs)
-        with torch.cuda.device(qkv.device):
+        with _on_device(qkv.device):
             N.check(N.lib.hapx_attention_backward(dqkv.data_ptr(), dscores.data_ptr(), ds.data_ptr(), dout.data_ptr(),
                                                   probs.data_ptr(), qkv.data_ptr(), L, n, H, D, _stream(qkv.device)))
         return dqkv, None, None, None

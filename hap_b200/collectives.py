@@ -29,6 +29,15 @@ from . import _native as N
 from . import comm as _comm
 
 _default: Optional[_comm.Comm] = None
+_defer_replicate = False
+
+
+def defer_replicate(on: bool) -> None:
+    """While on, the backward of :func:`replicate` hands the gradient through unchanged.  The step
+    driver turns this on when it reduces the gradients of all replicated parameters itself, as one
+    all_reduce over a flat buffer, instead of one all_reduce per parameter (collectives.py:176-180)."""
+    global _defer_replicate
+    _defer_replicate = bool(on)
 
 
 def set_default_comm(c: Optional[_comm.Comm]) -> None:
@@ -112,6 +121,8 @@ class _Replicate(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output):
+        if _defer_replicate:
+            return grad_output
         return get_default_comm().all_reduce([grad_output])[0]
 
 

@@ -50,6 +50,24 @@ def _stream(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+class _on_device:
+    """``with torch.cuda.device(d)`` costs several microseconds per use; switch only when the
+    tensor's device is not the current one (never, with one process per GPU)."""
+
+    def __init__(self, device):
+        self._ctx = None
+        if device.index is not None and device.index != torch.cuda.current_device():
+            self._ctx = torch.cuda.device(device)
+
+    def __enter__(self):
+        if self._ctx is not None:
+            self._ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self._ctx is not None:
+            self._ctx.__exit__(*exc)
+
+
 class _RawDeviceMemory:
     """Exposes a raw device range through ``__cuda_array_interface__`` so torch can view it."""
 
@@ -247,7 +265,7 @@ def dynamic_slice(tensor: torch.Tensor, dim: int, lengths: Sequence[int], rank: 
     shape = list(t.shape)
     shape[dim] = lengths[rank]
     out = torch.empty(shape, dtype=t.dtype, device=t.device)
-    with torch.cuda.device(t.device):
+    with _on_device(t.device):
         N.check(N.lib.hapx_dynamic_slice(out.data_ptr(), t.data_ptr(), dtype_code(t.dtype), _prod(t.shape[:dim]),
                                          _prod(t.shape[dim + 1:]), N.i64_array(lengths), len(lengths), int(rank),
                                          _stream(t.device)))
@@ -261,7 +279,7 @@ def dynamic_slice_backward(grad: torch.Tensor, dim: int, lengths: Sequence[int],
     shape = list(g.shape)
     shape[dim] = sum(lengths)
     out = torch.empty(shape, dtype=g.dtype, device=g.device)
-    with torch.cuda.device(g.device):
+    with _on_device(g.device):
         N.check(N.lib.hapx_dynamic_slice_backward(out.data_ptr(), g.data_ptr(), dtype_code(g.dtype), _prod(g.shape[:dim]),
                                                   _prod(g.shape[dim + 1:]), N.i64_array(lengths), len(lengths), int(rank),
                                                   _stream(g.device)))
@@ -350,7 +368,7 @@ def local_all_reduce_noalloc(inputs: Sequence[torch.Tensor], outputs: Sequence[t
             raise ValueError("local_all_reduce_noalloc: tensors must be contiguous, equally sized and on one device")
     if any(t.dtype != ref.dtype for t in inputs) or any(o.dtype != outputs[0].dtype for o in outputs):
         raise ValueError("local_all_reduce_noalloc: mixed dtypes")
-    with torch.cuda.device(ref.device):
+    with _on_device(ref.device):
         N.check(N.lib.hapx_local_all_reduce_noalloc(len(inputs), N.ptr_array([o.data_ptr() for o in outputs]),
                                                     N.ptr_array([t.data_ptr() for t in inputs]), dtype_code(ref.dtype),
                                                     dtype_code(outputs[0].dtype), float(scale), ref.numel(),

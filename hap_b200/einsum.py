@@ -19,7 +19,7 @@ from __future__ import annotations
 import torch
 
 from . import _native as N
-from .comm import _stream
+from .comm import _on_device, _stream
 
 CODES = ("bsd,bsec->becd", "edh,becd->bech", "ehd,bech->becd", "becd,bsec->bsd")
 
@@ -55,7 +55,7 @@ def bmm_nt(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype = torch.bflo
         if v % 8:
             raise ValueError(f"einsum: operand {what} {v} is not a multiple of 8 elements")
     out = torch.empty((bo, bi, m, n), dtype=out_dtype, device=a.device)
-    with torch.cuda.device(a.device):
+    with _on_device(a.device):
         N.check(N.lib.hapx_gemm_batched(out.data_ptr(), a.data_ptr(), b.data_ptr(), N.BF16 if out_dtype == torch.bfloat16 else N.F32,
                                         int(a_mn), int(b_mn), m, n, k, lda, ldb, n, bi, bo,
                                         a.stride(1) if bi > 1 else 0, a.stride(0) if bo > 1 else 0,

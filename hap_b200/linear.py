@@ -13,7 +13,7 @@ from typing import Optional
 import torch
 
 from . import _native as N
-from .comm import _stream
+from .comm import _on_device, _stream
 
 _EPILOGUES = {"none": 0, "relu": 1, "gelu": 2, "sigmoid": 3}
 
@@ -59,7 +59,7 @@ def linear_forward(x2: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor],
     if x2.dtype == torch.bfloat16 and k % 8:
         raise ValueError(f"linear: bfloat16 in_features must be a multiple of 8 (got {k})")
     y = torch.empty((m, n), dtype=out_dtype, device=x2.device)
-    with torch.cuda.device(x2.device):
+    with _on_device(x2.device):
         N.check(N.lib.hapx_linear_forward(y.data_ptr(), x2.data_ptr(), w.data_ptr(), b.data_ptr() if b is not None else None,
                                           _out_code(x2.dtype), _out_code(out_dtype), m, n, k, _EPILOGUES[epilogue],
                                           _stream(x2.device)))
@@ -90,7 +90,7 @@ def linear_dgrad(g2: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dt
     if g2.dtype == torch.bfloat16 and (n % 8 or k % 8):
         raise ValueError(f"linear backward: bfloat16 features must be multiples of 8 (got n={n}, k={k})")
     dx = torch.empty((m, k), dtype=out_dtype, device=g2.device)
-    with torch.cuda.device(g2.device):
+    with _on_device(g2.device):
         N.check(N.lib.hapx_linear_dgrad(dx.data_ptr(), g2.data_ptr(), w.data_ptr(), _out_code(g2.dtype), _out_code(out_dtype),
                                         m, n, k, _stream(g2.device)))
     return dx
@@ -113,7 +113,7 @@ def linear_wgrad(g2: torch.Tensor, x2: torch.Tensor, need_weight: bool = True, n
         raise ValueError(f"linear backward: bfloat16 features must be multiples of 8 (got n={n}, k={k})")
     dw = torch.empty((n, k), dtype=out_dtype, device=g2.device) if need_weight else None
     db = torch.empty((n,), dtype=out_dtype, device=g2.device) if need_bias else None
-    with torch.cuda.device(g2.device):
+    with _on_device(g2.device):
         N.check(N.lib.hapx_linear_wgrad(dw.data_ptr() if need_weight else None, db.data_ptr() if need_bias else None,
                                         g2.data_ptr(), x2.data_ptr(), _out_code(g2.dtype), _out_code(out_dtype), m, n, k,
                                         _stream(g2.device)))

@@ -154,6 +154,13 @@ def _spmd_worker(rank, world, store):
     worker = ProcessWorker(torch.fx.GraphModule(m, P.emit_lm(m, "dp_zero", ratios, rank, C.LM_BATCH)), reduce_loss=reduce)
     got = float(worker.step(tok.to(dev), tgt.to(dev)))
     assert abs(got - want) <= 1e-2 * abs(want), (got, want)
+    # the same step with the replicated parameters' gradients reduced as one flat bucket: same bits
+    m2 = copy.deepcopy(model).to(dev)
+    bucketed = ProcessWorker(torch.fx.GraphModule(m2, P.emit_lm(m2, "dp_zero", ratios, rank, C.LM_BATCH)), reduce_loss=reduce, comm=comm)
+    got2 = float(bucketed.step(tok.to(dev), tgt.to(dev)))
+    assert got2 == got
+    for (name, pa), (_, pb) in zip(worker.module.named_parameters(), bucketed.module.named_parameters()):
+        assert torch.equal(pa, pb), name
     comm.check()
     hap_b200.linear_ops.gemm_status()
     dist.barrier()

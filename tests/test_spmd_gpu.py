@@ -104,3 +104,30 @@ def test_language_model_step_matches_cpu_replay(plan):
         hap_b200.linear_ops.gemm_status()
     finally:
         comm.destroy()
+
+
+def test_bucketed_gradient_reduction_gives_the_same_step():
+    """ProcessWorker on a world of one: one flat all_reduce over the replicated parameters' gradients
+    (views of a heap buffer) must leave exactly the parameters the per-parameter all_reduces leave."""
+    import copy
+    from hap_b200 import plan as P
+    from hap_b200.spmd import ProcessWorker
+    model = C.lm_model(torch.bfloat16).to(DEV)
+    tok, tgt = (t.to(DEV) for t in C.lm_batch())
+    comm = hap_b200.single_comm(DEV, stage_bytes=16 << 20, heap_bytes=48 << 20)
+    hap_b200.collectives.set_default_comm(comm)
+    try:
+        workers = []
+        for use_bucket in (False, True):
+            m = copy.deepcopy(model)
+            graph = P.emit_lm(m, "dp", [1.0], 0, C.LM_BATCH)
+            workers.append(ProcessWorker(torch.fx.GraphModule(m, graph), comm=comm if use_bucket else None))
+        for _ in range(2):
+            a, b = (float(w.step(tok, tgt)) for w in workers)
+            assert a == b
+        for (name, pa), (_, pb) in zip(workers[0].module.named_parameters(), workers[1].module.named_parameters()):
+            assert torch.equal(pa, pb), name
+        comm.check()
+    finally:
+        hap_b200.collectives.set_default_comm(None)
+        comm.destroy()
