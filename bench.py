@@ -635,6 +635,8 @@ def run_lm(args):
     tok_h = torch.randint(0, 33278, (B, 256), generator=g).pin_memory()
     tgt_h = torch.randint(0, 33278, (B, 256), generator=g).pin_memory()
     tok, tgt = tok_h.to(dev), tgt_h.to(dev)
+    if args.lm_graph:
+        step = worker.capture(tok, tgt)
 
     def barrier():
         if dist is not None:
@@ -687,6 +689,7 @@ def run_lm(args):
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"Transformer LM training step ({L} layers, d_model 768, 12 heads, FFN 3072, pre-LN, vocab 33280, seq 256), "
                                f"plan {args.lm_plan}, global batch {B} split {lb}", "parameters": n_params,
+                   "executor": "CUDA graph of the whole iteration" if args.lm_graph else "eager fx GraphModule",
                    "l2": "activations and weights of a step exceed L2 by far", "loss": loss_host},
         "roofline": {"bound": "tensor", "kernel": "gemm2_bf16_kernel (all linear / attention contractions of the busiest rank)",
                      "achieved": achieved, "peak": peaks["bf16_tflops_sustained"] if "bf16_tflops_sustained" in peaks else peaks["bf16_tflops"],
@@ -744,6 +747,7 @@ def main():
     ap.add_argument("--lm-batch", type=int, default=32, help="samples per GPU")
     ap.add_argument("--lm-layers", type=int, default=12)
     ap.add_argument("--lm-plan", default="dp_zero", choices=["dp", "dp_zero"])
+    ap.add_argument("--lm-graph", action="store_true", help="capture the training step into a CUDA graph")
     ap.add_argument("--gemm-tokens", type=int, default=8192)
     args = ap.parse_args()
     if args.impl == "reference":

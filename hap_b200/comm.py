@@ -102,6 +102,9 @@ class Comm:
     def set_timeout_ms(self, ms: int) -> None:
         N.check(N.lib.hapx_comm_set_timeout_ms(self._h, int(ms)))
 
+    def set_stream_ordering(self, on: bool) -> None:
+        N.check(N.lib.hapx_comm_set_stream_ordering(self._h, int(bool(on))))
+
     def set_max_ctas(self, ctas: int) -> None:
         N.check(N.lib.hapx_comm_set_max_ctas(self._h, int(ctas)))
 

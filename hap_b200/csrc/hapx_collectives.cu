@@ -621,10 +621,12 @@ struct CallScope {  // orders calls issued on different streams; one collective 
   cudaStream_t stream;
   int enter() {
     HAPX_CUDA(cudaSetDevice(c->device));
+    if (!c->stream_ordering) return HAPX_OK;
     if (c->any_launched && c->last_stream != stream) HAPX_CUDA(cudaStreamWaitEvent(stream, c->last_done, 0));
     return HAPX_OK;
   }
   int leave() {
+    if (!c->stream_ordering) return HAPX_OK;
     HAPX_CUDA(cudaEventRecord(c->last_done, stream));
     c->last_stream = stream;
     c->any_launched = true;
@@ -763,7 +765,7 @@ int hapx_all_reduce(hapx_comm* c, void* const* dst, const void* const* src, int 
         HAPX_CUDA(cudaSetDevice(c->device));
         const long long vecs = (long long)((in_bytes + 15) / 16);
         int grid = (int)std::max<long long>(1, std::min<long long>((vecs + kThreads - 1) / kThreads, (long long)c->sm_count * 8));
-        if (c->any_launched && c->last_stream != stream) HAPX_CUDA(cudaStreamWaitEvent(stream, c->last_done, 0));
+        if (c->stream_ordering && c->any_launched && c->last_stream != stream) HAPX_CUDA(cudaStreamWaitEvent(stream, c->last_done, 0));
         stage_copy_kernel<<<grid, kThreads, 0, stream>>>(d, static_cast<const char*>(src[i]), (long long)in_bytes);
         HAPX_CUDA(cudaGetLastError());
         count_launch();

@@ -184,6 +184,13 @@ int hapx_comm_set_max_ctas(hapx_comm* c, int ctas) {
   return HAPX_OK;
 }
 
+int hapx_comm_set_stream_ordering(hapx_comm* c, int on) {
+  if (!c) return fail(HAPX_ERR_ARGUMENT, "null communicator");
+  c->stream_ordering = on != 0;
+  c->any_launched = false;
+  return HAPX_OK;
+}
+
 int hapx_comm_check(hapx_comm* c) {
   if (!c) return fail(HAPX_ERR_ARGUMENT, "null communicator");
   HAPX_CUDA(cudaSetDevice(c->device));

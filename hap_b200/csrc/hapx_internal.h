@@ -76,4 +76,5 @@ struct hapx_comm {
   cudaEvent_t last_done = nullptr;
   cudaStream_t last_stream = nullptr;
   bool any_launched = false;
+  bool stream_ordering = true;      // order calls issued on different streams with an event (off while a CUDA graph is captured)
 };

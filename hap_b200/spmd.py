@@ -147,6 +147,38 @@ class ProcessWorker:
             if id(p) not in bucketed:
                 p.grad = None
 
+    def capture(self, *example_inputs, warmup: int = 3):
+        """Record one whole iteration (zero_grad ... optimizer step) into a CUDA graph and return a
+        callable ``replay(*inputs) -> total loss`` that copies the inputs into the graph's static
+        buffers and launches the graph: the per-node Python dispatch of the eager step (the
+        reference's hot loop (i), ``worker.py:58-83``) disappears.  Needs a capturable optimizer
+        (this re-creates Adam with ``capturable=True``) and at least two collectives per iteration;
+        all ranks must replay the same number of times."""
+        lr = self.optimizer.param_groups[0]["lr"]
+        self.optimizer = torch.optim.Adam(self.module.parameters(), lr=lr, capturable=True)
+        static_in = [t.clone() for t in example_inputs]
+        if self.comm is not None:
+            self.comm.set_stream_ordering(False)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                self.step(*static_in)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            static_out = self.step(*static_in)
+        self._graph = graph
+
+        def replay(*inputs):
+            for dst, src in zip(static_in, inputs):
+                dst.copy_(src, non_blocking=True)
+            graph.replay()
+            return static_out
+
+        return replay
+
     def step(self, *inputs) -> torch.Tensor:
         from . import collectives
         self.zero_grad()

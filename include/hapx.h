@@ -100,6 +100,10 @@ int hapx_comm_heap(hapx_comm* c, int local_index, void** base, size_t* bytes);
 int hapx_comm_set_timeout_ms(hapx_comm* c, int ms);
 /* Cap the CTAs per rank that a collective launches (0 = one full wave). */
 int hapx_comm_set_max_ctas(hapx_comm* c, int ctas);
+/* Calls issued on different streams are ordered with an event by default.  Turn that off
+ * (on = 0) while the caller captures its stream into a CUDA graph and keeps all calls on that one
+ * stream: event records / waits against streams outside the capture would invalidate it. */
+int hapx_comm_set_stream_ordering(hapx_comm* c, int on);
 /* Synchronises the device and reports (then clears) the status words the kernels
  * leave behind: 0, or HAPX_ERR_PEER_TIMEOUT with details in hapx_last_error(). */
 int hapx_comm_check(hapx_comm* c);

@@ -131,3 +131,31 @@ def test_bucketed_gradient_reduction_gives_the_same_step():
     finally:
         hap_b200.collectives.set_default_comm(None)
         comm.destroy()
+
+
+def test_cuda_graph_replay_follows_the_eager_step():
+    """The whole iteration captured into a CUDA graph (ProcessWorker.capture) must walk the same loss
+    trajectory as the eager step."""
+    import copy
+    from hap_b200 import plan as P
+    from hap_b200.spmd import ProcessWorker
+    model = C.lm_model(torch.bfloat16).to(DEV)
+    tok, tgt = (t.to(DEV) for t in C.lm_batch())
+    comm = hap_b200.single_comm(DEV, stage_bytes=16 << 20, heap_bytes=48 << 20)
+    hap_b200.collectives.set_default_comm(comm)
+    try:
+        m1, m2 = copy.deepcopy(model), copy.deepcopy(model)
+        eager = ProcessWorker(torch.fx.GraphModule(m1, P.emit_lm(m1, "dp_zero", [1.0], 0, C.LM_BATCH)), comm=comm)
+        graphed = ProcessWorker(torch.fx.GraphModule(m2, P.emit_lm(m2, "dp_zero", [1.0], 0, C.LM_BATCH)), comm=comm)
+        replay = graphed.capture(tok, tgt, warmup=3)
+        want = [float(eager.step(tok, tgt)) for _ in range(6)]
+        got = [float(replay(tok, tgt)) for _ in range(3)]
+        comm.set_stream_ordering(True)
+        for a, b in zip(got, want[3:]):
+            assert abs(a - b) <= 1e-2 * abs(b), (got, want)
+        assert got[-1] < want[0]          # it is training
+        comm.check()
+        hap_b200.linear_ops.gemm_status()
+    finally:
+        hap_b200.collectives.set_default_comm(None)
+        comm.destroy()
