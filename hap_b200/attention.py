@@ -21,19 +21,22 @@ from .linear import linear
 
 
 def _classify_mask(mask: Optional[torch.Tensor], L: int):
-    """(causal flag, additive fp32 mask or None).  The LM's mask (-inf strictly above the diagonal,
-    0 elsewhere, ``models.py:72``) is recognised and handled without reading a mask tensor."""
+    """(causal flag, additive fp32 mask or None).  A mask tensor is always applied as an additive
+    (L, L) fp32 term inside the softmax kernel (-inf entries mask, as with the reference's LM mask,
+    ``models.py:72``); no value of it is inspected on the host, so nothing synchronises.  The string
+    ``"causal"`` selects the built-in causal masking without a tensor."""
     if mask is None:
         return 0, None
+    if isinstance(mask, str):
+        if mask != "causal":
+            raise ValueError(f"attention: unknown mask {mask!r}")
+        return 1, None
     if mask.dtype == torch.bool:
         add = torch.zeros(mask.shape, dtype=torch.float32, device=mask.device).masked_fill_(mask, float("-inf"))
     else:
         add = mask.float()
     if add.shape != (L, L):
         raise ValueError(f"attention: attn_mask must be ({L}, {L}), got {tuple(add.shape)}")
-    causal = torch.full((L, L), float("-inf"), device=add.device).triu_(1)
-    if torch.equal(add, causal):
-        return 1, None
     return 0, add.contiguous()
 
 

@@ -38,6 +38,8 @@ def test_attention_core_forward_backward(L, n, H, D, causal):
     hap_b200.linear_ops.gemm_status()
     close(got, want, "attention output")
     close(x.grad, ref_in.grad, "attention dqkv", tol=2e-2)
+    if causal:      # the built-in causal masking gives the same bits as the -inf mask tensor
+        assert torch.equal(A.attention(x.detach(), H, "causal"), got.detach())
 
 
 def test_general_additive_mask():
