@@ -7,6 +7,7 @@
 // of the tensor maps.  The contractions run on the batched tcgen05 GEMM (hapx_gemm_sm100.cu):
 //
 //   forward : S = Q K^T (fp32)  ->  P = softmax(scale * S + mask) (bf16, kept for backward)  ->  O = P V
+//             (for 128 < L <= 256 the softmax is the epilogue of the S GEMM: scores stay in tensor memory)
 //   backward: dV = P^T dO;  dP = dO V^T (fp32);  dS = scale * P * (dP - rowsum(dP * P));  dQ = dS K;  dK = dS^T Q
 //
 // The softmax kernels keep one row per warp in registers (L <= 1024).
@@ -20,7 +21,7 @@
 namespace hapx {
 namespace attn {
 
-constexpr int kMaxPerLane = 32;  // L <= 1024
+constexpr int kMaxPerLane = 32;  // L <= 1024; the kernels are instantiated for 8, 16 and 32 elements per lane
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -34,16 +35,17 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // rows = batch * L; row r is query (r % L).  S, P: [rows][Lp].  mask: additive [L][L] fp32 or null.
+template <int PL>
 __global__ void __launch_bounds__(256) softmax_fwd_kernel(const float* __restrict__ S, __nv_bfloat16* __restrict__ P, int L, int Lp,
                                                           long long rows, float scale, int causal, const float* __restrict__ mask) {
   const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31, q = (int)(row % L);
   const float* s = S + row * Lp;
-  float v[kMaxPerLane];
+  float v[PL];
   float mx = -INFINITY;
 #pragma unroll
-  for (int i = 0; i < kMaxPerLane; ++i) {
+  for (int i = 0; i < PL; ++i) {
     const int j = lane + 32 * i;
     float x = -INFINITY;
     if (j < L && !(causal && j > q)) {
@@ -56,7 +58,7 @@ __global__ void __launch_bounds__(256) softmax_fwd_kernel(const float* __restric
   mx = warp_max(mx);
   float sum = 0.f;
 #pragma unroll
-  for (int i = 0; i < kMaxPerLane; ++i) {
+  for (int i = 0; i < PL; ++i) {
     v[i] = (v[i] == -INFINITY) ? 0.f : __expf(v[i] - mx);
     sum += v[i];
   }
@@ -64,12 +66,13 @@ __global__ void __launch_bounds__(256) softmax_fwd_kernel(const float* __restric
   const float inv = 1.f / sum;
   __nv_bfloat16* p = P + row * Lp;
 #pragma unroll
-  for (int i = 0; i < kMaxPerLane; ++i) {
+  for (int i = 0; i < PL; ++i) {
     const int j = lane + 32 * i;
     if (j < Lp) p[j] = __float2bfloat16_rn(j < L ? v[i] * inv : 0.f);
   }
 }
 
+template <int PL>
 __global__ void __launch_bounds__(256) softmax_bwd_kernel(const __nv_bfloat16* __restrict__ P, const float* __restrict__ dP,
                                                           __nv_bfloat16* __restrict__ dS, int L, int Lp, long long rows, float scale) {
   const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -77,10 +80,10 @@ __global__ void __launch_bounds__(256) softmax_bwd_kernel(const __nv_bfloat16* _
   const int lane = threadIdx.x & 31;
   const __nv_bfloat16* p = P + row * Lp;
   const float* g = dP + row * Lp;
-  float pv[kMaxPerLane], gv[kMaxPerLane];
+  float pv[PL], gv[PL];
   float dot = 0.f;
 #pragma unroll
-  for (int i = 0; i < kMaxPerLane; ++i) {
+  for (int i = 0; i < PL; ++i) {
     const int j = lane + 32 * i;
     pv[i] = (j < L) ? __bfloat162float(p[j]) : 0.f;
     gv[i] = (j < L) ? g[j] : 0.f;
@@ -89,7 +92,7 @@ __global__ void __launch_bounds__(256) softmax_bwd_kernel(const __nv_bfloat16* _
   dot = warp_sum(dot);
   __nv_bfloat16* o = dS + row * Lp;
 #pragma unroll
-  for (int i = 0; i < kMaxPerLane; ++i) {
+  for (int i = 0; i < PL; ++i) {
     const int j = lane + 32 * i;
     if (j < Lp) o[j] = __float2bfloat16_rn(j < L ? scale * pv[i] * (gv[i] - dot) : 0.f);
   }
@@ -122,12 +125,25 @@ int hapx_attention_forward(void* out, void* probs, void* scores_ws, const void* 
   const Operand Vmn{base + 2 * E, true, row_qkv, D, 3 * E};
   const Operand S{scores_ws, false, Lp, L * Lp, H * L * Lp}, P{probs, false, Lp, L * Lp, H * L * Lp};
   const Operand O{out, false, N * E, D, E};
+  if (L > 128 && L <= 256) {
+    // the whole score row fits one accumulator tile: softmax runs in the GEMM's epilogue and the
+    // fp32 scores never leave tensor memory
+    const gemm::RowSoftmax sm{1.0f / sqrtf((float)D), causal, mask};
+    if (int e = gemm::gemm_bf16(P, 0, Q, K, nullptr, 0, L, L, D, (int)H, (int)N, stream, &sm)) return e;
+    return gemm::gemm_bf16(O, 0, P, Vmn, nullptr, 0, L, D, L, (int)H, (int)N, stream);
+  }
   // S[b] = Q[b] K[b]^T   (fp32)
   if (int e = gemm::gemm_bf16(S, 1, Q, K, nullptr, 0, L, L, D, (int)H, (int)N, stream)) return e;
   const long long rows = N * H * L;
-  attn::softmax_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(static_cast<const float*>(scores_ws),
-                                                                           static_cast<__nv_bfloat16*>(probs), (int)L, (int)Lp, rows,
-                                                                           1.0f / sqrtf((float)D), causal, mask);
+  {
+    const unsigned grid = (unsigned)((rows + 7) / 8);
+    const float* sp = static_cast<const float*>(scores_ws);
+    __nv_bfloat16* pp = static_cast<__nv_bfloat16*>(probs);
+    const float sc = 1.0f / sqrtf((float)D);
+    if (Lp <= 256) attn::softmax_fwd_kernel<8><<<grid, 256, 0, stream>>>(sp, pp, (int)L, (int)Lp, rows, sc, causal, mask);
+    else if (Lp <= 512) attn::softmax_fwd_kernel<16><<<grid, 256, 0, stream>>>(sp, pp, (int)L, (int)Lp, rows, sc, causal, mask);
+    else attn::softmax_fwd_kernel<32><<<grid, 256, 0, stream>>>(sp, pp, (int)L, (int)Lp, rows, sc, causal, mask);
+  }
   HAPX_CUDA(cudaGetLastError());
   count_launch();
   // O[b] = P[b] V[b]      (contraction over keys; V is MN-major as stored)
@@ -154,10 +170,16 @@ int hapx_attention_backward(void* dqkv, void* dscores_ws, void* ds_ws, const voi
   // dP[q, k] = sum_d dO[q, d] V[k, d]   (fp32)
   if (int e = gemm::gemm_bf16(dPf, 1, dO, V, nullptr, 0, L, L, D, (int)H, (int)N, stream)) return e;
   const long long rows = N * H * L;
-  attn::softmax_bwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(probs),
-                                                                           static_cast<const float*>(dscores_ws),
-                                                                           static_cast<__nv_bfloat16*>(ds_ws), (int)L, (int)Lp, rows,
-                                                                           1.0f / sqrtf((float)D));
+  {
+    const unsigned grid = (unsigned)((rows + 7) / 8);
+    const __nv_bfloat16* pp = static_cast<const __nv_bfloat16*>(probs);
+    const float* gp = static_cast<const float*>(dscores_ws);
+    __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(ds_ws);
+    const float sc = 1.0f / sqrtf((float)D);
+    if (Lp <= 256) attn::softmax_bwd_kernel<8><<<grid, 256, 0, stream>>>(pp, gp, dp, (int)L, (int)Lp, rows, sc);
+    else if (Lp <= 512) attn::softmax_bwd_kernel<16><<<grid, 256, 0, stream>>>(pp, gp, dp, (int)L, (int)Lp, rows, sc);
+    else attn::softmax_bwd_kernel<32><<<grid, 256, 0, stream>>>(pp, gp, dp, (int)L, (int)Lp, rows, sc);
+  }
   HAPX_CUDA(cudaGetLastError());
   count_launch();
   // dQ[q, d] = sum_k dS[q, k] K[k, d];   dK[k, d] = sum_q dS[q, k] Q[q, d]
