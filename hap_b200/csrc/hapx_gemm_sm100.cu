@@ -62,6 +62,7 @@ struct Params {
   int softmax, sm_causal;
   float sm_scale;
   const float* sm_mask;             // additive [M][N] fp32 or null
+  const unsigned* sm_mask_is_causal; // device word: non-zero when sm_mask is exactly the causal mask (then it is not read)
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -321,8 +322,9 @@ __device__ __forceinline__ void drain_tile_softmax(const Params& p, const CUtens
                                                    int& buf) {
   const int row = m0 + q * 32 + lane;          // query index inside this (batch, head) matrix
   const float k = p.sm_scale * 1.4426950408889634f;   // exp(x) = exp2(x * log2 e)
-  const float* mrow = (p.sm_mask != nullptr && row < p.M) ? p.sm_mask + (long long)row * p.N : nullptr;
-  const int last = p.sm_causal ? min(row, p.N - 1) : p.N - 1;   // last column that takes part
+  const bool mask_causal = p.sm_mask_is_causal != nullptr && *p.sm_mask_is_causal != 0u;
+  const float* mrow = (p.sm_mask != nullptr && !mask_causal && row < p.M) ? p.sm_mask + (long long)row * p.N : nullptr;
+  const int last = (p.sm_causal || mask_causal) ? min(row, p.N - 1) : p.N - 1;   // last column that takes part
   // three sweeps over the accumulator row in tensor memory (cheap to re-read): maximum, sum of
   // exponentials, normalised output - one exponential per element in each of the last two
   float mx = -INFINITY, sum = 0.f;
@@ -870,7 +872,7 @@ static int make_map(CUtensorMap* map, const Operand& op, long long mn_extent, lo
 struct DeviceState {
   bool ready = false;
   int sm_count = 0;
-  unsigned* error = nullptr;  // one device word per device for the kernels' error reports
+  unsigned* error = nullptr;  // device words: [0] the kernels' error reports, [1] scratch flag for callers
 };
 static DeviceState g_dev[64];
 static std::mutex g_dev_mutex;
@@ -886,8 +888,8 @@ static int device_state(DeviceState** out) {
   DeviceState& d = g_dev[device];
   if (!d.ready) {
     HAPX_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device));
-    HAPX_CUDA(cudaMalloc(&d.error, sizeof(unsigned)));
-    HAPX_CUDA(cudaMemset(d.error, 0, sizeof(unsigned)));
+    HAPX_CUDA(cudaMalloc(&d.error, 64));
+    HAPX_CUDA(cudaMemset(d.error, 0, 64));
     d.ready = true;
   }
   *out = &d;
@@ -1038,6 +1040,14 @@ static int launch2(const Operand& A, const Operand& B, const Operand& Dop, Param
   return HAPX_OK;
 }
 
+// A device word the attention code uses for its "mask is causal" flag (stream-ordered reuse).
+int scratch_flag(unsigned** out) {
+  DeviceState* dev = nullptr;
+  if (int e = device_state(&dev)) return e;
+  *out = dev->error + 1;
+  return HAPX_OK;
+}
+
 // D[b] = A[b] * B[b]^T for b in [0, batch): M x N outputs, contraction length Kc.
 int gemm_bf16(const Operand& Dop, int out_f32, const Operand& A, const Operand& B, const void* bias, int epilogue,
               long long M, long long N, long long Kc, int batch_in, int batch_out, cudaStream_t stream, const RowSoftmax* softmax) {
@@ -1058,6 +1068,7 @@ int gemm_bf16(const Operand& Dop, int out_f32, const Operand& A, const Operand& 
     if (!(M > BM && N > 64 && N <= 256) || out_f32 || A.mn_major || B.mn_major)
       return fail(HAPX_ERR_ARGUMENT, "gemm: row-softmax epilogue needs 128 < M, 64 < N <= 256, bf16 output, K-major operands");
     p.softmax = 1; p.sm_causal = softmax->causal; p.sm_scale = softmax->scale; p.sm_mask = softmax->mask;
+    p.sm_mask_is_causal = softmax->mask_is_causal;
   }
   p.a_shared_out = (batch_out > 1 && A.s_out == 0) ? 1 : 0;
   p.b_shared_out = (batch_out > 1 && B.s_out == 0) ? 1 : 0;
