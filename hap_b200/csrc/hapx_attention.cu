@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(1024) classify_mask_kernel(const float* __rest
 }
 
 static int check(long long L, long long N, long long H, long long D) {
-  if (L < 1 || N < 1 || H < 1 || D < 1) return fail(HAPX_ERR_EXTENT, "attention: extents must be positive");
+  if (L < 0 || N < 0 || H < 1 || D < 1) return fail(HAPX_ERR_EXTENT, "attention: negative extent");
   if (L > 32 * kMaxPerLane) return fail(HAPX_ERR_EXTENT, "attention: sequence length above 1024 is not supported");
   if (D % 8 != 0) return fail(HAPX_ERR_EXTENT, "attention: head dimension must be a multiple of 8");
   if (N * H > 0x7fffffff) return fail(HAPX_ERR_EXTENT, "attention: too many (batch, head) pairs");
@@ -130,6 +130,7 @@ extern "C" {
 int hapx_attention_forward(void* out, void* probs, void* scores_ws, const void* qkv, int64_t L, int64_t N, int64_t H, int64_t D,
                            int causal, const float* mask, hapx_stream stream_) {
   if (int e = attn::check(L, N, H, D)) return e;
+  if (L == 0 || N == 0) return HAPX_OK;   // an empty batch shard (sharding_round may hand a rank nothing)
   if (!out || !probs || !scores_ws || !qkv) return fail(HAPX_ERR_ARGUMENT, "attention_forward: null pointer");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const long long E = H * D, Lp = (L + 7) / 8 * 8, row_qkv = N * 3 * E;
@@ -176,6 +177,7 @@ int hapx_attention_forward(void* out, void* probs, void* scores_ws, const void* 
 int hapx_attention_backward(void* dqkv, void* dscores_ws, void* ds_ws, const void* dout, const void* probs, const void* qkv,
                             int64_t L, int64_t N, int64_t H, int64_t D, hapx_stream stream_) {
   if (int e = attn::check(L, N, H, D)) return e;
+  if (L == 0 || N == 0) return HAPX_OK;
   if (!dqkv || !dscores_ws || !ds_ws || !dout || !probs || !qkv) return fail(HAPX_ERR_ARGUMENT, "attention_backward: null pointer");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const long long E = H * D, Lp = (L + 7) / 8 * 8, row_qkv = N * 3 * E;

@@ -1053,7 +1053,11 @@ int gemm_bf16(const Operand& Dop, int out_f32, const Operand& A, const Operand& 
               long long M, long long N, long long Kc, int batch_in, int batch_out, cudaStream_t stream, const RowSoftmax* softmax) {
   if (M < 0 || N < 0 || Kc < 0 || batch_in < 1 || batch_out < 1) return fail(HAPX_ERR_EXTENT, "gemm: bad extent");
   if (M == 0 || N == 0) return HAPX_OK;
-  if (Kc == 0) return fail(HAPX_ERR_EXTENT, "gemm: empty contraction");
+  if (Kc == 0) {  // an empty contraction (e.g. the weight gradient of a rank that holds no samples): D = 0
+    if (batch_in * batch_out != 1 || Dop.ld != N || bias != nullptr) return fail(HAPX_ERR_EXTENT, "gemm: empty contraction");
+    HAPX_CUDA(cudaMemsetAsync(const_cast<void*>(Dop.ptr), 0, (size_t)M * N * (out_f32 ? 4 : 2), stream));
+    return HAPX_OK;
+  }
   if (M > 0x7fffffff || N > 0x7fffffff || Kc > 0x7fffffff) return fail(HAPX_ERR_EXTENT, "gemm: extent exceeds 2^31");
   if (!Dop.ptr || !A.ptr || !B.ptr) return fail(HAPX_ERR_ARGUMENT, "gemm: null pointer");
   DeviceState* dev = nullptr;

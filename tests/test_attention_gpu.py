@@ -71,3 +71,18 @@ def test_multi_head_attention_forward_drop_in():
     with pytest.raises(NotImplementedError):
         A.multi_head_attention_forward(xd, xd, xd, E, H, in_w.to(DEV), in_b.to(DEV), dropout_p=0.1, out_proj_weight=out_w.to(DEV),
                                        out_proj_bias=out_b.to(DEV))
+
+
+def test_empty_batch_shard():
+    """sharding_round can hand a rank zero samples; every op must then produce empty tensors."""
+    qkv = torch.zeros(16, 0, 3 * 64, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    out = A.attention(qkv, 2, "causal")
+    assert out.shape == (16, 0, 64)
+    out.sum().backward()
+    assert qkv.grad.shape == qkv.shape
+    x = torch.zeros(0, 64, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = torch.ones(32, 64, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = hap_b200.linear(x, w, None)
+    assert y.shape == (0, 32)
+    y.sum().backward()
+    assert float(w.grad.abs().sum()) == 0.0 and x.grad.shape == (0, 64)
