@@ -159,3 +159,34 @@ def test_cuda_graph_replay_follows_the_eager_step():
     finally:
         hap_b200.collectives.set_default_comm(None)
         comm.destroy()
+
+
+def test_language_model_on_eight_virtual_ranks_with_empty_shards():
+    """World 8, ratios r8, batch 8: sharding_round gives [2,2,1,1,1,1,0,0]-like splits, so some ranks
+    hold no samples at all and still take part in every collective."""
+    import copy
+    from hap_b200 import plan as P
+    r8 = [.22, .18, .15, .13, .11, .09, .07, .05]
+    lb = hap_b200.sharding_round(C.LM_BATCH, r8)
+    assert 0 in lb and sum(lb) == C.LM_BATCH
+    model = C.lm_model(torch.bfloat16)
+    tok, tgt = C.lm_batch()
+
+    def modules(ns, device):
+        mods = []
+        for r in range(8):
+            m = copy.deepcopy(model).to(device)
+            mods.append(torch.fx.GraphModule(m, P.emit_lm(m, "dp_zero", r8, r, C.LM_BATCH, ns)))
+        return mods
+
+    cpu = LockstepWorld(modules(C.lm_cpu_namespace(), "cpu"), OracleCollectives())
+    comm = hap_b200.local_comm(8, DEV, stage_bytes=8 << 20, heap_bytes=16 << 20)
+    try:
+        gpu = LockstepWorld(modules(hap_b200.plan.default_namespace(), DEV), hap_b200.LocalCollectives(comm))
+        want = float(cpu.step([(tok, tgt)] * 8))
+        got = float(gpu.step([(tok.to(DEV), tgt.to(DEV))] * 8))
+        assert abs(got - want) <= 1e-2 * abs(want), (got, want)
+        comm.check()
+        hap_b200.linear_ops.gemm_status()
+    finally:
+        comm.destroy()
