@@ -509,7 +509,10 @@ def run_gemm(args):
         return statistics.median(ts)
 
     launches0 = N.lib.hapx_launch_count()
+    wanted = [x.strip() for x in args.gemm_layers.split(",") if x.strip()]
     for name, n, k in LM_LAYERS:
+        if wanted and name not in wanted:
+            continue
         g = torch.Generator(dev).manual_seed(39)
         xs = [torch.randn(M, k, device=dev, generator=g).to(torch.bfloat16) for _ in range(SETS)]
         ws = [(torch.randn(n, k, device=dev, generator=g) * k ** -0.5).to(torch.bfloat16) for _ in range(SETS)]
@@ -749,6 +752,7 @@ def main():
     ap.add_argument("--lm-plan", default="dp_zero", choices=["dp", "dp_zero"])
     ap.add_argument("--lm-graph", action="store_true", help="capture the training step into a CUDA graph")
     ap.add_argument("--gemm-tokens", type=int, default=8192)
+    ap.add_argument("--gemm-layers", default="", help="comma-separated layer names to restrict the gemm workload to")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
