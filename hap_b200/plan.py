@@ -45,8 +45,9 @@ class MLP(torch.nn.Module):
 def default_namespace() -> SimpleNamespace:
     from . import collectives
     from .attention import multi_head_attention_forward
+    from .einsum import einsum
     from .linear import linear
-    return SimpleNamespace(collectives=collectives, linear=linear, mha=multi_head_attention_forward)
+    return SimpleNamespace(collectives=collectives, linear=linear, mha=multi_head_attention_forward, einsum=einsum)
 
 
 def shard_parameter_(module: torch.nn.Module, name: str, lengths: Sequence[int], dim: int, rank: int) -> None:
@@ -223,6 +224,122 @@ def emit_lm(model: TransformerLM, plan: str, ratios: Sequence[float], rank: int,
             model._full_extent[n] = full
             shard_parameter_(model, n, sharding_round(full, ratios), 0, rank)
     loss = _lm_forward(model, tok_r, tgt_r, ns, g, list(ratios), rank, plan)
+    g.output(loss)
+    g.lint()
+    return g
+
+
+# ---------------------------------------------------------------------------------------------
+# MoE Transformer (expert-parallel configuration)
+# ---------------------------------------------------------------------------------------------
+def top2_gating(x, gate_weight, n_expert: int, capacity: int):
+    """Top-2 gating with a fixed per-expert capacity, same semantics as the reference's fx-wrapped
+    ``top_2_gating`` (``models.py:477-502``): softmax gate, two best experts per token, slots handed
+    out in sequence order (all first choices before any second choice), 1-based slot numbers that
+    must stay below ``capacity``, combine weight = the raw gate probability.  Returns
+    (dispatch, combine), both (batch, seq, n_expert, capacity) in x's dtype.  Plain torch ops: the
+    planner treats this function as an opaque leaf (``hap.rs:2169``)."""
+    gates = torch.softmax(torch.matmul(x, gate_weight).float(), dim=2)                   # (b, s, e)
+    top_p, top_i = torch.topk(gates, 2, dim=2)                                           # (b, s, 2)
+    chosen = F.one_hot(top_i, n_expert)                                                  # (b, s, 2, e)
+    first, second = chosen[:, :, 0, :], chosen[:, :, 1, :]
+    slot1 = torch.cumsum(first, dim=1) * first                                           # 1-based
+    slot2 = (torch.cumsum(second, dim=1) + first.sum(dim=1, keepdim=True)) * second
+    keep1, keep2 = (slot1 > 0) & (slot1 < capacity), (slot2 > 0) & (slot2 < capacity)
+    combine = torch.zeros(*gates.shape, capacity, dtype=gates.dtype, device=x.device)    # (b, s, e, c)
+    for keep, slot, p in ((keep1, slot1, top_p[:, :, 0]), (keep2, slot2, top_p[:, :, 1])):
+        w = (p.unsqueeze(2) * keep).unsqueeze(3)                                         # (b, s, e, 1)
+        combine = combine + w * F.one_hot((slot * keep).clamp(max=capacity - 1), capacity)
+    dispatch = (combine > 0).to(x.dtype)
+    return dispatch, combine.to(x.dtype)
+
+
+class MoETransformerLM(torch.nn.Module):
+    """Post-LN MoE Transformer LM in the shape of the reference's ``Top2TransformerEncoderLayer``
+    (``models.py:301-366``): x = LN(x + MHA(x)); x = LN(x + MoE(x)) with top-2 gating over
+    ``n_expert`` expert FFNs (w1[e, d, h], relu, w2[e, h, d]); summed NLL loss."""
+
+    def __init__(self, vocab=33280, d_model=1024, nheads=16, d_ffn=4096, nlayers=8, seqlen=512, n_expert=32, capacity=20):
+        super().__init__()
+        self.vocab, self.d_model, self.nheads, self.nlayers, self.seqlen = vocab, d_model, nheads, nlayers, seqlen
+        self.n_expert, self.capacity = n_expert, capacity
+        self.embed = torch.nn.Embedding(vocab, d_model)
+        self.pos = torch.nn.Parameter(torch.randn(1, seqlen, d_model) * 0.02)
+        P_ = lambda *shape, scale=1.0: torch.nn.Parameter(torch.randn(*shape) * scale)
+        for i in range(nlayers):
+            self.register_parameter(f"l{i}_in_w", P_(3 * d_model, d_model, scale=d_model ** -0.5))
+            self.register_parameter(f"l{i}_in_b", torch.nn.Parameter(torch.zeros(3 * d_model)))
+            self.register_parameter(f"l{i}_out_w", P_(d_model, d_model, scale=d_model ** -0.5))
+            self.register_parameter(f"l{i}_out_b", torch.nn.Parameter(torch.zeros(d_model)))
+            self.register_parameter(f"l{i}_ln1_w", torch.nn.Parameter(torch.ones(d_model)))
+            self.register_parameter(f"l{i}_ln1_b", torch.nn.Parameter(torch.zeros(d_model)))
+            self.register_parameter(f"l{i}_gate", P_(d_model, n_expert, scale=d_model ** -0.5))
+            self.register_parameter(f"l{i}_w1", P_(n_expert, d_model, d_ffn, scale=d_model ** -0.5))
+            self.register_parameter(f"l{i}_w2", P_(n_expert, d_ffn, d_model, scale=d_ffn ** -0.5))
+            self.register_parameter(f"l{i}_ln2_w", torch.nn.Parameter(torch.ones(d_model)))
+            self.register_parameter(f"l{i}_ln2_b", torch.nn.Parameter(torch.zeros(d_model)))
+        self.dec_w = P_(vocab, d_model, scale=d_model ** -0.5)
+        self.dec_b = torch.nn.Parameter(torch.zeros(vocab))
+
+    def forward(self, tokens, targets):
+        ns = SimpleNamespace(collectives=None, linear=F.linear, mha=F.multi_head_attention_forward, einsum=torch.einsum)
+        return _moe_forward(self, tokens, targets, ns, None, None, None, None)
+
+
+def _moe_forward(m, tokens, targets, ns, emit, ratios, rank, batch):
+    col, linear, mha, einsum = ns.collectives, ns.linear, ns.mha, ns.einsum
+    E, H, ne, cap = m.d_model, m.nheads, m.n_expert, m.capacity
+
+    def param(name, sharded=False):
+        if emit is None:
+            return getattr(m, name) if "." not in name else m.get_parameter(name)
+        node = emit.get_attr(name)
+        return node if sharded else emit.call_function(col.replicate, (node,))   # expert weights: get_attr of the in-place shard (hap.rs:2591-2593)
+
+    call = (lambda fn, *a, **k: fn(*a, **k)) if emit is None else (lambda fn, *a, **k: emit.call_function(fn, a, k))
+    method = (lambda obj, name, *a: getattr(obj, name)(*a)) if emit is None else (lambda obj, name, *a: emit.call_method(name, (obj, *a)))
+
+    x = call(operator.add, call(F.embedding, tokens, param("embed.weight")), param("pos"))          # (b, s, E)
+    for i in range(m.nlayers):
+        h = method(x, "transpose", 0, 1)                                                               # (s, b, E)
+        att = call(mha, query=h, key=h, value=h, embed_dim_to_check=E, num_heads=H, in_proj_weight=param(f"l{i}_in_w"),
+                   in_proj_bias=param(f"l{i}_in_b"), bias_k=None, bias_v=None, add_zero_attn=False, dropout_p=0.0,
+                   out_proj_weight=param(f"l{i}_out_w"), out_proj_bias=param(f"l{i}_out_b"))
+        a = method(call(operator.getitem, att, 0), "transpose", 0, 1)
+        x = call(F.layer_norm, call(operator.add, x, a), (E,), param(f"l{i}_ln1_w"), param(f"l{i}_ln1_b"))
+        gated = call(top2_gating, x, param(f"l{i}_gate"), ne, cap)
+        dispatch, combine = call(operator.getitem, gated, 0), call(operator.getitem, gated, 1)
+        ein = call(einsum, "bsd,bsec->becd", x, dispatch)                                              # (b_r, e, c, d)
+        if emit is not None:   # batch-sharded -> expert-sharded (hap.rs:2713-2744: all_to_all(x, split=j, cat=i, ...))
+            le, lb = sharding_round(ne, ratios), sharding_round(batch, ratios)
+            ein = emit.call_function(col.all_to_all, (ein, 1, 0, le, lb, rank))                       # (b, e_r, c, d)
+        hid = call(F.relu, call(einsum, "edh,becd->bech", param(f"l{i}_w1", True), ein))
+        eo = call(einsum, "ehd,bech->becd", param(f"l{i}_w2", True), hid)
+        if emit is not None:
+            eo = emit.call_function(col.all_to_all, (eo, 0, 1, lb, le, rank))                         # (b_r, e, c, d)
+        y = call(einsum, "becd,bsec->bsd", eo, combine)
+        x = call(F.layer_norm, call(operator.add, x, y), (E,), param(f"l{i}_ln2_w"), param(f"l{i}_ln2_b"))
+    logits = call(linear, x, param("dec_w"), param("dec_b"))
+    logp = method(call(F.log_softmax, method(logits, "float"), -1), "reshape", -1, m.vocab)
+    return call(F.nll_loss, logp, method(targets, "reshape", -1), reduction="sum")
+
+
+def emit_moe(model: MoETransformerLM, ratios: Sequence[float], rank: int, batch: int, ns=None) -> torch.fx.Graph:
+    """Expert-parallel program: tokens batch-sharded by ``ratios``; expert weights w1/w2 sharded on
+    the expert dimension by ``sharding_round(n_expert, ratios)`` (cut in place); the dispatched
+    tokens travel batch-sharded -> expert-sharded -> batch-sharded through two uneven all_to_all
+    calls per layer; everything else replicated."""
+    ns = ns or default_namespace()
+    g = torch.fx.Graph()
+    tokens, targets = g.placeholder("tokens"), g.placeholder("targets")
+    lb = sharding_round(batch, ratios)
+    tok_r = g.call_function(operator.getitem, (g.call_method("split", (tokens, lb, 0)), rank))
+    tgt_r = g.call_function(operator.getitem, (g.call_method("split", (targets, lb, 0)), rank))
+    le = sharding_round(model.n_expert, ratios)
+    for i in range(model.nlayers):
+        shard_parameter_(model, f"l{i}_w1", le, 0, rank)
+        shard_parameter_(model, f"l{i}_w2", le, 0, rank)
+    loss = _moe_forward(model, tok_r, tgt_r, ns, g, list(ratios), rank, batch)
     g.output(loss)
     g.lint()
     return g

@@ -80,3 +80,25 @@ def lm_rank_modules(model, plan, ns, world=2, device="cpu"):
 def lm_cpu_namespace():
     from oracle import gloo_port
     return SimpleNamespace(collectives=gloo_port, linear=F.linear, mha=F.multi_head_attention_forward)
+
+
+# ---- MoE Transformer ---------------------------------------------------------------------------------
+MOE_SMALL = dict(vocab=64, d_model=64, nheads=2, d_ffn=128, nlayers=2, seqlen=16, n_expert=4, capacity=8)
+
+
+def moe_model(dtype=torch.float32):
+    torch.manual_seed(39)
+    return P.MoETransformerLM(**MOE_SMALL).to(dtype)
+
+
+def moe_rank_modules(model, ns, world=2, device="cpu", ratios=None):
+    mods = []
+    for r in range(world):
+        m = copy.deepcopy(model).to(device)
+        mods.append(torch.fx.GraphModule(m, P.emit_moe(m, ratios or RATIOS, r, LM_BATCH, ns)))
+    return mods
+
+
+def moe_cpu_namespace():
+    from oracle import gloo_port
+    return SimpleNamespace(collectives=gloo_port, linear=F.linear, mha=F.multi_head_attention_forward, einsum=torch.einsum)

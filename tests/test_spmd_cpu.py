@@ -110,3 +110,28 @@ def test_language_model_programs_reproduce_the_unsharded_model(plan):
                 n_sharded += 1
             torch.testing.assert_close(p.grad, g, rtol=1e-3, atol=1e-4)
     assert (n_sharded > 0) == (plan == "dp_zero")
+
+
+def test_expert_parallel_moe_program_reproduces_the_unsharded_model():
+    """MoE Transformer: experts sharded by sharding_round(n_expert, ratios), tokens batch-sharded, two
+    uneven all_to_all per layer (hap.rs:2713-2744) around the expert einsums (models.py:356-364)."""
+    import copy
+    from hap_b200 import sharding_round
+    model = C.moe_model()
+    tok, tgt = C.lm_batch()
+    ref = copy.deepcopy(model)
+    want = ref(tok, tgt)
+    want.backward()
+    world = LockstepWorld(C.moe_rank_modules(model, C.moe_cpu_namespace()), OracleCollectives())
+    names = [n.target.__name__ for n in world.modules[0].graph.nodes if n.op == "call_function" and hasattr(n.target, "__name__")]
+    assert names.count("all_to_all") == 2 * C.MOE_SMALL["nlayers"] and names.count("einsum") == 4 * C.MOE_SMALL["nlayers"]
+    losses = world.forward([(tok, tgt), (tok, tgt)])
+    assert abs(float(sum(losses)) - float(want)) <= 1e-5 * abs(float(want))
+    torch.stack(losses).sum().backward()
+    full = dict(ref.named_parameters())
+    for r, m in enumerate(world.modules):
+        for name, p in m.named_parameters():
+            g = full[name].grad
+            if p.shape != g.shape:
+                g = torch.split(g, sharding_round(g.shape[0], C.RATIOS), dim=0)[r]
+            torch.testing.assert_close(p.grad, g, rtol=1e-3, atol=1e-4)

@@ -190,3 +190,30 @@ def test_language_model_on_eight_virtual_ranks_with_empty_shards():
         hap_b200.linear_ops.gemm_status()
     finally:
         comm.destroy()
+
+
+def test_expert_parallel_moe_step_matches_cpu_replay():
+    """MoE Transformer step in bf16 on 2 virtual ranks: package attention, linear, einsums and the uneven
+    all_to_all against the CPU replay of the same fx programs."""
+    dtype = torch.bfloat16
+    model = C.moe_model(dtype)
+    tok, tgt = C.lm_batch()
+    cpu = LockstepWorld(C.moe_rank_modules(model, C.moe_cpu_namespace()), OracleCollectives())
+    comm = hap_b200.local_comm(2, DEV, stage_bytes=16 << 20, heap_bytes=32 << 20)
+    try:
+        gpu = LockstepWorld(C.moe_rank_modules(model, hap_b200.plan.default_namespace(), device=DEV), hap_b200.LocalCollectives(comm))
+        want = cpu.forward([(tok, tgt), (tok, tgt)])
+        got = gpu.forward([(tok.to(DEV), tgt.to(DEV))] * 2)
+        for r in range(2):
+            assert abs(float(got[r]) - float(want[r])) <= 2e-2 * abs(float(want[r])), (r, float(got[r]), float(want[r]))
+        torch.stack(want).sum().backward()
+        torch.stack(got).sum().backward()
+        for r in range(2):
+            for (name, pw), (_, pg) in zip(cpu.modules[r].named_parameters(), gpu.modules[r].named_parameters()):
+                assert pg.grad.shape == pw.grad.shape, name
+                d = (pg.grad.detach().float().cpu() - pw.grad.detach().float())
+                assert float(d.norm()) <= 1e-1 * float(pw.grad.float().norm()) + 1e-2, (r, name, float(d.norm()), float(pw.grad.float().norm()))
+        comm.check()
+        hap_b200.linear_ops.gemm_status()
+    finally:
+        comm.destroy()
