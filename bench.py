@@ -356,7 +356,7 @@ def run_sweep(args):
     L = hap_b200.sharding_round(ROWS, ratios_for(W))
     max_bytes = args.sweep_max_mib << 20
     stage = (max_bytes // W + (64 << 20) + 255) // 256 * 256      # all_reduce keeps its reduced slice there
-    heap = stage + max_bytes + max(L) * (max_bytes // ROWS) + (64 << 20)
+    heap = stage + max_bytes + max(L) * (max_bytes // ROWS) + int(max_bytes * max(ratios_for(W)) * 1.05) + (64 << 20)
     if emulated:
         comm = hap_b200.local_comm(W, dev, heap_bytes=heap, stage_bytes=stage)
         dist = None
@@ -425,6 +425,18 @@ def run_sweep(args):
                 ("reduce_scatter_by_group_call", lambda: comm.reduce_scatter(fulls, 0, L, N.MODE_GROUP_CALL), S * (W - 1) / W, alg_ag),
                 ("all_reduce", lambda: comm.all_reduce(fulls, scale=1.0 / W), 2 * S * (W - 1) / W, 2 * S * (W - 1) / W),
             ]
+            if cols >= W:
+                # uneven all_to_all in the reference profiler's convention (profiler.py:106-117): the (256, C) tensor is
+                # held column-sharded (cat dim 1), cut on dim 0 and exchanged, giving a row-sharded (L[r], C) result
+                LC = hap_b200.sharding_round(cols, ratios_for(W))
+                a2a_in = []
+                for i, r in enumerate(ranks):
+                    t = comm.symm_empty((ROWS, LC[r]), dtype, i)
+                    t.copy_(torch.randn(ROWS, LC[r], device=dev).to(dtype))
+                    a2a_in.append(t)
+                m = [[L[j] * LC[r] * es for j in range(W)] for r in range(W)]          # bytes r -> j
+                alg_a2a = max(max(sum(m[r][j] for j in range(W) if j != r), sum(m[i][r] for i in range(W) if i != r)) for r in range(W))
+                cases.append(("all_to_all", lambda: comm.all_to_all(a2a_in, 0, 1, L, LC), S * (W - 1) / W, alg_a2a))
             for name, fn, bus, alg in cases:
                 med, best = timed(fn, reps, inner=inner)
                 row = {"op": name, "dtype": dname, "bytes": S, "world": W, "ms_median": med, "ms_min": best, "calls_per_timing": inner,
@@ -436,14 +448,16 @@ def run_sweep(args):
                                "all_gather_by_group_call": lambda: gp.all_gather_by_group_call(shards[0], 0, L, rank),
                                "reduce_scatter": lambda: gp.reduce_scatter(fulls[0], 0, L, rank),
                                "reduce_scatter_by_group_call": lambda: gp.reduce_scatter_by_group_call(fulls[0], 0, L, rank),
-                               "all_reduce": lambda: gp.all_reduce(fulls[0])}[name]
+                               "all_reduce": lambda: gp.all_reduce(fulls[0]),
+                               "all_to_all": lambda: gp.all_to_all(a2a_in[0], 0, 1, L, LC, rank)}[name]
                         rmed, rbest = timed(ref, max(3, reps // 2), warm=2, inner=inner)
                         row["reference_on_nccl_ms_median"] = rmed
                         row["speedup_vs_reference_on_nccl"] = rmed / med
                 rows.append(row)
                 if rank == 0:
                     _print_sweep_row(row)
-            del out, shards, fulls
+            del out, shards, fulls, cases
+            a2a_in = None
             torch.cuda.empty_cache()
     comm.check()
     comm.destroy()
