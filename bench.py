@@ -726,6 +726,76 @@ def run_lm(args):
     if rank == 0:
         print(json.dumps(result), flush=True)
 
+
+# ----------------------------------------------------------------------------------------------
+# attention core and MoE einsums at the configurations' per-GPU shapes, next to torch's own kernels
+# ----------------------------------------------------------------------------------------------
+def run_ops(args):
+    import torch
+    import hap_b200
+    from hap_b200 import attention as A
+    from hap_b200.einsum import einsum
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timeit(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(args.steps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            b.synchronize()
+            ts.append(a.elapsed_time(b))
+        return statistics.median(ts)
+
+    rows = []
+    g = torch.Generator(dev).manual_seed(39)
+    for name, L, n, H, D, causal in (("LM attention", 256, 32, 12, 64, True), ("ViT attention", 197, 64, 12, 64, False),
+                                     ("MoE attention", 512, 16, 16, 64, True)):
+        E = H * D
+        qkv = torch.randn(L, n, 3 * E, device=dev, generator=g).to(torch.bfloat16).requires_grad_(True)
+        go = torch.randn(L, n, E, device=dev, generator=g).to(torch.bfloat16)
+        mask = "causal" if causal else None
+
+        def ours():
+            qkv.grad = None
+            A.attention(qkv, H, mask).backward(go)
+
+        def ref():
+            qkv.grad = None
+            q, k, v = (t.reshape(L, n * H, D).transpose(0, 1) for t in qkv.split(E, dim=2))
+            o = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=causal)
+            o.transpose(0, 1).reshape(L, n, E).backward(go)
+
+        flops = 3.5 * 4.0 * n * H * L * L * D * (0.5 if causal else 1.0)     # fwd 2 GEMMs + bwd 5 GEMMs (2.5x fwd)
+        t, tr = timeit(ours), timeit(ref)
+        rows.append({"op": name + " fwd+bwd", "shape": f"L={L} N={n} H={H} D={D}", "ms": t, "torch_ms": tr, "tflops": flops / t / 1e9})
+    b, s, e, c, d, h = 16, 512, 32, 20, 1024, 4096
+    x = torch.randn(b, s, d, device=dev, generator=g).to(torch.bfloat16)
+    disp = (torch.rand(b, s, e, c, device=dev, generator=g) < 0.003).to(torch.bfloat16)
+    for code, a_, b_, fl in (("bsd,bsec->becd", x, disp, 2.0 * b * s * e * c * d),
+                             ("becd,bsec->bsd", torch.randn(b, e, c, d, device=dev, generator=g).to(torch.bfloat16), disp, 2.0 * b * s * e * c * d)):
+        t, tr = timeit(lambda: einsum(code, a_, b_)), timeit(lambda: torch.einsum(code, a_, b_))
+        rows.append({"op": code, "shape": f"b={b} s={s} e={e} c={c} d={d}", "ms": t, "torch_ms": tr, "tflops": fl / t / 1e9})
+    for el in (7, 4, 2):        # experts on this GPU under the r8 split of 32 experts
+        bg = 128
+        w1 = (torch.randn(el, d, h, device=dev, generator=g) * d ** -0.5).to(torch.bfloat16)
+        inp = torch.randn(bg, el, c, d, device=dev, generator=g).to(torch.bfloat16)
+        fl = 2.0 * bg * el * c * d * h
+        t, tr = timeit(lambda: einsum("edh,becd->bech", w1, inp)), timeit(lambda: torch.einsum("edh,becd->bech", w1, inp))
+        rows.append({"op": "edh,becd->bech", "shape": f"b={bg} e={el} c={c} d={d} h={h}", "ms": t, "torch_ms": tr, "tflops": fl / t / 1e9})
+    hap_b200.linear_ops.gemm_status()
+    for r in rows:
+        print(f"{r['op']:26s} {r['shape']:36s} {r['ms']:8.4f} ms {r['tflops']:8.1f} TF/s   torch {r['torch_ms']:8.4f} ms", file=sys.stderr, flush=True)
+    print(json.dumps({"metric": "op_microbenchmarks", "rows": rows}), flush=True)
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
@@ -760,7 +830,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="size sweep instead of the single JSON line")
     ap.add_argument("--sweep-max-mib", type=int, default=1024)
-    ap.add_argument("--workload", default="collectives", choices=["collectives", "gemm", "lm"])
+    ap.add_argument("--workload", default="collectives", choices=["collectives", "gemm", "lm", "ops"])
     ap.add_argument("--lm-batch", type=int, default=32, help="samples per GPU")
     ap.add_argument("--lm-layers", type=int, default=12)
     ap.add_argument("--lm-plan", default="dp_zero", choices=["dp", "dp_zero"])
@@ -774,6 +844,8 @@ def main():
         run_gemm(args)
     elif args.workload == "lm":
         run_lm(args)
+    elif args.workload == "ops":
+        run_ops(args)
     elif args.sweep:
         run_sweep(args)
     else:
