@@ -49,6 +49,7 @@ struct Params {
   int m_tiles, n_tiles, k_blocks;
   unsigned* error;        // device word: 0 or a code left by a wait that ran out
   int tma_store;          // D's pitch and base allow bulk tensor stores
+  int fast_drain;         // tma_store, no activation, and the bias (if any) can be read as aligned 16-byte groups: see drain_fast
   int splits;             // > 1: the contraction is cut into `splits` ranges of kb_per_split slices, each
   int kb_per_split;       //      writing an fp32 partial tile to rows [split * m_pad, ...) of the workspace
   int m_pad;
@@ -201,6 +202,102 @@ __device__ __forceinline__ float apply_epilogue(float v, int epi) {
     case EPI_GELU: return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
     case EPI_SIGMOID: return 1.f / (1.f + __expf(-v));
     default: return v;
+  }
+}
+
+// Convert 32 accumulator columns (one tcgen05.ld) of this thread's row and put them into the
+// warp's swizzled staging tile.  `piece` says which part of the 128-byte staging row they fill.
+template <bool OUT_F32, bool BIAS>
+__device__ __forceinline__ void stage_columns(const unsigned (&r)[32], unsigned char* tile_row, int sw, int piece,
+                                              const __nv_bfloat16* bias, int col, int N) {
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  if constexpr (BIAS) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {   // 8 bias values per 16-byte load, the same address in every lane
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(bias + ((col + 8 * g + 8 <= N) ? col + 8 * g : 0)));
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        v[8 * g + 2 * e] += f.x;
+        v[8 * g + 2 * e + 1] += f.y;
+      }
+    }
+  }
+  if constexpr (OUT_F32) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      *reinterpret_cast<float4*>(tile_row + ((j ^ sw) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]), h1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+      __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]), h3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+      uint4 pk;
+      pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
+      pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
+      *reinterpret_cast<uint4*>(tile_row + (((4 * piece + j) ^ sw) << 4)) = pk;
+    }
+  }
+}
+
+// The common epilogue (bulk tensor stores, no activation, bias absent or readable in aligned
+// 16-byte groups straight from global memory): no shared bias tile and no barrier between the
+// epilogue warps, and the tcgen05.ld of the next 32 columns is in flight while the current ones
+// are converted.  The output width is a multiple of 8 (bf16) or 4 (fp32) here, so a group of 32
+// columns that starts inside the matrix may only overhang it by whole 16-byte groups; the
+// overhang is clipped by the tensor map and its bias reads are redirected to the first group
+// (with a bias the width is a multiple of 8 for either output type).
+template <int BN, bool OUT_F32, bool BIAS>
+__device__ __forceinline__ void drain_fast(const Params& p, const CUtensorMap* tmD, unsigned char* stage_gen, unsigned stage_u32,
+                                           unsigned t_row, int m0, int n0, int bi, int bo, int q, int lane, int& buf) {
+  constexpr int PIECES = OUT_F32 ? 1 : 2;          // 32-column groups per 128-byte staging row
+  constexpr int GROUPS = BN / 32;
+  unsigned char* warp_gen = stage_gen + q * (2 * kWarpTileBytes);
+  const unsigned warp_u32 = stage_u32 + q * (2 * kWarpTileBytes);
+  const int sw = lane & 7;
+  const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(p.bias);
+  const int live = min(GROUPS, (p.N - n0 + 31) / 32);   // groups that start inside the matrix (same in every thread)
+  unsigned char* row0 = warp_gen + lane * 128;
+  // one step: wait for `cur`, start loading the next group into `nxt`, convert and stage `cur`
+  auto step = [&](const unsigned (&cur)[32], unsigned (&nxt)[32], int g, int piece) {
+    tmem_ld_wait();
+    if (g + 1 < live) tmem_ld_32x32(t_row + (unsigned)(32 * (g + 1)), nxt);
+    if (piece == 0) {
+      if (lane == 0) bulk_wait_read_1();             // the store this warp issued two tiles ago has left the buffer
+      __syncwarp();
+    }
+    stage_columns<OUT_F32, BIAS>(cur, row0 + buf * kWarpTileBytes, sw, piece, bias, n0 + 32 * g, p.N);
+    if (piece == PIECES - 1 || g + 1 == live) {
+      fence_proxy_async();                           // make the rows visible to the bulk-copy engine
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_4d(tmD, warp_u32 + buf * kWarpTileBytes, n0 + 32 * (g - piece), m0 + q * 32, bi, bo);
+        bulk_commit_group();
+      }
+      buf ^= 1;
+    }
+  };
+  unsigned ra[32], rb[32];
+  tmem_ld_32x32(t_row, ra);
+#pragma unroll 1
+  for (int g = 0; g < live; g += 2) {
+    step(ra, rb, g, 0);
+    if (g + 1 < live) step(rb, ra, g + 1, PIECES - 1);
+  }
+}
+
+template <int BN>
+__device__ __forceinline__ void drain_fast_any(const Params& p, const CUtensorMap* tmD, unsigned char* stage_gen, unsigned stage_u32,
+                                               unsigned t_row, int m0, int n0, int bi, int bo, int q, int lane, int& buf) {
+  if (p.out_f32) {
+    if (p.bias) drain_fast<BN, true, true>(p, tmD, stage_gen, stage_u32, t_row, m0, n0, bi, bo, q, lane, buf);
+    else drain_fast<BN, true, false>(p, tmD, stage_gen, stage_u32, t_row, m0, n0, bi, bo, q, lane, buf);
+  } else {
+    if (p.bias) drain_fast<BN, false, true>(p, tmD, stage_gen, stage_u32, t_row, m0, n0, bi, bo, q, lane, buf);
+    else drain_fast<BN, false, false>(p, tmD, stage_gen, stage_u32, t_row, m0, n0, bi, bo, q, lane, buf);
   }
 }
 
@@ -543,19 +640,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int b = unit / tiles_per_batch, tile = unit - b * tiles_per_batch;
       const int bo = b / p.batch_in, bi = b - bo * p.batch_in;
       const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * BN;
-      // bias tile -> shared (fp32)
-      asm volatile("bar.sync 1, 128;" ::: "memory");   // previous tile's readers are done with bias_tile
-      for (int j = et; j < BN; j += kEpilogueThreads) {
-        float b = 0.f;
-        if (p.bias != nullptr && n0 + j < p.N) b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n0 + j]);
-        bias_tile[j] = b;
+      if (!p.fast_drain) {
+        // bias tile -> shared (fp32)
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // previous tile's readers are done with bias_tile
+        for (int j = et; j < BN; j += kEpilogueThreads) {
+          float b = 0.f;
+          if (p.bias != nullptr && n0 + j < p.N) b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n0 + j]);
+          bias_tile[j] = b;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
       ok = epilogue_all(mbar_wait(tfull_bar(acc), acc_phase));
       if (!ok) break;
       tc_fence_after();
       const unsigned t_row = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(acc * BN);
-      drain_tile<BN>(p, &tmD, p.tma_store != 0, store_gen, store_u32, bias_tile, t_row, m0, n0, bi, bo, q, lane, et, store_buf);
+      if (p.fast_drain) drain_fast_any<BN>(p, &tmD, store_gen, store_u32, t_row, m0, n0, bi, bo, q, lane, store_buf);
+      else drain_tile<BN>(p, &tmD, p.tma_store != 0, store_gen, store_u32, bias_tile, t_row, m0, n0, bi, bo, q, lane, et, store_buf);
       tc_fence_before();
       mbar_arrive(tempty_bar(acc));     // this thread has drained its part of the accumulator
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
@@ -631,25 +731,24 @@ __device__ __forceinline__ void umma2_commit_both(unsigned bar) {
                : "memory");
 }
 
-template <bool A_MN, bool B_MN>
+template <int BN_, bool A_MN, bool B_MN>
 struct Cfg2 {
-  static constexpr int BN = 256;                     // output columns per pair tile
-  static constexpr int STAGES = 6;
+  static constexpr int BN = BN_;                     // output columns per pair tile
+  static constexpr int STAGES = (BN_ >= 256) ? 6 : 8;
   static constexpr unsigned A_BYTES = BM * BK * 2;   // this CTA's 128 rows
   static constexpr unsigned B_BYTES = (BN / 2) * BK * 2;
   static constexpr unsigned STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr unsigned TMEM_COLS = 512;
+  static constexpr unsigned TMEM_COLS = 2 * BN_;
   static constexpr unsigned SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 2 * kStoreTileBytes + BN * 4 + 256;
   static constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
                                     ((unsigned)(BN >> 3) << 17) | ((unsigned)((2 * BM) >> 4) << 24);
 };
 
-template <bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool SOFTMAX>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmD, const Params p) {
-  using C = Cfg2<A_MN, B_MN>;
-  constexpr int BN = C::BN;
+  using C = Cfg2<BN, A_MN, B_MN>;
   extern __shared__ unsigned char smem_raw[];
   const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -718,7 +817,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             tma_load_4d_pair(sb, &tmB, k0, n0, bi, boB, leader_full);
           } else {
 #pragma unroll
-            for (int i = 0; i < BN / 128; ++i) tma_load_4d_pair(sb + i * 8192u, &tmB, n0 + 64 * i, k0, bi, boB, leader_full);
+            for (int i = 0; i < BN / 128; ++i) tma_load_4d_pair(sb + i * 8192u, &tmB, n0 + 64 * i, k0, bi, boB, leader_full);   // BN/2 columns per CTA
           }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -770,18 +869,21 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const int bo = b / p.batch_in, bi = b - bo * p.batch_in;
       // with split-K the partial tile goes to the workspace, whose rows are [split][m_pad]
       const int m0 = (tile % p.m_tiles) * (2 * BM) + (int)cta * BM + sp * p.m_pad, n0 = (tile / p.m_tiles) * BN;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      for (int j = et; j < BN; j += kEpilogueThreads) {
-        float b = 0.f;
-        if (p.bias != nullptr && n0 + j < p.N) b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n0 + j]);
-        bias_tile[j] = b;
+      if (!p.fast_drain) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        for (int j = et; j < BN; j += kEpilogueThreads) {
+          float b = 0.f;
+          if (p.bias != nullptr && n0 + j < p.N) b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n0 + j]);
+          bias_tile[j] = b;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
       ok = epilogue_all(mbar_wait(tfull_bar(acc), acc_phase));
       if (!ok) break;
       tc_fence_after();
       const unsigned t_row = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(acc * BN);
-      if (p.softmax) drain_tile_softmax<BN>(p, &tmD, store_gen, store_u32, t_row, m0, bi, bo, q, lane, store_buf);
+      if constexpr (SOFTMAX) drain_tile_softmax<BN>(p, &tmD, store_gen, store_u32, t_row, m0, bi, bo, q, lane, store_buf);
+      else if (p.fast_drain) drain_fast_any<BN>(p, &tmD, store_gen, store_u32, t_row, m0, n0, bi, bo, q, lane, store_buf);
       else drain_tile<BN>(p, &tmD, p.tma_store != 0, store_gen, store_u32, bias_tile, t_row, m0, n0, bi, bo, q, lane, et, store_buf);
       tc_fence_before();
       mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));   // tell the leader this thread has drained its rows
@@ -896,12 +998,22 @@ static int device_state(DeviceState** out) {
   return HAPX_OK;
 }
 
+// The barrier-free epilogue applies when D goes out through bulk tensor stores, there is no
+// activation, and a bias can be fetched in aligned groups of 8.
+static bool fast_drain_ok(const Params& p) {
+  static const bool off = std::getenv("HAPX_GEMM_SLOW_DRAIN") != nullptr;
+  if (off || !p.tma_store || p.epilogue != EPI_NONE || p.softmax) return false;
+  if (p.bias && ((reinterpret_cast<uintptr_t>(p.bias) & 15u) != 0 || (p.N & 7) != 0)) return false;
+  return true;
+}
+
 template <int BN, bool A_MN, bool B_MN>
 static int launch(const Operand& A, const Operand& B, const Operand& Dop, Params& p, cudaStream_t stream, int sm_count) {
   using C = Cfg<BN, A_MN, B_MN>;
   const int batch_out = p.batch / p.batch_in;
   CUtensorMap tmA, tmB, tmD;
   if (int e = make_out_map(&tmD, &p.tma_store, p.D, p.N, p.M, p.ldd, p.out_f32, p.batch_in, Dop.s_in, batch_out, Dop.s_out)) return e;
+  p.fast_drain = fast_drain_ok(p);
   if (int e = make_map(&tmA, A, p.M, p.Kc, BM, p.batch_in, p.a_shared_out ? 1 : batch_out)) return e;
   if (int e = make_map(&tmB, B, p.N, p.Kc, BN, p.batch_in, p.b_shared_out ? 1 : batch_out)) return e;
   p.m_tiles = (p.M + BM - 1) / BM;
@@ -965,10 +1077,10 @@ static int workspace(int device, size_t bytes, float** out) {
   return HAPX_OK;
 }
 
-template <bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool SOFTMAX = false>
 static int launch2(const Operand& A, const Operand& B, const Operand& Dop, Params& p, cudaStream_t stream, int sm_count) {
-  using C = Cfg2<A_MN, B_MN>;
-  auto kernel = gemm2_bf16_kernel<A_MN, B_MN>;
+  using C = Cfg2<BN, A_MN, B_MN>;
+  auto kernel = gemm2_bf16_kernel<BN, A_MN, B_MN, SOFTMAX>;
   static int max_clusters = 0;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
@@ -1019,6 +1131,7 @@ static int launch2(const Operand& A, const Operand& B, const Operand& Dop, Param
   const int batch_out = p.batch / p.batch_in;
   const long long out_rows = p.splits > 1 ? (long long)p.splits * p.m_pad : p.M;
   if (int e = make_out_map(&tmD, &p.tma_store, p.D, p.N, out_rows, p.ldd, p.out_f32, p.batch_in, Dop.s_in, batch_out, Dop.s_out)) return e;
+  p.fast_drain = fast_drain_ok(p);
   if (p.splits > 1 && !p.tma_store) return fail(HAPX_ERR_EXTENT, "gemm: split-K needs an output width that is a multiple of 4");
   if (p.softmax && !p.tma_store) return fail(HAPX_ERR_EXTENT, "gemm: the row-softmax epilogue needs a 16-byte aligned output pitch");
   if (int e = make_map(&tmA, A, p.M, p.Kc, BM, p.batch_in, p.a_shared_out ? 1 : batch_out)) return e;
@@ -1080,9 +1193,11 @@ int gemm_bf16(const Operand& Dop, int out_f32, const Operand& A, const Operand& 
   // SM pairs (256 x 256 tiles, half the B traffic per SM) whenever there is more than one row tile
   static const bool pair_kernel = std::getenv("HAPX_GEMM_SINGLE_CTA") == nullptr;
   if (pair_kernel && M > BM && N > 64) {
-    if (!a_mn && !b_mn) return launch2<false, false>(A, B, Dop, p, stream, dev->sm_count);
-    if (!a_mn && b_mn) return launch2<false, true>(A, B, Dop, p, stream, dev->sm_count);
-    if (a_mn && b_mn) return launch2<true, true>(A, B, Dop, p, stream, dev->sm_count);
+    // (256 x 128 pair tiles were measured too: slower than 256 x 256 even where they fill the waves better)
+    if (softmax) return launch2<256, false, false, true>(A, B, Dop, p, stream, dev->sm_count);   // the only variant that carries the softmax epilogue
+    if (!a_mn && !b_mn) return launch2<256, false, false>(A, B, Dop, p, stream, dev->sm_count);
+    if (!a_mn && b_mn) return launch2<256, false, true>(A, B, Dop, p, stream, dev->sm_count);
+    if (a_mn && b_mn) return launch2<256, true, true>(A, B, Dop, p, stream, dev->sm_count);
   }
   // single-CTA tiles: fewest waves first, then the wider tile
   auto waves = [&](int bn) {
