@@ -756,9 +756,10 @@ def run_ops(args):
         return statistics.median(ts)
 
     rows = []
+    parts = set(args.ops.split(","))
     g = torch.Generator(dev).manual_seed(39)
     for name, L, n, H, D, causal in (("LM attention", 256, 32, 12, 64, True), ("ViT attention", 197, 64, 12, 64, False),
-                                     ("MoE attention", 512, 16, 16, 64, True)):
+                                     ("MoE attention", 512, 16, 16, 64, True)) if "attention" in parts else ():
         E = H * D
         qkv = torch.randn(L, n, 3 * E, device=dev, generator=g).to(torch.bfloat16).requires_grad_(True)
         go = torch.randn(L, n, E, device=dev, generator=g).to(torch.bfloat16)
@@ -781,19 +782,51 @@ def run_ops(args):
     x = torch.randn(b, s, d, device=dev, generator=g).to(torch.bfloat16)
     disp = (torch.rand(b, s, e, c, device=dev, generator=g) < 0.003).to(torch.bfloat16)
     for code, a_, b_, fl in (("bsd,bsec->becd", x, disp, 2.0 * b * s * e * c * d),
-                             ("becd,bsec->bsd", torch.randn(b, e, c, d, device=dev, generator=g).to(torch.bfloat16), disp, 2.0 * b * s * e * c * d)):
+                             ("becd,bsec->bsd", torch.randn(b, e, c, d, device=dev, generator=g).to(torch.bfloat16), disp, 2.0 * b * s * e * c * d)) if "einsum" in parts else ():
         t, tr = timeit(lambda: einsum(code, a_, b_)), timeit(lambda: torch.einsum(code, a_, b_))
         rows.append({"op": code, "shape": f"b={b} s={s} e={e} c={c} d={d}", "ms": t, "torch_ms": tr, "tflops": fl / t / 1e9})
-    for el in (7, 4, 2):        # experts on this GPU under the r8 split of 32 experts
+    for el in (7, 4, 2) if "einsum" in parts else ():        # experts on this GPU under the r8 split of 32 experts
         bg = 128
         w1 = (torch.randn(el, d, h, device=dev, generator=g) * d ** -0.5).to(torch.bfloat16)
         inp = torch.randn(bg, el, c, d, device=dev, generator=g).to(torch.bfloat16)
         fl = 2.0 * bg * el * c * d * h
         t, tr = timeit(lambda: einsum("edh,becd->bech", w1, inp)), timeit(lambda: torch.einsum("edh,becd->bech", w1, inp))
         rows.append({"op": "edh,becd->bech", "shape": f"b={bg} e={el} c={c} d={d} h={h}", "ms": t, "torch_ms": tr, "tflops": fl / t / 1e9})
+    if "tail" in parts:
+        # step tail: clip by the gradient norm + Adam over the parameter tensors of the Transformer-LM
+        # configuration (bf16; 12 layers + embeddings + head), against torch's clip_grad_norm_ + Adam
+        from hap_b200.optim import ClipAdam
+        shapes = [(33280, 768), (256, 768)] + [s_ for _ in range(12) for s_ in
+                  ((768,), (768,), (2304, 768), (2304,), (768, 768), (768,), (768,), (768,), (3072, 768), (3072,), (768, 3072), (768,))] + [(768,), (768,), (33280, 768), (33280,)]
+        mine_p = [torch.nn.Parameter((torch.randn(s_, device=dev, generator=g) * 0.02).to(torch.bfloat16)) for s_ in shapes]
+        ref_p = [torch.nn.Parameter(p_.detach().clone()) for p_ in mine_p]
+        for p_, q_ in zip(mine_p, ref_p):
+            p_.grad = (torch.randn(p_.shape, device=dev, generator=g) * 0.01).to(torch.bfloat16)
+            q_.grad = p_.grad.clone()
+        fused, ref_opt = ClipAdam(mine_p, lr=5e-4, max_norm=0.5), torch.optim.Adam(ref_p, lr=5e-4)
+
+        def ref_tail():
+            torch.nn.utils.clip_grad_norm_(ref_p, 0.5)
+            ref_opt.step()
+
+        elems = sum(p_.numel() for p_ in mine_p)
+        tail_bytes = elems * 2 * 8                    # norm pass reads g; update reads g, p, m, v and writes p, m, v
+        t_eager, tr = timeit(fused.step), timeit(ref_tail)
+        # the kernels alone: the same step replayed from a CUDA graph (no host time between launches)
+        side = torch.cuda.Stream()
+        tail_graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(tail_graph, stream=side):
+                fused.step()
+        t = timeit(tail_graph.replay)
+        peak = float(measured_peaks()[0]["hbm_gbs"])
+        rows.append({"op": "clip + Adam step tail", "shape": f"{len(shapes)} tensors, {elems / 1e6:.1f} M bf16 elements", "ms": t, "torch_ms": tr,
+                     "eager_ms": t_eager, "tflops": 0.0, "gbs": tail_bytes / t / 1e6, "frac_of_hbm_peak": tail_bytes / t / 1e6 / peak})
     hap_b200.linear_ops.gemm_status()
     for r in rows:
-        print(f"{r['op']:26s} {r['shape']:36s} {r['ms']:8.4f} ms {r['tflops']:8.1f} TF/s   torch {r['torch_ms']:8.4f} ms", file=sys.stderr, flush=True)
+        extra = f"  {r['gbs']:8.0f} GB/s ({100 * r['frac_of_hbm_peak']:.0f}% of measured HBM peak; {r['eager_ms']:.4f} ms issued eagerly)" if "gbs" in r else ""
+        print(f"{r['op']:26s} {r['shape']:36s} {r['ms']:8.4f} ms {r['tflops']:8.1f} TF/s   torch {r['torch_ms']:8.4f} ms{extra}", file=sys.stderr, flush=True)
     print(json.dumps({"metric": "op_microbenchmarks", "rows": rows}), flush=True)
 
 def run_reference_arm(args):
@@ -837,6 +870,7 @@ def main():
     ap.add_argument("--lm-graph", action="store_true", help="capture the training step into a CUDA graph")
     ap.add_argument("--gemm-tokens", type=int, default=8192)
     ap.add_argument("--gemm-layers", default="", help="comma-separated layer names to restrict the gemm workload to")
+    ap.add_argument("--ops", default="attention,einsum,tail", help="parts of the ops workload to run")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

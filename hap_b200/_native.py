@@ -17,6 +17,7 @@ IPC_HANDLE_BYTES = 64
 OK, ERR_ARGUMENT, ERR_EXTENT, ERR_DTYPE, ERR_CUDA, ERR_PEER_TIMEOUT, ERR_STAGING, ERR_STATE = 0, -1, -2, -3, -4, -5, -6, -7
 F32, BF16, F16, F64, B8, B16, B32, B64 = range(8)
 MODE_PADDING, MODE_GROUP_CALL = 0, 1
+OPTIM_STATE_FLOATS = 2056
 
 _i64, _int, _dbl, _vp, _sz = C.c_int64, C.c_int, C.c_double, C.c_void_p, C.c_size_t
 _pp = C.POINTER(C.c_void_p)
@@ -53,6 +54,8 @@ SIGNATURES = {
     "hapx_gemm_status": (_int, []),
     "hapx_attention_forward": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp]),
     "hapx_attention_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
+    "hapx_grad_sqnorm": (_int, [_int, _pp, _pi64, _int, _vp, _int, _vp]),
+    "hapx_clip_adam_apply": (_int, [_int, _pp, _pp, _pp, _pp, _pi64, _int, _dbl, _dbl, _dbl, _dbl, _dbl, _dbl, _vp, _int, _vp]),
     "hapx_local_all_reduce_noalloc": (_int, [_int, _pp, _pp, _int, _int, _dbl, _i64, _vp]),
     "hapx_debug_host_walk": (_int, [_int, _int, _int, _int, _i64, _i64, _i64, _int, _pi64, _pi64, _pp,
                                      C.POINTER(_sz), _vp, _sz, _vp]),

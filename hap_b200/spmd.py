@@ -29,13 +29,22 @@ def _is_collective(target) -> bool:
     return getattr(target, "__name__", None) in _COLLECTIVE_NAMES and module in ("collectives", "gloo_port")
 
 
+def _make_optimizer(params, lr, clip):
+    """Fused clip + Adam kernels for parameters on a GPU; torch's Adam (clipped by the caller) for
+    host tensors, which only the CPU checks of the executors use."""
+    if params and all(p.is_cuda and p.dtype in (torch.float32, torch.bfloat16) for p in params):
+        from .optim import ClipAdam
+        return ClipAdam(params, lr=lr, max_norm=clip)
+    return torch.optim.Adam(params, lr=lr)
+
+
 class LockstepWorld:
     def __init__(self, modules: Sequence[torch.fx.GraphModule], backend, lr: float = 5e-4, clip: float = 0.5):
         self.modules = list(modules)
         self.world = len(self.modules)
         self.backend = backend
         self.clip = clip
-        self.optimizers = [torch.optim.Adam(m.parameters(), lr=lr) for m in self.modules]
+        self.optimizers = [_make_optimizer(list(m.parameters()), lr, clip) for m in self.modules]
         self._nodes = [list(m.graph.nodes) for m in self.modules]
         if len({len(n) for n in self._nodes}) != 1:
             raise ValueError("SPMD ranks must run the same node sequence")
@@ -90,7 +99,8 @@ class LockstepWorld:
         total = torch.stack([l.detach() for l in losses]).sum()
         torch.stack(losses).sum().backward()
         for m, opt in zip(self.modules, self.optimizers):
-            torch.nn.utils.clip_grad_norm_(m.parameters(), self.clip)
+            if isinstance(opt, torch.optim.Optimizer):      # host tensors: the reference's own pair
+                torch.nn.utils.clip_grad_norm_(m.parameters(), self.clip)
             opt.step()
         return total
 
@@ -106,10 +116,18 @@ class ProcessWorker:
     """
 
     def __init__(self, module: torch.fx.GraphModule, lr: float = 5e-4, clip: float = 0.5,
-                 reduce_loss: Callable[[torch.Tensor], torch.Tensor] = None, comm=None):
+                 reduce_loss: Callable[[torch.Tensor], torch.Tensor] = None, comm=None, fused_tail: bool = None):
         self.module = module
         self.clip = clip
-        self.optimizer = torch.optim.Adam(module.parameters(), lr=lr)
+        params = list(module.parameters())
+        on_gpu = bool(params) and all(p.is_cuda and p.dtype in (torch.float32, torch.bfloat16) for p in params)
+        self.fused_tail = on_gpu if fused_tail is None else bool(fused_tail)
+        if self.fused_tail:
+            # clip by the local-shard norm + Adam as multi-tensor kernels without a host round trip
+            from .optim import ClipAdam
+            self.optimizer = ClipAdam(params, lr=lr, max_norm=clip)
+        else:
+            self.optimizer = torch.optim.Adam(params, lr=lr)
         self.reduce_loss = reduce_loss
         self.comm = comm
         self._buckets = []          # (flat tensor in the heap, [parameters])
@@ -152,10 +170,11 @@ class ProcessWorker:
         callable ``replay(*inputs) -> total loss`` that copies the inputs into the graph's static
         buffers and launches the graph: the per-node Python dispatch of the eager step (the
         reference's hot loop (i), ``worker.py:58-83``) disappears.  Needs a capturable optimizer
-        (this re-creates Adam with ``capturable=True``) and at least two collectives per iteration;
+        (the fused step tail is; torch's Adam is re-created with ``capturable=True``) and at least two collectives per iteration;
         all ranks must replay the same number of times."""
-        lr = self.optimizer.param_groups[0]["lr"]
-        self.optimizer = torch.optim.Adam(self.module.parameters(), lr=lr, capturable=True)
+        if not self.fused_tail:
+            lr = self.optimizer.param_groups[0]["lr"]
+            self.optimizer = torch.optim.Adam(self.module.parameters(), lr=lr, capturable=True)
         static_in = [t.clone() for t in example_inputs]
         if self.comm is not None:
             self.comm.set_stream_ordering(False)
@@ -196,6 +215,7 @@ class ProcessWorker:
                 self.comm.all_reduce([flat], inplace=True)
         else:
             loss.backward()
-        torch.nn.utils.clip_grad_norm_(self.module.parameters(), self.clip)
+        if not self.fused_tail:
+            torch.nn.utils.clip_grad_norm_(self.module.parameters(), self.clip)
         self.optimizer.step()
         return total

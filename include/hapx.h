@@ -216,6 +216,33 @@ int hapx_attention_backward(void* dqkv, void* dscores_ws, void* ds_ws, const voi
 int hapx_local_all_reduce_noalloc(int world, void* const* dst, const void* const* src, int in_dtype, int out_dtype,
                                   double scale, int64_t n, hapx_stream stream);
 
+/* ---- step tail: gradient clipping + Adam over the local parameter shards ----------
+ * Replaces torch.nn.utils.clip_grad_norm_(dmodel.parameters(), 0.5) and optimizer.step() of
+ * the reference's iteration (worker.py:74, 76; optimizer created at worker.py:47 as
+ * torch.optim.Adam with default betas / eps) by multi-tensor kernels that never synchronise
+ * with the host.  The norm is the 2-norm over the shards THIS rank holds, as in the reference
+ * (no collective).
+ *
+ * `state`: HAPX_OPTIM_STATE_FLOATS floats of device memory owned by the caller, zero-filled
+ * once before the first step: [0] steps taken so far, [1] last gradient norm, [2] last clip
+ * coefficient, [8...] partial sums of squares.
+ *
+ * hapx_grad_sqnorm adds the sum of squares of `n` gradient tensors (numel[i] elements of
+ * `dtype`, HAPX_F32 or HAPX_BF16) into the state; reset != 0 starts a new sum.  Call it once
+ * per dtype group, the first with reset = 1.
+ * hapx_clip_adam_apply scales every gradient by min(1, max_norm / (norm + 1e-6)) (max_norm <= 0:
+ * no clipping, the state's sum is not read), then applies the Adam update in fp32 and rounds
+ * once: exp_avg, exp_avg_sq and params have `dtype`; gradients are left unmodified (the
+ * reference's clip_grad_norm_ scales them in place).  advance_step != 0 increments the step
+ * count after the update: pass it on the last group of an iteration. */
+#define HAPX_OPTIM_STATE_FLOATS 2056
+int hapx_grad_sqnorm(int n, const void* const* grads, const int64_t* numel, int dtype, float* state, int reset,
+                     hapx_stream stream);
+int hapx_clip_adam_apply(int n, void* const* params, const void* const* grads, void* const* exp_avg,
+                         void* const* exp_avg_sq, const int64_t* numel, int dtype, double lr, double beta1, double beta2,
+                         double eps, double weight_decay, double max_norm, float* state, int advance_step,
+                         hapx_stream stream);
+
 /* ---- diagnostics ----------------------------------------------------------------
  * No counterpart in the reference.  Walks the kernels' tiling of ONE rank's pull over
  * HOST buffers (op: 0 gather, 1 all-to-all, 2 slice, 3 slice-backward), bounds-checking
