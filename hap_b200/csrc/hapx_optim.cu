@@ -17,7 +17,7 @@ namespace hapx {
 namespace optim {
 
 constexpr int kListMax = 64;            // tensors per launch (kernel parameters stay below 4 KiB)
-constexpr int kChunk = 16384;           // elements per block visit
+constexpr int kChunk = 8192;            // elements per block visit
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;             // 16-byte loads in flight per thread in the norm kernel
 constexpr int kUnrollAdam = 2;         // ... per stream (g, p, m, v) in the update kernel
@@ -84,55 +84,75 @@ __device__ __forceinline__ float block_sum(float x) {
   return s;   // valid in thread 0
 }
 
-// Block b visits the chunks whose global index (over all tensors of the list, in list order) is
-// congruent to b modulo the grid size.
+// Work schedule shared by both kernels: the tensors of a list are cut into chunks of kChunk
+// elements, numbered through the list; block b takes the chunks b, b + G, b + 2G, ...  Thread 0
+// builds the prefix sums of the chunk counts once per block; a chunk's tensor is then found by
+// bisection (the same few shared-memory reads in every thread).
+template <typename List>
+__device__ __forceinline__ long long build_schedule(const List& list, long long* prefix) {
+  if (threadIdx.x == 0) {
+    long long run = 0;
+    for (int t = 0; t < list.n; ++t) {
+      prefix[t] = run;
+      run += (list.numel[t] + kChunk - 1) / kChunk;
+    }
+    prefix[list.n] = run;
+  }
+  __syncthreads();
+  return prefix[list.n];
+}
+__device__ __forceinline__ int tensor_of_chunk(const long long* prefix, int n, long long chunk) {
+  int lo = 0, hi = n - 1;            // largest t with prefix[t] <= chunk
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (prefix[mid] <= chunk) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 4) sqnorm_kernel(const NormList list, float* state, int reset) {
+  __shared__ long long s_prefix[kListMax + 1];
+  const long long total_chunks = build_schedule(list, s_prefix);
   float acc = 0.f;
-  long long chunk_base = 0;
-  const int G = gridDim.x, b = blockIdx.x;
-  for (int t = 0; t < list.n; ++t) {
-    const long long n = list.numel[t];
-    const long long chunks = (n + kChunk - 1) / kChunk;
+  for (long long gc = blockIdx.x; gc < total_chunks; gc += gridDim.x) {
+    const int t = tensor_of_chunk(s_prefix, list.n, gc);
+    const long long n = list.numel[t], c = gc - s_prefix[t];
     const T* g = reinterpret_cast<const T*>(list.g[t]);
     const bool vec = (reinterpret_cast<uintptr_t>(g) & 15u) == 0;
-    long long c = ((b - chunk_base) % G + G) % G;
-    for (; c < chunks; c += G) {
-      const long long lo = c * kChunk, hi = min(lo + (long long)kChunk, n);
-      if (vec) {
-        using W = Words<T>;
-        constexpr int N = W::N;
-        const T* gc = g + lo;                                   // 32-bit offsets inside the chunk
-        const int len = (int)(hi - lo), full = (len / N) * N;
-        // kUnroll independent 16-byte loads per thread are in flight before any is used
-        for (int i0 = threadIdx.x * N; i0 < full; i0 += kThreads * N * kUnroll) {
-          uint4 x[kUnroll];
+    const long long lo = c * kChunk, hi = min(lo + (long long)kChunk, n);
+    if (vec) {
+      using W = Words<T>;
+      constexpr int N = W::N;
+      const T* gp = g + lo;                                   // 32-bit offsets inside the chunk
+      const int len = (int)(hi - lo), full = (len / N) * N;
+      // kUnroll independent 16-byte loads per thread are in flight before any is used
+      for (int i0 = threadIdx.x * N; i0 < full; i0 += kThreads * N * kUnroll) {
+        uint4 x[kUnroll];
 #pragma unroll
-          for (int u = 0; u < kUnroll; ++u) {
-            const int i = i0 + u * kThreads * N;
-            x[u] = (i < full) ? *reinterpret_cast<const uint4*>(gc + i) : make_uint4(0u, 0u, 0u, 0u);   // zeros add nothing
-          }
+        for (int u = 0; u < kUnroll; ++u) {
+          const int i = i0 + u * kThreads * N;
+          x[u] = (i < full) ? *reinterpret_cast<const uint4*>(gp + i) : make_uint4(0u, 0u, 0u, 0u);   // zeros add nothing
+        }
 #pragma unroll
-          for (int u = 0; u < kUnroll; ++u) {
+        for (int u = 0; u < kUnroll; ++u) {
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-              float f[2] = {0.f, 0.f};
-              W::unpack(word_of(x[u], w), f);
+          for (int w = 0; w < 4; ++w) {
+            float f[2] = {0.f, 0.f};
+            W::unpack(word_of(x[u], w), f);
 #pragma unroll
-              for (int k = 0; k < W::PER; ++k) acc = fmaf(f[k], f[k], acc);
-            }
+            for (int k = 0; k < W::PER; ++k) acc = fmaf(f[k], f[k], acc);
           }
         }
-        for (int i = full + threadIdx.x; i < len; i += kThreads) { const float f = to_f(gc[i]); acc = fmaf(f, f, acc); }
-      } else {
-        for (long long i = lo + threadIdx.x; i < hi; i += kThreads) { const float f = to_f(g[i]); acc = fmaf(f, f, acc); }
       }
+      for (int i = full + threadIdx.x; i < len; i += kThreads) { const float f = to_f(gp[i]); acc = fmaf(f, f, acc); }
+    } else {
+      for (long long i = lo + threadIdx.x; i < hi; i += kThreads) { const float f = to_f(g[i]); acc = fmaf(f, f, acc); }
     }
-    chunk_base += chunks;
   }
   const float s = block_sum(acc);
   if (threadIdx.x == 0) {
-    float* slot = state + 8 + b;
+    float* slot = state + 8 + blockIdx.x;
     *slot = reset ? s : *slot + s;
   }
 }
@@ -140,7 +160,7 @@ __global__ void __launch_bounds__(kThreads, 4) sqnorm_kernel(const NormList list
 // state[0] = number of optimizer steps taken so far; state[8 + i] = partial sums of squares.
 // state[1] (norm) and state[2] (clip coefficient) are written for the host to inspect.
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 3) clip_adam_kernel(const AdamList list, float* state, int slots, double lr_d, double beta1_d,
+__global__ void __launch_bounds__(kThreads, 4) clip_adam_kernel(const AdamList list, float* state, int slots, double lr_d, double beta1_d,
                                                              double beta2_d, float eps, float weight_decay, float max_norm) {
   __shared__ float s_coef, s_step_size, s_inv_bc2s;
   // the host-side reference forms 1 - beta in double and rounds it to float once
@@ -187,66 +207,62 @@ __global__ void __launch_bounds__(kThreads, 3) clip_adam_kernel(const AdamList l
     p = fmaf(-step_size, __fdividef(m, denom), p);
   };
 
-  long long chunk_base = 0;
-  const int G = gridDim.x, b = blockIdx.x;
-  for (int t = 0; t < list.n; ++t) {
-    const long long n = list.numel[t];
-    const long long chunks = (n + kChunk - 1) / kChunk;
+  __shared__ long long s_prefix[kListMax + 1];
+  const long long total_chunks = build_schedule(list, s_prefix);
+  for (long long gc = blockIdx.x; gc < total_chunks; gc += gridDim.x) {
+    const int t = tensor_of_chunk(s_prefix, list.n, gc);
+    const long long n = list.numel[t], c = gc - s_prefix[t];
     T* p = reinterpret_cast<T*>(list.p[t]);
     const T* g = reinterpret_cast<const T*>(list.g[t]);
     T* m = reinterpret_cast<T*>(list.m[t]);
     T* v = reinterpret_cast<T*>(list.v[t]);
     const bool vec = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
                        reinterpret_cast<uintptr_t>(v)) & 15u) == 0;
-    long long c = ((b - chunk_base) % G + G) % G;
-    for (; c < chunks; c += G) {
-      const long long lo = c * kChunk, hi = min(lo + (long long)kChunk, n);
-      long long tail = lo;
-      if (vec) {
-        using W = Words<T>;
-        constexpr int N = W::N;
-        T* pc = p + lo; const T* gc = g + lo; T* mc = m + lo; T* vc = v + lo;     // 32-bit offsets inside the chunk
-        const int full = ((int)(hi - lo) / N) * N;
-        for (int i0 = threadIdx.x * N; i0 < full; i0 += kThreads * N * kUnrollAdam) {
-          uint4 xp[kUnrollAdam], xg[kUnrollAdam], xm[kUnrollAdam], xv[kUnrollAdam];
+    const long long lo = c * kChunk, hi = min(lo + (long long)kChunk, n);
+    long long tail = lo;
+    if (vec) {
+      using W = Words<T>;
+      constexpr int N = W::N;
+      T* pc = p + lo; const T* gp = g + lo; T* mc = m + lo; T* vc = v + lo;     // 32-bit offsets inside the chunk
+      const int full = ((int)(hi - lo) / N) * N;
+      for (int i0 = threadIdx.x * N; i0 < full; i0 += kThreads * N * kUnrollAdam) {
+        uint4 xp[kUnrollAdam], xg[kUnrollAdam], xm[kUnrollAdam], xv[kUnrollAdam];
 #pragma unroll
-          for (int u = 0; u < kUnrollAdam; ++u) {          // all loads first: 4 * kUnrollAdam in flight per thread
-            const int i = i0 + u * kThreads * N;
-            if (i < full) {
-              xp[u] = *reinterpret_cast<const uint4*>(pc + i);
-              xg[u] = *reinterpret_cast<const uint4*>(gc + i);
-              xm[u] = *reinterpret_cast<const uint4*>(mc + i);
-              xv[u] = *reinterpret_cast<const uint4*>(vc + i);
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < kUnrollAdam; ++u) {
-            const int i = i0 + u * kThreads * N;
-            if (i < full) {
-#pragma unroll
-              for (int w = 0; w < 4; ++w) {                  // word by word: 1 (fp32) or 2 (bf16) elements
-                float fp[2], fg[2], fm[2], fv[2];
-                W::unpack(word_of(xp[u], w), fp); W::unpack(word_of(xg[u], w), fg);
-                W::unpack(word_of(xm[u], w), fm); W::unpack(word_of(xv[u], w), fv);
-#pragma unroll
-                for (int k = 0; k < W::PER; ++k) update(fp[k], fg[k], fm[k], fv[k]);
-                set_word(xp[u], w, W::pack(fp)); set_word(xm[u], w, W::pack(fm)); set_word(xv[u], w, W::pack(fv));
-              }
-              *reinterpret_cast<uint4*>(pc + i) = xp[u];
-              *reinterpret_cast<uint4*>(mc + i) = xm[u];
-              *reinterpret_cast<uint4*>(vc + i) = xv[u];
-            }
+        for (int u = 0; u < kUnrollAdam; ++u) {          // all loads first: 4 * kUnrollAdam in flight per thread
+          const int i = i0 + u * kThreads * N;
+          if (i < full) {
+            xp[u] = *reinterpret_cast<const uint4*>(pc + i);
+            xg[u] = *reinterpret_cast<const uint4*>(gp + i);
+            xm[u] = *reinterpret_cast<const uint4*>(mc + i);
+            xv[u] = *reinterpret_cast<const uint4*>(vc + i);
           }
         }
-        tail = lo + full;
+#pragma unroll
+        for (int u = 0; u < kUnrollAdam; ++u) {
+          const int i = i0 + u * kThreads * N;
+          if (i < full) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {                  // word by word: 1 (fp32) or 2 (bf16) elements
+              float fp[2], fg[2], fm[2], fv[2];
+              W::unpack(word_of(xp[u], w), fp); W::unpack(word_of(xg[u], w), fg);
+              W::unpack(word_of(xm[u], w), fm); W::unpack(word_of(xv[u], w), fv);
+#pragma unroll
+              for (int k = 0; k < W::PER; ++k) update(fp[k], fg[k], fm[k], fv[k]);
+              set_word(xp[u], w, W::pack(fp)); set_word(xm[u], w, W::pack(fm)); set_word(xv[u], w, W::pack(fv));
+            }
+            *reinterpret_cast<uint4*>(pc + i) = xp[u];
+            *reinterpret_cast<uint4*>(mc + i) = xm[u];
+            *reinterpret_cast<uint4*>(vc + i) = xv[u];
+          }
+        }
       }
-      for (long long i = tail + threadIdx.x; i < hi; i += kThreads) {
-        float fp = to_f(p[i]), fm = to_f(m[i]), fv = to_f(v[i]);
-        update(fp, to_f(g[i]), fm, fv);
-        from_f(p[i], fp); from_f(m[i], fm); from_f(v[i], fv);
-      }
+      tail = lo + full;
     }
-    chunk_base += chunks;
+    for (long long i = tail + threadIdx.x; i < hi; i += kThreads) {
+      float fp = to_f(p[i]), fm = to_f(m[i]), fv = to_f(v[i]);
+      update(fp, to_f(g[i]), fm, fv);
+      from_f(p[i], fp); from_f(m[i], fm); from_f(v[i], fv);
+    }
   }
 }
 
@@ -255,7 +271,7 @@ __global__ void advance_step_kernel(float* state) { state[0] += 1.f; }
 static int grid_for(const long long* numel, int n, int sm_count) {
   long long chunks = 0;
   for (int i = 0; i < n; ++i) chunks += (numel[i] + kChunk - 1) / kChunk;
-  long long g = (long long)sm_count * 3;   // one resident wave (3 blocks per SM)
+  long long g = (long long)sm_count * 4;   // one resident wave (4 blocks per SM)
   if (g > kSlots) g = kSlots;
   if (chunks < g) g = chunks;
   return g < 1 ? 1 : (int)g;

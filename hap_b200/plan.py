@@ -230,6 +230,126 @@ def emit_lm(model: TransformerLM, plan: str, ratios: Sequence[float], rank: int,
 
 
 # ---------------------------------------------------------------------------------------------
+# Vision Transformer (the image-classification configuration)
+# ---------------------------------------------------------------------------------------------
+class ViT(torch.nn.Module):
+    """ViT in the shape of the reference's ``VTransformer`` (``models.py:147-177``): patch embedding,
+    a class token in front, learned positions, ``nlayers`` encoder blocks without a mask, the class
+    token's embedding through a linear head, ``log_softmax`` + summed ``nll_loss``.
+
+    The patch embedding is a convolution whose kernel equals its stride, i.e. a linear map of each
+    flattened patch: it is written as ``reshape`` / ``permute`` + ``linear`` so that it runs on the same
+    tensor-core GEMM as every other projection.  Blocks are the pre-LN blocks of
+    :class:`TransformerLM` with GELU in the MLP.  Defaults are ViT-B/16 on 224 x 224 images.
+    """
+
+    def __init__(self, image=224, patch=16, channels=3, d_model=768, nheads=12, d_ffn=3072, nlayers=12, nclasses=1000):
+        super().__init__()
+        if image % patch:
+            raise ValueError("image size must be a multiple of the patch size")
+        self.image, self.patch, self.channels = image, patch, channels
+        self.d_model, self.nheads, self.nlayers, self.nclasses = d_model, nheads, nlayers, nclasses
+        self.grid = image // patch
+        self.seqlen = self.grid * self.grid + 1
+        pdim = channels * patch * patch
+        self.patch_w = torch.nn.Parameter(torch.randn(d_model, pdim) * pdim ** -0.5)
+        self.patch_b = torch.nn.Parameter(torch.zeros(d_model))
+        self.cls = torch.nn.Parameter(torch.randn(1, 1, d_model) * 0.02)
+        self.pos = torch.nn.Parameter(torch.randn(self.seqlen, 1, d_model) * 0.02)
+        for i in range(nlayers):
+            self.register_parameter(f"l{i}_ln1_w", torch.nn.Parameter(torch.ones(d_model)))
+            self.register_parameter(f"l{i}_ln1_b", torch.nn.Parameter(torch.zeros(d_model)))
+            self.register_parameter(f"l{i}_in_w", torch.nn.Parameter(torch.randn(3 * d_model, d_model) * d_model ** -0.5))
+            self.register_parameter(f"l{i}_in_b", torch.nn.Parameter(torch.zeros(3 * d_model)))
+            self.register_parameter(f"l{i}_out_w", torch.nn.Parameter(torch.randn(d_model, d_model) * d_model ** -0.5))
+            self.register_parameter(f"l{i}_out_b", torch.nn.Parameter(torch.zeros(d_model)))
+            self.register_parameter(f"l{i}_ln2_w", torch.nn.Parameter(torch.ones(d_model)))
+            self.register_parameter(f"l{i}_ln2_b", torch.nn.Parameter(torch.zeros(d_model)))
+            self.register_parameter(f"l{i}_w1", torch.nn.Parameter(torch.randn(d_ffn, d_model) * d_model ** -0.5))
+            self.register_parameter(f"l{i}_b1", torch.nn.Parameter(torch.zeros(d_ffn)))
+            self.register_parameter(f"l{i}_w2", torch.nn.Parameter(torch.randn(d_model, d_ffn) * d_ffn ** -0.5))
+            self.register_parameter(f"l{i}_b2", torch.nn.Parameter(torch.zeros(d_model)))
+        self.lnf_w = torch.nn.Parameter(torch.ones(d_model))
+        self.lnf_b = torch.nn.Parameter(torch.zeros(d_model))
+        self.head_w = torch.nn.Parameter(torch.randn(nclasses, d_model) * d_model ** -0.5)
+        self.head_b = torch.nn.Parameter(torch.zeros(nclasses))
+
+    def forward(self, images, labels):
+        """Unsharded reference forward: images (B, C, H, W), labels (B,) int64 -> summed NLL."""
+        ns = SimpleNamespace(collectives=None, linear=F.linear, mha=F.multi_head_attention_forward)
+        return _vit_forward(self, images, labels, ns, None, None, None, "none")
+
+
+def _vit_forward(m, images, labels, ns, emit, ratios, rank, plan):
+    col, linear, mha = ns.collectives, ns.linear, ns.mha
+    E, H, G, P_, C_ = m.d_model, m.nheads, m.grid, m.patch, m.channels
+
+    def param(name, shardable=False):
+        if emit is None:
+            return getattr(m, name)
+        node = emit.get_attr(name)
+        if plan == "dp_zero" and shardable:
+            return emit.call_function(col.all_gather, (node, 0, sharding_round(m._full_extent[name], ratios), rank))
+        return emit.call_function(col.replicate, (node,))
+
+    call = (lambda fn, *a, **k: fn(*a, **k)) if emit is None else (lambda fn, *a, **k: emit.call_function(fn, a, k))
+    method = (lambda obj, name, *a: getattr(obj, name)(*a)) if emit is None else (lambda obj, name, *a: emit.call_method(name, (obj, *a)))
+
+    # (B, C, G*P, G*P) -> (B, G*G, C*P*P): one row per patch, elements in the order a conv kernel reads them
+    x = method(images, "reshape", -1, C_, G, P_, G, P_)
+    x = method(x, "permute", 0, 2, 4, 1, 3, 5)
+    x = method(x, "reshape", -1, G * G, C_ * P_ * P_)
+    x = call(linear, x, param("patch_w", True), param("patch_b"))          # (B, G*G, E)
+    x = method(x, "transpose", 0, 1)                                        # (G*G, B, E)
+    cls = method(param("cls"), "expand", -1, method(x, "size", 1), -1)      # (1, B, E)
+    x = call(torch.cat, [cls, x], 0)                                        # (L, B, E): the (L, N, E) layout
+    x = call(operator.add, x, param("pos"))
+    for i in range(m.nlayers):
+        h = call(F.layer_norm, x, (E,), param(f"l{i}_ln1_w"), param(f"l{i}_ln1_b"))
+        att = call(mha, query=h, key=h, value=h, embed_dim_to_check=E, num_heads=H,
+                   in_proj_weight=param(f"l{i}_in_w", True), in_proj_bias=param(f"l{i}_in_b", True), bias_k=None, bias_v=None,
+                   add_zero_attn=False, dropout_p=0.0, out_proj_weight=param(f"l{i}_out_w", True),
+                   out_proj_bias=param(f"l{i}_out_b"), attn_mask=None)
+        x = call(operator.add, x, call(operator.getitem, att, 0))
+        h = call(F.layer_norm, x, (E,), param(f"l{i}_ln2_w"), param(f"l{i}_ln2_b"))
+        h = call(linear, h, param(f"l{i}_w1", True), param(f"l{i}_b1", True))
+        h = call(F.gelu, h)
+        h = call(linear, h, param(f"l{i}_w2", True), param(f"l{i}_b2"))
+        x = call(operator.add, x, h)
+    x = call(operator.getitem, x, 0)                                        # the class token: (B, E)
+    x = call(F.layer_norm, x, (E,), param("lnf_w"), param("lnf_b"))
+    logits = call(linear, x, param("head_w", True), param("head_b", True))
+    logp = call(F.log_softmax, method(logits, "float"), -1)
+    return call(F.nll_loss, logp, labels, reduction="sum")
+
+
+def emit_vit(model: ViT, plan: str, ratios: Sequence[float], rank: int, batch: int, ns=None) -> torch.fx.Graph:
+    """fx graph of the ViT training forward for one rank; plans as in :func:`emit_lm` (``"dp"``:
+    images and labels batch-sharded by ``ratios``, parameters replicated; ``"dp_zero"``: projection
+    weights additionally sharded on dim 0 and all-gathered at their use)."""
+    ns = ns or default_namespace()
+    if plan not in ("dp", "dp_zero"):
+        raise ValueError(f"unknown plan {plan!r}")
+    g = torch.fx.Graph()
+    images, labels = g.placeholder("images"), g.placeholder("labels")
+    lb = sharding_round(batch, ratios)
+    img_r = g.call_function(operator.getitem, (g.call_method("split", (images, lb, 0)), rank))
+    lab_r = g.call_function(operator.getitem, (g.call_method("split", (labels, lb, 0)), rank))
+    model._full_extent = {}
+    if plan == "dp_zero":
+        names = [n for i in range(model.nlayers) for n in (f"l{i}_in_w", f"l{i}_in_b", f"l{i}_out_w", f"l{i}_w1", f"l{i}_b1", f"l{i}_w2")]
+        names += ["patch_w", "head_w", "head_b"]
+        for n in names:
+            full = getattr(model, n).shape[0]
+            model._full_extent[n] = full
+            shard_parameter_(model, n, sharding_round(full, ratios), 0, rank)
+    loss = _vit_forward(model, img_r, lab_r, ns, g, list(ratios), rank, plan)
+    g.output(loss)
+    g.lint()
+    return g
+
+
+# ---------------------------------------------------------------------------------------------
 # MoE Transformer (expert-parallel configuration)
 # ---------------------------------------------------------------------------------------------
 def top2_gating(x, gate_weight, n_expert: int, capacity: int):

@@ -82,6 +82,29 @@ def lm_cpu_namespace():
     return SimpleNamespace(collectives=gloo_port, linear=F.linear, mha=F.multi_head_attention_forward)
 
 
+# ---- Vision Transformer ------------------------------------------------------------------------------
+VIT_SMALL = dict(image=16, patch=4, channels=3, d_model=64, nheads=2, d_ffn=128, nlayers=2, nclasses=10)
+
+
+def vit_model(dtype=torch.float32):
+    torch.manual_seed(39)
+    return P.ViT(**VIT_SMALL).to(dtype)
+
+
+def vit_batch(dtype=torch.float32):
+    g = torch.Generator().manual_seed(2024)
+    return (torch.randn(LM_BATCH, VIT_SMALL["channels"], VIT_SMALL["image"], VIT_SMALL["image"], generator=g).to(dtype),
+            torch.randint(0, VIT_SMALL["nclasses"], (LM_BATCH,), generator=g))
+
+
+def vit_rank_modules(model, plan, ns, world=2, device="cpu", ratios=None):
+    mods = []
+    for r in range(world):
+        m = copy.deepcopy(model).to(device)
+        mods.append(torch.fx.GraphModule(m, P.emit_vit(m, plan, ratios or RATIOS, r, LM_BATCH, ns)))
+    return mods
+
+
 # ---- MoE Transformer ---------------------------------------------------------------------------------
 MOE_SMALL = dict(vocab=64, d_model=64, nheads=2, d_ffn=128, nlayers=2, seqlen=16, n_expert=4, capacity=8)
 

@@ -112,6 +112,42 @@ def test_language_model_programs_reproduce_the_unsharded_model(plan):
     assert (n_sharded > 0) == (plan == "dp_zero")
 
 
+@pytest.mark.parametrize("plan", ["dp", "dp_zero"])
+def test_vit_programs_reproduce_the_unsharded_model(plan):
+    """ViT (patch embedding as a linear map of flattened patches, class token, unmasked MHA, GELU MLP,
+    summed NLL over the class token), ratios [.6,.4]; also checked against a convolutional patch
+    embedding, which is what the reference's model uses (models.py:147-177)."""
+    import copy
+    from hap_b200 import sharding_round
+    model = C.vit_model()
+    img, lab = C.vit_batch()
+    ref = copy.deepcopy(model)
+    want = ref(img, lab)
+    want.backward()
+    # the reshape/permute + linear equals Conv2d(kernel = stride = patch)
+    k = C.VIT_SMALL
+    conv = torch.nn.functional.conv2d(img, model.patch_w.detach().view(k["d_model"], k["channels"], k["patch"], k["patch"]),
+                                      model.patch_b.detach(), stride=k["patch"])
+    mine = torch.nn.functional.linear(
+        img.reshape(-1, k["channels"], 4, k["patch"], 4, k["patch"]).permute(0, 2, 4, 1, 3, 5).reshape(-1, 16, 48),
+        model.patch_w.detach(), model.patch_b.detach())
+    torch.testing.assert_close(mine, conv.flatten(2).transpose(1, 2), rtol=1e-5, atol=1e-5)
+    world = LockstepWorld(C.vit_rank_modules(model, plan, C.lm_cpu_namespace()), OracleCollectives())
+    losses = world.forward([(img, lab), (img, lab)])
+    assert abs(float(sum(losses)) - float(want)) <= 1e-5 * abs(float(want))
+    torch.stack(losses).sum().backward()
+    full = dict(ref.named_parameters())
+    n_sharded = 0
+    for r, m in enumerate(world.modules):
+        for name, p in m.named_parameters():
+            g = full[name].grad
+            if p.shape != g.shape:
+                g = torch.split(g, sharding_round(g.shape[0], C.RATIOS), dim=0)[r]
+                n_sharded += 1
+            torch.testing.assert_close(p.grad, g, rtol=1e-3, atol=1e-4)
+    assert (n_sharded > 0) == (plan == "dp_zero")
+
+
 def test_expert_parallel_moe_program_reproduces_the_unsharded_model():
     """MoE Transformer: experts sharded by sharding_round(n_expert, ratios), tokens batch-sharded, two
     uneven all_to_all per layer (hap.rs:2713-2744) around the expert einsums (models.py:356-364)."""

@@ -106,6 +106,37 @@ def test_language_model_step_matches_cpu_replay(plan):
         comm.destroy()
 
 
+@pytest.mark.parametrize("plan", ["dp", "dp_zero"])
+def test_vit_step_matches_cpu_replay(plan):
+    """ViT step in bf16 with the heterogeneous ratios [.3,.25,.2,.25] on 4 virtual ranks: patch
+    embedding, unmasked attention with an odd sequence length (17), GELU MLP and the class-token
+    head on the package's GPU path against the CPU replay of the same fx programs."""
+    dtype = torch.bfloat16
+    r4 = [.3, .25, .2, .25]
+    model = C.vit_model(dtype)
+    img, lab = C.vit_batch(dtype)
+    cpu = LockstepWorld(C.vit_rank_modules(model, plan, C.lm_cpu_namespace(), world=4, ratios=r4), OracleCollectives())
+    comm = hap_b200.local_comm(4, DEV, stage_bytes=16 << 20, heap_bytes=32 << 20)
+    try:
+        gpu = LockstepWorld(C.vit_rank_modules(model, plan, hap_b200.plan.default_namespace(), world=4, device=DEV, ratios=r4),
+                            hap_b200.LocalCollectives(comm))
+        want = cpu.forward([(img, lab)] * 4)
+        got = gpu.forward([(img.to(DEV), lab.to(DEV))] * 4)
+        for r in range(4):
+            assert abs(float(got[r]) - float(want[r])) <= 2e-2 * abs(float(want[r])), (plan, r, float(got[r]), float(want[r]))
+        torch.stack(want).sum().backward()
+        torch.stack(got).sum().backward()
+        for r in range(4):
+            for (name, pw), (_, pg) in zip(cpu.modules[r].named_parameters(), gpu.modules[r].named_parameters()):
+                assert pg.grad.shape == pw.grad.shape, name
+                d = (pg.grad.detach().float().cpu() - pw.grad.detach().float())
+                assert float(d.norm()) <= 5e-2 * float(pw.grad.float().norm()) + 1e-3, (plan, r, name, float(d.norm()), float(pw.grad.float().norm()))
+        comm.check()
+        hap_b200.linear_ops.gemm_status()
+    finally:
+        comm.destroy()
+
+
 def test_bucketed_gradient_reduction_gives_the_same_step():
     """ProcessWorker on a world of one: one flat all_reduce over the replicated parameters' gradients
     (views of a heap buffer) must leave exactly the parameters the per-parameter all_reduces leave."""
