@@ -13,6 +13,8 @@ from . import linear as linear_ops
 from .linear import linear
 from . import plan, spmd, attention
 from .einsum import einsum
+from .loss import nll_log_softmax_sum
+from .optim import ClipAdam
 
 __all__ = ["Comm", "init_process_comm", "local_comm", "single_comm", "collectives", "LocalCollectives",
            "sharding_round", "sharding_round_", "linear", "linear_ops", "plan", "spmd", "attention", "einsum"]

@@ -42,12 +42,25 @@ class MLP(torch.nn.Module):
         return F.mse_loss(self.fc2(F.gelu(self.fc1(x))), y, reduction="sum")
 
 
+def _summed_nll(ns, call, method, logits, targets, classes):
+    """The models' loss: ``log_softmax`` + ``nll_loss(reduction='sum')`` as the two nodes the planner
+    emits (``hap.rs:1808, 1858``), or as the namespace's single fused op when it has one."""
+    fused = getattr(ns, "nll", None)
+    if fused is not None:
+        return call(fused, logits, targets)
+    logp = call(F.log_softmax, method(logits, "float"), -1)
+    logp = method(logp, "reshape", -1, classes)
+    return call(F.nll_loss, logp, method(targets, "reshape", -1), reduction="sum")
+
+
 def default_namespace() -> SimpleNamespace:
     from . import collectives
     from .attention import multi_head_attention_forward
     from .einsum import einsum
     from .linear import linear
-    return SimpleNamespace(collectives=collectives, linear=linear, mha=multi_head_attention_forward, einsum=einsum)
+    from .loss import nll_log_softmax_sum
+    return SimpleNamespace(collectives=collectives, linear=linear, mha=multi_head_attention_forward, einsum=einsum,
+                           nll=nll_log_softmax_sum)
 
 
 def shard_parameter_(module: torch.nn.Module, name: str, lengths: Sequence[int], dim: int, rank: int) -> None:
@@ -189,10 +202,7 @@ def _lm_forward(m, tokens, targets, ns, emit, ratios, rank, plan):
         x = call(operator.add, x, h)
     x = call(F.layer_norm, x, (E,), param("lnf_w"), param("lnf_b"))
     logits = call(linear, x, param("dec_w", True), param("dec_b", True))  # (S, B, V)
-    logp = call(F.log_softmax, method(logits, "float"), -1)
-    logp = method(logp, "reshape", -1, m.vocab)
-    tgt = method(method(targets, "transpose", 0, 1), "reshape", -1)
-    return call(F.nll_loss, logp, tgt, reduction="sum")
+    return _summed_nll(ns, call, method, logits, method(targets, "transpose", 0, 1), m.vocab)
 
 
 def _device_of(m):
@@ -319,8 +329,7 @@ def _vit_forward(m, images, labels, ns, emit, ratios, rank, plan):
     x = call(operator.getitem, x, 0)                                        # the class token: (B, E)
     x = call(F.layer_norm, x, (E,), param("lnf_w"), param("lnf_b"))
     logits = call(linear, x, param("head_w", True), param("head_b", True))
-    logp = call(F.log_softmax, method(logits, "float"), -1)
-    return call(F.nll_loss, logp, labels, reduction="sum")
+    return _summed_nll(ns, call, method, logits, labels, m.nclasses)
 
 
 def emit_vit(model: ViT, plan: str, ratios: Sequence[float], rank: int, batch: int, ns=None) -> torch.fx.Graph:
@@ -440,8 +449,7 @@ def _moe_forward(m, tokens, targets, ns, emit, ratios, rank, batch):
         y = call(einsum, "becd,bsec->bsd", eo, combine)
         x = call(F.layer_norm, call(operator.add, x, y), (E,), param(f"l{i}_ln2_w"), param(f"l{i}_ln2_b"))
     logits = call(linear, x, param("dec_w"), param("dec_b"))
-    logp = method(call(F.log_softmax, method(logits, "float"), -1), "reshape", -1, m.vocab)
-    return call(F.nll_loss, logp, method(targets, "reshape", -1), reduction="sum")
+    return _summed_nll(ns, call, method, logits, targets, m.vocab)
 
 
 def emit_moe(model: MoETransformerLM, ratios: Sequence[float], rank: int, batch: int, ns=None) -> torch.fx.Graph:

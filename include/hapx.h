@@ -243,6 +243,21 @@ int hapx_clip_adam_apply(int n, void* const* params, const void* const* grads, v
                          double eps, double weight_decay, double max_norm, float* state, int advance_step,
                          hapx_stream stream);
 
+/* ---- loss: log_softmax + nll_loss(reduction='sum') in one pass ---------------------
+ * Replaces the pair of fx nodes the planner emits for the models' loss (hap.rs:1808
+ * log_softmax, hap.rs:1858 nll_loss; models.py:116-117): logits [rows][classes] (row pitch
+ * `pitch` elements, HAPX_F32 or HAPX_BF16), int64 targets [rows].
+ * forward writes row_lse[r] = logsumexp(logits[r]) and row_loss[r] = row_lse[r] -
+ * logits[r][target[r]] (fp32); the loss is the sum of row_loss.  A target outside
+ * [0, classes), such as torch's ignore_index -100, gives a zero loss and a zero gradient row.
+ * backward writes grad_logits[r][c] = *grad_out * (exp(logits[r][c] - row_lse[r]) - [c == target[r]])
+ * in the logits' dtype; grad_out is a device scalar. */
+int hapx_nll_logsoftmax_forward(const void* logits, const int64_t* targets, float* row_loss, float* row_lse, int dtype,
+                                int64_t rows, int64_t classes, int64_t pitch, hapx_stream stream);
+int hapx_nll_logsoftmax_backward(const void* logits, const int64_t* targets, const float* row_lse, const float* grad_out,
+                                 void* grad_logits, int dtype, int64_t rows, int64_t classes, int64_t pitch,
+                                 int64_t grad_pitch, hapx_stream stream);
+
 /* ---- diagnostics ----------------------------------------------------------------
  * No counterpart in the reference.  Walks the kernels' tiling of ONE rank's pull over
  * HOST buffers (op: 0 gather, 1 all-to-all, 2 slice, 3 slice-backward), bounds-checking
