@@ -14,6 +14,7 @@ from .linear import linear
 from . import plan, spmd, attention
 from .einsum import einsum
 from .loss import nll_log_softmax_sum
+from .norm import layer_norm
 from .optim import ClipAdam
 
 __all__ = ["Comm", "init_process_comm", "local_comm", "single_comm", "collectives", "LocalCollectives",

@@ -42,6 +42,11 @@ class MLP(torch.nn.Module):
         return F.mse_loss(self.fc2(F.gelu(self.fc1(x))), y, reduction="sum")
 
 
+def _ln(ns):
+    """layer_norm of the namespace (this package's kernels by default), else torch's."""
+    return getattr(ns, "layer_norm", None) or F.layer_norm
+
+
 def _summed_nll(ns, call, method, logits, targets, classes):
     """The models' loss: ``log_softmax`` + ``nll_loss(reduction='sum')`` as the two nodes the planner
     emits (``hap.rs:1808, 1858``), or as the namespace's single fused op when it has one."""
@@ -59,8 +64,9 @@ def default_namespace() -> SimpleNamespace:
     from .einsum import einsum
     from .linear import linear
     from .loss import nll_log_softmax_sum
+    from .norm import layer_norm
     return SimpleNamespace(collectives=collectives, linear=linear, mha=multi_head_attention_forward, einsum=einsum,
-                           nll=nll_log_softmax_sum)
+                           nll=nll_log_softmax_sum, layer_norm=layer_norm)
 
 
 def shard_parameter_(module: torch.nn.Module, name: str, lengths: Sequence[int], dim: int, rank: int) -> None:
@@ -183,24 +189,25 @@ def _lm_forward(m, tokens, targets, ns, emit, ratios, rank, plan):
     call = (lambda fn, *a, **k: fn(*a, **k)) if emit is None else (lambda fn, *a, **k: emit.call_function(fn, a, k))
     method = (lambda obj, name, *a: getattr(obj, name)(*a)) if emit is None else (lambda obj, name, *a: emit.call_method(name, (obj, *a)))
 
-    x = call(F.embedding, tokens, param("embed.weight"))                  # (B, S, E)
-    x = method(x, "transpose", 0, 1)                                       # (S, B, E): the (L, N, E) layout
+    # look the tokens up in (S, B) order: the activations are then contiguous in the (L, N, E) layout the
+    # attention handler wants (hap.rs:1284-1287) instead of a transposed view that every layer_norm copies
+    x = call(F.embedding, method(tokens, "transpose", 0, 1), param("embed.weight"))   # (S, B, E)
     x = call(operator.add, x, param("pos"))
     S = m.seqlen
     mask = call(torch.triu, call(torch.full, (S, S), float("-inf"), device=_device_of(m), dtype=m.pos.dtype), 1)
     for i in range(m.nlayers):
-        h = call(F.layer_norm, x, (E,), param(f"l{i}_ln1_w"), param(f"l{i}_ln1_b"))
+        h = call(_ln(ns), x, (E,), param(f"l{i}_ln1_w"), param(f"l{i}_ln1_b"))
         att = call(mha, query=h, key=h, value=h, embed_dim_to_check=E, num_heads=H,
                    in_proj_weight=param(f"l{i}_in_w", True), in_proj_bias=param(f"l{i}_in_b", True), bias_k=None, bias_v=None,
                    add_zero_attn=False, dropout_p=0.0, out_proj_weight=param(f"l{i}_out_w", True),
                    out_proj_bias=param(f"l{i}_out_b"), attn_mask=mask)
         x = call(operator.add, x, call(operator.getitem, att, 0))
-        h = call(F.layer_norm, x, (E,), param(f"l{i}_ln2_w"), param(f"l{i}_ln2_b"))
+        h = call(_ln(ns), x, (E,), param(f"l{i}_ln2_w"), param(f"l{i}_ln2_b"))
         h = call(linear, h, param(f"l{i}_w1", True), param(f"l{i}_b1", True))
         h = call(F.relu, h)
         h = call(linear, h, param(f"l{i}_w2", True), param(f"l{i}_b2"))
         x = call(operator.add, x, h)
-    x = call(F.layer_norm, x, (E,), param("lnf_w"), param("lnf_b"))
+    x = call(_ln(ns), x, (E,), param("lnf_w"), param("lnf_b"))
     logits = call(linear, x, param("dec_w", True), param("dec_b", True))  # (S, B, V)
     return _summed_nll(ns, call, method, logits, method(targets, "transpose", 0, 1), m.vocab)
 
@@ -315,19 +322,19 @@ def _vit_forward(m, images, labels, ns, emit, ratios, rank, plan):
     x = call(torch.cat, [cls, x], 0)                                        # (L, B, E): the (L, N, E) layout
     x = call(operator.add, x, param("pos"))
     for i in range(m.nlayers):
-        h = call(F.layer_norm, x, (E,), param(f"l{i}_ln1_w"), param(f"l{i}_ln1_b"))
+        h = call(_ln(ns), x, (E,), param(f"l{i}_ln1_w"), param(f"l{i}_ln1_b"))
         att = call(mha, query=h, key=h, value=h, embed_dim_to_check=E, num_heads=H,
                    in_proj_weight=param(f"l{i}_in_w", True), in_proj_bias=param(f"l{i}_in_b", True), bias_k=None, bias_v=None,
                    add_zero_attn=False, dropout_p=0.0, out_proj_weight=param(f"l{i}_out_w", True),
                    out_proj_bias=param(f"l{i}_out_b"), attn_mask=None)
         x = call(operator.add, x, call(operator.getitem, att, 0))
-        h = call(F.layer_norm, x, (E,), param(f"l{i}_ln2_w"), param(f"l{i}_ln2_b"))
+        h = call(_ln(ns), x, (E,), param(f"l{i}_ln2_w"), param(f"l{i}_ln2_b"))
         h = call(linear, h, param(f"l{i}_w1", True), param(f"l{i}_b1", True))
         h = call(F.gelu, h)
         h = call(linear, h, param(f"l{i}_w2", True), param(f"l{i}_b2"))
         x = call(operator.add, x, h)
     x = call(operator.getitem, x, 0)                                        # the class token: (B, E)
-    x = call(F.layer_norm, x, (E,), param("lnf_w"), param("lnf_b"))
+    x = call(_ln(ns), x, (E,), param("lnf_w"), param("lnf_b"))
     logits = call(linear, x, param("head_w", True), param("head_b", True))
     return _summed_nll(ns, call, method, logits, labels, m.nclasses)
 
@@ -435,7 +442,7 @@ def _moe_forward(m, tokens, targets, ns, emit, ratios, rank, batch):
                    in_proj_bias=param(f"l{i}_in_b"), bias_k=None, bias_v=None, add_zero_attn=False, dropout_p=0.0,
                    out_proj_weight=param(f"l{i}_out_w"), out_proj_bias=param(f"l{i}_out_b"))
         a = method(call(operator.getitem, att, 0), "transpose", 0, 1)
-        x = call(F.layer_norm, call(operator.add, x, a), (E,), param(f"l{i}_ln1_w"), param(f"l{i}_ln1_b"))
+        x = call(_ln(ns), call(operator.add, x, a), (E,), param(f"l{i}_ln1_w"), param(f"l{i}_ln1_b"))
         gated = call(top2_gating, x, param(f"l{i}_gate"), ne, cap)
         dispatch, combine = call(operator.getitem, gated, 0), call(operator.getitem, gated, 1)
         ein = call(einsum, "bsd,bsec->becd", x, dispatch)                                              # (b_r, e, c, d)
@@ -447,7 +454,7 @@ def _moe_forward(m, tokens, targets, ns, emit, ratios, rank, batch):
         if emit is not None:
             eo = emit.call_function(col.all_to_all, (eo, 0, 1, lb, le, rank))                         # (b_r, e, c, d)
         y = call(einsum, "becd,bsec->bsd", eo, combine)
-        x = call(F.layer_norm, call(operator.add, x, y), (E,), param(f"l{i}_ln2_w"), param(f"l{i}_ln2_b"))
+        x = call(_ln(ns), call(operator.add, x, y), (E,), param(f"l{i}_ln2_w"), param(f"l{i}_ln2_b"))
     logits = call(linear, x, param("dec_w"), param("dec_b"))
     return _summed_nll(ns, call, method, logits, targets, m.vocab)
 

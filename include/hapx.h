@@ -258,6 +258,21 @@ int hapx_nll_logsoftmax_backward(const void* logits, const int64_t* targets, con
                                  void* grad_logits, int dtype, int64_t rows, int64_t classes, int64_t pitch,
                                  int64_t grad_pitch, hapx_stream stream);
 
+/* ---- layer_norm over the last dimension ---------------------------------------------
+ * Replaces the torch.nn.functional.layer_norm nodes of the Transformer programs (planner
+ * handler hap.rs:1637-1660; nn.LayerNorm of the reference's encoder layers, models.py:319-320).
+ * x, y, dy, dx: [rows][E] contiguous, gamma / beta: [E] (beta may be null), all of `dtype`
+ * (HAPX_F32 or HAPX_BF16); E a multiple of 8, at most 2048.  mean / rstd: fp32 [rows], written
+ * by forward and read by backward.
+ * backward needs `partial`: 2 * E * hapx_layer_norm_backward_blocks(rows) floats of scratch;
+ * dgamma / dbeta may be null.  The parameter gradients are summed in a fixed order. */
+int hapx_layer_norm_forward(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd, int dtype,
+                            int64_t rows, int64_t E, double eps, hapx_stream stream);
+int hapx_layer_norm_backward_blocks(int64_t rows);
+int hapx_layer_norm_backward(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd, void* dx,
+                             void* dgamma, void* dbeta, float* partial, int dtype, int64_t rows, int64_t E,
+                             hapx_stream stream);
+
 /* ---- diagnostics ----------------------------------------------------------------
  * No counterpart in the reference.  Walks the kernels' tiling of ONE rank's pull over
  * HOST buffers (op: 0 gather, 1 all-to-all, 2 slice, 3 slice-backward), bounds-checking
