@@ -1103,19 +1103,25 @@ static int launch2(const Operand& A, const Operand& B, const Operand& Dop, Param
   p.n_tiles = (p.N + C::BN - 1) / C::BN;
   p.k_blocks = (p.Kc + BK - 1) / BK;
   p.splits = 1; p.kb_per_split = p.k_blocks; p.m_pad = 0;
-  // Few output tiles but a long contraction (weight gradients): cut the contraction so that all SM
-  // pairs have work.  Take the smallest split count that fills >= 85 % of the waves it needs.
+  // A long contraction over few output tiles (weight gradients, the input gradient of the vocabulary
+  // projection) leaves SM pairs idle or the last wave nearly empty: cut the contraction into `splits`
+  // ranges whose fp32 partial tiles a second kernel adds in a fixed order.  The split count minimises
+  // a small cost model, in microseconds: waves x slices per unit x 0.28 (one 256 x 256 x 64 slice on
+  // an SM pair) + 3 for the ramp, and for a split the partial tiles written and read back at about
+  // 4 TB/s plus the second launch.
   const int tiles = p.m_tiles * p.n_tiles;
-  if (p.batch == 1 && tiles * 4 <= max_clusters && p.k_blocks >= 16) {
+  static const bool split_model = std::getenv("HAPX_GEMM_NO_SPLITK") == nullptr;
+  if (split_model && !SOFTMAX && p.batch == 1 && p.k_blocks >= 16 && (p.N & 3) == 0) {
+    auto waves = [&](long long units) { return (double)((units + max_clusters - 1) / max_clusters); };
+    const double out_bytes = (double)p.M * p.N * (p.out_f32 ? 4.0 : 2.0), partial_bytes = (double)p.M * p.N * 4.0;
     int best = 1;
-    double best_eff = (double)tiles / (((tiles + max_clusters - 1) / max_clusters) * (double)max_clusters);
-    for (int sp = 2; sp <= 32 && sp * 4 <= p.k_blocks; ++sp) {
+    double best_cost = waves(tiles) * p.k_blocks * 0.28 + 3.0;
+    for (int sp = 2; sp <= 16 && sp * 8 <= p.k_blocks; ++sp) {
       const int per = (p.k_blocks + sp - 1) / sp;
       if ((sp - 1) * per >= p.k_blocks) continue;            // an empty last range
-      const int units = tiles * sp;
-      const double eff = (double)units / (((units + max_clusters - 1) / max_clusters) * (double)max_clusters);
-      if (eff > best_eff + 1e-9) { best = sp; best_eff = eff; }
-      if (eff >= 0.85) break;
+      if ((double)sp * partial_bytes > 512e6) break;         // keep the workspace bounded
+      const double cost = waves((long long)tiles * sp) * per * 0.28 + 3.0 + 3.0 + (2.0 * sp * partial_bytes + out_bytes) / 4e6;
+      if (cost < 0.9 * best_cost) { best = sp; best_cost = cost; }
     }
     if (best > 1) { p.splits = best; p.kb_per_split = (p.k_blocks + best - 1) / best; p.m_pad = p.m_tiles * 2 * BM; }
   }
