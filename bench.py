@@ -755,6 +755,20 @@ def run_ops(args):
             ts.append(a.elapsed_time(b))
         return statistics.median(ts)
 
+    def graphed(fn):
+        """fn recorded into a CUDA graph (after a warm-up on a side stream): its replay costs device time only."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        return graph.replay
+
     rows = []
     parts = set(args.ops.split(","))
     g = torch.Generator(dev).manual_seed(39)
@@ -792,6 +806,48 @@ def run_ops(args):
         fl = 2.0 * bg * el * c * d * h
         t, tr = timeit(lambda: einsum("edh,becd->bech", w1, inp)), timeit(lambda: torch.einsum("edh,becd->bech", w1, inp))
         rows.append({"op": "edh,becd->bech", "shape": f"b={bg} e={el} c={c} d={d} h={h}", "ms": t, "torch_ms": tr, "tflops": fl / t / 1e9})
+    peak_gbs = float(measured_peaks()[0]["hbm_gbs"])
+    if "norm" in parts:
+        # layer_norm forward + backward on the activations of one Transformer-LM layer (8192 tokens x 768, bf16)
+        from hap_b200.norm import layer_norm
+        rows_, E_ = 8192, 768
+        xn = torch.randn(rows_, E_, device=dev, generator=g).to(torch.bfloat16).requires_grad_(True)
+        wn = torch.ones(E_, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        bn = torch.zeros(E_, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        dyn = torch.randn(rows_, E_, device=dev, generator=g).to(torch.bfloat16)
+
+        def ln_step(fn):
+            def run():
+                xn.grad = wn.grad = bn.grad = None
+                fn(xn, (E_,), wn, bn, 1e-5).backward(dyn)
+            return run
+
+        t_eager = timeit(ln_step(layer_norm))
+        t, tr = timeit(graphed(ln_step(layer_norm))), timeit(graphed(ln_step(torch.nn.functional.layer_norm)))
+        nbytes = 5 * rows_ * E_ * 2            # forward: x in, y out; backward: x, dy in, dx out
+        rows.append({"op": "layer_norm fwd+bwd", "shape": f"rows={rows_} E={E_} bf16", "ms": t, "torch_ms": tr, "tflops": 0.0,
+                     "gbs": nbytes / t / 1e6, "frac_of_hbm_peak": nbytes / t / 1e6 / peak_gbs, "eager_ms": t_eager})
+    if "loss" in parts:
+        # log_softmax + summed nll_loss forward + backward on the LM head's logits (8192 tokens x 33280, bf16)
+        from hap_b200.loss import nll_log_softmax_sum
+        rows_, V_ = 8192, 33280
+        lg = torch.randn(rows_, V_, device=dev, generator=g).to(torch.bfloat16).requires_grad_(True)
+        tg = torch.randint(0, V_, (rows_,), device=dev, generator=g)
+
+        def ours_loss():
+            lg.grad = None
+            nll_log_softmax_sum(lg, tg).backward()
+
+        def ref_loss():
+            lg.grad = None
+            torch.nn.functional.nll_loss(torch.nn.functional.log_softmax(lg.float(), -1), tg, reduction="sum").backward()
+
+        t_eager = timeit(ours_loss)
+        t, tr = timeit(graphed(ours_loss)), timeit(graphed(ref_loss))
+        nbytes = 3 * rows_ * V_ * 2            # forward reads the logits; backward reads them and writes the gradient
+        rows.append({"op": "log_softmax + nll fwd+bwd", "shape": f"rows={rows_} V={V_} bf16", "ms": t, "torch_ms": tr, "tflops": 0.0,
+                     "gbs": nbytes / t / 1e6, "frac_of_hbm_peak": nbytes / t / 1e6 / peak_gbs, "eager_ms": t_eager})
+        del lg
     if "tail" in parts:
         # step tail: clip by the gradient norm + Adam over the parameter tensors of the Transformer-LM
         # configuration (bf16; 12 layers + embeddings + head), against torch's clip_grad_norm_ + Adam
@@ -870,7 +926,7 @@ def main():
     ap.add_argument("--lm-graph", action="store_true", help="capture the training step into a CUDA graph")
     ap.add_argument("--gemm-tokens", type=int, default=8192)
     ap.add_argument("--gemm-layers", default="", help="comma-separated layer names to restrict the gemm workload to")
-    ap.add_argument("--ops", default="attention,einsum,tail", help="parts of the ops workload to run")
+    ap.add_argument("--ops", default="attention,einsum,norm,loss,tail", help="parts of the ops workload to run")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -59,7 +59,7 @@ SIGNATURES = {
     "hapx_nll_logsoftmax_forward": (_int, [_vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _vp]),
     "hapx_nll_logsoftmax_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _vp]),
     "hapx_layer_norm_forward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _dbl, _vp]),
-    "hapx_layer_norm_backward_blocks": (_int, [_i64]),
+    "hapx_layer_norm_backward_blocks": (_int, [_i64, _i64]),
     "hapx_layer_norm_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _vp]),
     "hapx_local_all_reduce_noalloc": (_int, [_int, _pp, _pp, _int, _int, _dbl, _i64, _vp]),
     "hapx_debug_host_walk": (_int, [_int, _int, _int, _int, _i64, _i64, _i64, _int, _pi64, _pi64, _pp,

@@ -18,17 +18,19 @@ constexpr int kWarpsPerBlock = 4;
 constexpr int kThreads = kWarpsPerBlock * 32;
 constexpr int kMaxVec = 8;           // 16-byte groups of 8 elements per lane: rows up to 8 * 8 * 32 = 2048 elements
 
+// Eight consecutive elements of a row: kept packed (as loaded) while they wait to be used.
 template <typename T>
 struct Row;
 template <>
 struct Row<__nv_bfloat16> {
-  // 8 elements = one 16-byte load
-  static __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
-    const uint4 v = *reinterpret_cast<const uint4*>(p);
-    const unsigned w[4] = {v.x, v.y, v.z, v.w};
+  struct Packed { uint4 v; };       // one 16-byte load
+  static __device__ __forceinline__ Packed load(const __nv_bfloat16* p) { return Packed{*reinterpret_cast<const uint4*>(p)}; }
+  static __device__ __forceinline__ void unpack(const Packed& q, float (&f)[8]) {
+    const unsigned w[4] = {q.v.x, q.v.y, q.v.z, q.v.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
   }
+  static __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) { unpack(load(p), f); }
   static __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
     unsigned w[4];
 #pragma unroll
@@ -41,10 +43,14 @@ struct Row<__nv_bfloat16> {
 };
 template <>
 struct Row<float> {
-  static __device__ __forceinline__ void load8(const float* p, float (&f)[8]) {
-    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  struct Packed { float4 a, b; };
+  static __device__ __forceinline__ Packed load(const float* p) {
+    return Packed{*reinterpret_cast<const float4*>(p), *reinterpret_cast<const float4*>(p + 4)};
   }
+  static __device__ __forceinline__ void unpack(const Packed& q, float (&f)[8]) {
+    f[0] = q.a.x; f[1] = q.a.y; f[2] = q.a.z; f[3] = q.a.w; f[4] = q.b.x; f[5] = q.b.y; f[6] = q.b.z; f[7] = q.b.w;
+  }
+  static __device__ __forceinline__ void load8(const float* p, float (&f)[8]) { unpack(load(p), f); }
   static __device__ __forceinline__ void store8(float* p, const float (&f)[8]) {
     *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
     *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
@@ -79,18 +85,29 @@ __global__ void __launch_bounds__(kThreads) layer_norm_forward_kernel(const T* _
     }
   }
   const float inv_e = 1.f / (float)E;
-  for (long long row = (long long)blockIdx.x * kWarpsPerBlock + warp; row < rows; row += (long long)gridDim.x * kWarpsPerBlock) {
-    const T* xr = x + row * E;
+  const long long stride = (long long)gridDim.x * kWarpsPerBlock;
+  long long row = (long long)blockIdx.x * kWarpsPerBlock + warp;
+  typename Row<T>::Packed nxt[NV];            // the next row of this warp is loaded while the current one is worked on
+  if (row < rows) {
+#pragma unroll
+    for (int v = 0; v < NV; ++v)
+      if (lane + 32 * v < groups) nxt[v] = Row<T>::load(x + row * E + 8 * (lane + 32 * v));
+  }
+  for (; row < rows; row += stride) {
     float f[NV][8];
     float s = 0.f;
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
-      const int g = lane + 32 * v;
-      if (g < groups) {
-        Row<T>::load8(xr + 8 * g, f[v]);
+      if (lane + 32 * v < groups) {
+        Row<T>::unpack(nxt[v], f[v]);
 #pragma unroll
         for (int k = 0; k < 8; ++k) s += f[v][k];
       }
+    }
+    if (row + stride < rows) {
+#pragma unroll
+      for (int v = 0; v < NV; ++v)
+        if (lane + 32 * v < groups) nxt[v] = Row<T>::load(x + (row + stride) * E + 8 * (lane + 32 * v));
     }
     const float mean = warp_sum(s) * inv_e;
     float q = 0.f;
@@ -119,7 +136,7 @@ __global__ void __launch_bounds__(kThreads) layer_norm_forward_kernel(const T* _
 
 // dx = rstd * (dy*gamma - mean(dy*gamma) - xhat * mean(dy*gamma*xhat));  partial[b][0][e] += dy*xhat, partial[b][1][e] += dy
 template <typename T, int NV>
-__global__ void __launch_bounds__(kThreads) layer_norm_backward_kernel(const T* __restrict__ x, const T* __restrict__ dy,
+__global__ void __launch_bounds__(kThreads, (NV <= 3 ? 3 : 2)) layer_norm_backward_kernel(const T* __restrict__ x, const T* __restrict__ dy,
                                                                        const T* __restrict__ gamma, const float* __restrict__ mean_in,
                                                                        const float* __restrict__ rstd_in, T* __restrict__ dx,
                                                                        float* __restrict__ partial, long long rows, int E) {
@@ -134,18 +151,38 @@ __global__ void __launch_bounds__(kThreads) layer_norm_backward_kernel(const T* 
     for (int k = 0; k < 8; ++k) { dg[v][k] = 0.f; db[v][k] = 0.f; }
   }
   const float inv_e = 1.f / (float)E;
-  for (long long row = (long long)blockIdx.x * kWarpsPerBlock + warp; row < rows; row += (long long)gridDim.x * kWarpsPerBlock) {
-    const T* xr = x + row * E;
-    const T* gr = dy + row * E;
+  const long long stride = (long long)gridDim.x * kWarpsPerBlock;
+  long long row = (long long)blockIdx.x * kWarpsPerBlock + warp;
+  typename Row<T>::Packed nx[NV], ng[NV];      // next row of x and dy, in flight while the current row is worked on
+  if (row < rows) {
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      if (lane + 32 * v < groups) {
+        nx[v] = Row<T>::load(x + row * E + 8 * (lane + 32 * v));
+        ng[v] = Row<T>::load(dy + row * E + 8 * (lane + 32 * v));
+      }
+    }
+  }
+  for (; row < rows; row += stride) {
     const float mean = mean_in[row], rstd = rstd_in[row];
     float xh[NV][8], gy[NV][8];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      if (lane + 32 * v < groups) { Row<T>::unpack(nx[v], xh[v]); Row<T>::unpack(ng[v], gy[v]); }
+    }
+    if (row + stride < rows) {
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        if (lane + 32 * v < groups) {
+          nx[v] = Row<T>::load(x + (row + stride) * E + 8 * (lane + 32 * v));
+          ng[v] = Row<T>::load(dy + (row + stride) * E + 8 * (lane + 32 * v));
+        }
+      }
+    }
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
-      const int g = lane + 32 * v;
-      if (g < groups) {
-        Row<T>::load8(xr + 8 * g, xh[v]);
-        Row<T>::load8(gr + 8 * g, gy[v]);
+      if (lane + 32 * v < groups) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           xh[v][k] = (xh[v][k] - mean) * rstd;
@@ -193,14 +230,24 @@ __global__ void __launch_bounds__(kThreads) layer_norm_backward_kernel(const T* 
   for (int e = threadIdx.x; e < E; e += kThreads) { out[e] = s_acc[0][e]; out[E + e] = s_acc[1][e]; }
 }
 
-// dgamma[e] = sum_b partial[b][0][e], dbeta[e] = sum_b partial[b][1][e], blocks added in index order
+// dgamma[e] = sum_b partial[b][0][e], dbeta[e] = sum_b partial[b][1][e].  A thread block owns 32 of the
+// 2E columns; its 8 warps add the partial rows w, w + 8, ... and the eight sums are added in warp order.
 template <typename T>
-__global__ void layer_norm_param_grad_kernel(const float* __restrict__ partial, int blocks, int E, T* __restrict__ dgamma,
-                                             T* __restrict__ dbeta) {
-  const int e = blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= 2 * E) return;
+__global__ void __launch_bounds__(256) layer_norm_param_grad_kernel(const float* __restrict__ partial, int blocks, int E,
+                                                                    T* __restrict__ dgamma, T* __restrict__ dbeta) {
+  __shared__ float s_sum[8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int e = blockIdx.x * 32 + lane;
   float s = 0.f;
-  for (int b = 0; b < blocks; ++b) s += partial[(long long)b * 2 * E + e];
+  if (e < 2 * E) {
+#pragma unroll 4
+    for (int b = warp; b < blocks; b += 8) s += partial[(long long)b * 2 * E + e];
+  }
+  s_sum[warp][lane] = s;
+  __syncthreads();
+  if (warp != 0 || e >= 2 * E) return;
+#pragma unroll
+  for (int w = 1; w < 8; ++w) s += s_sum[w][lane];
   if (e < E) {
     if (dgamma) { if constexpr (sizeof(T) == 2) dgamma[e] = __float2bfloat16_rn(s); else dgamma[e] = s; }
   } else if (dbeta) {
@@ -244,8 +291,9 @@ using namespace hapx::norm;
 
 extern "C" {
 
-int hapx_layer_norm_backward_blocks(int64_t rows) {
-  const long long cap = (long long)sm_count() * 2;
+int hapx_layer_norm_backward_blocks(int64_t rows, int64_t E) {
+  // one resident wave: 3 blocks per SM for rows of up to 768 elements, 2 above (register budget)
+  const long long cap = (long long)sm_count() * (E <= 768 ? 3 : 2);
   const long long need = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
   return (int)(need < 1 ? 1 : (need < cap ? need : cap));
 }
@@ -282,7 +330,7 @@ int hapx_layer_norm_backward(const void* x, const void* dy, const void* gamma, c
   int grid = 0;
   if (rows > 0) {
     if (!x || !dy || !gamma || !mean || !rstd || !dx) return fail(HAPX_ERR_ARGUMENT, "layer_norm_backward: null argument");
-    grid = hapx_layer_norm_backward_blocks(rows);
+    grid = hapx_layer_norm_backward_blocks(rows, E);
     const int nv = (int)((E / 8 + 31) / 32);
 #define HAPX_LN_BWD(T)                                                                                       \
   switch (nv) {                                                                                              \
@@ -298,7 +346,7 @@ int hapx_layer_norm_backward(const void* x, const void* dy, const void* gamma, c
     count_launch(1);
   }
   if (dgamma || dbeta) {
-    const int threads = 256, blocks = (int)((2 * E + threads - 1) / threads);
+    const int threads = 256, blocks = (int)((2 * E + 31) / 32);
     if (dtype == HAPX_BF16)
       layer_norm_param_grad_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(partial, grid, (int)E, static_cast<__nv_bfloat16*>(dgamma),
                                                                                   static_cast<__nv_bfloat16*>(dbeta));

@@ -45,7 +45,7 @@ class _LayerNorm(torch.autograd.Function):
         need_w, need_b = ctx.needs_input_grad[1], ctx.has_bias and ctx.needs_input_grad[2]
         dw = torch.empty_like(w) if need_w else None
         db = torch.empty_like(w) if need_b else None
-        blocks = N.lib.hapx_layer_norm_backward_blocks(rows)
+        blocks = N.lib.hapx_layer_norm_backward_blocks(rows, E)
         partial = torch.empty(2 * E * blocks, dtype=torch.float32, device=xc.device)
         with torch.cuda.device(xc.device):
             N.check(N.lib.hapx_layer_norm_backward(xc.data_ptr(), dyc.data_ptr(), w.data_ptr(), mean.data_ptr(), rstd.data_ptr(),

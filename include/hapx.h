@@ -264,11 +264,11 @@ int hapx_nll_logsoftmax_backward(const void* logits, const int64_t* targets, con
  * x, y, dy, dx: [rows][E] contiguous, gamma / beta: [E] (beta may be null), all of `dtype`
  * (HAPX_F32 or HAPX_BF16); E a multiple of 8, at most 2048.  mean / rstd: fp32 [rows], written
  * by forward and read by backward.
- * backward needs `partial`: 2 * E * hapx_layer_norm_backward_blocks(rows) floats of scratch;
+ * backward needs `partial`: 2 * E * hapx_layer_norm_backward_blocks(rows, E) floats of scratch;
  * dgamma / dbeta may be null.  The parameter gradients are summed in a fixed order. */
 int hapx_layer_norm_forward(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd, int dtype,
                             int64_t rows, int64_t E, double eps, hapx_stream stream);
-int hapx_layer_norm_backward_blocks(int64_t rows);
+int hapx_layer_norm_backward_blocks(int64_t rows, int64_t E);
 int hapx_layer_norm_backward(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd, void* dx,
                              void* dgamma, void* dbeta, float* partial, int dtype, int64_t rows, int64_t E,
                              hapx_stream stream);
