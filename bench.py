@@ -626,16 +626,49 @@ def run_lm(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     W = n_gpus
-    B = args.lm_batch * W
+    kind = args.lm_model
+    per_gpu = args.lm_batch if args.lm_batch > 0 else {"lm": 32, "vit": 64, "moe": 16}[kind]
+    B = per_gpu * W
     ratios = ratios_for(W)
+    if kind == "vit" and W in (4, 8):      # the heterogeneous ratios of the ViT configuration, replicated to 8
+        ratios = [x / (W // 4) for x in [0.3, 0.25, 0.2, 0.25] * (W // 4)]
     torch.manual_seed(39)
-    model = P.TransformerLM(nlayers=args.lm_layers).to(torch.bfloat16).to(dev)
+    L = args.lm_layers if args.lm_layers > 0 else {"lm": 12, "vit": 12, "moe": 8}[kind]
+    g = torch.Generator().manual_seed(2024)
+    lb = hap_b200.sharding_round(B, ratios)
+    bmax = max(lb)
+    if kind == "lm":
+        model = P.TransformerLM(nlayers=L)
+        emit = lambda m, r: P.emit_lm(m, args.lm_plan, ratios, r, B)
+        in_h = (torch.randint(0, 33278, (B, 256), generator=g), torch.randint(0, 33278, (B, 256), generator=g))
+        M = bmax * 256
+        fwd = L * (2.0 * M * 768 * (2304 + 768 + 3072 + 3072) + 2 * 2.0 * bmax * 12 * 256 * 256 * 64) + 2.0 * M * 768 * 33280
+        desc = f"Transformer LM training step ({L} layers, d_model 768, 12 heads, FFN 3072, pre-LN, vocab 33280, seq 256), plan {args.lm_plan}"
+    elif kind == "vit":
+        model = P.ViT(nlayers=L)
+        emit = lambda m, r: P.emit_vit(m, args.lm_plan, ratios, r, B)
+        in_h = (torch.randn(B, 3, 224, 224, generator=g).to(torch.bfloat16), torch.randint(0, 1000, (B,), generator=g))
+        M = bmax * 197
+        fwd = L * (2.0 * M * 768 * (2304 + 768 + 3072 + 3072) + 2 * 2.0 * bmax * 12 * 197 * 197 * 64) + 2.0 * bmax * 196 * 768 * 768
+        desc = f"ViT-B/16 training step ({L} layers, d 768, 12 heads, MLP 3072, 224x224x3 images, 1000 classes), plan {args.lm_plan}"
+    else:
+        model = P.MoETransformerLM(nlayers=L)
+        emit = lambda m, r: P.emit_moe(m, ratios, r, B)
+        in_h = (torch.randint(0, 33278, (B, 512), generator=g), torch.randint(0, 33278, (B, 512), generator=g))
+        M = bmax * 512
+        e_max = max(hap_b200.sharding_round(32, ratios))
+        fwd = L * (2.0 * M * 1024 * (3072 + 1024) + 2 * 2.0 * bmax * 16 * 512 * 512 * 64        # attention projections + core
+                   + 2 * 2.0 * bmax * 512 * 32 * 20 * 1024                                      # dense dispatch / combine einsums
+                   + 2 * 2.0 * B * e_max * 20 * 1024 * 4096) + 2.0 * M * 1024 * 33280           # expert FFNs of the busiest rank
+        desc = (f"MoE Transformer training step ({L} layers, d_model 1024, 16 heads, 32 experts FFN 4096, top-2 gating, capacity 20, "
+                f"vocab 33280, seq 512), expert parallel, experts per rank {hap_b200.sharding_round(32, ratios)}")
+    model = model.to(torch.bfloat16).to(dev)
     n_params = sum(p.numel() for p in model.parameters())
     if W == 1:
         dist = None
         comm = hap_b200.single_comm(dev, stage_bytes=256 << 20, heap_bytes=(320 << 20) + 2 * n_params)
         hap_b200.collectives.set_default_comm(comm)
-        graph = P.emit_lm(model, args.lm_plan, ratios, 0, B)
+        graph = emit(model, 0)
         worker = ProcessWorker(torch.fx.GraphModule(model, graph), comm=comm)
         step = worker.step
     else:
@@ -643,14 +676,12 @@ def run_lm(args):
         dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=W)
         comm = hap_b200.init_process_comm(stage_bytes=256 << 20, heap_bytes=(320 << 20) + 2 * n_params)
         hap_b200.collectives.set_default_comm(comm)
-        graph = P.emit_lm(model, args.lm_plan, ratios, rank, B)
+        graph = emit(model, rank)
         # the reference sums the partial losses with dist.reduce (worker.py:63-64); here through the package's all_reduce
         worker = ProcessWorker(torch.fx.GraphModule(model, graph),
                                reduce_loss=lambda t: comm.all_reduce([t.reshape(1).float()])[0], comm=comm)
         step = worker.step
-    g = torch.Generator().manual_seed(2024)
-    tok_h = torch.randint(0, 33278, (B, 256), generator=g).pin_memory()
-    tgt_h = torch.randint(0, 33278, (B, 256), generator=g).pin_memory()
+    tok_h, tgt_h = in_h[0].pin_memory(), in_h[1].pin_memory()
     tok, tgt = tok_h.to(dev), tgt_h.to(dev)
     if args.lm_graph:
         step = worker.capture(tok, tgt)
@@ -695,17 +726,12 @@ def run_lm(args):
     hap_b200.linear_ops.gemm_status()
     peaks, peak_kind = measured_peaks()
     # GEMM flops of one step on the busiest rank (largest batch share): 3 x forward, 2*M*N*K each
-    lb = hap_b200.sharding_round(B, ratios)
-    M = max(lb) * 256
-    L = args.lm_layers
-    fwd = L * (2.0 * M * 768 * (2304 + 768 + 3072 + 3072) + 2 * 2.0 * max(lb) * 12 * 256 * 256 * 64) + 2.0 * M * 768 * 33280
     achieved = 3 * fwd / (ms * 1e-3) / 1e12
     result = {
         "metric": "spmd_step_samples_per_s", "value": B / (ms * 1e-3), "unit": "samples/s", "n_gpus": n_gpus, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"Transformer LM training step ({L} layers, d_model 768, 12 heads, FFN 3072, pre-LN, vocab 33280, seq 256), "
-                               f"plan {args.lm_plan}, global batch {B} split {lb}", "parameters": n_params,
+        "config": {"workload": f"{desc}, global batch {B} split {lb}", "parameters": n_params,
                    "executor": "CUDA graph of the whole iteration" if args.lm_graph else "eager fx GraphModule",
                    "l2": "activations and weights of a step exceed L2 by far", "loss": loss_host},
         "roofline": {"bound": "tensor", "kernel": "gemm2_bf16_kernel (all linear / attention contractions of the busiest rank)",
@@ -713,12 +739,12 @@ def run_lm(args):
                      "unit": "TFLOP/s", "frac": achieved / (peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]),
                      "peak_kind": peak_kind + " (sustained: the kernels run inside a long step)", "traffic": None,
                      "note": "whole-step time, so this fraction also pays for every non-GEMM op of the step"},
-        "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": int(2 * B * 256 * 8) * (1 if dist is None else 1),
+        "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": int(tok_h.numel() * tok_h.element_size() + tgt_h.numel() * tgt_h.element_size()),
                 "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms, "steps": e2e_steps},
         "gpu_launches": int(launches), "clocks": clocks,
     }
     comm.destroy()
-    if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
+    if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline and kind == "lm":
         result["cpu_baseline"] = run_lm_cpu(2, 2, 2)
     if dist is not None:
         dist.barrier()
@@ -920,8 +946,9 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="size sweep instead of the single JSON line")
     ap.add_argument("--sweep-max-mib", type=int, default=1024)
     ap.add_argument("--workload", default="collectives", choices=["collectives", "gemm", "lm", "ops"])
-    ap.add_argument("--lm-batch", type=int, default=32, help="samples per GPU")
-    ap.add_argument("--lm-layers", type=int, default=12)
+    ap.add_argument("--lm-model", default="lm", choices=["lm", "vit", "moe"], help="which program the lm workload steps")
+    ap.add_argument("--lm-batch", type=int, default=0, help="samples per GPU (0: the configuration's 32 / 64 / 16)")
+    ap.add_argument("--lm-layers", type=int, default=0, help="0: the configuration's 12 / 12 / 8")
     ap.add_argument("--lm-plan", default="dp_zero", choices=["dp", "dp_zero"])
     ap.add_argument("--lm-graph", action="store_true", help="capture the training step into a CUDA graph")
     ap.add_argument("--gemm-tokens", type=int, default=8192)
