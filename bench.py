@@ -459,6 +459,47 @@ def run_sweep(args):
             del out, shards, fulls, cases
             a2a_in = None
             torch.cuda.empty_cache()
+    # Secondary sweep in the reference's own convention (profiler.py:85-104, plot_collective_by_group_call.py:15-23):
+    # a 4 MiB (256, 4096) fp32 tensor split on dim 1 (strided shards, 256 runs per shard) with the largest ratio swept
+    # from the even split to 0.95 and the rest shared evenly.
+    cols = 4096
+    for max_ratio in [1.0 / W, 0.25, 0.5, 0.75, 0.95]:
+        if max_ratio < 1.0 / W - 1e-9:
+            continue
+        raw = [max_ratio] + [(1.0 - max_ratio) / (W - 1)] * (W - 1)
+        LS = hap_b200.sharding_round(cols, [x / sum(raw) for x in raw])
+        comm.symm_reset()
+        shards, fulls = [], []
+        for i, r in enumerate(ranks):
+            g = torch.Generator(dev).manual_seed(1000 + r)
+            sh = comm.symm_empty((ROWS, LS[r]), torch.float32, i)
+            sh.copy_(torch.randn(ROWS, LS[r], device=dev, generator=g))
+            fu = comm.symm_empty((ROWS, cols), torch.float32, i)
+            fu.copy_(torch.randn(ROWS, cols, device=dev, generator=g))
+            shards.append(sh)
+            fulls.append(fu)
+        S = ROWS * cols * 4
+        s_r = [ROWS * LS[r] * 4 for r in range(W)]
+        alg = max(max(s_r[r] * (W - 1), S - s_r[r]) for r in range(W))
+        for name, fn in (("all_gather dim1", lambda: comm.all_gather(shards, 1, LS, N.MODE_PADDING)),
+                         ("all_gather_by_group_call dim1", lambda: comm.all_gather(shards, 1, LS, N.MODE_GROUP_CALL)),
+                         ("reduce_scatter dim1", lambda: comm.reduce_scatter(fulls, 1, LS, N.MODE_PADDING))):
+            med, best = timed(fn, 20, inner=10)
+            row = {"op": name, "dtype": "f32", "bytes": S, "world": W, "max_ratio": max_ratio, "lengths": LS, "ms_median": med,
+                   "ms_min": best, "calls_per_timing": 10, "busbw_GBps": S * (W - 1) / W / (med * 1e-3) / 1e9,
+                   "alg_GBps": alg / (med * 1e-3) / 1e9}
+            if not emulated:
+                row["frac_nvlink_900"] = row["alg_GBps"] / NVLINK_NOMINAL_GBS
+                ref = {"all_gather dim1": lambda: gp.all_gather(shards[0], 1, LS, rank),
+                       "all_gather_by_group_call dim1": lambda: gp.all_gather_by_group_call(shards[0], 1, LS, rank),
+                       "reduce_scatter dim1": lambda: gp.reduce_scatter(fulls[0], 1, LS, rank)}[name]
+                rmed, _ = timed(ref, 10, warm=2, inner=10)
+                row["reference_on_nccl_ms_median"] = rmed
+                row["speedup_vs_reference_on_nccl"] = rmed / med
+            rows.append(row)
+            if rank == 0:
+                print(f"max ratio {max_ratio:5.3f}  ", end="")
+                _print_sweep_row(row)
     comm.check()
     comm.destroy()
     if dist is not None:
