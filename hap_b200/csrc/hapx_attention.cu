@@ -35,7 +35,17 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-// rows = batch * L; row r is query (r % L).  S, P: [rows][Lp].  mask: additive [L][L] fp32 or null.
+// rows = batch * L; row r is query (r % L).  S, P: [rows][Lp] with Lp a multiple of 8, so every lane
+// moves groups of 4 consecutive elements: 16-byte loads of fp32 scores, 8-byte stores of bf16
+// probabilities.  Lane l owns the groups l, l + 32, ...  mask: additive [L][L] fp32 or null.
+__device__ __forceinline__ void store_bf16x4(__nv_bfloat16* p, float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 w;
+  w.x = *reinterpret_cast<const unsigned*>(&lo);
+  w.y = *reinterpret_cast<const unsigned*>(&hi);
+  *reinterpret_cast<uint2*>(p) = w;
+}
+
 template <int PL>
 __global__ void __launch_bounds__(256) softmax_fwd_kernel(const float* __restrict__ S, __nv_bfloat16* __restrict__ P, int L, int Lp,
                                                           long long rows, float scale, int causal, const float* __restrict__ mask) {
@@ -43,33 +53,52 @@ __global__ void __launch_bounds__(256) softmax_fwd_kernel(const float* __restric
   if (row >= rows) return;
   const int lane = threadIdx.x & 31, q = (int)(row % L);
   const float* s = S + row * Lp;
-  float v[PL];
+  const int last = causal ? q : L - 1;          // columns after `last` take no part
+  constexpr int NG = PL / 4;
+  float v[NG][4];
   float mx = -INFINITY;
+  const bool mask_vec = mask != nullptr && (L & 3) == 0 && (reinterpret_cast<uintptr_t>(mask) & 15u) == 0;
 #pragma unroll
-  for (int i = 0; i < PL; ++i) {
-    const int j = lane + 32 * i;
-    float x = -INFINITY;
-    if (j < L && !(causal && j > q)) {
-      x = s[j] * scale;
-      if (mask) x += mask[(long long)q * L + j];
+  for (int i = 0; i < NG; ++i) {
+    const int j0 = 4 * (lane + 32 * i);
+    float4 x = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    if (j0 <= last && j0 < Lp) {
+      x = *reinterpret_cast<const float4*>(s + j0);
+      x.x *= scale; x.y *= scale; x.z *= scale; x.w *= scale;
+      if (mask_vec) {
+        const float4 m = *reinterpret_cast<const float4*>(mask + (long long)q * L + j0);
+        x.x += m.x; x.y += m.y; x.z += m.z; x.w += m.w;
+      } else if (mask) {
+        const float* m = mask + (long long)q * L + j0;
+        if (j0 < L) x.x += m[0];
+        if (j0 + 1 < L) x.y += m[1];
+        if (j0 + 2 < L) x.z += m[2];
+        if (j0 + 3 < L) x.w += m[3];
+      }
+      if (j0 + 1 > last) x.y = -INFINITY;
+      if (j0 + 2 > last) x.z = -INFINITY;
+      if (j0 + 3 > last) x.w = -INFINITY;
     }
-    v[i] = x;
-    mx = fmaxf(mx, x);
+    v[i][0] = x.x; v[i][1] = x.y; v[i][2] = x.z; v[i][3] = x.w;
+    mx = fmaxf(fmaxf(mx, fmaxf(x.x, x.y)), fmaxf(x.z, x.w));
   }
   mx = warp_max(mx);
   float sum = 0.f;
 #pragma unroll
-  for (int i = 0; i < PL; ++i) {
-    v[i] = (v[i] == -INFINITY) ? 0.f : __expf(v[i] - mx);
-    sum += v[i];
+  for (int i = 0; i < NG; ++i) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      v[i][k] = (v[i][k] == -INFINITY) ? 0.f : __expf(v[i][k] - mx);
+      sum += v[i][k];
+    }
   }
   sum = warp_sum(sum);
   const float inv = 1.f / sum;
   __nv_bfloat16* p = P + row * Lp;
 #pragma unroll
-  for (int i = 0; i < PL; ++i) {
-    const int j = lane + 32 * i;
-    if (j < Lp) p[j] = __float2bfloat16_rn(j < L ? v[i] * inv : 0.f);
+  for (int i = 0; i < NG; ++i) {
+    const int j0 = 4 * (lane + 32 * i);
+    if (j0 < Lp) store_bf16x4(p + j0, v[i][0] * inv, v[i][1] * inv, v[i][2] * inv, v[i][3] * inv);   // excluded columns hold 0
   }
 }
 
@@ -81,21 +110,33 @@ __global__ void __launch_bounds__(256) softmax_bwd_kernel(const __nv_bfloat16* _
   const int lane = threadIdx.x & 31;
   const __nv_bfloat16* p = P + row * Lp;
   const float* g = dP + row * Lp;
-  float pv[PL], gv[PL];
+  constexpr int NG = PL / 4;
+  float pv[NG][4], gv[NG][4];
   float dot = 0.f;
 #pragma unroll
-  for (int i = 0; i < PL; ++i) {
-    const int j = lane + 32 * i;
-    pv[i] = (j < L) ? __bfloat162float(p[j]) : 0.f;
-    gv[i] = (j < L) ? g[j] : 0.f;
-    dot += pv[i] * gv[i];
+  for (int i = 0; i < NG; ++i) {
+    const int j0 = 4 * (lane + 32 * i);
+    uint2 pw = make_uint2(0u, 0u);
+    float4 gw = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (j0 < Lp) {                       // P is zero in the padding columns [L, Lp) and where the mask excluded a key
+      pw = *reinterpret_cast<const uint2*>(p + j0);
+      gw = *reinterpret_cast<const float4*>(g + j0);
+    }
+    pv[i][0] = __uint_as_float(pw.x << 16); pv[i][1] = __uint_as_float(pw.x & 0xffff0000u);
+    pv[i][2] = __uint_as_float(pw.y << 16); pv[i][3] = __uint_as_float(pw.y & 0xffff0000u);
+    gv[i][0] = (j0 < L) ? gw.x : 0.f; gv[i][1] = (j0 + 1 < L) ? gw.y : 0.f;
+    gv[i][2] = (j0 + 2 < L) ? gw.z : 0.f; gv[i][3] = (j0 + 3 < L) ? gw.w : 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) dot = fmaf(pv[i][k], gv[i][k], dot);
   }
   dot = warp_sum(dot);
   __nv_bfloat16* o = dS + row * Lp;
 #pragma unroll
-  for (int i = 0; i < PL; ++i) {
-    const int j = lane + 32 * i;
-    if (j < Lp) o[j] = __float2bfloat16_rn(j < L ? scale * pv[i] * (gv[i] - dot) : 0.f);
+  for (int i = 0; i < NG; ++i) {
+    const int j0 = 4 * (lane + 32 * i);
+    if (j0 < Lp)
+      store_bf16x4(o + j0, scale * pv[i][0] * (gv[i][0] - dot), scale * pv[i][1] * (gv[i][1] - dot),
+                   scale * pv[i][2] * (gv[i][2] - dot), scale * pv[i][3] * (gv[i][3] - dot));
   }
 }
 

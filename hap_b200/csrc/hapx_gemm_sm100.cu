@@ -1240,11 +1240,60 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16
   if (rg == 0 && c < N)
     partial[(long long)blockIdx.y * N + c] = (part[0][threadIdx.x] + part[1][threadIdx.x]) + (part[2][threadIdx.x] + part[3][threadIdx.x]);
 }
+// Vector variant for 16-byte aligned rows (pitch and width multiples of 8): a block covers 256 columns
+// (32 threads x 8 columns, one 16-byte load each) x 8 row groups of a 64-row slice, so every thread
+// has 8 independent loads in flight.
+constexpr int kColsumSliceRows = 64;
+__global__ void __launch_bounds__(256) colsum_partial_vec_kernel(const __nv_bfloat16* __restrict__ g, long long ldg, int M, int N,
+                                                                 float* __restrict__ partial) {
+  __shared__ float part[8][256];
+  const int ct = threadIdx.x & 31, rg = threadIdx.x >> 5;
+  const int c = blockIdx.x * 256 + ct * 8;
+  const int r0 = blockIdx.y * kColsumSliceRows;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (c < N) {
+    uint4 v[kColsumSliceRows / 8];
+#pragma unroll
+    for (int i = 0; i < kColsumSliceRows / 8; ++i) {
+      const int r = r0 + rg + 8 * i;
+      v[i] = (r < M) ? *reinterpret_cast<const uint4*>(g + (long long)r * ldg + c) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int i = 0; i < kColsumSliceRows / 8; ++i) {
+      const unsigned w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        acc[2 * k] += __uint_as_float(w[k] << 16);
+        acc[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u);
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) part[rg][ct * 8 + k] = acc[k];
+  __syncthreads();
+  const int col = blockIdx.x * 256 + threadIdx.x;
+  if (col < N) {
+    float s = part[0][threadIdx.x];
+#pragma unroll
+    for (int q = 1; q < 8; ++q) s += part[q][threadIdx.x];
+    partial[(long long)blockIdx.y * N + col] = s;
+  }
+}
+// Adds the slices of 32 columns per block: warp w takes slices w, w + 8, ...; the eight sums are added in warp order.
 __global__ void __launch_bounds__(256) colsum_final_kernel(const float* __restrict__ partial, int slices, int N, void* out, int out_f32) {
-  const int c = blockIdx.x * 256 + threadIdx.x;
-  if (c >= N) return;
+  __shared__ float s_sum[8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   float s = 0.f;
-  for (int i = 0; i < slices; ++i) s += partial[(long long)i * N + c];
+  if (c < N) {
+#pragma unroll 4
+    for (int i = warp; i < slices; i += 8) s += partial[(long long)i * N + c];
+  }
+  s_sum[warp][lane] = s;
+  __syncthreads();
+  if (warp != 0 || c >= N) return;
+#pragma unroll
+  for (int w = 1; w < 8; ++w) s += s_sum[w][lane];
   if (out_f32) reinterpret_cast<float*>(out)[c] = s;
   else reinterpret_cast<__nv_bfloat16*>(out)[c] = __float2bfloat16_rn(s);
 }
@@ -1254,14 +1303,20 @@ int colsum_bf16(const void* g, long long m, long long n, void* out, int out_f32,
   if (m < 0 || m > 0x7fffffff || n > 0x7fffffff) return fail(HAPX_ERR_EXTENT, "linear_wgrad: extent out of range");
   int device = 0;
   HAPX_CUDA(cudaGetDevice(&device));
-  const int rows_per_slice = (int)std::max<long long>(128, (m + 65534) / 65535);
+  const bool vec = (n % 8 == 0) && (reinterpret_cast<uintptr_t>(g) & 15u) == 0 && (m + kColsumSliceRows - 1) / kColsumSliceRows <= 65535;
+  const int rows_per_slice = vec ? kColsumSliceRows : (int)std::max<long long>(128, (m + 65534) / 65535);
   const int slices = (int)std::max<long long>(1, (m + rows_per_slice - 1) / rows_per_slice);
   float* ws = nullptr;
   if (int e = workspace(device, (size_t)slices * n * sizeof(float), &ws)) return e;
-  dim3 grid((unsigned)((n + 63) / 64), (unsigned)slices);
-  colsum_partial_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(g), n, (int)m, (int)n, rows_per_slice, ws);
+  if (vec) {
+    dim3 grid((unsigned)((n + 255) / 256), (unsigned)slices);
+    colsum_partial_vec_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(g), n, (int)m, (int)n, ws);
+  } else {
+    dim3 grid((unsigned)((n + 63) / 64), (unsigned)slices);
+    colsum_partial_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(g), n, (int)m, (int)n, rows_per_slice, ws);
+  }
   HAPX_CUDA(cudaGetLastError());
-  colsum_final_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(ws, slices, (int)n, out, out_f32);
+  colsum_final_kernel<<<(unsigned)((n + 31) / 32), 256, 0, stream>>>(ws, slices, (int)n, out, out_f32);
   HAPX_CUDA(cudaGetLastError());
   count_launch(2);
   return HAPX_OK;
