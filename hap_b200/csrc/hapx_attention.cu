@@ -46,15 +46,26 @@ __device__ __forceinline__ void store_bf16x4(__nv_bfloat16* p, float a, float b,
   *reinterpret_cast<uint2*>(p) = w;
 }
 
+// The kernel is bound by instruction issue, not by HBM, unless it is written frugally: 32-bit row
+// arithmetic (rows < 2^31 is checked on the host), the scale folded with log2(e) into one multiply,
+// exp2 on the special-function unit, no work at all for groups of columns the causal rule excludes.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int PL>
 __global__ void __launch_bounds__(256) softmax_fwd_kernel(const float* __restrict__ S, __nv_bfloat16* __restrict__ P, int L, int Lp,
                                                           long long rows, float scale, int causal, const float* __restrict__ mask) {
-  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const int lane = threadIdx.x & 31, q = (int)(row % L);
-  const float* s = S + row * Lp;
+  const unsigned row = blockIdx.x * 8u + (threadIdx.x >> 5);
+  if (row >= (unsigned)rows) return;
+  const int lane = threadIdx.x & 31, q = (int)(row % (unsigned)L);
+  const float* s = S + (size_t)row * (unsigned)Lp;
   const int last = causal ? q : L - 1;          // columns after `last` take no part
   constexpr int NG = PL / 4;
+  constexpr float kLog2e = 1.4426950408889634f;
+  const float scale2 = scale * kLog2e;          // softmax(x) = 2^(x log2 e - max) / sum
   float v[NG][4];
   float mx = -INFINITY;
   const bool mask_vec = mask != nullptr && (L & 3) == 0 && (reinterpret_cast<uintptr_t>(mask) & 15u) == 0;
@@ -62,39 +73,45 @@ __global__ void __launch_bounds__(256) softmax_fwd_kernel(const float* __restric
   for (int i = 0; i < NG; ++i) {
     const int j0 = 4 * (lane + 32 * i);
     float4 x = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-    if (j0 <= last && j0 < Lp) {
+    if (j0 <= last) {                           // last < L <= Lp
       x = *reinterpret_cast<const float4*>(s + j0);
-      x.x *= scale; x.y *= scale; x.z *= scale; x.w *= scale;
+      x.x *= scale2; x.y *= scale2; x.z *= scale2; x.w *= scale2;
       if (mask_vec) {
-        const float4 m = *reinterpret_cast<const float4*>(mask + (long long)q * L + j0);
-        x.x += m.x; x.y += m.y; x.z += m.z; x.w += m.w;
+        const float4 m = *reinterpret_cast<const float4*>(mask + (size_t)q * (unsigned)L + j0);
+        x.x = fmaf(m.x, kLog2e, x.x); x.y = fmaf(m.y, kLog2e, x.y); x.z = fmaf(m.z, kLog2e, x.z); x.w = fmaf(m.w, kLog2e, x.w);
       } else if (mask) {
-        const float* m = mask + (long long)q * L + j0;
-        if (j0 < L) x.x += m[0];
-        if (j0 + 1 < L) x.y += m[1];
-        if (j0 + 2 < L) x.z += m[2];
-        if (j0 + 3 < L) x.w += m[3];
+        const float* m = mask + (size_t)q * (unsigned)L + j0;
+        x.x = fmaf(m[0], kLog2e, x.x);
+        if (j0 + 1 < L) x.y = fmaf(m[1], kLog2e, x.y);
+        if (j0 + 2 < L) x.z = fmaf(m[2], kLog2e, x.z);
+        if (j0 + 3 < L) x.w = fmaf(m[3], kLog2e, x.w);
       }
-      if (j0 + 1 > last) x.y = -INFINITY;
-      if (j0 + 2 > last) x.z = -INFINITY;
-      if (j0 + 3 > last) x.w = -INFINITY;
+      if (j0 + 3 > last) {                      // the group straddles the last column
+        if (j0 + 1 > last) x.y = -INFINITY;
+        if (j0 + 2 > last) x.z = -INFINITY;
+        x.w = -INFINITY;
+      }
+      mx = fmaxf(fmaxf(mx, fmaxf(x.x, x.y)), fmaxf(x.z, x.w));
     }
     v[i][0] = x.x; v[i][1] = x.y; v[i][2] = x.z; v[i][3] = x.w;
-    mx = fmaxf(fmaxf(mx, fmaxf(x.x, x.y)), fmaxf(x.z, x.w));
   }
   mx = warp_max(mx);
   float sum = 0.f;
 #pragma unroll
   for (int i = 0; i < NG; ++i) {
+    if (4 * (lane + 32 * i) <= last) {          // 2^(-inf - max) = 0 for excluded columns inside a live group
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      v[i][k] = (v[i][k] == -INFINITY) ? 0.f : __expf(v[i][k] - mx);
-      sum += v[i][k];
+      for (int k = 0; k < 4; ++k) {
+        v[i][k] = fast_exp2(v[i][k] - mx);
+        sum += v[i][k];
+      }
+    } else {
+      v[i][0] = v[i][1] = v[i][2] = v[i][3] = 0.f;
     }
   }
   sum = warp_sum(sum);
   const float inv = 1.f / sum;
-  __nv_bfloat16* p = P + row * Lp;
+  __nv_bfloat16* p = P + (size_t)row * (unsigned)Lp;
 #pragma unroll
   for (int i = 0; i < NG; ++i) {
     const int j0 = 4 * (lane + 32 * i);
@@ -105,11 +122,11 @@ __global__ void __launch_bounds__(256) softmax_fwd_kernel(const float* __restric
 template <int PL>
 __global__ void __launch_bounds__(256) softmax_bwd_kernel(const __nv_bfloat16* __restrict__ P, const float* __restrict__ dP,
                                                           __nv_bfloat16* __restrict__ dS, int L, int Lp, long long rows, float scale) {
-  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
+  const unsigned row = blockIdx.x * 8u + (threadIdx.x >> 5);
+  if (row >= (unsigned)rows) return;
   const int lane = threadIdx.x & 31;
-  const __nv_bfloat16* p = P + row * Lp;
-  const float* g = dP + row * Lp;
+  const __nv_bfloat16* p = P + (size_t)row * (unsigned)Lp;
+  const float* g = dP + (size_t)row * (unsigned)Lp;
   constexpr int NG = PL / 4;
   float pv[NG][4], gv[NG][4];
   float dot = 0.f;
@@ -130,7 +147,7 @@ __global__ void __launch_bounds__(256) softmax_bwd_kernel(const __nv_bfloat16* _
     for (int k = 0; k < 4; ++k) dot = fmaf(pv[i][k], gv[i][k], dot);
   }
   dot = warp_sum(dot);
-  __nv_bfloat16* o = dS + row * Lp;
+  __nv_bfloat16* o = dS + (size_t)row * (unsigned)Lp;
 #pragma unroll
   for (int i = 0; i < NG; ++i) {
     const int j0 = 4 * (lane + 32 * i);
@@ -156,7 +173,7 @@ static int check(long long L, long long N, long long H, long long D) {
   if (L < 0 || N < 0 || H < 1 || D < 1) return fail(HAPX_ERR_EXTENT, "attention: negative extent");
   if (L > 32 * kMaxPerLane) return fail(HAPX_ERR_EXTENT, "attention: sequence length above 1024 is not supported");
   if (D % 8 != 0) return fail(HAPX_ERR_EXTENT, "attention: head dimension must be a multiple of 8");
-  if (N * H > 0x7fffffff) return fail(HAPX_ERR_EXTENT, "attention: too many (batch, head) pairs");
+  if (N * H > 0x7fffffff || N * H * L > 0x7fffffff) return fail(HAPX_ERR_EXTENT, "attention: too many (batch, head, query) rows");
   return HAPX_OK;
 }
 
