@@ -746,6 +746,8 @@ def run_lm(args):
     b.record()
     barrier()
     launches = N.lib.hapx_launch_count() - l0
+    if args.lm_graph:       # a replay issues no host-side launches: count the kernels recorded into the graph
+        launches = worker.captured_launches * args.steps
     clocks = sampler.finish()
     ms = a.elapsed_time(b) / args.steps
     # end to end: tokens come from pinned host memory every step, the loss goes back to the host

@@ -185,10 +185,13 @@ class ProcessWorker:
                 self.step(*static_in)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        from . import _native as N
         graph = torch.cuda.CUDAGraph()
+        before = N.lib.hapx_launch_count()
         with torch.cuda.graph(graph):
             static_out = self.step(*static_in)
         self._graph = graph
+        self.captured_launches = int(N.lib.hapx_launch_count() - before)    # kernels of this library in one replay
 
         def replay(*inputs):
             for dst, src in zip(static_in, inputs):
