@@ -1,0 +1,98 @@
+"""fx passes that point a planner-generated program at this package's kernels.
+
+The planner stores function objects in its ``call_function`` nodes (``hap.rs:899-902``).  For the
+collectives the replacement module is installed before the planner runs, or
+:func:`hap_b200.collectives.retarget_fx_graph` is applied afterwards; for the tensor ops the
+planner names torch functions directly (``torch.nn.functional.linear`` at ``hap.rs:995, 1032``,
+``multi_head_attention_forward`` at ``hap.rs:1243, 1301``, ``torch.einsum`` at ``hap.rs:2240, 2273``,
+``layer_norm`` at ``hap.rs:1637-1660``, ``log_softmax`` / ``nll_loss`` at ``hap.rs:1808, 1858``), so an
+emitted graph is rewritten node by node here.  Every replacement takes the same arguments as the
+function it replaces, so only ``node.target`` changes - except for the loss pair, which is folded
+into one node.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+import torch.nn.functional as F
+
+
+def _is(target, *candidates) -> bool:
+    return any(target is c for c in candidates)
+
+
+def retarget_tensor_ops(graph: torch.fx.Graph, fold_loss: bool = True) -> Dict[str, int]:
+    """Rewrite ``graph`` in place; returns how many nodes of each kind were changed.
+
+    * ``F.linear`` -> :func:`hap_b200.linear`
+    * ``F.multi_head_attention_forward`` -> :func:`hap_b200.attention.multi_head_attention_forward`
+    * ``torch.einsum`` with one of the four MoE codes -> :func:`hap_b200.einsum`
+    * ``F.layer_norm`` -> :func:`hap_b200.layer_norm`
+    * ``nll_loss(log_softmax(x[.float()], -1)[.reshape(-1, V)], y[.reshape(-1)], reduction='sum')``
+      -> :func:`hap_b200.nll_log_softmax_sum` ``(x, y)`` when the intermediate nodes have no other user.
+    """
+    from .attention import multi_head_attention_forward
+    from .einsum import CODES as SUPPORTED_CODES, einsum
+    from .linear import linear
+    from .loss import nll_log_softmax_sum
+    from .norm import layer_norm
+
+    changed = {"linear": 0, "multi_head_attention_forward": 0, "einsum": 0, "layer_norm": 0, "loss": 0}
+    for node in list(graph.nodes):
+        if node.op != "call_function":
+            continue
+        t = node.target
+        if _is(t, F.linear, torch._C._nn.linear):
+            node.target = linear
+            changed["linear"] += 1
+        elif _is(t, F.multi_head_attention_forward):
+            node.target = multi_head_attention_forward
+            changed["multi_head_attention_forward"] += 1
+        elif _is(t, torch.einsum) and node.args and isinstance(node.args[0], str) and node.args[0].replace(" ", "") in SUPPORTED_CODES:
+            node.target = einsum
+            changed["einsum"] += 1
+        elif _is(t, F.layer_norm):
+            node.target = layer_norm
+            changed["layer_norm"] += 1
+        elif fold_loss and _is(t, F.nll_loss) and _fold_loss(graph, node, nll_log_softmax_sum):
+            changed["loss"] += 1
+    graph.lint()
+    return changed
+
+
+def _peel(node, method: str):
+    """If ``node`` is ``x.<method>(...)`` return ``x`` else ``node`` itself."""
+    if isinstance(node, torch.fx.Node) and node.op == "call_method" and node.target == method:
+        return node.args[0], node
+    return node, None
+
+
+def _fold_loss(graph: torch.fx.Graph, nll: torch.fx.Node, fused) -> bool:
+    if nll.kwargs.get("reduction") != "sum" or len(nll.args) < 2 or len(nll.args) > 2:
+        return False
+    if any(k not in ("reduction",) for k in nll.kwargs):
+        return False
+    logp, tgt = nll.args[0], nll.args[1]
+    logp_src, reshape_node = _peel(logp, "reshape")
+    if not (isinstance(logp_src, torch.fx.Node) and logp_src.op == "call_function"
+            and _is(logp_src.target, F.log_softmax, torch.log_softmax)):
+        return False
+    dim = logp_src.args[1] if len(logp_src.args) > 1 else logp_src.kwargs.get("dim")
+    if dim != -1:
+        return False
+    logits, float_node = _peel(logp_src.args[0], "float")
+    tgt_src, tgt_reshape = _peel(tgt, "reshape")
+    if tgt_reshape is not None and tuple(tgt_reshape.args[1:]) != (-1,):
+        return False
+    # the intermediates must feed nothing else
+    for n in (logp_src, reshape_node, float_node):
+        if n is not None and len(n.users) != 1:
+            return False
+    with graph.inserting_before(nll):
+        new = graph.call_function(fused, (logits, tgt_src))
+    nll.replace_all_uses_with(new)
+    for n in (nll, reshape_node, logp_src, float_node, tgt_reshape):
+        if n is not None and not n.users:
+            graph.erase_node(n)
+    return True

@@ -1,0 +1,80 @@
+"""Rewriting a program that names torch's functions (as the planner emits it) onto the package's ops."""
+import copy
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from tests import spmd_common as C
+
+
+def _names(graph):
+    return [getattr(n.target, "__name__", str(n.target)) for n in graph.nodes if n.op == "call_function"]
+
+
+def test_targets_are_swapped_and_the_loss_pair_is_folded():
+    import hap_b200
+    from hap_b200 import fxpass
+    from hap_b200 import plan as P
+    model = C.lm_model()
+    graph = P.emit_lm(copy.deepcopy(model), "dp_zero", C.RATIOS, 0, C.LM_BATCH, C.lm_cpu_namespace())   # torch's functions
+    before = _names(graph)
+    assert "log_softmax" in before and "nll_loss" in before
+    changed = fxpass.retarget_tensor_ops(graph)
+    nl = C.LM_SMALL["nlayers"]
+    assert changed == {"linear": 2 * nl + 1, "multi_head_attention_forward": nl, "einsum": 0, "layer_norm": 2 * nl + 1, "loss": 1}
+    after = [n for n in graph.nodes if n.op == "call_function"]
+    assert not any(n.target in (F.linear, F.layer_norm, F.multi_head_attention_forward, F.nll_loss, F.log_softmax) for n in after)
+    assert sum(n.target is hap_b200.nll_log_softmax_sum for n in after) == 1
+    assert not any(n.op == "call_method" and n.target == "float" for n in graph.nodes)
+    # collectives are left alone (they belong to the other pass)
+    assert _names(graph).count("all_gather") == before.count("all_gather")
+
+    moe = C.moe_model()
+    g2 = P.emit_moe(copy.deepcopy(moe), C.RATIOS, 0, C.LM_BATCH, C.moe_cpu_namespace())
+    changed = fxpass.retarget_tensor_ops(g2)
+    assert changed["einsum"] == 4 * C.MOE_SMALL["nlayers"] and changed["loss"] == 1
+
+
+def test_loss_is_not_folded_when_the_log_probabilities_are_used_elsewhere():
+    from hap_b200 import fxpass
+    g = torch.fx.Graph()
+    x, y = g.placeholder("x"), g.placeholder("y")
+    logp = g.call_function(F.log_softmax, (x, -1))
+    loss = g.call_function(F.nll_loss, (logp, y), {"reduction": "sum"})
+    g.output((loss, logp))
+    assert fxpass.retarget_tensor_ops(g)["loss"] == 0
+    g2 = torch.fx.Graph()
+    x, y = g2.placeholder("x"), g2.placeholder("y")
+    loss = g2.call_function(F.nll_loss, (g2.call_function(F.log_softmax, (x, -1)), y), {"reduction": "mean"})
+    g2.output(loss)
+    assert fxpass.retarget_tensor_ops(g2)["loss"] == 0
+
+
+@pytest.mark.gpu
+def test_rewritten_program_matches_the_natively_emitted_one():
+    import hap_b200
+    from hap_b200 import fxpass
+    from hap_b200 import plan as P
+    from hap_b200.spmd import LockstepWorld
+    dev = torch.device("cuda:0")
+    model = C.lm_model(torch.bfloat16)
+    tok, tgt = (t.to(dev) for t in C.lm_batch())
+    comm = hap_b200.local_comm(2, dev, stage_bytes=16 << 20, heap_bytes=32 << 20)
+    try:
+        native = LockstepWorld(C.lm_rank_modules(model, "dp_zero", P.default_namespace(), device=dev), hap_b200.LocalCollectives(comm))
+        # the same program with torch's functions as targets, then rewritten
+        ns = P.default_namespace()
+        torch_ns = type(ns)(collectives=ns.collectives, linear=F.linear, mha=F.multi_head_attention_forward)
+        mods = C.lm_rank_modules(model, "dp_zero", torch_ns, device=dev)
+        for m in mods:
+            assert fxpass.retarget_tensor_ops(m.graph)["loss"] == 1
+            m.recompile()
+        rewritten = LockstepWorld(mods, hap_b200.LocalCollectives(comm))
+        a = native.forward([(tok, tgt), (tok, tgt)])
+        b = rewritten.forward([(tok, tgt), (tok, tgt)])
+        for x, y in zip(a, b):
+            assert float(x) == float(y)
+        comm.check()
+    finally:
+        comm.destroy()

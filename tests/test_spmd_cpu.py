@@ -171,3 +171,50 @@ def test_expert_parallel_moe_program_reproduces_the_unsharded_model():
             if p.shape != g.shape:
                 g = torch.split(g, sharding_round(g.shape[0], C.RATIOS), dim=0)[r]
             torch.testing.assert_close(p.grad, g, rtol=1e-3, atol=1e-4)
+
+
+def _gloo_program_worker(rank, world, store, kind, out_dir):
+    sys.path.insert(0, ROOT)
+    import copy
+    import torch.distributed as dist
+    from tests import spmd_common as C2
+    dist.init_process_group("gloo", rank=rank, world_size=world, init_method=f"file://{store}")
+    if kind == "lm":
+        m = copy.deepcopy(C2.lm_model())
+        graph, inputs = C2.P.emit_lm(m, "dp_zero", C2.RATIOS, rank, C2.LM_BATCH, C2.lm_cpu_namespace()), C2.lm_batch()
+    elif kind == "vit":
+        m = copy.deepcopy(C2.vit_model())
+        graph, inputs = C2.P.emit_vit(m, "dp_zero", C2.RATIOS, rank, C2.LM_BATCH, C2.lm_cpu_namespace()), C2.vit_batch()
+    else:
+        m = copy.deepcopy(C2.moe_model())
+        graph, inputs = C2.P.emit_moe(m, C2.RATIOS, rank, C2.LM_BATCH, C2.moe_cpu_namespace()), C2.lm_batch()
+    worker = ProcessWorker(torch.fx.GraphModule(m, graph), reduce_loss=lambda t: (dist.all_reduce(t), t)[1])
+    totals = [float(worker.step(*inputs)) for _ in range(2)]
+    torch.save({"totals": totals, "params": {n: p.detach().clone() for n, p in worker.module.named_parameters()}},
+               os.path.join(out_dir, f"rank{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("kind", ["lm", "vit", "moe"])
+def test_two_gloo_processes_run_the_transformer_programs(kind):
+    """The N > 1 host path for the Transformer programs: one process per rank over gloo with the port of the
+    reference's collectives (all_to_all included) must walk the same two steps as the lockstep replay."""
+    if kind == "lm":
+        mods, inputs = C.lm_rank_modules(C.lm_model(), "dp_zero", C.lm_cpu_namespace()), C.lm_batch()
+    elif kind == "vit":
+        mods, inputs = C.vit_rank_modules(C.vit_model(), "dp_zero", C.lm_cpu_namespace()), C.vit_batch()
+    else:
+        mods, inputs = C.moe_rank_modules(C.moe_model(), C.moe_cpu_namespace()), C.lm_batch()
+    world = LockstepWorld(mods, OracleCollectives())
+    want_totals = [float(world.step([inputs, inputs])) for _ in range(2)]
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_gloo_program_worker, args=(2, os.path.join(d, "store"), kind, d), nprocs=2, join=True)
+        for r in range(2):
+            got = torch.load(os.path.join(d, f"rank{r}.pt"), weights_only=False)
+            for a, b in zip(got["totals"], want_totals):
+                assert abs(a - b) <= 1e-4 * abs(b), (kind, got["totals"], want_totals)
+            for name, p in world.modules[r].named_parameters():
+                # Adam moves every entry by about lr per step whatever the gradient's size: entries whose
+                # gradient is rounding noise may differ by the distance of two steps (lr = 5e-4)
+                assert float((got["params"][name] - p.detach()).abs().max()) <= 2.5 * 5e-4, (kind, name)
