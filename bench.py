@@ -292,8 +292,13 @@ def run_gpu_arm(args):
         alg = (W + 1) * S
         dom = ("pull_reduce_kernel<float,float> (reduce_scatter)", rs_ms) if rs_ms >= ag_ms else ("pull_copy_kernel (all_gather)", ag_ms)
         achieved = alg / (dom[1] * 1e-3) / 1e9
+        # DRAM traffic per launch from the ncu capture of the same kernels at 128 MiB (summary under profiles/:
+        # reduce 1.198 GB, copy 1.152 GB for 1.208 GB algorithmic), scaled with the tensor size - it grows in
+        # proportion, every byte is touched once
+        ratio = 0.992 if dom[0].startswith("pull_reduce") else 0.954
         roofline = {"bound": "hbm", "kernel": dom[0], "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": achieved / peaks["hbm_gbs"], "peak_kind": peak_kind, "traffic": None,
+                    "frac": achieved / peaks["hbm_gbs"], "peak_kind": peak_kind, "traffic": int(ratio * alg),
+                    "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum at 128 MiB, scaled by size",
                     "algorithmic_bytes_per_launch": alg, "launch_ms": dom[1]}
     else:
         s = [L[r] * cols * es for r in range(W)]
