@@ -100,11 +100,13 @@ class ClipAdam:
             packed = {}
             for code, idx in live.items():
                 key = (code, tuple(idx))
-                fixed = self._fixed.get(key)
-                if fixed is None:       # parameter / moment addresses and sizes do not change between steps
-                    fixed = self._fixed[key] = (
-                        N.ptr_array([self.params[i].data_ptr() for i in idx]), N.ptr_array([self.exp_avg[i].data_ptr() for i in idx]),
-                        N.ptr_array([self.exp_avg_sq[i].data_ptr() for i in idx]), N.i64_array([self.params[i].numel() for i in idx]))
+                where = [self.params[i].data_ptr() for i in idx]
+                cached = self._fixed.get(key)
+                if cached is None or cached[0] != where:       # parameter addresses normally stay put between steps
+                    cached = self._fixed[key] = (where, (
+                        N.ptr_array(where), N.ptr_array([self.exp_avg[i].data_ptr() for i in idx]),
+                        N.ptr_array([self.exp_avg_sq[i].data_ptr() for i in idx]), N.i64_array([self.params[i].numel() for i in idx])))
+                fixed = cached[1]
                 grads = (C.c_void_p * len(idx))(*[self.params[i].grad.data_ptr() for i in idx])
                 packed[code] = (len(idx), grads) + fixed
             if self.max_norm is not None:
