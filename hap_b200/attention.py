@@ -10,7 +10,6 @@ package's linear kernels and the attention core on the batched tensor-core GEMMs
 """
 from __future__ import annotations
 
-import math
 from typing import Optional
 
 import torch

@@ -29,7 +29,6 @@ unmodified reference side by side on gloo ranks and requires identical results.
 """
 from __future__ import annotations
 
-from typing import List, Sequence
 
 import torch
 import torch.distributed as dist

@@ -10,7 +10,7 @@ import torch
 import hap_b200
 from hap_b200 import _native as N
 from oracle import collectives_math as cm
-from tests.helpers import exact_op, load_golden, oracle_backward, oracle_forward
+from tests.helpers import exact_op, load_golden
 
 pytestmark = pytest.mark.gpu
 

@@ -8,7 +8,6 @@ point gives the same bits as the communicator-based hapx_all_reduce on two calls
 second with other data and another size, so leftovers of the first call in the shared scratch
 would show), and that oversized calls are refused.  It is collected last on purpose.
 """
-import ctypes as C
 
 import pytest
 import torch
