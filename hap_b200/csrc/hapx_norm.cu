@@ -231,23 +231,25 @@ __global__ void __launch_bounds__(kThreads, (NV <= 3 ? 3 : 2)) layer_norm_backwa
 }
 
 // dgamma[e] = sum_b partial[b][0][e], dbeta[e] = sum_b partial[b][1][e].  A thread block owns 32 of the
-// 2E columns; its 8 warps add the partial rows w, w + 8, ... and the eight sums are added in warp order.
+// 2E columns; its 32 warps add the partial rows w, w + 32, ... (a dozen dependent loads each instead of
+// several dozen: the kernel is latency-bound) and the 32 sums are added in warp order.
+constexpr int kGradWarps = 32;
 template <typename T>
-__global__ void __launch_bounds__(256) layer_norm_param_grad_kernel(const float* __restrict__ partial, int blocks, int E,
-                                                                    T* __restrict__ dgamma, T* __restrict__ dbeta) {
-  __shared__ float s_sum[8][32];
+__global__ void __launch_bounds__(kGradWarps * 32) layer_norm_param_grad_kernel(const float* __restrict__ partial, int blocks, int E,
+                                                                                T* __restrict__ dgamma, T* __restrict__ dbeta) {
+  __shared__ float s_sum[kGradWarps][32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int e = blockIdx.x * 32 + lane;
   float s = 0.f;
   if (e < 2 * E) {
 #pragma unroll 4
-    for (int b = warp; b < blocks; b += 8) s += partial[(long long)b * 2 * E + e];
+    for (int b = warp; b < blocks; b += kGradWarps) s += partial[(long long)b * 2 * E + e];
   }
   s_sum[warp][lane] = s;
   __syncthreads();
   if (warp != 0 || e >= 2 * E) return;
 #pragma unroll
-  for (int w = 1; w < 8; ++w) s += s_sum[w][lane];
+  for (int w = 1; w < kGradWarps; ++w) s += s_sum[w][lane];
   if (e < E) {
     if (dgamma) { if constexpr (sizeof(T) == 2) dgamma[e] = __float2bfloat16_rn(s); else dgamma[e] = s; }
   } else if (dbeta) {
@@ -346,7 +348,7 @@ int hapx_layer_norm_backward(const void* x, const void* dy, const void* gamma, c
     count_launch(1);
   }
   if (dgamma || dbeta) {
-    const int threads = 256, blocks = (int)((2 * E + 31) / 32);
+    const int threads = kGradWarps * 32, blocks = (int)((2 * E + 31) / 32);
     if (dtype == HAPX_BF16)
       layer_norm_param_grad_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(partial, grid, (int)E, static_cast<__nv_bfloat16*>(dgamma),
                                                                                   static_cast<__nv_bfloat16*>(dbeta));
