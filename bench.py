@@ -1,15 +1,23 @@
 #!/usr/bin/env python
-"""Benchmark of the uneven-collective hot path (the reference's collective micro-benchmark
-configuration: a (256, C) tensor split on dim 0 by ratios [.22,.18,.15,.13,.11,.09,.07,.05]).
+"""Benchmark of the hot path: the uneven collectives and the synthesized SPMD training step.
 
     python bench.py --gpus 1 --steps K --warmup W            # 8 virtual ranks on one GPU (HBM bound)
     torchrun --nproc-per-node N ... bench.py --gpus N ...    # one rank per GPU over NVLink (N = 2, 4, 8)
     python bench.py --impl reference ...                     # the CPU port of the reference on gloo ranks
 
-A step = one uneven all_gather + one reduce_scatter + one all_reduce of a tensor of
-``--size-mib`` MiB.  ``value`` is the nccl-tests style bus bandwidth of the step
-(bus bytes = S(W-1)/W + S(W-1)/W + 2S(W-1)/W), summed over the GPUs of the job.
-Prints ONE JSON line on rank 0.
+The default run prints ONE JSON line on rank 0 with three parts:
+
+* the collective micro-benchmark (the line's ``metric`` / ``value``): a step = one uneven all_gather +
+  one reduce_scatter + one all_reduce of a (256, C) fp32 tensor of ``--size-mib`` MiB split on dim 0 by
+  the ratios [.22,.18,.15,.13,.11,.09,.07,.05]; ``value`` is the nccl-tests style bus bandwidth of the
+  step (bus bytes = S(W-1)/W + S(W-1)/W + 2S(W-1)/W), summed over the GPUs of the job;
+* ``parity``: outside every timed region, the drop-in ``hap_b200.collectives`` functions (and the list
+  API on one GPU) on small seeded tensors, both ordinary torch tensors (staged) and heap-resident
+  ones, checked against the CPU oracle;
+* ``spmd_step``: samples/s of the Transformer-LM training step (plan dp_zero, the whole iteration
+  replayed from a CUDA graph), with its tensor roofline and its own end-to-end figure.
+
+``--workload gemm|lm|ops`` and ``--sweep`` run the individual studies.
 """
 from __future__ import annotations
 
@@ -26,10 +34,12 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+# a collective that gets stuck in a benchmark should fail in seconds, not after the library's ten minutes
+os.environ.setdefault("HAPX_TIMEOUT_MS", "30000")
+
 R8 = [.22, .18, .15, .13, .11, .09, .07, .05]
 ROWS = 256
 NVLINK_NOMINAL_GBS = 900.0      # per direction per GPU
-NVLINK_MEASURED_GBS = 770.0     # peer copy measured on this pool
 
 
 def ratios_for(world):
@@ -142,19 +152,74 @@ class ClockSampler(threading.Thread):
 # ----------------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------------
-def run_gpu_arm(args):
+def collective_config(W, size_mib, emulated):
+    """The `config` of the collective micro-benchmark; the reference arm prints the same object."""
+    import hap_b200
+    cols = (size_mib << 20) // (ROWS * 4)
+    return {"workload": f"uneven collective micro-benchmark: all_gather + reduce_scatter + all_reduce of a "
+                        f"({ROWS}, {cols}) fp32 tensor ({size_mib} MiB) split on dim 0",
+            "world": W, "sharding_lengths": hap_b200.sharding_round(ROWS, ratios_for(W)), "ratios": "r8 (first W renormalised)",
+            "ranks": ("8 virtual ranks on ONE GPU (an emulation of the 8-GPU exchange, one cooperative launch per collective, HBM bound): "
+                      "not a point of a scaling curve") if emulated else "one process per GPU, peer loads over NVLink",
+            "inputs": "resident in the peer-visible heap", "l2": "inputs larger than L2 (126 MB)",
+            "cpu_arm": "the reference arm and cpu_baseline time a bounded sample of this workload (a smaller tensor, see cpu_baseline.sample)"}
+
+
+class Job:
+    """Process-wide state of one bench run: rank, device, torch.distributed (N > 1 only)."""
+
+    def __init__(self, n_gpus):
+        import torch
+        self.n_gpus = n_gpus
+        self.rank = int(os.environ.get("RANK", 0))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", 0))
+        world_env = int(os.environ.get("WORLD_SIZE", 1))
+        if n_gpus > 1 and world_env != n_gpus:
+            raise SystemExit(f"--gpus {n_gpus} needs a launcher with WORLD_SIZE={n_gpus} (torchrun); got {world_env}")
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        self.dist = None
+        if n_gpus > 1:
+            import torch.distributed as dist
+            dist.init_process_group("cpu:gloo,cuda:nccl", rank=self.rank, world_size=n_gpus)
+            self.dist = dist
+
+    def barrier(self):
+        import torch
+        if self.dist is not None:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(self, *xs):
+        import torch
+        if self.dist is None:
+            return xs if len(xs) > 1 else xs[0]
+        t = torch.tensor(list(xs), dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        out = [float(v) for v in t]
+        return out if len(out) > 1 else out[0]
+
+    def everyone(self, obj):
+        """All ranks' `obj` in rank order (host transport)."""
+        if self.dist is None:
+            return [obj]
+        got = [None] * self.n_gpus
+        self.dist.all_gather_object(got, obj)
+        return got
+
+    def finish(self):
+        if self.dist is not None:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
+def run_collective_bench(args, job):
+    """The collective micro-benchmark: the JSON line's metric / value / roofline / e2e."""
     import torch
     import hap_b200
     from hap_b200 import _native as N
 
-    n_gpus = args.gpus
-    rank = int(os.environ.get("RANK", 0))
-    local_rank = int(os.environ.get("LOCAL_RANK", 0))
-    world_env = int(os.environ.get("WORLD_SIZE", 1))
-    if n_gpus > 1 and world_env != n_gpus:
-        raise SystemExit(f"--gpus {n_gpus} needs a launcher with WORLD_SIZE={n_gpus} (torchrun); got {world_env}")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
+    n_gpus, rank, dev, dist = job.n_gpus, job.rank, job.dev, job.dist
     S = args.size_mib << 20
     dtype = torch.float32
     es = 4
@@ -167,10 +232,7 @@ def run_gpu_arm(args):
 
     if emulated:
         comm = hap_b200.local_comm(W, dev, heap_bytes=heap, stage_bytes=stage)
-        dist = None
     else:
-        import torch.distributed as dist
-        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=n_gpus)
         comm = hap_b200.init_process_comm(heap_bytes=heap, stage_bytes=stage)
         hap_b200.collectives.set_default_comm(comm)
     ranks = comm.ranks()
@@ -187,12 +249,7 @@ def run_gpu_arm(args):
         shards.append(sh)
         fulls.append(fu)
     ag_out = [torch.empty(ROWS, cols, dtype=dtype, device=dev) for _ in ranks]
-
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
+    barrier = job.barrier
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
     def step(events=None):
@@ -212,7 +269,7 @@ def run_gpu_arm(args):
         step()
     barrier()
     comm.check()
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(job.local_rank)
     sampler.start()
     launches0 = N.lib.hapx_launch_count()
     events = []
@@ -228,18 +285,27 @@ def run_gpu_arm(args):
     comm.check()
     total_ms = t_begin.elapsed_time(t_end)
     op_ms = [sum(m[k].elapsed_time(m[k + 1]) for m in events) / len(events) for k in range(3)]
-
-    def max_over_ranks(x):
-        if dist is None:
-            return x
-        t = torch.tensor([x], dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t[0])
-
-    total_ms = max_over_ranks(total_ms)
-    op_ms = [max_over_ranks(x) for x in op_ms]
+    total_ms = job.max_over_ranks(total_ms)
+    op_ms = list(job.max_over_ranks(*op_ms))
     ms_per_step = total_ms / args.steps
     busbw = bus_bytes(S, W) / (ms_per_step * 1e-3) / 1e9
+
+    # ---- the link's own rate: rank 0 reads rank 1's copy of the 'fulls' tensor with the copy kernel ----
+    peer_copy = None
+    if dist is not None:
+        dst = ag_out[0]
+        ts = []
+        for _ in range(4):
+            barrier()
+            if rank == 0:
+                a, b = ev(), ev()
+                a.record()
+                comm.get(1, fulls[0], out=dst)
+                b.record()
+                b.synchronize()
+                ts.append(a.elapsed_time(b))
+        barrier()
+        peer_copy = job.max_over_ranks(S / (min(ts[1:]) * 1e-3) / 1e9 if rank == 0 else 0.0)
 
     # ---- end to end through the public API with host buffers --------------------------------------
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
@@ -266,14 +332,13 @@ def run_gpu_arm(args):
 
     e2e_step()
     barrier()
-    t0 = time.perf_counter()
     b0, b1 = ev(), ev()
     b0.record()
     for _ in range(e2e_steps):
         e2e_step()
     b1.record()
     barrier()
-    e2e_ms = max_over_ranks(b0.elapsed_time(b1)) / e2e_steps
+    e2e_ms = job.max_over_ranks(b0.elapsed_time(b1)) / e2e_steps
     comm.check()
     h2d = sum(h.numel() * 4 for h in host_shards) + nl * host_full.numel() * 4
     d2h = sum(h.numel() * 4 for h in host_out)
@@ -281,7 +346,8 @@ def run_gpu_arm(args):
         h2d, d2h = h2d * n_gpus, d2h * n_gpus   # whole job (every rank copies its own)
     e2e = {"value": bus_bytes(S, W) / (e2e_ms * 1e-3) / 1e9 * n_gpus, "unit": "GB/s", "h2d_bytes_per_step": int(h2d),
            "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms, "steps": e2e_steps,
-           "api": "hap_b200.LocalCollectives" if emulated else "hap_b200.collectives (drop-in)"}
+           "api": "hap_b200.LocalCollectives" if emulated else "hap_b200.collectives (drop-in)",
+           "note": "ordinary torch tensors: every call also pays the copy into the staging area"}
 
     # ---- roofline of the dominant kernel -----------------------------------------------------------
     peaks, peak_kind = measured_peaks()
@@ -307,37 +373,160 @@ def run_gpu_arm(args):
         achieved = alg / (dom[1] * 1e-3) / 1e9
         roofline = {"bound": "nvlink", "kernel": dom[0], "achieved": achieved, "peak": NVLINK_NOMINAL_GBS, "unit": "GB/s",
                     "frac": achieved / NVLINK_NOMINAL_GBS, "peak_kind": "nominal per direction per GPU",
-                    "frac_of_measured_peer_copy": achieved / NVLINK_MEASURED_GBS, "traffic": None,
-                    "algorithmic_bytes_per_launch": alg, "launch_ms": dom[1]}
+                    "peer_copy_GBps": peer_copy, "frac_of_peer_copy": achieved / peer_copy if peer_copy else None,
+                    "peer_copy_source": "measured in this run: rank 0 reads the tensor from rank 1 with the library's copy kernel, best of 3",
+                    "traffic": None, "algorithmic_bytes_per_launch": alg, "launch_ms": dom[1]}
 
     ops = {}
     for name, ms, bb in (("all_gather", ag_ms, S * (W - 1) / W), ("reduce_scatter", rs_ms, S * (W - 1) / W),
                          ("all_reduce", ar_ms, 2 * S * (W - 1) / W)):
         ops[name] = {"ms": ms, "busbw_GBps": bb / (ms * 1e-3) / 1e9}
 
-    result = None
-    if rank == 0:
-        result = {
-            "metric": "uneven_collective_bus_bandwidth", "value": busbw * n_gpus, "unit": "GB/s", "n_gpus": n_gpus,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"uneven collective micro-benchmark: all_gather + reduce_scatter + all_reduce of a "
-                                   f"({ROWS}, {cols}) fp32 tensor ({args.size_mib} MiB) split on dim 0",
-                       "world": W, "sharding_lengths": L, "ratios": "r8 (first W renormalised)",
-                       "ranks": "8 virtual ranks on one GPU, one cooperative launch per collective" if emulated
-                                else "one process per GPU, peer loads over NVLink",
-                       "inputs": "resident in the peer-visible heap", "l2": "inputs larger than L2 (126 MB)"},
-            "ops": ops, "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
-        }
-    # release device memory before the CPU baseline runs
+    result = {
+        "metric": "uneven_collective_bus_bandwidth", "value": busbw * n_gpus, "unit": "GB/s", "n_gpus": n_gpus,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": collective_config(W, args.size_mib, emulated),
+        "ops": ops, "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+    }
+    # release device memory before the next leg runs
     del shards, fulls, ag_out
+    hap_b200.collectives.set_default_comm(None)
     comm.destroy()
-    if rank == 0 and emulated and not args.no_cpu_baseline:
+    torch.cuda.empty_cache()
+    return result
+
+
+def run_parity(job):
+    """Outside any timed region: the public collectives on small seeded tensors against the CPU oracle.
+
+    N > 1: the drop-in ``hap_b200.collectives`` functions (forward and autograd backward), one process per
+    GPU; every rank's inputs travel over gloo so that each rank can evaluate the oracle for itself.
+    N = 1: the list API on 8 virtual ranks.  Inputs are ordinary torch tensors (copied into the staging
+    area by the library) in one pass and heap-resident tensors (read in place) in another.
+    Gathers / re-sharding must agree bit for bit; reductions within 1e-5 (fp32) / 1e-2 (bf16) relative."""
+    import torch
+    import hap_b200
+    from hap_b200 import collectives as col
+    from oracle import collectives_math as cm
+
+    dev, rank = job.dev, job.rank
+    emulated = job.dist is None
+    W = 8 if emulated else job.n_gpus
+    ratios = ratios_for(W)
+    comm = (hap_b200.local_comm(W, dev, heap_bytes=96 << 20, stage_bytes=32 << 20) if emulated
+            else hap_b200.init_process_comm(heap_bytes=96 << 20, stage_bytes=32 << 20))
+    if not emulated:
+        col.set_default_comm(comm)
+    mine = comm.ranks()
+    stats = {"cases": 0, "failed": [], "max_rel_err": 0.0, "exact_cases": 0}
+    tol = {torch.float32: 1e-5, torch.bfloat16: 1e-2}
+
+    def gen(shape, seed, dtype):
+        return torch.randn(*shape, generator=torch.Generator().manual_seed(seed)).to(dtype)
+
+    def place(t, where, i):
+        if where == "heap":
+            out = comm.symm_empty(tuple(t.shape), t.dtype, i)
+            out.copy_(t)
+            return out
+        return t.to(dev)
+
+    def all_ranks(per_local):
+        """[tensor of rank 0, ..., tensor of rank W-1] on the host, from this process's local ranks."""
+        if emulated:
+            return [t.detach().cpu() for t in per_local]
+        return job.everyone(per_local[0].detach().cpu())
+
+    def judge(name, got_local, want_all, exact, dtype):
+        stats["cases"] += 1
+        for i, r in enumerate(mine):
+            got, want = got_local[i].detach().cpu(), want_all[r]
+            if exact:
+                ok = got.shape == want.shape and torch.equal(got, want)
+            else:
+                err = float((got.double() - want.double()).abs().max()) if want.numel() else 0.0
+                scale = float(want.double().abs().max()) if want.numel() else 1.0
+                rel = err / max(scale, 1e-30)
+                stats["max_rel_err"] = max(stats["max_rel_err"], rel)
+                ok = got.shape == want.shape and rel <= tol[dtype]
+            if not ok:
+                stats["failed"].append(f"{name} rank {r}")
+        if exact:
+            stats["exact_cases"] += 1
+
+    lc = hap_b200.LocalCollectives(comm) if emulated else None
+    for where in ("staged", "heap"):
+        for dtype in (torch.float32, torch.bfloat16):
+            for total, other, dim in ((37, 129, 0), (256, 200, 1)):
+                comm.symm_reset()
+                Ls = hap_b200.sharding_round(total, ratios)
+                tag = f"{where}/{str(dtype)[6:]}/dim{dim}"
+                shard_shape = lambda r: [Ls[r] if d == dim else other for d in range(2)]
+                full_shape = [total if d == dim else other for d in range(2)]
+                # all_gather, both entry points, forward + backward (the uneven reduce_scatter of the gradients)
+                xs = [place(gen(shard_shape(r), 1000 + r, dtype), where, i).requires_grad_(not emulated) for i, r in enumerate(mine)]
+                ws = [gen(full_shape, 2000 + r, dtype).to(dev) for r in mine]
+                for fname in ("all_gather", "all_gather_by_group_call"):
+                    if emulated:
+                        outs = getattr(lc, fname)(xs, dim, Ls)
+                    else:
+                        xs[0].grad = None
+                        outs = [getattr(col, fname)(xs[0], dim, Ls, rank)]
+                        (outs[0] * ws[0]).sum().backward()
+                    x_all = all_ranks(xs)
+                    judge(f"{fname} {tag}", outs, cm.all_gather(x_all, dim, Ls), True, dtype)
+                    if not emulated:
+                        judge(f"{fname} backward {tag}", [xs[0].grad], cm.all_gather_backward(all_ranks(ws), dim, Ls), False, dtype)
+                # reduce_scatter, both entry points, forward + backward (the uneven all_gather of the gradients)
+                comm.symm_reset()
+                ys = [place(gen(full_shape, 3000 + r, dtype), where, i).requires_grad_(not emulated) for i, r in enumerate(mine)]
+                vs = [gen(shard_shape(r), 4000 + r, dtype).to(dev) for r in mine]
+                for fname in ("reduce_scatter", "reduce_scatter_by_group_call"):
+                    if emulated:
+                        outs = getattr(lc, fname)(ys, dim, Ls)
+                    else:
+                        ys[0].grad = None
+                        outs = [getattr(col, fname)(ys[0], dim, Ls, rank)]
+                        (outs[0] * vs[0]).sum().backward()
+                    judge(f"{fname} {tag}", outs, cm.reduce_scatter(all_ranks(ys), dim, Ls), False, dtype)
+                    if not emulated:
+                        judge(f"{fname} backward {tag}", [ys[0].grad], cm.reduce_scatter_backward(all_ranks(vs), dim, Ls), True, dtype)
+                # all_reduce
+                outs = lc.all_reduce(ys) if emulated else [col.all_reduce(ys[0].detach())]
+                judge(f"all_reduce {tag}", outs, cm.all_reduce(all_ranks(ys)), False, dtype)
+            # all_to_all, both orders of the two dims
+            sl, cl = hap_b200.sharding_round(24, ratios), hap_b200.sharding_round(40, ratios)
+            for sd, cd in ((0, 1), (1, 0)):
+                comm.symm_reset()
+                shp = lambda r: [sum(sl) if d == sd else (cl[r] if d == cd else 5) for d in range(3)]
+                zs = [place(gen(shp(r), 7000 + r, dtype), where, i) for i, r in enumerate(mine)]
+                outs = lc.all_to_all(zs, sd, cd, sl, cl) if emulated else [col.all_to_all(zs[0], sd, cd, sl, cl, rank)]
+                judge(f"all_to_all {where}/{str(dtype)[6:]}/{sd}{cd}", outs, cm.all_to_all(all_ranks(zs), sd, cd, sl, cl), True, dtype)
+    comm.check()
+    col.set_default_comm(None)
+    comm.destroy()
+    failed = [f for fl in job.everyone(stats["failed"]) for f in fl]
+    max_rel = job.max_over_ranks(stats["max_rel_err"])
+    return {"ok": not failed, "cases": stats["cases"], "exact_cases": stats["exact_cases"], "max_rel_err": max_rel,
+            "failed": failed[:8], "world": W,
+            "api": "hap_b200.LocalCollectives on 8 virtual ranks" if emulated else "hap_b200.collectives (drop-in, autograd) on one process per GPU",
+            "inputs": ["ordinary torch tensors (staged)", "heap-resident (read in place)"],
+            "oracle": "oracle/collectives_math.py", "tolerance": {"gathers": "bit-exact", "f32": 1e-5, "bf16": 1e-2}}
+
+
+def run_default(args):
+    job = Job(args.gpus)
+    result = run_collective_bench(args, job)
+    result["parity"] = run_parity(job)
+    if not args.no_spmd_step:
+        result["spmd_step"] = run_lm_step(args, job)
+    if job.rank == 0 and job.n_gpus == 1 and not args.no_cpu_baseline:
         result["cpu_baseline"] = run_cpu_arm(8, args.cpu_size_mib << 20, args.cpu_steps, 2)
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
-    if rank == 0:
+        if "spmd_step" in result:
+            result["spmd_step"]["cpu_baseline"] = run_lm_cpu(2, 2, 2)
+    job.finish()
+    if job.rank == 0:
         print(json.dumps(result), flush=True)
 
 
@@ -510,9 +699,9 @@ def run_sweep(args):
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
-    if rank == 0:
-        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-        with open(os.path.join(ROOT, "gpurun_out", f"sweep_{n_gpus}gpu.json"), "w") as f:
+    if rank == 0 and args.sweep_out:
+        os.makedirs(os.path.dirname(os.path.abspath(args.sweep_out)), exist_ok=True)
+        with open(args.sweep_out, "w") as f:
             json.dump(rows, f, indent=1)
 
 
@@ -614,23 +803,22 @@ def run_gemm(args):
 #  batch 32 per GPU of uniform token ids; data parallel with ratio-sharded FFN/attention weights)
 # ----------------------------------------------------------------------------------------------
 def _lm_cpu_worker(rank, world, store, batch_per_rank, out_path, layers):
-    import copy
     import torch
     import torch.distributed as dist
     import torch.nn.functional as F
     from types import SimpleNamespace
     sys.path.insert(0, ROOT)
     from hap_b200 import plan as P
-    from hap_b200.spmd import ProcessWorker
     from oracle import gloo_port
+    from oracle.cpu_executors import CpuProcessWorker
     torch.set_num_threads(max(1, (os.cpu_count() or 1) // world))
     dist.init_process_group("gloo", rank=rank, world_size=world, init_method=f"file://{store}")
     torch.manual_seed(39)
     model = P.TransformerLM(nlayers=layers).to(torch.bfloat16)
-    ns = SimpleNamespace(collectives=gloo_port, linear=F.linear, mha=F.multi_head_attention_forward)
+    ns = SimpleNamespace(collectives=gloo_port, linear=F.linear, mha=F.multi_head_attention_forward, dropout=F.dropout)
     B = batch_per_rank * world
-    graph = P.emit_lm(model, "dp_zero", ratios_for(world), rank, B, ns)
-    worker = ProcessWorker(torch.fx.GraphModule(model, graph))
+    graph = P.emit_lm(model, "dp_zero", ratios_for(world), rank, B, ns, dropout_p=0.1)
+    worker = CpuProcessWorker(torch.fx.GraphModule(model, graph))
     g = torch.Generator().manual_seed(2024)
     tok = torch.randint(0, 33278, (B, 256), generator=g)
     tgt = torch.randint(0, 33278, (B, 256), generator=g)
@@ -653,26 +841,23 @@ def run_lm_cpu(world, batch_per_rank, layers):
     cores = os.cpu_count() or 1
     # a step's cost is proportional to the layer count (the embedding/decoder part is counted once too often, in the CPU's favour)
     return {"value": r["batch"] / r["s"] * layers / 12.0, "unit": "samples/s", "cores": cores, "kind": "port",
-            "sample": f"{world} gloo ranks x {max(1, cores // world)} threads, same fx program (dp_zero) with the CPU port of the collectives "
-                      f"and torch CPU ops, {layers} of 12 layers, batch {batch_per_rank} per rank, 1 step after 1 warm-up; "
+            "sample": f"{world} gloo ranks x {max(1, cores // world)} threads, same fx program (dp_zero, dropout 0.1) with the CPU port of the "
+                      f"collectives and torch CPU ops, {layers} of 12 layers, batch {batch_per_rank} per rank, 1 step after 1 warm-up; "
                       f"value scaled by {layers}/12",
             "step_s": r["s"]}
 
 
-def run_lm(args):
-    import copy
+def lm_step(args, job, kind, plan, use_graph, dropout_p):
+    """Time the training step of one program (``kind``: lm / vit / moe) at job.n_gpus GPUs: device time per
+    step (CUDA events, max over ranks) and the end-to-end time with the inputs coming from pinned host memory
+    every step and the loss read back on the host."""
     import torch
     import hap_b200
     from hap_b200 import plan as P
     from hap_b200 import _native as N
-    from hap_b200.spmd import LockstepWorld, ProcessWorker
-    n_gpus = args.gpus
-    rank = int(os.environ.get("RANK", 0))
-    local_rank = int(os.environ.get("LOCAL_RANK", 0))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
+    from hap_b200.spmd import ProcessWorker
+    n_gpus, rank, dev, dist = job.n_gpus, job.rank, job.dev, job.dist
     W = n_gpus
-    kind = args.lm_model
     per_gpu = args.lm_batch if args.lm_batch > 0 else {"lm": 32, "vit": 64, "moe": 16}[kind]
     B = per_gpu * W
     ratios = ratios_for(W)
@@ -685,62 +870,54 @@ def run_lm(args):
     bmax = max(lb)
     if kind == "lm":
         model = P.TransformerLM(nlayers=L)
-        emit = lambda m, r: P.emit_lm(m, args.lm_plan, ratios, r, B)
+        emit = lambda m, r: P.emit_lm(m, plan, ratios, r, B, dropout_p=dropout_p)
         in_h = (torch.randint(0, 33278, (B, 256), generator=g), torch.randint(0, 33278, (B, 256), generator=g))
         M = bmax * 256
         fwd = L * (2.0 * M * 768 * (2304 + 768 + 3072 + 3072) + 2 * 2.0 * bmax * 12 * 256 * 256 * 64) + 2.0 * M * 768 * 33280
-        desc = f"Transformer LM training step ({L} layers, d_model 768, 12 heads, FFN 3072, pre-LN, vocab 33280, seq 256), plan {args.lm_plan}"
+        desc = f"Transformer LM training step ({L} layers, d_model 768, 12 heads, FFN 3072, pre-LN, vocab 33280, seq 256, dropout {dropout_p}), plan {plan}"
     elif kind == "vit":
         model = P.ViT(nlayers=L)
-        emit = lambda m, r: P.emit_vit(m, args.lm_plan, ratios, r, B)
+        emit = lambda m, r: P.emit_vit(m, plan, ratios, r, B, dropout_p=dropout_p)
         in_h = (torch.randn(B, 3, 224, 224, generator=g).to(torch.bfloat16), torch.randint(0, 1000, (B,), generator=g))
         M = bmax * 197
         fwd = L * (2.0 * M * 768 * (2304 + 768 + 3072 + 3072) + 2 * 2.0 * bmax * 12 * 197 * 197 * 64) + 2.0 * bmax * 196 * 768 * 768
-        desc = f"ViT-B/16 training step ({L} layers, d 768, 12 heads, MLP 3072, 224x224x3 images, 1000 classes), plan {args.lm_plan}"
+        desc = f"ViT-B/16 training step ({L} layers, d 768, 12 heads, MLP 3072, 224x224x3 images, 1000 classes, dropout {dropout_p}), plan {plan}"
     else:
         model = P.MoETransformerLM(nlayers=L)
-        emit = lambda m, r: P.emit_moe(m, ratios, r, B)
+        emit = lambda m, r: P.emit_moe(m, ratios, r, B, dropout_p=dropout_p)
         in_h = (torch.randint(0, 33278, (B, 512), generator=g), torch.randint(0, 33278, (B, 512), generator=g))
         M = bmax * 512
         e_max = max(hap_b200.sharding_round(32, ratios))
         fwd = L * (2.0 * M * 1024 * (3072 + 1024) + 2 * 2.0 * bmax * 16 * 512 * 512 * 64        # attention projections + core
-                   + 2 * 2.0 * bmax * 512 * 32 * 20 * 1024                                      # dense dispatch / combine einsums
                    + 2 * 2.0 * B * e_max * 20 * 1024 * 4096) + 2.0 * M * 1024 * 33280           # expert FFNs of the busiest rank
         desc = (f"MoE Transformer training step ({L} layers, d_model 1024, 16 heads, 32 experts FFN 4096, top-2 gating, capacity 20, "
-                f"vocab 33280, seq 512), expert parallel, experts per rank {hap_b200.sharding_round(32, ratios)}")
+                f"vocab 33280, seq 512, dropout {dropout_p}), expert parallel, experts per rank {hap_b200.sharding_round(32, ratios)}")
     model = model.to(torch.bfloat16).to(dev)
     n_params = sum(p.numel() for p in model.parameters())
+    hap_b200.dropout.manual_seed(39 + rank)
     if W == 1:
-        dist = None
         comm = hap_b200.single_comm(dev, stage_bytes=256 << 20, heap_bytes=(320 << 20) + 2 * n_params)
         hap_b200.collectives.set_default_comm(comm)
         graph = emit(model, 0)
         worker = ProcessWorker(torch.fx.GraphModule(model, graph), comm=comm)
-        step = worker.step
     else:
-        import torch.distributed as dist
-        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=W)
         comm = hap_b200.init_process_comm(stage_bytes=256 << 20, heap_bytes=(320 << 20) + 2 * n_params)
         hap_b200.collectives.set_default_comm(comm)
         graph = emit(model, rank)
         # the reference sums the partial losses with dist.reduce (worker.py:63-64); here through the package's all_reduce
         worker = ProcessWorker(torch.fx.GraphModule(model, graph),
                                reduce_loss=lambda t: comm.all_reduce([t.reshape(1).float()])[0], comm=comm)
-        step = worker.step
+    step = worker.step
     tok_h, tgt_h = in_h[0].pin_memory(), in_h[1].pin_memory()
     tok, tgt = tok_h.to(dev), tgt_h.to(dev)
-    if args.lm_graph:
+    if use_graph:
         step = worker.capture(tok, tgt)
-
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
+    barrier = job.barrier
 
     for _ in range(max(args.warmup, 3)):
         step(tok, tgt)
     barrier()
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(job.local_rank)
     sampler.start()
     l0 = N.lib.hapx_launch_count()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -751,53 +928,111 @@ def run_lm(args):
     b.record()
     barrier()
     launches = N.lib.hapx_launch_count() - l0
-    if args.lm_graph:       # a replay issues no host-side launches: count the kernels recorded into the graph
+    if use_graph:       # a replay issues no host-side launches: count the kernels recorded into the graph
         launches = worker.captured_launches * args.steps
     clocks = sampler.finish()
     ms = a.elapsed_time(b) / args.steps
-    # end to end: tokens come from pinned host memory every step, the loss goes back to the host
-    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+
+    # ---- end to end: every step's inputs come from pinned host memory, every step's loss goes back to the host.
+    # The upload of step i+1 runs on a second stream while step i computes; the loss of step i is read after step
+    # i+1 has been queued (the reference only logs it, worker.py:63-70), so the host never idles the GPU.
+    e2e_steps = max(3, args.steps)
+    up = torch.cuda.Stream()
+    main = torch.cuda.current_stream()
+    stage = [[torch.empty_like(tok), torch.empty_like(tgt)] for _ in range(2)]
+    ready = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    loss_h = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+    loss_ev = [torch.cuda.Event() for _ in range(2)]
+
+    def upload(i):
+        k = i & 1
+        with torch.cuda.stream(up):
+            up.wait_event(consumed[k])
+            stage[k][0].copy_(tok_h, non_blocking=True)
+            stage[k][1].copy_(tgt_h, non_blocking=True)
+            ready[k].record(up)
+
+    def e2e_loop(n):
+        losses = []
+        for k in range(2):
+            consumed[k].record(main)
+        upload(0)
+        for i in range(n):
+            k = i & 1
+            if i + 1 < n:
+                upload(i + 1)
+            main.wait_event(ready[k])
+            out = step(stage[k][0], stage[k][1])
+            consumed[k].record(main)
+            loss_h[k].copy_(out.detach().reshape(1).float(), non_blocking=True)
+            loss_ev[k].record(main)
+            if i >= 1:
+                loss_ev[k ^ 1].synchronize()
+                losses.append(float(loss_h[k ^ 1]))
+        loss_ev[(n - 1) & 1].synchronize()
+        losses.append(float(loss_h[(n - 1) & 1]))
+        return losses
+
+    e2e_loop(3)
     c, d = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    t0 = time.perf_counter()
     c.record()
-    for _ in range(e2e_steps):
-        loss = step(tok_h.to(dev, non_blocking=True), tgt_h.to(dev, non_blocking=True))
-        loss_host = float(loss)
+    losses = e2e_loop(e2e_steps)
     d.record()
+    torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
     barrier()
     e2e_ms = c.elapsed_time(d) / e2e_steps
-    if dist is not None:
-        t = torch.tensor([ms, e2e_ms], dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(t[0]), float(t[1])
+    ms, e2e_ms, wall_ms = job.max_over_ranks(ms, e2e_ms, wall_ms)
     comm.check()
     hap_b200.linear_ops.gemm_status()
     peaks, peak_kind = measured_peaks()
     # GEMM flops of one step on the busiest rank (largest batch share): 3 x forward, 2*M*N*K each
     achieved = 3 * fwd / (ms * 1e-3) / 1e12
+    peak = peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]
     result = {
         "metric": "spmd_step_samples_per_s", "value": B / (ms * 1e-3), "unit": "samples/s", "n_gpus": n_gpus, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{desc}, global batch {B} split {lb}", "parameters": n_params,
-                   "executor": "CUDA graph of the whole iteration" if args.lm_graph else "eager fx GraphModule",
-                   "l2": "activations and weights of a step exceed L2 by far", "loss": loss_host},
+        "config": {"workload": f"{desc}, global batch {B} split {lb}", "parameters": n_params, "plan": plan, "batch_split": lb,
+                   "executor": "CUDA graph of the whole iteration" if use_graph else "eager fx GraphModule",
+                   "l2": "activations and weights of a step exceed L2 by far", "loss": losses[-1]},
         "roofline": {"bound": "tensor", "kernel": "gemm2_bf16_kernel (all linear / attention contractions of the busiest rank)",
-                     "achieved": achieved, "peak": peaks["bf16_tflops_sustained"] if "bf16_tflops_sustained" in peaks else peaks["bf16_tflops"],
-                     "unit": "TFLOP/s", "frac": achieved / (peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]),
+                     "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                      "peak_kind": peak_kind + " (sustained: the kernels run inside a long step)", "traffic": None,
                      "note": "whole-step time, so this fraction also pays for every non-GEMM op of the step"},
-        "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": int(tok_h.numel() * tok_h.element_size() + tgt_h.numel() * tgt_h.element_size()),
-                "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms, "steps": e2e_steps},
+        "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s",
+                "h2d_bytes_per_step": int(tok_h.numel() * tok_h.element_size() + tgt_h.numel() * tgt_h.element_size()) * n_gpus,
+                "d2h_bytes_per_step": 4 * n_gpus, "ms_per_step": e2e_ms, "host_wall_ms_per_step": wall_ms, "steps": e2e_steps,
+                "pipeline": "inputs uploaded on a second stream one step ahead, loss read one step late"},
         "gpu_launches": int(launches), "clocks": clocks,
     }
+    del worker, step, model
+    hap_b200.collectives.set_default_comm(None)
     comm.destroy()
-    if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline and kind == "lm":
+    torch.cuda.empty_cache()
+    return result
+
+
+def run_lm_step(args, job):
+    """The `spmd_step` object of the default line: the Transformer-LM configuration, plan dp_zero, graph replay,
+    attention and residual dropout 0.1 as in the reference's throughput runs (config.py:33)."""
+    r = lm_step(args, job, "lm", "dp_zero", True, args.lm_dropout)
+    return {"samples_per_s": r["value"], "ms_per_step": r["ms_per_step"], "plan": r["config"]["plan"],
+            "batch_split": r["config"]["batch_split"], "workload": r["config"]["workload"], "executor": r["config"]["executor"],
+            "roofline": r["roofline"], "e2e": r["e2e"], "loss": r["config"]["loss"], "gpu_launches": r["gpu_launches"],
+            "clocks": r["clocks"], "dtype": "bf16"}
+
+
+def run_lm(args):
+    job = Job(args.gpus)
+    result = lm_step(args, job, args.lm_model, args.lm_plan, args.lm_graph, args.lm_dropout)
+    if job.rank == 0 and job.n_gpus == 1 and not args.no_cpu_baseline and args.lm_model == "lm":
         result["cpu_baseline"] = run_lm_cpu(2, 2, 2)
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
-    if rank == 0:
+    job.finish()
+    if job.rank == 0:
         print(json.dumps(result), flush=True)
 
 
@@ -963,17 +1198,15 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
         return
-    W = 8 if args.gpus == 1 else args.gpus
+    emulated = args.gpus == 1
+    W = 8 if emulated else args.gpus
     size = args.cpu_size_mib << 20
     base = run_cpu_arm(W, size, max(1, args.steps), max(1, args.warmup))
-    cols = size // (ROWS * 4)
     line = {
         "impl": "reference", "metric": "uneven_collective_bus_bandwidth", "value": base["value"], "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"uneven collective micro-benchmark: all_gather + reduce_scatter + all_reduce of a "
-                               f"({ROWS}, {cols}) fp32 tensor split on dim 0; CPU sample of {args.cpu_size_mib} MiB per step",
-                   "world": W, "ranks": "gloo ranks on the host cores"},
+        "config": collective_config(W, args.size_mib, emulated),
         "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -991,7 +1224,10 @@ def main():
     ap.add_argument("--cpu-size-mib", type=int, default=64, help="tensor size of the bounded CPU sample")
     ap.add_argument("--cpu-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-spmd-step", action="store_true", help="default run: skip the Transformer-LM training step")
+    ap.add_argument("--lm-dropout", type=float, default=0.1, help="dropout of the lm workload (the reference trains with 0.1)")
     ap.add_argument("--sweep", action="store_true", help="size sweep instead of the single JSON line")
+    ap.add_argument("--sweep-out", default="", help="write the sweep's rows to this JSON file")
     ap.add_argument("--sweep-max-mib", type=int, default=1024)
     ap.add_argument("--workload", default="collectives", choices=["collectives", "gemm", "lm", "ops"])
     ap.add_argument("--lm-model", default="lm", choices=["lm", "vit", "moe"], help="which program the lm workload steps")
@@ -1014,7 +1250,7 @@ def main():
     elif args.sweep:
         run_sweep(args)
     else:
-        run_gpu_arm(args)
+        run_default(args)
 
 
 if __name__ == "__main__":

@@ -11,7 +11,7 @@ from . import collectives
 from .local import LocalCollectives
 from . import linear as linear_ops
 from .linear import linear
-from . import plan, spmd, attention, fxpass, profiler
+from . import plan, spmd, attention, fxpass, profiler, dropout
 from .einsum import einsum
 from .loss import nll_log_softmax_sum
 from .norm import layer_norm

@@ -19,7 +19,7 @@ F32, BF16, F16, F64, B8, B16, B32, B64 = range(8)
 MODE_PADDING, MODE_GROUP_CALL = 0, 1
 OPTIM_STATE_FLOATS = 2056
 
-_i64, _int, _dbl, _vp, _sz = C.c_int64, C.c_int, C.c_double, C.c_void_p, C.c_size_t
+_i64, _int, _dbl, _vp, _sz, _u64 = C.c_int64, C.c_int, C.c_double, C.c_void_p, C.c_size_t, C.c_uint64
 _pp = C.POINTER(C.c_void_p)
 _pi64 = C.POINTER(C.c_int64)
 
@@ -34,13 +34,17 @@ SIGNATURES = {
     "hapx_comm_ipc_handle": (_int, [_vp, _vp]),
     "hapx_comm_open_peers": (_int, [_vp, _vp]),
     "hapx_comm_attach_peer": (_int, [_vp, _int, _vp]),
+    "hapx_comm_close_peers": (_int, [_vp]),
     "hapx_comm_destroy": (_int, [_vp]),
+    "hapx_comm_poll": (_int, [_vp]),
+    "hapx_comm_calls_issued": (_int, [_vp, C.POINTER(_i64)]),
     "hapx_comm_world": (_int, [_vp, C.POINTER(_int), C.POINTER(_int), C.POINTER(_int)]),
     "hapx_comm_heap": (_int, [_vp, _int, _pp, C.POINTER(_sz)]),
     "hapx_comm_set_timeout_ms": (_int, [_vp, _int]),
     "hapx_comm_set_max_ctas": (_int, [_vp, _int]),
     "hapx_comm_set_stream_ordering": (_int, [_vp, _int]),
     "hapx_comm_check": (_int, [_vp]),
+    "hapx_comm_get": (_int, [_vp, _int, _sz, _vp, _sz, _vp]),
     "hapx_all_gather": (_int, [_vp, _pp, _pp, _int, _i64, _i64, _pi64, _int, _vp]),
     "hapx_reduce_scatter": (_int, [_vp, _pp, _pp, _int, _int, _dbl, _i64, _i64, _pi64, _int, _vp]),
     "hapx_all_reduce": (_int, [_vp, _pp, _pp, _int, _int, _dbl, _i64, _vp]),
@@ -61,7 +65,12 @@ SIGNATURES = {
     "hapx_layer_norm_forward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _dbl, _vp]),
     "hapx_layer_norm_backward_blocks": (_int, [_i64, _i64]),
     "hapx_layer_norm_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _vp]),
+    "hapx_rng_seed": (_int, [_u64, _vp]),
+    "hapx_rng_advance": (_int, [_vp]),
+    "hapx_dropout": (_int, [_vp, _vp, _int, _i64, _dbl, _u64, _vp]),
+    "hapx_dropout_mask": (_int, [_vp, _i64, _dbl, _u64, _vp]),
     "hapx_local_all_reduce_noalloc": (_int, [_int, _pp, _pp, _int, _int, _dbl, _i64, _vp]),
+    "hapx_local_all_reduce_noalloc_status": (_int, []),
     "hapx_debug_host_walk": (_int, [_int, _int, _int, _int, _i64, _i64, _i64, _int, _pi64, _pi64, _pp,
                                      C.POINTER(_sz), _vp, _sz, _vp]),
 }

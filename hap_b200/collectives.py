@@ -45,6 +45,10 @@ def set_default_comm(c: Optional[_comm.Comm]) -> None:
     _default = c
 
 
+def has_default_comm() -> bool:
+    return _default is not None
+
+
 def get_default_comm() -> _comm.Comm:
     """The process communicator; created from the default ``torch.distributed`` group on first use."""
     global _default

@@ -89,15 +89,37 @@ class Comm:
         self.debug_sync = os.environ.get("HAPX_DEBUG_SYNC", "0") == "1"
 
     # ---- lifecycle -------------------------------------------------------------------
-    def destroy(self) -> None:
-        if self._h:
-            self._heap_views = [None] * self.n_local
-            N.check(N.lib.hapx_comm_destroy(self._h))
-            self._h = None
+    def destroy(self, group=None) -> None:
+        """Release the communicator.  Ranks that are separate processes tear down in two phases -
+        close the mappings of the peers' heaps, meet at a barrier, free the own heap - because a
+        heap must not be freed while a peer still has it mapped.  The barrier runs on ``group`` (or
+        the default ``torch.distributed`` group) when this is a multi-process communicator and
+        ``torch.distributed`` is still initialised; call ``destroy`` on all ranks."""
+        if not self._h:
+            return
+        self._heap_views = [None] * self.n_local
+        if self.n_local == 1 and self.world > 1:
+            import torch.distributed as dist
+            N.check(N.lib.hapx_comm_close_peers(self._h))
+            if dist.is_available() and dist.is_initialized():
+                with torch.cuda.device(self.device):
+                    dist.barrier(group=group)
+        N.check(N.lib.hapx_comm_destroy(self._h))
+        self._h = None
 
     def check(self) -> None:
         """Synchronise and raise if a kernel recorded an error (e.g. a peer that never arrived)."""
         N.check(N.lib.hapx_comm_check(self._h))
+
+    def poll(self) -> None:
+        """Raise if a kernel that has already run gave up waiting for a peer.  No synchronisation:
+        one read of pinned host memory.  Every collective call makes the same test on entry."""
+        N.check(N.lib.hapx_comm_poll(self._h))
+
+    def calls_issued(self) -> int:
+        n = C.c_int64()
+        N.check(N.lib.hapx_comm_calls_issued(self._h, C.byref(n)))
+        return n.value
 
     def set_timeout_ms(self, ms: int) -> None:
         N.check(N.lib.hapx_comm_set_timeout_ms(self._h, int(ms)))
@@ -133,6 +155,22 @@ class Comm:
 
     def symm_reset(self) -> None:
         self._heap_cursor = [0] * self.n_local
+
+    def get(self, peer: int, peer_tensor_like: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One-sided read of the peer's copy of a heap tensor: ``peer_tensor_like`` is THIS rank's
+        tensor from :meth:`symm_empty`; ranks that allocate from their heaps in the same order hold
+        their counterpart at the same offset, and that counterpart on ``peer`` is what is read.
+        No handshake: order it against the peer's writes yourself (e.g. a barrier)."""
+        heap = self._heap(0)
+        off = peer_tensor_like.data_ptr() - heap.data_ptr()
+        nbytes = peer_tensor_like.numel() * peer_tensor_like.element_size()
+        if off < 0 or off + nbytes > heap.numel():
+            raise ValueError("get: the tensor does not live in this communicator's heap")
+        out = torch.empty_like(peer_tensor_like, memory_format=torch.contiguous_format) if out is None else out
+        if not out.is_cuda or not out.is_contiguous():
+            raise RuntimeError("get: the destination must be a contiguous CUDA tensor")
+        N.check(N.lib.hapx_comm_get(self._h, int(peer), off, out.data_ptr(), nbytes, _stream(self.device)))
+        return out
 
     # ---- helpers ---------------------------------------------------------------------------
     def _lists(self, tensors: Sequence[torch.Tensor], what: str) -> List[torch.Tensor]:
@@ -359,7 +397,10 @@ def local_all_reduce_noalloc(inputs: Sequence[torch.Tensor], outputs: Sequence[t
     ``outputs[r]`` may be ``inputs[r]``); all scratch is a fixed 16 MiB array inside the library,
     which limits the call to 8 ranks and roughly 460 000 float32 elements at 8 ranks (a larger call
     raises ``HapxError`` with code ``ERR_STAGING``).  The first call on a device should happen
-    outside stream capture.  Calls share the scratch: do not let two of them overlap on the GPU.
+    outside stream capture and while device memory is still available (the driver reserves the
+    array when it first loads the library's code on that device).  Calls share the scratch: do not
+    let two of them overlap on the GPU.  :func:`local_all_reduce_noalloc_status` reports a bounded
+    wait that ran out inside the kernels.
     """
     if len(inputs) != len(outputs) or not inputs:
         raise ValueError("local_all_reduce_noalloc: need one output per input")
@@ -376,3 +417,9 @@ def local_all_reduce_noalloc(inputs: Sequence[torch.Tensor], outputs: Sequence[t
                                                     N.ptr_array([t.data_ptr() for t in inputs]), dtype_code(ref.dtype),
                                                     dtype_code(outputs[0].dtype), float(scale), ref.numel(),
                                                     _stream(ref.device)))
+
+
+def local_all_reduce_noalloc_status() -> None:
+    """Synchronise the current device and raise if a kernel of an earlier
+    :func:`local_all_reduce_noalloc` gave up on a bounded wait (its outputs are then unwritten)."""
+    N.check(N.lib.hapx_local_all_reduce_noalloc_status())

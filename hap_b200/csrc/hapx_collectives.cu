@@ -58,6 +58,7 @@ struct PullParams {
   int order_log2;   // copy kernels visit tiles in 2^order_log2 interleaved streams (0 = in order)
   unsigned seq;
   unsigned long long timeout_ns;
+  unsigned* host_status;  // mapped host word that mirrors a timeout (may be null)
   float scale;
   long long A, B, C;
   long long L1[HAPX_MAX_WORLD], P1[HAPX_MAX_WORLD], tot1;  // sharded / split dim
@@ -153,9 +154,13 @@ __device__ inline bool wait_flag(const unsigned long long* p, unsigned shift, un
   return false;
 }
 
-__device__ inline void report_timeout(Ctrl* my, unsigned seq, int peer) {
+__device__ inline void report_timeout(Ctrl* my, unsigned seq, int peer, unsigned* host_status) {
   if (atomicCAS(&my->status, 0u, (unsigned)(-HAPX_ERR_PEER_TIMEOUT)) == 0u)
     my->status_info = ((unsigned long long)seq << 32) | (unsigned)peer;
+  if (host_status) {   // lets the host notice at its next call, without a synchronisation
+    *reinterpret_cast<volatile unsigned*>(host_status) = (unsigned)(-HAPX_ERR_PEER_TIMEOUT);
+    __threadfence_system();
+  }
 }
 
 struct Shared {
@@ -185,7 +190,7 @@ __device__ inline void begin_collective(const PullParams& P, const LocalRank& lr
         off = v & ((1ull << 40) - 1);
       } else {
         sh.abort = 1;
-        report_timeout(my, P.seq, p);
+        report_timeout(my, P.seq, p, P.host_status);
       }
     }
     sh.base[p] = (p == rank && P.self_only) ? lr.src : (P.heap[p] + off);
@@ -220,7 +225,7 @@ __device__ inline void end_collective(const PullParams& P, const LocalRank& lr, 
     const int p = tid;
     st_release_sys(&reinterpret_cast<Ctrl*>(P.heap[p])->done[rank], (unsigned long long)P.seq);
     unsigned long long v;
-    if (!sh.abort && !wait_flag(&my->done[p], 0, P.seq, P.timeout_ns, &v)) report_timeout(my, P.seq, p);
+    if (!sh.abort && !wait_flag(&my->done[p], 0, P.seq, P.timeout_ns, &v)) report_timeout(my, P.seq, p, P.host_status);
   }
   __syncthreads();
   if (tid == 0) my->cta_done = 0;
@@ -520,6 +525,7 @@ static PullKernel reduce_kernel_for(int in_dtype, int out_dtype) {
 }
 
 static unsigned next_seq(hapx_comm* c) {
+  ++c->calls;
   c->seq = (c->seq + 1) & 0xffffffu;
   if (c->seq == 0) c->seq = 1;
   return c->seq;
@@ -527,6 +533,11 @@ static unsigned next_seq(hapx_comm* c) {
 
 static int check_ready(hapx_comm* c) {
   if (!c) return fail(HAPX_ERR_ARGUMENT, "null communicator");
+  // a kernel of an earlier call whose wait on a peer ran out has left its outputs unwritten: refuse
+  // further work until hapx_comm_check() has reported and cleared it (no synchronisation needed here)
+  if (c->host_status && *static_cast<volatile unsigned*>(c->host_status) != 0u)
+    return fail(HAPX_ERR_PEER_TIMEOUT, "an earlier collective of this communicator gave up waiting for a peer; its outputs are not valid "
+                                       "(hapx_comm_check reports the details and clears the error)");
   for (int p = 0; p < c->world; ++p)
     if (!c->mapped[p]) return fail(HAPX_ERR_STATE, "peer heap of rank " + std::to_string(p) + " is not mapped (call hapx_comm_open_peers)");
   return HAPX_OK;
@@ -639,6 +650,7 @@ static void init_params(hapx_comm* c, PullParams& P, int op, int es_in, int es_o
   P.op = op; P.world = c->world; P.n_local = c->n_local; P.es_in = es_in; P.es_out = es_out;
   P.scale = 1.f;
   P.timeout_ns = (unsigned long long)c->timeout_ms * 1000000ull;
+  P.host_status = c->host_status_dev;
   P.order_log2 = c->order_log2;
   for (int p = 0; p < c->world; ++p) P.heap[p] = c->heap[p];
 }
@@ -868,6 +880,31 @@ int hapx_dynamic_slice(void* dst, const void* src, int dtype, int64_t outer, int
   return slice_impl(OP_SLICE, dst, src, dtype, outer, inner, lengths, world, rank, static_cast<cudaStream_t>(stream));
 }
 
+int hapx_comm_get(hapx_comm* c, int peer, size_t peer_offset, void* dst, size_t bytes, hapx_stream stream_) {
+  if (int e = check_ready(c)) return e;
+  if (c->local_mode || c->n_local != 1) return fail(HAPX_ERR_STATE, "comm_get: needs a one-process-per-GPU communicator");
+  if (peer < 0 || peer >= c->world) return fail(HAPX_ERR_ARGUMENT, "comm_get: peer out of range");
+  const size_t user = kCtrlBytes + c->stage_bytes;
+  if (peer_offset > c->heap_bytes - user || bytes > c->heap_bytes - user - peer_offset)
+    return fail(HAPX_ERR_EXTENT, "comm_get: range outside the peer's user area");
+  if (bytes == 0) return HAPX_OK;
+  if (!dst) return fail(HAPX_ERR_ARGUMENT, "comm_get: null destination");
+  HAPX_CUDA(cudaSetDevice(c->device));
+  // a one-rank "slice" of bytes: the copy kernel without the flag protocol, reading the peer's mapping
+  const int64_t one = (int64_t)bytes;
+  PullParams P = PullParams();
+  P.op = OP_SLICE; P.world = 1; P.n_local = 1; P.es_in = 1; P.es_out = 1; P.self_only = 1; P.scale = 1.f;
+  P.order_log2 = 0;
+  P.A = 1; P.C = 1;
+  fill_prefix(&one, 1, P.L1, P.P1, &P.tot1);
+  P.lr[0].rank = 0;
+  P.lr[0].src = c->heap[peer] + user + peer_offset;
+  P.lr[0].dst = static_cast<char*>(dst);
+  hapx_comm tmp;
+  tmp.world = 1; tmp.n_local = 1; tmp.sm_count = c->sm_count; tmp.local_mode = false; tmp.max_ctas = c->max_ctas;
+  return launch_pull(&tmp, pull_copy_kernel, P, kCopyTile, static_cast<cudaStream_t>(stream_));
+}
+
 int hapx_dynamic_slice_backward(void* dst, const void* src, int dtype, int64_t outer, int64_t inner, const int64_t* lengths,
                                 int world, int rank, hapx_stream stream) {
   return slice_impl(OP_UNSLICE, dst, src, dtype, outer, inner, lengths, world, rank, static_cast<cudaStream_t>(stream));
@@ -949,8 +986,9 @@ int hapx_local_all_reduce_noalloc(int world, void* const* dst, const void* const
   view.heap_bytes = kNoAllocRankBytes; view.stage_bytes = kNoAllocRankBytes - kCtrlBytes;
   view.sm_count = nd.sm_count;
   for (int r = 0; r < world; ++r) { view.heap[r] = nd.base + (size_t)r * kNoAllocRankBytes; view.mapped[r] = true; }
-  // the control blocks keep the previous call's flags and counters: start from zero
-  for (int r = 0; r < world; ++r) HAPX_CUDA(cudaMemsetAsync(view.heap[r], 0, kCtrlBytes, stream));
+  // the control blocks keep the previous call's flags and counters: start from zero (the status words
+  // behind them stay, so that a wait that ran out is still there for the status query)
+  for (int r = 0; r < world; ++r) HAPX_CUDA(cudaMemsetAsync(view.heap[r], 0, offsetof(Ctrl, status), stream));
 
   int64_t lengths[HAPX_MAX_WORLD];
   long long L[HAPX_MAX_WORLD], Pfx[HAPX_MAX_WORLD], total;
@@ -991,6 +1029,31 @@ int hapx_local_all_reduce_noalloc(int world, void* const* dst, const void* const
   if (nd.seq == 0) nd.seq = 1;
   G.seq = nd.seq;
   return launch_pull(&view, pull_copy_kernel, G, kCopyTile, stream);
+}
+
+int hapx_local_all_reduce_noalloc_status(void) {
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  int device = 0;
+  HAPX_CUDA(cudaGetDevice(&device));
+  if (device < 0 || device >= 64) return fail(HAPX_ERR_ARGUMENT, "all_reduce_noalloc_status: device index out of range");
+  NoAllocDevice& nd = g_noalloc_dev[device];
+  if (!nd.ready) return HAPX_OK;   // nothing has run on this device yet
+  HAPX_CUDA(cudaDeviceSynchronize());
+  int rc = HAPX_OK;
+  std::string msg;
+  for (int r = 0; r < kNoAllocMaxWorld; ++r) {
+    Ctrl host;
+    char* block = nd.base + (size_t)r * kNoAllocRankBytes;
+    HAPX_CUDA(cudaMemcpy(&host, block, sizeof(Ctrl), cudaMemcpyDeviceToHost));
+    if (host.status != 0) {
+      rc = -static_cast<int>(host.status);
+      msg += "virtual rank " + std::to_string(r) + ": device wait ran out (waiting for rank " +
+             std::to_string(host.status_info & 0xffffffffu) + "); ";
+      HAPX_CUDA(cudaMemset(block + offsetof(Ctrl, cta_done), 0, sizeof(Ctrl) - offsetof(Ctrl, cta_done)));
+    }
+  }
+  if (rc != HAPX_OK) return fail(rc, msg);
+  return HAPX_OK;
 }
 
 /* Diagnostic, host memory only: walks the warp tiling of one rank's pull (the same

@@ -37,10 +37,28 @@ static int common_init(hapx_comm* c) {
     int v = std::atoi(e);
     if (v >= 0 && v <= 10) c->order_log2 = v;
   }
+  if (const char* e = std::getenv("HAPX_TIMEOUT_MS")) {  // default bound of the device-side waits on peers
+    long v = std::atol(e);
+    if (v >= 1 && v <= 0x7fffffffL) c->timeout_ms = (int)v;
+  }
   HAPX_CUDA(cudaSetDevice(c->device));
   HAPX_CUDA(cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, c->device));
   HAPX_CUDA(cudaEventCreateWithFlags(&c->last_done, cudaEventDisableTiming));
+  void* hs = nullptr;
+  HAPX_CUDA(cudaHostAlloc(&hs, 64, cudaHostAllocMapped));
+  std::memset(hs, 0, 64);
+  c->host_status = static_cast<unsigned*>(hs);
+  void* ds = nullptr;
+  HAPX_CUDA(cudaHostGetDevicePointer(&ds, hs, 0));
+  c->host_status_dev = static_cast<unsigned*>(ds);
   return HAPX_OK;
+}
+
+static void common_release(hapx_comm* c) {
+  if (c->last_done) cudaEventDestroy(c->last_done);
+  if (c->host_status) cudaFreeHost(c->host_status);
+  c->last_done = nullptr;
+  c->host_status = c->host_status_dev = nullptr;
 }
 
 }  // namespace hapx
@@ -60,10 +78,10 @@ int hapx_comm_create(hapx_comm** out, int world, int rank, int device, size_t he
   hapx_comm* c = new hapx_comm();
   c->world = world; c->n_local = 1; c->first_rank = rank; c->device = device;
   c->heap_bytes = heap_bytes; c->stage_bytes = stage_bytes;
-  if (int e = common_init(c)) { delete c; return e; }
+  if (int e = common_init(c)) { common_release(c); delete c; return e; }
   void* p = nullptr;
   cudaError_t err = cudaMalloc(&p, heap_bytes);
-  if (err != cudaSuccess) { delete c; return fail(HAPX_ERR_CUDA, std::string("cudaMalloc(heap): ") + cudaGetErrorString(err)); }
+  if (err != cudaSuccess) { common_release(c); delete c; return fail(HAPX_ERR_CUDA, std::string("cudaMalloc(heap): ") + cudaGetErrorString(err)); }
   cudaMemset(p, 0, kCtrlBytes);
   cudaDeviceSynchronize();
   c->heap[rank] = static_cast<char*>(p);
@@ -78,15 +96,16 @@ int hapx_comm_create_local(hapx_comm** out, int world, int device, size_t heap_b
   hapx_comm* c = new hapx_comm();
   c->world = world; c->n_local = world; c->first_rank = 0; c->device = device; c->local_mode = true;
   c->heap_bytes = heap_bytes; c->stage_bytes = stage_bytes;
-  if (int e = common_init(c)) { delete c; return e; }
+  if (int e = common_init(c)) { common_release(c); delete c; return e; }
   int coop = 0;
   cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device);
-  if (!coop) { delete c; return fail(HAPX_ERR_CUDA, "device does not support cooperative launch"); }
+  if (!coop) { common_release(c); delete c; return fail(HAPX_ERR_CUDA, "device does not support cooperative launch"); }
   for (int r = 0; r < world; ++r) {
     void* p = nullptr;
     cudaError_t err = cudaMalloc(&p, heap_bytes);
     if (err != cudaSuccess) {
       for (int q = 0; q < r; ++q) cudaFree(c->heap[q]);
+      common_release(c);
       delete c;
       return fail(HAPX_ERR_CUDA, std::string("cudaMalloc(heap): ") + cudaGetErrorString(err));
     }
@@ -139,19 +158,44 @@ int hapx_comm_attach_peer(hapx_comm* c, int peer, void* mapped_base) {
   return HAPX_OK;
 }
 
-int hapx_comm_destroy(hapx_comm* c) {
+int hapx_comm_close_peers(hapx_comm* c) {
   if (!c) return HAPX_OK;
   cudaSetDevice(c->device);
   cudaDeviceSynchronize();
   for (int p = 0; p < c->world; ++p)
-    if (c->ipc_opened[p]) cudaIpcCloseMemHandle(c->heap[p]);
+    if (c->ipc_opened[p]) {
+      cudaIpcCloseMemHandle(c->heap[p]);
+      c->ipc_opened[p] = false;
+      c->mapped[p] = false;
+      c->heap[p] = nullptr;
+    }
+  return HAPX_OK;
+}
+
+int hapx_comm_destroy(hapx_comm* c) {
+  if (!c) return HAPX_OK;
+  hapx_comm_close_peers(c);
   if (c->local_mode) {
     for (int p = 0; p < c->world; ++p) cudaFree(c->heap[p]);
   } else {
     cudaFree(c->heap[c->first_rank]);
   }
-  if (c->last_done) cudaEventDestroy(c->last_done);
+  common_release(c);
   delete c;
+  return HAPX_OK;
+}
+
+int hapx_comm_calls_issued(hapx_comm* c, int64_t* calls) {
+  if (!c || !calls) return fail(HAPX_ERR_ARGUMENT, "null argument");
+  *calls = c->calls;
+  return HAPX_OK;
+}
+
+int hapx_comm_poll(hapx_comm* c) {
+  if (!c) return fail(HAPX_ERR_ARGUMENT, "null communicator");
+  if (c->host_status && *static_cast<volatile unsigned*>(c->host_status) != 0u)
+    return fail(HAPX_ERR_PEER_TIMEOUT, "an earlier collective of this communicator gave up waiting for a peer; its outputs are not valid "
+                                       "(hapx_comm_check reports the details and clears the error)");
   return HAPX_OK;
 }
 
@@ -211,6 +255,7 @@ int hapx_comm_check(hapx_comm* c) {
                            sizeof(Ctrl) - offsetof(Ctrl, cta_done)));
     }
   }
+  if (c->host_status) *static_cast<volatile unsigned*>(c->host_status) = 0u;
   if (rc != HAPX_OK) return fail(rc, msg);
   return HAPX_OK;
 }

@@ -24,6 +24,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "hapx_internal.h"
 
@@ -973,6 +974,7 @@ static int make_map(CUtensorMap* map, const Operand& op, long long mn_extent, lo
 
 struct DeviceState {
   bool ready = false;
+  int index = 0;
   int sm_count = 0;
   unsigned* error = nullptr;  // device words: [0] the kernels' error reports, [1] scratch flag for callers
 };
@@ -992,6 +994,7 @@ static int device_state(DeviceState** out) {
     HAPX_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device));
     HAPX_CUDA(cudaMalloc(&d.error, 64));
     HAPX_CUDA(cudaMemset(d.error, 0, 64));
+    d.index = device;
     d.ready = true;
   }
   *out = &d;
@@ -1008,8 +1011,9 @@ static bool fast_drain_ok(const Params& p) {
 }
 
 template <int BN, bool A_MN, bool B_MN>
-static int launch(const Operand& A, const Operand& B, const Operand& Dop, Params& p, cudaStream_t stream, int sm_count) {
+static int launch(const Operand& A, const Operand& B, const Operand& Dop, Params& p, cudaStream_t stream, const DeviceState& dev) {
   using C = Cfg<BN, A_MN, B_MN>;
+  const int sm_count = dev.sm_count;
   const int batch_out = p.batch / p.batch_in;
   CUtensorMap tmA, tmB, tmD;
   if (int e = make_out_map(&tmD, &p.tma_store, p.D, p.N, p.M, p.ldd, p.out_f32, p.batch_in, Dop.s_in, batch_out, Dop.s_out)) return e;
@@ -1021,10 +1025,13 @@ static int launch(const Operand& A, const Operand& B, const Operand& Dop, Params
   p.n_tiles = (p.N + BN - 1) / BN;
   p.k_blocks = (p.Kc + BK - 1) / BK;
   auto kernel = gemm_bf16_kernel<BN, A_MN, B_MN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    HAPX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES));
-    attr_set = true;
+  {  // function attributes are per device
+    static bool attr_set[64] = {};
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    if (!attr_set[dev.index]) {
+      HAPX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES));
+      attr_set[dev.index] = true;
+    }
   }
   const long long units = (long long)p.m_tiles * p.n_tiles * p.batch;
   if (units > 0x7fffffff) return fail(HAPX_ERR_EXTENT, "gemm: too many tiles");
@@ -1061,27 +1068,46 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
   }
 }
 
-struct Workspace { float* ptr = nullptr; size_t bytes = 0; };
+// Scratch for split-K partial tiles and bias-gradient partial sums: one block per device.  The
+// block only ever grows, and a block it outgrew is kept until the process exits, because a CUDA
+// graph recorded earlier may still write to it on every replay.  Growing allocates and therefore
+// cannot happen while the stream is being captured: run the step eagerly first (the step driver's
+// capture() does).  The block is shared by all streams of the device: GEMMs that use it (split-K,
+// bias gradients) must be ordered against each other, as they are on one stream.
+struct Workspace { float* ptr = nullptr; size_t bytes = 0; std::vector<void*> outgrown; };
 static Workspace g_ws[64];
 
-// Grows the per-device split-K workspace (the only allocation on this path; it happens when a
-// larger problem is seen for the first time, never in steady state).
-static int workspace(int device, size_t bytes, float** out) {
+static int workspace(int device, cudaStream_t stream, size_t bytes, float** out) {
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
   Workspace& w = g_ws[device];
   if (w.bytes < bytes) {
-    if (w.ptr) { HAPX_CUDA(cudaDeviceSynchronize()); HAPX_CUDA(cudaFree(w.ptr)); w.ptr = nullptr; w.bytes = 0; }
-    HAPX_CUDA(cudaMalloc(&w.ptr, bytes));
-    w.bytes = bytes;
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    HAPX_CUDA(cudaStreamIsCapturing(stream, &capturing));
+    if (capturing != cudaStreamCaptureStatusNone)
+      return fail(HAPX_ERR_STATE, "gemm: the scratch block of this stream must grow to " + std::to_string(bytes) +
+                                      " bytes, which cannot happen during stream capture; run the same step once outside the capture first");
+    const size_t want = std::max(bytes, w.bytes + w.bytes / 2);
+    void* p = nullptr;
+    HAPX_CUDA(cudaMalloc(&p, want));
+    if (w.ptr) w.outgrown.push_back(w.ptr);
+    w.ptr = static_cast<float*>(p);
+    w.bytes = want;
   }
   *out = w.ptr;
   return HAPX_OK;
 }
 
 template <int BN, bool A_MN, bool B_MN, bool SOFTMAX = false>
-static int launch2(const Operand& A, const Operand& B, const Operand& Dop, Params& p, cudaStream_t stream, int sm_count) {
+static int launch2(const Operand& A, const Operand& B, const Operand& Dop, Params& p, cudaStream_t stream, const DeviceState& dev) {
   using C = Cfg2<BN, A_MN, B_MN>;
   auto kernel = gemm2_bf16_kernel<BN, A_MN, B_MN, SOFTMAX>;
-  static int max_clusters = 0;
+  const int sm_count = dev.sm_count;
+  static int max_clusters_of[64] = {};      // per device: function attributes and occupancy belong to one
+  int max_clusters = 0;
+  {
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    max_clusters = max_clusters_of[dev.index];
+  }
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1098,6 +1124,8 @@ static int launch2(const Operand& A, const Operand& B, const Operand& Dop, Param
     HAPX_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
     if (n < 1) return fail(HAPX_ERR_CUDA, "gemm: no SM pair can host the two-CTA kernel");
     max_clusters = n;
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    max_clusters_of[dev.index] = n;
   }
   p.m_tiles = (p.M + 2 * BM - 1) / (2 * BM);
   p.n_tiles = (p.N + C::BN - 1) / C::BN;
@@ -1128,9 +1156,7 @@ static int launch2(const Operand& A, const Operand& B, const Operand& Dop, Param
   Params user = p;   // what the caller asked for (output, bias, activation)
   float* ws = nullptr;
   if (p.splits > 1) {
-    int device = 0;
-    HAPX_CUDA(cudaGetDevice(&device));
-    if (int e = workspace(device, (size_t)p.splits * p.m_pad * p.N * sizeof(float), &ws)) return e;
+    if (int e = workspace(dev.index, stream, (size_t)p.splits * p.m_pad * p.N * sizeof(float), &ws)) return e;
     p.D = ws; p.ldd = p.N; p.out_f32 = 1; p.bias = nullptr; p.epilogue = EPI_NONE;
   }
   CUtensorMap tmA, tmB, tmD;
@@ -1200,10 +1226,10 @@ int gemm_bf16(const Operand& Dop, int out_f32, const Operand& A, const Operand& 
   static const bool pair_kernel = std::getenv("HAPX_GEMM_SINGLE_CTA") == nullptr;
   if (pair_kernel && M > BM && N > 64) {
     // (256 x 128 pair tiles were measured too: slower than 256 x 256 even where they fill the waves better)
-    if (softmax) return launch2<256, false, false, true>(A, B, Dop, p, stream, dev->sm_count);   // the only variant that carries the softmax epilogue
-    if (!a_mn && !b_mn) return launch2<256, false, false>(A, B, Dop, p, stream, dev->sm_count);
-    if (!a_mn && b_mn) return launch2<256, false, true>(A, B, Dop, p, stream, dev->sm_count);
-    if (a_mn && b_mn) return launch2<256, true, true>(A, B, Dop, p, stream, dev->sm_count);
+    if (softmax) return launch2<256, false, false, true>(A, B, Dop, p, stream, *dev);   // the only variant that carries the softmax epilogue
+    if (!a_mn && !b_mn) return launch2<256, false, false>(A, B, Dop, p, stream, *dev);
+    if (!a_mn && b_mn) return launch2<256, false, true>(A, B, Dop, p, stream, *dev);
+    if (a_mn && b_mn) return launch2<256, true, true>(A, B, Dop, p, stream, *dev);
   }
   // single-CTA tiles: fewest waves first, then the wider tile
   auto waves = [&](int bn) {
@@ -1212,7 +1238,7 @@ int gemm_bf16(const Operand& Dop, int out_f32, const Operand& A, const Operand& 
   };
   const int bn = (waves(256) <= waves(128)) ? 256 : 128;
 #define HAPX_GEMM_CASE(BN_, AMN_, BMN_) \
-  if (bn == BN_ && a_mn == AMN_ && b_mn == BMN_) return launch<BN_, AMN_, BMN_>(A, B, Dop, p, stream, dev->sm_count);
+  if (bn == BN_ && a_mn == AMN_ && b_mn == BMN_) return launch<BN_, AMN_, BMN_>(A, B, Dop, p, stream, *dev);
   HAPX_GEMM_CASE(256, false, false)
   HAPX_GEMM_CASE(128, false, false)
   HAPX_GEMM_CASE(256, false, true)
@@ -1307,7 +1333,7 @@ int colsum_bf16(const void* g, long long m, long long n, void* out, int out_f32,
   const int rows_per_slice = vec ? kColsumSliceRows : (int)std::max<long long>(128, (m + 65534) / 65535);
   const int slices = (int)std::max<long long>(1, (m + rows_per_slice - 1) / rows_per_slice);
   float* ws = nullptr;
-  if (int e = workspace(device, (size_t)slices * n * sizeof(float), &ws)) return e;
+  if (int e = workspace(device, stream, (size_t)slices * n * sizeof(float), &ws)) return e;
   if (vec) {
     dim3 grid((unsigned)((n + 255) / 256), (unsigned)slices);
     colsum_partial_vec_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(g), n, (int)m, (int)n, ws);

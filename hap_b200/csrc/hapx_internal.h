@@ -78,7 +78,12 @@ struct hapx_comm {
   bool mapped[HAPX_MAX_WORLD] = {};
   bool ipc_opened[HAPX_MAX_WORLD] = {};
   unsigned seq = 0;                 // sequence number of the last collective launched
-  int timeout_ms = 10000;
+  long long calls = 0;              // collectives launched so far (never wraps; for callers that count them)
+  int timeout_ms = 600000;          // bound of a device-side wait on a peer; HAPX_TIMEOUT_MS overrides the default
+  // One word of mapped pinned host memory that a kernel sets (besides the status word in the control
+  // block) when a wait runs out: the host reads it at the entry of the next call without synchronising.
+  unsigned* host_status = nullptr;      // host address
+  unsigned* host_status_dev = nullptr;  // the same word as the device sees it
   int max_ctas = 0;
   int order_log2 = 6;               // copy kernels interleave 64 tile streams (see pull_copy_kernel)
   int sm_count = 0;

@@ -1,0 +1,88 @@
+"""``F.dropout`` for the synthesized programs, and the generator state behind every dropout of the
+package (this one and the dropout on the attention probabilities).
+
+The planner emits ``torch.nn.functional.dropout(input, p)`` (``hap.rs:1446-1464``); the reference trains
+with ``dropout = 0.1`` (``config.py:33``).  :func:`dropout` has the same signature.  Masks come from a
+counter-based generator: a pure function of (seed, iteration counter, call id, element index), so the
+backward pass regenerates the mask instead of saving it.  Seed and iteration counter live in device
+memory: :func:`manual_seed` sets them, :func:`advance` steps the counter with a one-thread kernel - the
+step driver calls it once per iteration, and because it is a kernel, a step replayed from a CUDA graph
+draws fresh masks on every replay.  Call ids number the dropout sites in program order; they restart at
+:func:`advance`, so a replayed graph and the eager step it was recorded from use the same ids.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _native as N
+from .comm import _on_device, _stream
+
+_next_call_id = 0
+
+
+def new_call_id() -> int:
+    """Id for one dropout site of the current iteration (shared with the attention kernels)."""
+    global _next_call_id
+    _next_call_id += 1
+    return _next_call_id
+
+
+def manual_seed(seed: int, device=None) -> None:
+    """Seed the device's generator and reset its iteration counter."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with _on_device(device):
+        N.check(N.lib.hapx_rng_seed(int(seed) & 0xFFFFFFFFFFFFFFFF, _stream(device)))
+
+
+def advance(device=None) -> None:
+    """Step the iteration counter (device side) and restart the call ids (host side)."""
+    global _next_call_id
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with _on_device(device):
+        N.check(N.lib.hapx_rng_advance(_stream(device)))
+    _next_call_id = 0
+
+
+def _apply(x: torch.Tensor, p: float, call_id: int, out: torch.Tensor = None) -> torch.Tensor:
+    x = x.contiguous()
+    y = torch.empty_like(x) if out is None else out
+    code = N.BF16 if x.dtype == torch.bfloat16 else N.F32
+    with _on_device(x.device):
+        N.check(N.lib.hapx_dropout(y.data_ptr(), x.data_ptr(), code, x.numel(), float(p), call_id, _stream(x.device)))
+    return y
+
+
+class _Dropout(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, p, call_id):
+        ctx.meta = (p, call_id)
+        return _apply(x, p, call_id)
+
+    @staticmethod
+    def backward(ctx, grad):
+        p, call_id = ctx.meta
+        return _apply(grad, p, call_id), None, None
+
+
+def dropout(input: torch.Tensor, p: float = 0.5, training: bool = True, inplace: bool = False) -> torch.Tensor:
+    """Drop-in for ``torch.nn.functional.dropout`` on CUDA bfloat16 / float32 tensors."""
+    if not input.is_cuda:
+        raise RuntimeError(f"dropout: hap_b200 has no CPU path; tensor is on {input.device}")
+    if input.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError(f"dropout: bfloat16 or float32 only, got {input.dtype}")
+    if not 0.0 <= p < 1.0:
+        raise ValueError(f"dropout: p must be in [0, 1), got {p}")
+    if inplace:
+        raise NotImplementedError("dropout: the planner never emits inplace=True (hap.rs:1450)")
+    if not training or p == 0.0:
+        return input
+    return _Dropout.apply(input, float(p), new_call_id())
+
+
+def keep_mask(n: int, p: float, call_id: int, device=None) -> torch.Tensor:
+    """The keep mask (uint8, n elements) that call ``call_id`` draws in the current iteration."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    mask = torch.empty(n, dtype=torch.uint8, device=device)
+    with _on_device(device):
+        N.check(N.lib.hapx_dropout_mask(mask.data_ptr(), n, float(p), call_id, _stream(device)))
+    return mask

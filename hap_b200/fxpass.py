@@ -29,16 +29,18 @@ def retarget_tensor_ops(graph: torch.fx.Graph, fold_loss: bool = True) -> Dict[s
     * ``F.multi_head_attention_forward`` -> :func:`hap_b200.attention.multi_head_attention_forward`
     * ``torch.einsum`` with one of the four MoE codes -> :func:`hap_b200.einsum`
     * ``F.layer_norm`` -> :func:`hap_b200.layer_norm`
+    * ``F.dropout`` (``hap.rs:1446-1464``) -> :func:`hap_b200.dropout.dropout`
     * ``nll_loss(log_softmax(x[.float()], -1)[.reshape(-1, V)], y[.reshape(-1)], reduction='sum')``
       -> :func:`hap_b200.nll_log_softmax_sum` ``(x, y)`` when the intermediate nodes have no other user.
     """
     from .attention import multi_head_attention_forward
+    from .dropout import dropout
     from .einsum import CODES as SUPPORTED_CODES, einsum
     from .linear import linear
     from .loss import nll_log_softmax_sum
     from .norm import layer_norm
 
-    changed = {"linear": 0, "multi_head_attention_forward": 0, "einsum": 0, "layer_norm": 0, "loss": 0}
+    changed = {"linear": 0, "multi_head_attention_forward": 0, "einsum": 0, "layer_norm": 0, "dropout": 0, "loss": 0}
     for node in list(graph.nodes):
         if node.op != "call_function":
             continue
@@ -55,6 +57,9 @@ def retarget_tensor_ops(graph: torch.fx.Graph, fold_loss: bool = True) -> Dict[s
         elif _is(t, F.layer_norm):
             node.target = layer_norm
             changed["layer_norm"] += 1
+        elif _is(t, F.dropout):
+            node.target = dropout
+            changed["dropout"] += 1
         elif fold_loss and _is(t, F.nll_loss) and _fold_loss(graph, node, nll_log_softmax_sum):
             changed["loss"] += 1
     graph.lint()

@@ -61,12 +61,24 @@ def _summed_nll(ns, call, method, logits, targets, classes):
 def default_namespace() -> SimpleNamespace:
     from . import collectives
     from .attention import multi_head_attention_forward
+    from .dropout import dropout
     from .einsum import einsum
     from .linear import linear
     from .loss import nll_log_softmax_sum
     from .norm import layer_norm
     return SimpleNamespace(collectives=collectives, linear=linear, mha=multi_head_attention_forward, einsum=einsum,
-                           nll=nll_log_softmax_sum, layer_norm=layer_norm)
+                           nll=nll_log_softmax_sum, layer_norm=layer_norm, dropout=dropout)
+
+
+def _dropout_of(ns, call, p):
+    """``x -> dropout(x, p)`` as the planner emits it (``torch.nn.functional.dropout(input, p)``,
+    ``hap.rs:1446-1464``), or the identity for p == 0.  The sites are those of the reference's encoder
+    layers (``torch.nn.TransformerEncoderLayer`` with ``dropout``, ``models.py:40, 74``): after the
+    attention block, after the FFN activation and after the FFN."""
+    if not p:
+        return lambda x: x
+    fn = getattr(ns, "dropout", None) or F.dropout
+    return lambda x: call(fn, x, p)
 
 
 def shard_parameter_(module: torch.nn.Module, name: str, lengths: Sequence[int], dim: int, rank: int) -> None:
@@ -166,7 +178,7 @@ class TransformerLM(torch.nn.Module):
         return _lm_forward(self, tokens, targets, ns, None, None, None, "none")
 
 
-def _lm_forward(m, tokens, targets, ns, emit, ratios, rank, plan):
+def _lm_forward(m, tokens, targets, ns, emit, ratios, rank, plan, dropout_p=0.0):
     """The model's forward written once; `emit` (an fx graph) turns parameter reads and collectives
     into nodes, otherwise it runs eagerly on the unsharded module."""
     col, linear, mha = ns.collectives, ns.linear, ns.mha
@@ -189,6 +201,7 @@ def _lm_forward(m, tokens, targets, ns, emit, ratios, rank, plan):
     call = (lambda fn, *a, **k: fn(*a, **k)) if emit is None else (lambda fn, *a, **k: emit.call_function(fn, a, k))
     method = (lambda obj, name, *a: getattr(obj, name)(*a)) if emit is None else (lambda obj, name, *a: emit.call_method(name, (obj, *a)))
 
+    drop = _dropout_of(ns, call, dropout_p)
     # look the tokens up in (S, B) order: the activations are then contiguous in the (L, N, E) layout the
     # attention handler wants (hap.rs:1284-1287) instead of a transposed view that every layer_norm copies
     x = call(F.embedding, method(tokens, "transpose", 0, 1), param("embed.weight"))   # (S, B, E)
@@ -199,14 +212,14 @@ def _lm_forward(m, tokens, targets, ns, emit, ratios, rank, plan):
         h = call(_ln(ns), x, (E,), param(f"l{i}_ln1_w"), param(f"l{i}_ln1_b"))
         att = call(mha, query=h, key=h, value=h, embed_dim_to_check=E, num_heads=H,
                    in_proj_weight=param(f"l{i}_in_w", True), in_proj_bias=param(f"l{i}_in_b", True), bias_k=None, bias_v=None,
-                   add_zero_attn=False, dropout_p=0.0, out_proj_weight=param(f"l{i}_out_w", True),
+                   add_zero_attn=False, dropout_p=float(dropout_p), out_proj_weight=param(f"l{i}_out_w", True),
                    out_proj_bias=param(f"l{i}_out_b"), attn_mask=mask)
-        x = call(operator.add, x, call(operator.getitem, att, 0))
+        x = call(operator.add, x, drop(call(operator.getitem, att, 0)))
         h = call(_ln(ns), x, (E,), param(f"l{i}_ln2_w"), param(f"l{i}_ln2_b"))
         h = call(linear, h, param(f"l{i}_w1", True), param(f"l{i}_b1", True))
-        h = call(F.relu, h)
+        h = drop(call(F.relu, h))
         h = call(linear, h, param(f"l{i}_w2", True), param(f"l{i}_b2"))
-        x = call(operator.add, x, h)
+        x = call(operator.add, x, drop(h))
     x = call(_ln(ns), x, (E,), param("lnf_w"), param("lnf_b"))
     logits = call(linear, x, param("dec_w", True), param("dec_b", True))  # (S, B, V)
     return _summed_nll(ns, call, method, logits, method(targets, "transpose", 0, 1), m.vocab)
@@ -216,13 +229,17 @@ def _device_of(m):
     return next(m.parameters()).device
 
 
-def emit_lm(model: TransformerLM, plan: str, ratios: Sequence[float], rank: int, batch: int, ns=None) -> torch.fx.Graph:
+def emit_lm(model: TransformerLM, plan: str, ratios: Sequence[float], rank: int, batch: int, ns=None,
+            dropout_p: float = 0.0) -> torch.fx.Graph:
     """fx graph of the language model's training forward for one rank.
 
     ``"dp"``      - batch-sharded tokens/targets, every parameter replicated (gradient all-reduce);
     ``"dp_zero"`` - as above, but attention and FFN weights, the first FFN bias and the decoder live
                     sharded on dim 0 by ``ratios`` (cut in place on the module) and are all-gathered
                     at their use; their gradients come back through the uneven reduce_scatter.
+    ``dropout_p`` > 0 adds the reference's dropout (``config.py:33``): on the attention probabilities
+    (the attention node's ``dropout_p``, ``hap.rs:1257, 1307``) and as ``F.dropout`` nodes after the
+    attention block, the FFN activation and the FFN.
     """
     ns = ns or default_namespace()
     if plan not in ("dp", "dp_zero"):
@@ -240,7 +257,7 @@ def emit_lm(model: TransformerLM, plan: str, ratios: Sequence[float], rank: int,
             full = getattr(model, n).shape[0]
             model._full_extent[n] = full
             shard_parameter_(model, n, sharding_round(full, ratios), 0, rank)
-    loss = _lm_forward(model, tok_r, tgt_r, ns, g, list(ratios), rank, plan)
+    loss = _lm_forward(model, tok_r, tgt_r, ns, g, list(ratios), rank, plan, dropout_p)
     g.output(loss)
     g.lint()
     return g
@@ -297,7 +314,7 @@ class ViT(torch.nn.Module):
         return _vit_forward(self, images, labels, ns, None, None, None, "none")
 
 
-def _vit_forward(m, images, labels, ns, emit, ratios, rank, plan):
+def _vit_forward(m, images, labels, ns, emit, ratios, rank, plan, dropout_p=0.0):
     col, linear, mha = ns.collectives, ns.linear, ns.mha
     E, H, G, P_, C_ = m.d_model, m.nheads, m.grid, m.patch, m.channels
 
@@ -312,6 +329,7 @@ def _vit_forward(m, images, labels, ns, emit, ratios, rank, plan):
     call = (lambda fn, *a, **k: fn(*a, **k)) if emit is None else (lambda fn, *a, **k: emit.call_function(fn, a, k))
     method = (lambda obj, name, *a: getattr(obj, name)(*a)) if emit is None else (lambda obj, name, *a: emit.call_method(name, (obj, *a)))
 
+    drop = _dropout_of(ns, call, dropout_p)
     # (B, C, G*P, G*P) -> (B, G*G, C*P*P): one row per patch, elements in the order a conv kernel reads them
     x = method(images, "reshape", -1, C_, G, P_, G, P_)
     x = method(x, "permute", 0, 2, 4, 1, 3, 5)
@@ -325,21 +343,22 @@ def _vit_forward(m, images, labels, ns, emit, ratios, rank, plan):
         h = call(_ln(ns), x, (E,), param(f"l{i}_ln1_w"), param(f"l{i}_ln1_b"))
         att = call(mha, query=h, key=h, value=h, embed_dim_to_check=E, num_heads=H,
                    in_proj_weight=param(f"l{i}_in_w", True), in_proj_bias=param(f"l{i}_in_b", True), bias_k=None, bias_v=None,
-                   add_zero_attn=False, dropout_p=0.0, out_proj_weight=param(f"l{i}_out_w", True),
+                   add_zero_attn=False, dropout_p=float(dropout_p), out_proj_weight=param(f"l{i}_out_w", True),
                    out_proj_bias=param(f"l{i}_out_b"), attn_mask=None)
-        x = call(operator.add, x, call(operator.getitem, att, 0))
+        x = call(operator.add, x, drop(call(operator.getitem, att, 0)))
         h = call(_ln(ns), x, (E,), param(f"l{i}_ln2_w"), param(f"l{i}_ln2_b"))
         h = call(linear, h, param(f"l{i}_w1", True), param(f"l{i}_b1", True))
-        h = call(F.gelu, h)
+        h = drop(call(F.gelu, h))
         h = call(linear, h, param(f"l{i}_w2", True), param(f"l{i}_b2"))
-        x = call(operator.add, x, h)
+        x = call(operator.add, x, drop(h))
     x = call(operator.getitem, x, 0)                                        # the class token: (B, E)
     x = call(_ln(ns), x, (E,), param("lnf_w"), param("lnf_b"))
     logits = call(linear, x, param("head_w", True), param("head_b", True))
     return _summed_nll(ns, call, method, logits, labels, m.nclasses)
 
 
-def emit_vit(model: ViT, plan: str, ratios: Sequence[float], rank: int, batch: int, ns=None) -> torch.fx.Graph:
+def emit_vit(model: ViT, plan: str, ratios: Sequence[float], rank: int, batch: int, ns=None,
+             dropout_p: float = 0.0) -> torch.fx.Graph:
     """fx graph of the ViT training forward for one rank; plans as in :func:`emit_lm` (``"dp"``:
     images and labels batch-sharded by ``ratios``, parameters replicated; ``"dp_zero"``: projection
     weights additionally sharded on dim 0 and all-gathered at their use)."""
@@ -359,7 +378,7 @@ def emit_vit(model: ViT, plan: str, ratios: Sequence[float], rank: int, batch: i
             full = getattr(model, n).shape[0]
             model._full_extent[n] = full
             shard_parameter_(model, n, sharding_round(full, ratios), 0, rank)
-    loss = _vit_forward(model, img_r, lab_r, ns, g, list(ratios), rank, plan)
+    loss = _vit_forward(model, img_r, lab_r, ns, g, list(ratios), rank, plan, dropout_p)
     g.output(loss)
     g.lint()
     return g
@@ -369,18 +388,20 @@ def emit_vit(model: ViT, plan: str, ratios: Sequence[float], rank: int, batch: i
 # MoE Transformer (expert-parallel configuration)
 # ---------------------------------------------------------------------------------------------
 def top2_gating(x, gate_weight, n_expert: int, capacity: int):
-    """Top-2 gating with a fixed per-expert capacity, same semantics as the reference's fx-wrapped
-    ``top_2_gating`` (``models.py:477-502``): softmax gate, two best experts per token, slots handed
-    out in sequence order (all first choices before any second choice), 1-based slot numbers that
-    must stay below ``capacity``, combine weight = the raw gate probability.  Returns
-    (dispatch, combine), both (batch, seq, n_expert, capacity) in x's dtype.  Plain torch ops: the
-    planner treats this function as an opaque leaf (``hap.rs:2169``)."""
+    """Top-2 gating with a fixed per-expert capacity; reproduces the reference's fx-wrapped
+    ``top_2_gating`` (``models.py:477-502``) entry for entry: softmax gate, two best experts per
+    token, 1-based slot numbers handed out in sequence order per (choice, expert), and the
+    second-choice slots of an expert shifted by the SUM of that expert's first-choice slot numbers
+    (``models.py:482-484`` sums ``position_in_expert``, i.e. n(n+1)/2 for n first choices, not n).
+    A slot number must stay below ``capacity`` (slot 0 is never used); combine weight = the raw gate
+    probability.  Returns (dispatch, combine), both (batch, seq, n_expert, capacity) in x's dtype.
+    Plain torch ops: the planner treats this function as an opaque leaf (``hap.rs:2169``)."""
     gates = torch.softmax(torch.matmul(x, gate_weight).float(), dim=2)                   # (b, s, e)
     top_p, top_i = torch.topk(gates, 2, dim=2)                                           # (b, s, 2)
     chosen = F.one_hot(top_i, n_expert)                                                  # (b, s, 2, e)
     first, second = chosen[:, :, 0, :], chosen[:, :, 1, :]
     slot1 = torch.cumsum(first, dim=1) * first                                           # 1-based
-    slot2 = (torch.cumsum(second, dim=1) + first.sum(dim=1, keepdim=True)) * second
+    slot2 = (torch.cumsum(second, dim=1) + slot1.sum(dim=1, keepdim=True)) * second
     keep1, keep2 = (slot1 > 0) & (slot1 < capacity), (slot2 > 0) & (slot2 < capacity)
     combine = torch.zeros(*gates.shape, capacity, dtype=gates.dtype, device=x.device)    # (b, s, e, c)
     for keep, slot, p in ((keep1, slot1, top_p[:, :, 0]), (keep2, slot2, top_p[:, :, 1])):
@@ -422,7 +443,7 @@ class MoETransformerLM(torch.nn.Module):
         return _moe_forward(self, tokens, targets, ns, None, None, None, None)
 
 
-def _moe_forward(m, tokens, targets, ns, emit, ratios, rank, batch):
+def _moe_forward(m, tokens, targets, ns, emit, ratios, rank, batch, dropout_p=0.0):
     col, linear, mha, einsum = ns.collectives, ns.linear, ns.mha, ns.einsum
     E, H, ne, cap = m.d_model, m.nheads, m.n_expert, m.capacity
 
@@ -435,13 +456,14 @@ def _moe_forward(m, tokens, targets, ns, emit, ratios, rank, batch):
     call = (lambda fn, *a, **k: fn(*a, **k)) if emit is None else (lambda fn, *a, **k: emit.call_function(fn, a, k))
     method = (lambda obj, name, *a: getattr(obj, name)(*a)) if emit is None else (lambda obj, name, *a: emit.call_method(name, (obj, *a)))
 
+    drop = _dropout_of(ns, call, dropout_p)      # the Top-2 layer drops only after its attention block (models.py:346-351)
     x = call(operator.add, call(F.embedding, tokens, param("embed.weight")), param("pos"))          # (b, s, E)
     for i in range(m.nlayers):
         h = method(x, "transpose", 0, 1)                                                               # (s, b, E)
         att = call(mha, query=h, key=h, value=h, embed_dim_to_check=E, num_heads=H, in_proj_weight=param(f"l{i}_in_w"),
-                   in_proj_bias=param(f"l{i}_in_b"), bias_k=None, bias_v=None, add_zero_attn=False, dropout_p=0.0,
+                   in_proj_bias=param(f"l{i}_in_b"), bias_k=None, bias_v=None, add_zero_attn=False, dropout_p=float(dropout_p),
                    out_proj_weight=param(f"l{i}_out_w"), out_proj_bias=param(f"l{i}_out_b"))
-        a = method(call(operator.getitem, att, 0), "transpose", 0, 1)
+        a = drop(method(call(operator.getitem, att, 0), "transpose", 0, 1))
         x = call(_ln(ns), call(operator.add, x, a), (E,), param(f"l{i}_ln1_w"), param(f"l{i}_ln1_b"))
         gated = call(top2_gating, x, param(f"l{i}_gate"), ne, cap)
         dispatch, combine = call(operator.getitem, gated, 0), call(operator.getitem, gated, 1)
@@ -459,7 +481,8 @@ def _moe_forward(m, tokens, targets, ns, emit, ratios, rank, batch):
     return _summed_nll(ns, call, method, logits, targets, m.vocab)
 
 
-def emit_moe(model: MoETransformerLM, ratios: Sequence[float], rank: int, batch: int, ns=None) -> torch.fx.Graph:
+def emit_moe(model: MoETransformerLM, ratios: Sequence[float], rank: int, batch: int, ns=None,
+             dropout_p: float = 0.0) -> torch.fx.Graph:
     """Expert-parallel program: tokens batch-sharded by ``ratios``; expert weights w1/w2 sharded on
     the expert dimension by ``sharding_round(n_expert, ratios)`` (cut in place); the dispatched
     tokens travel batch-sharded -> expert-sharded -> batch-sharded through two uneven all_to_all
@@ -474,7 +497,7 @@ def emit_moe(model: MoETransformerLM, ratios: Sequence[float], rank: int, batch:
     for i in range(model.nlayers):
         shard_parameter_(model, f"l{i}_w1", le, 0, rank)
         shard_parameter_(model, f"l{i}_w2", le, 0, rank)
-    loss = _moe_forward(model, tok_r, tgt_r, ns, g, list(ratios), rank, batch)
+    loss = _moe_forward(model, tok_r, tgt_r, ns, g, list(ratios), rank, batch, dropout_p)
     g.output(loss)
     g.lint()
     return g

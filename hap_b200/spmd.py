@@ -21,33 +21,56 @@ from typing import Callable, List, Sequence
 import torch
 from torch.fx.node import map_arg
 
+from . import dropout as _dropout
 from .collectives import NAMES as _COLLECTIVE_NAMES
 
 
-def _is_collective(target) -> bool:
+def _is_collective(target, modules=("collectives",)) -> bool:
     module = (getattr(target, "__module__", "") or "").split(".")[-1]
-    return getattr(target, "__name__", None) in _COLLECTIVE_NAMES and module in ("collectives", "gloo_port")
+    return getattr(target, "__name__", None) in _COLLECTIVE_NAMES and module in modules
 
 
-def _make_optimizer(params, lr, clip):
-    """Fused clip + Adam kernels for parameters on a GPU; torch's Adam (clipped by the caller) for
-    host tensors, which only the CPU checks of the executors use."""
-    if params and all(p.is_cuda and p.dtype in (torch.float32, torch.bfloat16) for p in params):
-        from .optim import ClipAdam
-        return ClipAdam(params, lr=lr, max_norm=clip)
-    return torch.optim.Adam(params, lr=lr)
+def _program_has_dropout(module) -> bool:
+    """True when the fx program holds a dropout node or an attention node with dropout_p > 0."""
+    for n in getattr(module, "graph", torch.fx.Graph()).nodes:
+        if n.op != "call_function":
+            continue
+        name = getattr(n.target, "__name__", "")
+        if name == "dropout" or (name == "multi_head_attention_forward" and float(n.kwargs.get("dropout_p", 0.0) or 0.0) > 0.0):
+            return True
+    return False
+
+
+def _fused_step_tail(params, lr, clip):
+    """clip by the local-shard norm + Adam as multi-tensor kernels (``worker.py:74, 76``); GPU only."""
+    from .optim import ClipAdam
+    if not params or not all(p.is_cuda and p.dtype in (torch.float32, torch.bfloat16) for p in params):
+        raise RuntimeError("hap_b200.spmd: parameters must be float32 / bfloat16 CUDA tensors (there is no CPU path)")
+    return ClipAdam(params, lr=lr, max_norm=clip)
 
 
 class LockstepWorld:
+    collective_modules = ("collectives",)      # modules whose eight functions are collective nodes
+
     def __init__(self, modules: Sequence[torch.fx.GraphModule], backend, lr: float = 5e-4, clip: float = 0.5):
         self.modules = list(modules)
         self.world = len(self.modules)
         self.backend = backend
         self.clip = clip
-        self.optimizers = [_make_optimizer(list(m.parameters()), lr, clip) for m in self.modules]
+        self.optimizers = [self._make_optimizer(list(m.parameters()), lr, clip) for m in self.modules]
         self._nodes = [list(m.graph.nodes) for m in self.modules]
         if len({len(n) for n in self._nodes}) != 1:
             raise ValueError("SPMD ranks must run the same node sequence")
+
+    def _make_optimizer(self, params, lr, clip):
+        return _fused_step_tail(params, lr, clip)
+
+    def _optimizer_step(self, module, optimizer) -> None:
+        optimizer.step()       # the fused tail clips by the local-shard norm itself
+
+    def _new_iteration(self) -> None:
+        if any(_program_has_dropout(m) for m in self.modules):
+            _dropout.advance()
 
     def forward(self, inputs_per_rank: Sequence[Sequence[torch.Tensor]]) -> List[torch.Tensor]:
         envs = [dict() for _ in range(self.world)]
@@ -65,7 +88,7 @@ class LockstepWorld:
                     for part in n.target.split("."):
                         obj = getattr(obj, part)
                     envs[r][n] = obj
-            elif n0.op == "call_function" and _is_collective(n0.target):
+            elif n0.op == "call_function" and _is_collective(n0.target, self.collective_modules):
                 name = n0.target.__name__
                 per_rank = [map_arg(n.args, load(r)) for r, n in enumerate(step)]
                 tensors = [a[0] for a in per_rank]
@@ -93,15 +116,14 @@ class LockstepWorld:
 
     def step(self, inputs_per_rank) -> float:
         """One training iteration for all ranks; returns the global loss (sum of the partial losses)."""
+        self._new_iteration()
         for opt in self.optimizers:
             opt.zero_grad()
         losses = self.forward(inputs_per_rank)
         total = torch.stack([l.detach() for l in losses]).sum()
         torch.stack(losses).sum().backward()
         for m, opt in zip(self.modules, self.optimizers):
-            if isinstance(opt, torch.optim.Optimizer):      # host tensors: the reference's own pair
-                torch.nn.utils.clip_grad_norm_(m.parameters(), self.clip)
-            opt.step()
+            self._optimizer_step(m, opt)
         return total
 
 
@@ -116,23 +138,24 @@ class ProcessWorker:
     """
 
     def __init__(self, module: torch.fx.GraphModule, lr: float = 5e-4, clip: float = 0.5,
-                 reduce_loss: Callable[[torch.Tensor], torch.Tensor] = None, comm=None, fused_tail: bool = None):
+                 reduce_loss: Callable[[torch.Tensor], torch.Tensor] = None, comm=None):
         self.module = module
         self.clip = clip
-        params = list(module.parameters())
-        on_gpu = bool(params) and all(p.is_cuda and p.dtype in (torch.float32, torch.bfloat16) for p in params)
-        self.fused_tail = on_gpu if fused_tail is None else bool(fused_tail)
-        if self.fused_tail:
-            # clip by the local-shard norm + Adam as multi-tensor kernels without a host round trip
-            from .optim import ClipAdam
-            self.optimizer = ClipAdam(params, lr=lr, max_norm=clip)
-        else:
-            self.optimizer = torch.optim.Adam(params, lr=lr)
+        self.lr = lr
+        # clip by the local-shard norm + Adam as multi-tensor kernels without a host round trip
+        self.optimizer = self._make_optimizer(list(module.parameters()), lr, clip)
         self.reduce_loss = reduce_loss
         self.comm = comm
+        self.uses_dropout = _program_has_dropout(module)
         self._buckets = []          # (flat tensor in the heap, [parameters])
         if comm is not None:
             self._build_buckets()
+
+    def _make_optimizer(self, params, lr, clip):
+        return _fused_step_tail(params, lr, clip)
+
+    def _optimizer_step(self) -> None:
+        self.optimizer.step()
 
     def _build_buckets(self) -> None:
         names = [n.args[0].target for n in self.module.graph.nodes
@@ -169,31 +192,42 @@ class ProcessWorker:
         """Record one whole iteration (zero_grad ... optimizer step) into a CUDA graph and return a
         callable ``replay(*inputs) -> total loss`` that copies the inputs into the graph's static
         buffers and launches the graph: the per-node Python dispatch of the eager step (the
-        reference's hot loop (i), ``worker.py:58-83``) disappears.  Needs a capturable optimizer
-        (the fused step tail is; torch's Adam is re-created with ``capturable=True``) and at least two collectives per iteration;
-        all ranks must replay the same number of times."""
-        if not self.fused_tail:
-            lr = self.optimizer.param_groups[0]["lr"]
-            self.optimizer = torch.optim.Adam(self.module.parameters(), lr=lr, capturable=True)
-        static_in = [t.clone() for t in example_inputs]
-        if self.comm is not None:
-            self.comm.set_stream_ordering(False)
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            for _ in range(warmup):
-                self.step(*static_in)
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
+        reference's hot loop (i), ``worker.py:58-83``) disappears.  The flag words of the
+        collectives carry call numbers that are baked into the graph, so an iteration must hold at
+        least two collectives of this library (then no flag of one replay can satisfy a wait of the
+        next; checked here) and all ranks must replay the same number of times."""
         from . import _native as N
-        graph = torch.cuda.CUDAGraph()
-        before = N.lib.hapx_launch_count()
-        with torch.cuda.graph(graph):
-            static_out = self.step(*static_in)
+        from . import collectives
+        comm = self.comm if self.comm is not None else (collectives.get_default_comm() if collectives.has_default_comm() else None)
+        static_in = [t.clone() for t in example_inputs]
+        if comm is not None:
+            comm.set_stream_ordering(False)     # no event may be recorded into the graph and waited on outside it
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(warmup):
+                    self.step(*static_in)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = N.lib.hapx_launch_count()
+            calls_before = comm.calls_issued() if comm is not None else 0
+            with torch.cuda.graph(graph):
+                static_out = self.step(*static_in)
+            calls = (comm.calls_issued() - calls_before) if comm is not None else 0
+        finally:
+            if comm is not None:
+                comm.set_stream_ordering(True)
+        if comm is not None and comm.world > 1 and calls < 2:
+            raise RuntimeError("ProcessWorker.capture: an iteration with fewer than two collectives cannot be replayed safely "
+                               "(its flag words would repeat from one replay to the next)")
         self._graph = graph
         self.captured_launches = int(N.lib.hapx_launch_count() - before)    # kernels of this library in one replay
 
         def replay(*inputs):
+            if comm is not None:
+                comm.poll()
             for dst, src in zip(static_in, inputs):
                 dst.copy_(src, non_blocking=True)
             graph.replay()
@@ -203,6 +237,10 @@ class ProcessWorker:
 
     def step(self, *inputs) -> torch.Tensor:
         from . import collectives
+        if self.comm is not None:
+            self.comm.poll()        # a collective of an earlier step that gave up on a peer raises here
+        if self.uses_dropout:
+            _dropout.advance()      # new masks for this iteration (a kernel: also on every graph replay)
         self.zero_grad()
         loss = self.module(*inputs)
         total = loss.detach().clone()
@@ -218,7 +256,5 @@ class ProcessWorker:
                 self.comm.all_reduce([flat], inplace=True)
         else:
             loss.backward()
-        if not self.fused_tail:
-            torch.nn.utils.clip_grad_norm_(self.module.parameters(), self.clip)
-        self.optimizer.step()
+        self._optimizer_step()
         return total

@@ -92,12 +92,28 @@ int hapx_comm_ipc_handle(hapx_comm* c, void* out_handle);
 int hapx_comm_open_peers(hapx_comm* c, const void* handles /* world * 64 bytes, rank order */);
 /* Alternative to open_peers when the caller maps peer heaps itself. */
 int hapx_comm_attach_peer(hapx_comm* c, int peer, void* mapped_base);
+/* Tear-down.  hapx_comm_destroy closes the mappings of the peers' heaps and frees this rank's own
+ * heap.  Freeing a heap that a peer still has mapped is undefined, so ranks that run as separate
+ * processes should tear down in two phases: every rank calls hapx_comm_close_peers, all ranks meet at
+ * a host barrier of the caller's, then every rank calls hapx_comm_destroy. */
+int hapx_comm_close_peers(hapx_comm* c);
 int hapx_comm_destroy(hapx_comm* c);
 int hapx_comm_world(hapx_comm* c, int* world, int* n_local, int* first_rank);
 /* User area of local rank `local_index`'s heap. */
 int hapx_comm_heap(hapx_comm* c, int local_index, void** base, size_t* bytes);
-/* Upper bound for device-side waits on peers, in milliseconds (default 10000). */
+/* Upper bound for device-side waits on peers, in milliseconds.  Default 600000 (ten minutes: a
+ * peer that is merely late - logging, a checkpoint, a data stall - must not be mistaken for a dead
+ * one), or the value of the environment variable HAPX_TIMEOUT_MS when the communicator is created.
+ * When a wait runs out the kernel skips its data movement (its outputs stay unwritten) and leaves an
+ * error behind that every later collective call on the communicator returns as
+ * HAPX_ERR_PEER_TIMEOUT, without synchronising, until hapx_comm_check has reported and cleared it. */
 int hapx_comm_set_timeout_ms(hapx_comm* c, int ms);
+/* The same test the collectives make on entry, by itself: HAPX_ERR_PEER_TIMEOUT if a kernel of an
+ * earlier call has given up on a peer.  Reads one word of pinned host memory; no synchronisation,
+ * so it only sees kernels that have already run. */
+int hapx_comm_poll(hapx_comm* c);
+/* Number of collectives launched on this communicator so far. */
+int hapx_comm_calls_issued(hapx_comm* c, int64_t* calls);
 /* Cap the CTAs per rank that a collective launches (0 = one full wave). */
 int hapx_comm_set_max_ctas(hapx_comm* c, int ctas);
 /* Calls issued on different streams are ordered with an event by default.  Turn that off
@@ -150,6 +166,15 @@ int hapx_dynamic_slice(void* dst, const void* src, int dtype, int64_t outer, int
 int hapx_dynamic_slice_backward(void* dst, const void* src, int dtype, int64_t outer, int64_t inner,
                                 const int64_t* lengths, int world, int rank, hapx_stream stream);
 
+/* One-sided read: copy `bytes` bytes that start `peer_offset` bytes into the USER AREA of rank
+ * `peer`'s heap (hapx_comm_heap) into local memory at dst, with the copy kernel of the collectives
+ * (16-byte peer loads over NVLink) and no handshake: the caller orders it against the peer's writes
+ * (a host barrier, or a collective in between).  No counterpart in the reference; it is the
+ * primitive the collectives are built from, exposed for measuring the peer-copy rate of a link
+ * (the denominator the all_gather / reduce_scatter fractions are quoted against) and for callers
+ * that manage their own synchronisation.  One-process-per-GPU communicators only. */
+int hapx_comm_get(hapx_comm* c, int peer, size_t peer_offset, void* dst, size_t bytes, hapx_stream stream);
+
 /* ---- ratio-sharded F.linear on the tensor cores --------------------------------------------
  * Replace the F.linear nodes the planner emits (hap.rs:1030-1037; sharding variants
  * hap.rs:2787-2816: data parallel = uneven m, column parallel = uneven n) and their autograd
@@ -199,11 +224,33 @@ int hapx_attention_forward(void* out, void* probs, void* scores_ws, const void* 
 int hapx_attention_backward(void* dqkv, void* dscores_ws, void* ds_ws, const void* dout, const void* probs,
                             const void* qkv, int64_t L, int64_t N, int64_t H, int64_t D, hapx_stream stream);
 
+/* ---- dropout ---------------------------------------------------------------------------------
+ * Replaces the torch.nn.functional.dropout(input, p) nodes the planner emits (hap.rs:1446-1464;
+ * the encoder layers of models.py:40,74,83-88 are built with config.py:33 dropout = 0.1) and supplies
+ * the random bits for the dropout on the attention probabilities (dropout_p of the attention node,
+ * hap.rs:1257, 1307, 1319).  The generator is counter based: a mask is a pure function of
+ * (seed, iteration counter, call_id, element index), so backward passes regenerate it instead of
+ * storing it.  Seed and iteration counter live in device memory, one pair per device:
+ * hapx_rng_seed sets the seed and zeroes the counter, hapx_rng_advance adds one to the counter (a
+ * one-thread kernel: recorded into a CUDA graph it advances on every replay).  Call hapx_rng_advance
+ * once per training iteration; call_id distinguishes the dropout sites within an iteration.
+ * The first use on a device allocates the 16-byte state: make it outside any stream capture.
+ * hapx_dropout: y[i] = keep(i) ? x[i] / (1 - p) : 0 over n elements of HAPX_BF16 or HAPX_F32
+ * (y may equal x).  The backward pass is the same call on the incoming gradient with the same
+ * call_id in the same iteration.  hapx_dropout_mask writes keep(i) as bytes (for tests). */
+int hapx_rng_seed(uint64_t seed, hapx_stream stream);
+int hapx_rng_advance(hapx_stream stream);
+int hapx_dropout(void* y, const void* x, int dtype, int64_t n, double p, uint64_t call_id, hapx_stream stream);
+int hapx_dropout_mask(unsigned char* mask, int64_t n, double p, uint64_t call_id, hapx_stream stream);
+
 /* all_reduce that allocates nothing.  No counterpart in the reference.
  * Same values as hapx_all_reduce on a local (single-device) communicator of `world` virtual
  * ranks, but without a communicator: all scratch (control blocks, staged inputs, reduced
  * slices) is a 16 MiB device array built into the library, so the call performs no cudaMalloc /
- * cudaFree and needs none to have happened.  For hosts that cannot allocate when the
+ * cudaFree.  The array is part of the library's device code: the driver reserves it when it loads
+ * that code on a device, which with lazy loading is the FIRST call on the device - make one warm-up
+ * call per device while memory is still available; only from then on is nothing reserved any more.
+ * For hosts that cannot allocate when the
  * collective is due (all device memory already owned by another allocator, or a thread that
  * must not take cudaMalloc's device-wide synchronisation).
  * dst[r], src[r]: n elements each, r = 0..world-1, src 16-byte aligned or not (inputs are
@@ -212,9 +259,14 @@ int hapx_attention_backward(void* dqkv, void* dscores_ws, void* ds_ws, const voi
  * slice = ceil(n/world) rounded up to 16 bytes (about 460 000 float32 elements at world 8);
  * beyond that the call returns HAPX_ERR_STAGING.
  * The first call on a device resolves the array's device address; make it outside any stream
- * capture.  Calls share the array: calls whose kernels overlap on the GPU race. */
+ * capture.  Calls share the array: calls whose kernels overlap on the GPU race.
+ * A bounded wait inside the kernels that runs out leaves the outputs unwritten and a status word in
+ * the array, which stays there until hapx_local_all_reduce_noalloc_status reads it. */
 int hapx_local_all_reduce_noalloc(int world, void* const* dst, const void* const* src, int in_dtype, int out_dtype,
                                   double scale, int64_t n, hapx_stream stream);
+/* Synchronises the current device and reports (then clears) a wait that ran out in an earlier
+ * hapx_local_all_reduce_noalloc on it: 0 or HAPX_ERR_PEER_TIMEOUT.  No counterpart in the reference. */
+int hapx_local_all_reduce_noalloc_status(void);
 
 /* ---- step tail: gradient clipping + Adam over the local parameter shards ----------
  * Replaces torch.nn.utils.clip_grad_norm_(dmodel.parameters(), 0.5) and optimizer.step() of

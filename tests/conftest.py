@@ -23,6 +23,10 @@ def _build_native():
 
 _build_native()
 
+# Device-side waits on peers default to ten minutes (a late peer is not a dead one); a test that gets a
+# collective wrong should fail in seconds instead.
+os.environ.setdefault("HAPX_TIMEOUT_MS", "20000")
+
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); deselect with -m 'not gpu'")

@@ -1,0 +1,90 @@
+"""The dropout kernel (``F.dropout`` of the synthesized programs, ``hap.rs:1446-1464``) on the GPU.
+
+The random mask cannot match torch's generator, so parity is checked GIVEN the mask: the library
+exports the keep mask a call draws, and the output must equal ``x * mask / (1 - p)`` (rounded once to
+the tensor's dtype) bit for bit; the backward pass must use the same mask; the keep rate must be
+1 - p within sampling error; a new iteration must draw a new mask."""
+import pytest
+import torch
+
+import hap_b200
+from hap_b200 import dropout as D
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n", [1, 7, 8, 4099, 1 << 20])
+def test_output_equals_masked_input(dtype, n):
+    D.manual_seed(1234, DEV)
+    D.advance(DEV)
+    p = 0.1
+    x = torch.randn(n, generator=torch.Generator().manual_seed(n)).to(dtype).to(DEV).requires_grad_(True)
+    y = D.dropout(x, p)
+    call_id = D._next_call_id                       # the id this call took
+    mask = D.keep_mask(n, p, call_id, DEV).bool()
+    want = torch.where(mask, (x.detach().float() * (1.0 / (1.0 - p))), torch.zeros((), device=DEV)).to(dtype)
+    assert torch.equal(y.detach(), want)
+    g = torch.randn(n, generator=torch.Generator().manual_seed(n + 1)).to(dtype).to(DEV)
+    y.backward(g)
+    want_g = torch.where(mask, (g.float() * (1.0 / (1.0 - p))), torch.zeros((), device=DEV)).to(dtype)
+    assert torch.equal(x.grad, want_g)
+
+
+def test_keep_rate_and_fresh_masks_per_iteration_and_site():
+    D.manual_seed(7, DEV)
+    n, p = 1 << 22, 0.1
+    D.advance(DEV)
+    a = D.keep_mask(n, p, 1, DEV)
+    b = D.keep_mask(n, p, 2, DEV)            # another site in the same iteration
+    assert torch.equal(a, D.keep_mask(n, p, 1, DEV))   # the same site again: the same mask
+    D.advance(DEV)
+    c = D.keep_mask(n, p, 1, DEV)            # the same site in the next iteration
+    for m in (a, b, c):
+        rate = float(m.float().mean())
+        assert abs(rate - (1 - p)) < 5 * (p * (1 - p) / n) ** 0.5 + 1e-5, rate     # 5 sigma + threshold rounding
+    for u, v in ((a, b), (a, c), (b, c)):
+        agree = float((u == v).float().mean())
+        assert abs(agree - ((1 - p) ** 2 + p ** 2)) < 2e-3, agree                    # independent masks
+    D.manual_seed(7, DEV)
+    D.advance(DEV)
+    assert torch.equal(a, D.keep_mask(n, p, 1, DEV))   # reseeding reproduces the sequence
+
+
+def test_graph_replay_draws_new_masks():
+    D.manual_seed(99, DEV)
+    x = torch.ones(4096, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty_like(x)
+
+    def step():
+        D.advance(DEV)
+        out.copy_(D.dropout(x, 0.5))
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    seen = []
+    for _ in range(3):
+        graph.replay()
+        torch.cuda.synchronize()
+        seen.append(out.clone())
+    assert not torch.equal(seen[0], seen[1]) and not torch.equal(seen[1], seen[2])
+
+
+def test_eval_mode_and_p_zero_are_the_identity_and_bad_inputs_raise():
+    x = torch.randn(64, device=DEV)
+    assert D.dropout(x, 0.3, training=False) is x
+    assert D.dropout(x, 0.0) is x
+    with pytest.raises(ValueError):
+        D.dropout(x, 1.0)
+    with pytest.raises(RuntimeError):
+        D.dropout(x.cpu(), 0.1)
+    with pytest.raises(TypeError):
+        D.dropout(x.half(), 0.1)

@@ -17,14 +17,15 @@ def test_targets_are_swapped_and_the_loss_pair_is_folded():
     from hap_b200 import fxpass
     from hap_b200 import plan as P
     model = C.lm_model()
-    graph = P.emit_lm(copy.deepcopy(model), "dp_zero", C.RATIOS, 0, C.LM_BATCH, C.lm_cpu_namespace())   # torch's functions
+    graph = P.emit_lm(copy.deepcopy(model), "dp_zero", C.RATIOS, 0, C.LM_BATCH, C.lm_cpu_namespace(), dropout_p=0.1)   # torch's functions
     before = _names(graph)
     assert "log_softmax" in before and "nll_loss" in before
     changed = fxpass.retarget_tensor_ops(graph)
     nl = C.LM_SMALL["nlayers"]
-    assert changed == {"linear": 2 * nl + 1, "multi_head_attention_forward": nl, "einsum": 0, "layer_norm": 2 * nl + 1, "loss": 1}
+    assert changed == {"linear": 2 * nl + 1, "multi_head_attention_forward": nl, "einsum": 0, "layer_norm": 2 * nl + 1, "dropout": 3 * nl, "loss": 1}
     after = [n for n in graph.nodes if n.op == "call_function"]
-    assert not any(n.target in (F.linear, F.layer_norm, F.multi_head_attention_forward, F.nll_loss, F.log_softmax) for n in after)
+    assert not any(n.target in (F.linear, F.layer_norm, F.multi_head_attention_forward, F.nll_loss, F.log_softmax, F.dropout) for n in after)
+    assert all(n.kwargs["dropout_p"] == 0.1 for n in after if n.target is hap_b200.attention.multi_head_attention_forward)
     assert sum(n.target is hap_b200.nll_log_softmax_sum for n in after) == 1
     assert not any(n.op == "call_method" and n.target == "float" for n in graph.nodes)
     # collectives are left alone (they belong to the other pass)

@@ -76,6 +76,43 @@ def test_backward_matches_oracle(m, n, k):
     close(bd.grad, db, "bias grad")
 
 
+# The per-GPU GEMMs of the Transformer-LM configuration at full size (8192 tokens): too large for a
+# full float64 product on the CPU in seconds, so the oracle is evaluated on a seeded sample of rows
+# and columns of each result (the whole contraction length for every sampled entry).
+FULL_SHAPES = [(8192, 33280, 768),     # vocabulary projection: its input gradient takes the 520-slice split-K path
+               (8192, 768, 768), (8192, 3072, 768), (8192, 768, 3072), (8192, 2304, 768)]
+
+
+def _sample(extent, count, seed):
+    g = torch.Generator().manual_seed(seed)
+    idx = torch.randperm(extent, generator=g)[:min(count, extent)].sort().values
+    # always include the edges of the first / last tile
+    return torch.unique(torch.cat([idx, torch.tensor([0, extent - 1, min(extent - 1, 255), min(extent - 1, 256)])]))
+
+
+@pytest.mark.parametrize("m,n,k", FULL_SHAPES)
+def test_full_size_lm_gemms_on_sampled_entries(m, n, k):
+    x, w, b = gen((m, k), 21), gen((n, k), 22, k ** -0.5), gen((n,), 23)
+    g = gen((m, n), 24)
+    xd, wd, bd = (t.to(DEV).requires_grad_(True) for t in (x, w, b))
+    y = hap_b200.linear(xd, wd, bd)
+    y.backward(g.to(DEV))
+    L.gemm_status()
+    rows, cols, ks = _sample(m, 192, 31), _sample(n, 384, 32), _sample(k, 256, 33)
+    xs, ws = x.double(), w.double()
+    g_rows, g_cols = g[rows].double(), g[:, cols].double()     # slices first: the full matrix in float64 is 2 GB
+    # forward: y[rows, cols]
+    want = xs[rows] @ ws[cols].t() + b.double()[cols]
+    close(y.detach()[rows.to(DEV)][:, cols.to(DEV)], want, "forward (sampled)")
+    # dgrad: dx[rows, ks] = g[rows, :] @ w[:, ks]
+    want = g_rows @ ws[:, ks]
+    close(xd.grad[rows.to(DEV)][:, ks.to(DEV)], want, "dgrad (sampled)")
+    # wgrad: dw[cols, ks] = g[:, cols]^T @ x[:, ks]
+    want = g_cols.t() @ xs[:, ks]
+    close(wd.grad[cols.to(DEV)][:, ks.to(DEV)], want, "wgrad (sampled)")
+    close(bd.grad[cols.to(DEV)], g_cols.sum(0), "bias grad (sampled)")
+
+
 def test_leading_dims_are_flattened():
     x, w = gen((4, 50, 64), 11), gen((96, 64), 12)
     xd, wd = x.to(DEV).requires_grad_(True), w.to(DEV).requires_grad_(True)

@@ -120,7 +120,8 @@ def _spmd_worker(rank, world, store):
     import hap_b200
     from hap_b200 import collectives as col
     from hap_b200 import plan as P
-    from hap_b200.spmd import LockstepWorld, ProcessWorker
+    from hap_b200.spmd import ProcessWorker
+    from oracle.cpu_executors import CpuLockstepWorld
     from oracle.lockstep_backend import OracleCollectives
     from tests import spmd_common as C
     torch.cuda.set_device(rank)
@@ -136,7 +137,7 @@ def _spmd_worker(rank, world, store):
     for plan in ("dp", "tp"):
         model, dims = C.reference_model()
         x, y = C.batch(dims)
-        cpu = LockstepWorld(C.rank_modules(model, plan, C.cpu_namespace(), world=world), OracleCollectives())
+        cpu = CpuLockstepWorld(C.rank_modules(model, plan, C.cpu_namespace(), world=world), OracleCollectives())
         want = [float(cpu.step([(x, y)] * world)) for _ in range(2)]
         m = copy.deepcopy(model).to(dev)
         worker = ProcessWorker(torch.fx.GraphModule(m, P.emit_mlp(m, plan, ratios, rank, C.BATCH)), reduce_loss=reduce)
@@ -148,7 +149,7 @@ def _spmd_worker(rank, world, store):
     # bf16 Transformer LM, ZeRO-style sharded weights
     model = C.lm_model(torch.bfloat16)
     tok, tgt = C.lm_batch()
-    cpu = LockstepWorld(C.lm_rank_modules(model, "dp_zero", C.lm_cpu_namespace(), world=world), OracleCollectives())
+    cpu = CpuLockstepWorld(C.lm_rank_modules(model, "dp_zero", C.lm_cpu_namespace(), world=world), OracleCollectives())
     want = float(cpu.step([(tok, tgt)] * world))
     m = copy.deepcopy(model).to(dev)
     worker = ProcessWorker(torch.fx.GraphModule(m, P.emit_lm(m, "dp_zero", ratios, rank, C.LM_BATCH)), reduce_loss=reduce)

@@ -10,7 +10,7 @@ import pytest
 import torch
 import torch.multiprocessing as mp
 
-from hap_b200.spmd import LockstepWorld, ProcessWorker
+from oracle.cpu_executors import CpuLockstepWorld as LockstepWorld, CpuProcessWorker as ProcessWorker
 from oracle.lockstep_backend import OracleCollectives
 from tests import spmd_common as C
 

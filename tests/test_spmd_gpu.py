@@ -9,6 +9,7 @@ import torch
 
 import hap_b200
 from hap_b200.spmd import LockstepWorld
+from oracle.cpu_executors import CpuLockstepWorld
 from oracle.lockstep_backend import OracleCollectives
 from tests import spmd_common as C
 
@@ -35,7 +36,7 @@ def test_training_step_matches_cpu_replay(plan, dtype, tol):
     x, y = C.batch(dims, dtype)
     # the CPU replay runs in the same dtype, so both sides round at the same places and differ only
     # in accumulation order
-    cpu = LockstepWorld(C.rank_modules(model, plan, C.cpu_namespace()), OracleCollectives())
+    cpu = CpuLockstepWorld(C.rank_modules(model, plan, C.cpu_namespace()), OracleCollectives())
     comm = hap_b200.local_comm(2, DEV, stage_bytes=64 << 20, heap_bytes=96 << 20)
     try:
         gpu = LockstepWorld(C.rank_modules(model.to(dtype), plan, hap_b200.plan.default_namespace(), device=DEV),
@@ -84,7 +85,7 @@ def test_language_model_step_matches_cpu_replay(plan):
     dtype = torch.bfloat16
     model = C.lm_model(dtype)
     tok, tgt = C.lm_batch()
-    cpu = LockstepWorld(C.lm_rank_modules(model, plan, C.lm_cpu_namespace()), OracleCollectives())
+    cpu = CpuLockstepWorld(C.lm_rank_modules(model, plan, C.lm_cpu_namespace()), OracleCollectives())
     comm = hap_b200.local_comm(2, DEV, stage_bytes=16 << 20, heap_bytes=32 << 20)
     try:
         gpu = LockstepWorld(C.lm_rank_modules(model, plan, hap_b200.plan.default_namespace(), device=DEV),
@@ -115,7 +116,7 @@ def test_vit_step_matches_cpu_replay(plan):
     r4 = [.3, .25, .2, .25]
     model = C.vit_model(dtype)
     img, lab = C.vit_batch(dtype)
-    cpu = LockstepWorld(C.vit_rank_modules(model, plan, C.lm_cpu_namespace(), world=4, ratios=r4), OracleCollectives())
+    cpu = CpuLockstepWorld(C.vit_rank_modules(model, plan, C.lm_cpu_namespace(), world=4, ratios=r4), OracleCollectives())
     comm = hap_b200.local_comm(4, DEV, stage_bytes=16 << 20, heap_bytes=32 << 20)
     try:
         gpu = LockstepWorld(C.vit_rank_modules(model, plan, hap_b200.plan.default_namespace(), world=4, device=DEV, ratios=r4),
@@ -210,7 +211,7 @@ def test_language_model_on_eight_virtual_ranks_with_empty_shards():
             mods.append(torch.fx.GraphModule(m, P.emit_lm(m, "dp_zero", r8, r, C.LM_BATCH, ns)))
         return mods
 
-    cpu = LockstepWorld(modules(C.lm_cpu_namespace(), "cpu"), OracleCollectives())
+    cpu = CpuLockstepWorld(modules(C.lm_cpu_namespace(), "cpu"), OracleCollectives())
     comm = hap_b200.local_comm(8, DEV, stage_bytes=8 << 20, heap_bytes=16 << 20)
     try:
         gpu = LockstepWorld(modules(hap_b200.plan.default_namespace(), DEV), hap_b200.LocalCollectives(comm))
@@ -229,7 +230,7 @@ def test_expert_parallel_moe_step_matches_cpu_replay():
     dtype = torch.bfloat16
     model = C.moe_model(dtype)
     tok, tgt = C.lm_batch()
-    cpu = LockstepWorld(C.moe_rank_modules(model, C.moe_cpu_namespace()), OracleCollectives())
+    cpu = CpuLockstepWorld(C.moe_rank_modules(model, C.moe_cpu_namespace()), OracleCollectives())
     comm = hap_b200.local_comm(2, DEV, stage_bytes=16 << 20, heap_bytes=32 << 20)
     try:
         gpu = LockstepWorld(C.moe_rank_modules(model, hap_b200.plan.default_namespace(), device=DEV), hap_b200.LocalCollectives(comm))
@@ -248,6 +249,74 @@ def test_expert_parallel_moe_step_matches_cpu_replay():
                 # The contractions themselves are held to 1e-2 in test_einsum_gpu.py; here a flip must be survivable
                 tol = 0.5
                 assert float(d.norm()) <= tol * float(pw.grad.float().norm()) + 1e-2, (r, name, float(d.norm()), float(pw.grad.float().norm()))
+        comm.check()
+        hap_b200.linear_ops.gemm_status()
+    finally:
+        comm.destroy()
+
+
+# ---- one step of each program at the configurations' full layer widths ----------------------------------
+# One layer instead of 12 / 12 / 8 and batch 8, but every tensor has the width the benchmark configuration
+# gives it (d_model, FFN, vocabulary, sequence length, image and patch size, expert count and capacity), so
+# the vocabulary projection with its split-K input gradient, the 197-token attention and the 32-expert
+# einsums run inside a real step.  The CPU side replays the same fx programs in float32 on the
+# bf16-rounded parameters (torch's CPU kernels; seconds).
+def _full_width_case(kind):
+    import copy
+    from hap_b200 import plan as P
+    torch.manual_seed(39)
+    g = torch.Generator().manual_seed(2024)
+    B = 8
+    if kind == "lm":
+        model = P.TransformerLM(nlayers=1)
+        inputs = (torch.randint(0, 33278, (B, 256), generator=g), torch.randint(0, 33278, (B, 256), generator=g))
+        emit = lambda m, r, ns: P.emit_lm(m, "dp_zero", C.RATIOS, r, B, ns)
+        cpu_ns = C.lm_cpu_namespace()
+    elif kind == "vit":
+        model = P.ViT(nlayers=1)
+        inputs = (torch.randn(B, 3, 224, 224, generator=g), torch.randint(0, 1000, (B,), generator=g))
+        emit = lambda m, r, ns: P.emit_vit(m, "dp_zero", C.RATIOS, r, B, ns)
+        cpu_ns = C.lm_cpu_namespace()
+    else:
+        model = P.MoETransformerLM(nlayers=1)
+        inputs = (torch.randint(0, 33278, (B, 512), generator=g), torch.randint(0, 33278, (B, 512), generator=g))
+        emit = lambda m, r, ns: P.emit_moe(m, C.RATIOS, r, B, ns)
+        cpu_ns = C.moe_cpu_namespace()
+    model = model.to(torch.bfloat16)
+
+    def modules(ns, device, dtype):
+        mods = []
+        for r in range(2):
+            m = copy.deepcopy(model).to(device=device, dtype=dtype)
+            mods.append(torch.fx.GraphModule(m, emit(m, r, ns)))
+        return mods
+
+    return modules, cpu_ns, inputs
+
+
+@pytest.mark.parametrize("kind", ["lm", "vit", "moe"])
+def test_full_width_single_layer_step_matches_cpu_replay(kind):
+    modules, cpu_ns, inputs = _full_width_case(kind)
+    cpu = CpuLockstepWorld(modules(cpu_ns, "cpu", torch.float32), OracleCollectives())
+    cpu_in = tuple(t.float() if t.is_floating_point() else t for t in inputs)
+    gpu_in = tuple((t.to(torch.bfloat16) if t.is_floating_point() else t).to(DEV) for t in inputs)
+    comm = hap_b200.local_comm(2, DEV, stage_bytes=128 << 20, heap_bytes=192 << 20)
+    try:
+        gpu = LockstepWorld(modules(hap_b200.plan.default_namespace(), DEV, torch.bfloat16), hap_b200.LocalCollectives(comm))
+        want = cpu.forward([cpu_in] * 2)
+        got = gpu.forward([gpu_in] * 2)
+        for r in range(2):
+            assert abs(float(got[r]) - float(want[r])) <= 1e-2 * abs(float(want[r])), (kind, r, float(got[r]), float(want[r]))
+        torch.stack(want).sum().backward()
+        torch.stack(got).sum().backward()
+        # bf16 activations against a float32 replay: whole-tensor agreement of every parameter gradient;
+        # with top-2 routing a flipped token moves the gradients of two experts, hence the looser bound
+        tol = 0.5 if kind == "moe" else 6e-2
+        for r in range(2):
+            for (name, pw), (_, pg) in zip(cpu.modules[r].named_parameters(), gpu.modules[r].named_parameters()):
+                assert pg.grad is not None and pg.grad.shape == pw.grad.shape, name
+                d = (pg.grad.detach().float().cpu() - pw.grad.detach().float())
+                assert float(d.norm()) <= tol * float(pw.grad.float().norm()) + 1e-2, (kind, r, name, float(d.norm()), float(pw.grad.float().norm()))
         comm.check()
         hap_b200.linear_ops.gemm_status()
     finally:
