@@ -58,6 +58,9 @@ SIGNATURES = {
     "hapx_gemm_status": (_int, []),
     "hapx_attention_forward": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp]),
     "hapx_attention_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
+    "hapx_attention_fused_forward": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _dbl, _u64, _vp]),
+    "hapx_attention_fused_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _dbl, _u64, _vp]),
+    "hapx_attention_dropout_mask": (_int, [_vp, _i64, _i64, _i64, _dbl, _u64, _vp]),
     "hapx_grad_sqnorm": (_int, [_int, _pp, _pi64, _int, _vp, _int, _vp]),
     "hapx_clip_adam_apply": (_int, [_int, _pp, _pp, _pp, _pp, _pi64, _int, _dbl, _dbl, _dbl, _dbl, _dbl, _dbl, _vp, _int, _vp]),
     "hapx_nll_logsoftmax_forward": (_int, [_vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _vp]),

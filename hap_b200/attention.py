@@ -6,7 +6,10 @@ in_proj_bias=..., out_proj_weight=..., out_proj_bias=..., attn_mask=..., embed_d
 num_heads=H, bias_k=None, bias_v=None, add_zero_attn=False, dropout_p=p)`` on (L, N, E) tensors
 (``hap.rs:1297-1329``); only N is ever sharded (``hap.rs:2903-2926``).  :func:`multi_head_attention_forward`
 takes the same keyword arguments and returns ``(output, None)``; the two projections run on the
-package's linear kernels and the attention core on the batched tensor-core GEMMs plus softmax kernels.
+package's linear kernels.  The attention core runs as one fused tensor-core kernel per direction for
+head dimension 64 (scores, softmax, dropout on the probabilities and the value product stay on the SM;
+backward recomputes them), and on batched GEMMs plus softmax kernels for other head dimensions
+(without dropout).
 """
 from __future__ import annotations
 
@@ -15,8 +18,11 @@ from typing import Optional
 import torch
 
 from . import _native as N
+from . import dropout as _dropout
 from .comm import _on_device, _stream
 from .linear import linear
+
+FUSED_HEAD_DIM = 64
 
 
 def _classify_mask(mask: Optional[torch.Tensor], L: int):
@@ -72,8 +78,52 @@ class _Attention(torch.autograd.Function):
         return dqkv, None, None, None
 
 
-def attention(qkv: torch.Tensor, num_heads: int, attn_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """softmax(Q K^T / sqrt(d) + mask) V for packed ``qkv`` of shape (L, N, 3E), bfloat16, on CUDA."""
+class _FusedAttention(torch.autograd.Function):
+    """The fused kernels (head dimension 64): saves qkv, the output and one float per row."""
+
+    @staticmethod
+    def forward(ctx, qkv, num_heads, causal, mask, dropout_p, call_id):
+        L, n, e3 = qkv.shape
+        E = e3 // 3
+        qkv = qkv.contiguous()
+        out = torch.empty((L, n, E), dtype=torch.bfloat16, device=qkv.device)
+        lse2 = torch.empty((n * num_heads, L), dtype=torch.float32, device=qkv.device)
+        with _on_device(qkv.device):
+            N.check(N.lib.hapx_attention_fused_forward(out.data_ptr(), lse2.data_ptr(), qkv.data_ptr(), L, n, num_heads, FUSED_HEAD_DIM,
+                                                       int(causal), mask.data_ptr() if mask is not None else None, float(dropout_p),
+                                                       int(call_id), _stream(qkv.device)))
+        ctx.save_for_backward(qkv, out, lse2, mask)
+        ctx.meta = (L, n, num_heads, int(causal), float(dropout_p), int(call_id))
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse2, mask = ctx.saved_tensors
+        L, n, H, causal, dropout_p, call_id = ctx.meta
+        dout = dout.contiguous()
+        dqkv = torch.empty_like(qkv)
+        delta = torch.empty_like(lse2)
+        with _on_device(qkv.device):
+            N.check(N.lib.hapx_attention_fused_backward(dqkv.data_ptr(), delta.data_ptr(), dout.data_ptr(), out.data_ptr(), lse2.data_ptr(),
+                                                        qkv.data_ptr(), L, n, H, FUSED_HEAD_DIM, causal,
+                                                        mask.data_ptr() if mask is not None else None, dropout_p, call_id,
+                                                        _stream(qkv.device)))
+        return dqkv, None, None, None, None, None
+
+
+def attention_keep_mask(L: int, n: int, num_heads: int, dropout_p: float, call_id: int, device=None) -> torch.Tensor:
+    """The keep mask (uint8, (n * num_heads, L, L)) the fused kernels draw for attention call ``call_id``
+    in the current iteration."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    mask = torch.empty((n * num_heads, L, L), dtype=torch.uint8, device=device)
+    with _on_device(device):
+        N.check(N.lib.hapx_attention_dropout_mask(mask.data_ptr(), L, n, num_heads, float(dropout_p), int(call_id), _stream(device)))
+    return mask
+
+
+def attention(qkv: torch.Tensor, num_heads: int, attn_mask: Optional[torch.Tensor] = None, dropout_p: float = 0.0) -> torch.Tensor:
+    """softmax(Q K^T / sqrt(d) + mask) V for packed ``qkv`` of shape (L, N, 3E), bfloat16, on CUDA, with
+    dropout on the probabilities when ``dropout_p`` > 0."""
     if not qkv.is_cuda:
         raise RuntimeError(f"attention: hap_b200 has no CPU path; tensor is on {qkv.device}")
     if qkv.dtype != torch.bfloat16:
@@ -81,6 +131,13 @@ def attention(qkv: torch.Tensor, num_heads: int, attn_mask: Optional[torch.Tenso
     if qkv.dim() != 3 or qkv.shape[2] % (3 * num_heads):
         raise ValueError("attention: qkv must be (L, N, 3 * num_heads * head_dim)")
     causal, mask = _classify_mask(attn_mask, qkv.shape[0])
+    if not 0.0 <= dropout_p < 1.0:
+        raise ValueError(f"attention: dropout_p must be in [0, 1), got {dropout_p}")
+    if qkv.shape[2] // (3 * num_heads) == FUSED_HEAD_DIM and qkv.shape[1] > 0:
+        call_id = _dropout.new_call_id() if dropout_p > 0.0 else 0
+        return _FusedAttention.apply(qkv, num_heads, causal, mask, dropout_p, call_id)
+    if dropout_p > 0.0:
+        raise NotImplementedError("attention: dropout on the probabilities needs head dimension 64 (the fused kernels)")
     return _Attention.apply(qkv, num_heads, causal, mask)
 
 
@@ -94,10 +151,8 @@ def multi_head_attention_forward(query, key, value, embed_dim_to_check, num_head
         raise NotImplementedError("attention: only self-attention (query is key is value) is emitted by the planner")
     if bias_k is not None or bias_v is not None or add_zero_attn or key_padding_mask is not None or use_separate_proj_weight:
         raise NotImplementedError("attention: bias_k / bias_v / add_zero_attn / key_padding_mask / separate weights are not emitted by the planner")
-    if dropout_p and training:
-        raise NotImplementedError("attention: dropout on the attention probabilities is not built yet (use dropout_p=0)")
     if query.shape[-1] != embed_dim_to_check:
         raise ValueError("attention: embedding dimension mismatch")
     qkv = linear(query, in_proj_weight, in_proj_bias)
-    out = attention(qkv, num_heads, attn_mask)
+    out = attention(qkv, num_heads, attn_mask, float(dropout_p) if training else 0.0)
     return linear(out, out_proj_weight, out_proj_bias), None

@@ -27,6 +27,7 @@
 #include <vector>
 
 #include "hapx_internal.h"
+#include "hapx_tc.h"
 
 namespace hapx {
 namespace gemm {
@@ -36,7 +37,6 @@ constexpr int BK = 64;                 // bf16 elements: one 128-byte swizzle ro
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
 constexpr int kEpilogueThreads = 128;
-constexpr unsigned long long kWaitNs = 2000000000ull;  // upper bound of any single wait
 
 enum Epilogue { EPI_NONE = 0, EPI_RELU = 1, EPI_GELU = 2, EPI_SIGMOID = 3 };
 
@@ -67,133 +67,9 @@ struct Params {
   const unsigned* sm_mask_is_causal; // device word: non-zero when sm_mask is exactly the causal mask (then it is not read)
 };
 
-// ---- PTX wrappers -------------------------------------------------------------------------------
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
-  unsigned ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait: false when the phase did not complete within kWaitNs.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_ns();
-  for (unsigned it = 0; it < 0x7fffffffu; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 63u && global_ns() - t0 > kWaitNs) return false;
-  }
-  return false;
-}
-__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-// All tensor maps are 4-D: (contiguous index, row, batch_in, batch_out).
-__device__ __forceinline__ void tma_load_4d(unsigned dst, const CUtensorMap* map, int x, int y, int bi, int bo, unsigned bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
-      "l"(map), "r"(x), "r"(y), "r"(bi), "r"(bo), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
-  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(unsigned dst_smem, unsigned cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void umma_bf16(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned idesc,
-                                          unsigned accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Arrive on an mbarrier once every tcgen05.mma issued so far by this thread has completed.
-__device__ __forceinline__ void umma_commit(unsigned bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_32x32(unsigned taddr, unsigned (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-// AND-reduction of a predicate over the 128 epilogue threads (named barrier 2), so that they
-// take the same branch after a bounded wait.
-__device__ __forceinline__ bool epilogue_all(bool mine) {
-  unsigned out;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.b32 p, %1, 0;\n\t"
-      "bar.red.and.pred q, 2, 128, p;\n\t"
-      "selp.u32 %0, 1, 0, q;\n\t}"
-      : "=r"(out)
-      : "r"((unsigned)mine)
-      : "memory");
-  return out != 0;
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor (version 1 = Blackwell, 128-byte swizzle).  Offsets in bytes.
-__device__ __forceinline__ unsigned long long make_desc(unsigned smem_addr, unsigned lbo_bytes, unsigned sbo_bytes) {
-  unsigned long long d = 0;
-  d |= (unsigned long long)((smem_addr & 0x3ffffu) >> 4);
-  d |= (unsigned long long)((lbo_bytes >> 4) & 0x3fffu) << 16;
-  d |= (unsigned long long)((sbo_bytes >> 4) & 0x3fffu) << 32;
-  d |= 1ull << 46;   // descriptor version
-  d |= 2ull << 61;   // SWIZZLE_128B
-  return d;
-}
-
+using namespace tc;   // PTX wrappers (hapx_tc.h)
 
 // ---- epilogue -------------------------------------------------------------------------------------
-__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, unsigned src_smem, int x, int y, int bi, int bo) {
-  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map), "r"(src_smem), "r"(x),
-               "r"(y), "r"(bi), "r"(bo)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
 constexpr unsigned kStoreTileBytes = 128 * 128;   // staging: 128 rows x 128 bytes (64 bf16 or 32 fp32 columns), two of them
 constexpr unsigned kWarpTileBytes = 32 * 128;     // the 32 rows one epilogue warp owns
 
@@ -962,7 +838,7 @@ static int make_out_map(CUtensorMap* map, int* ok, void* ptr, long long cols, lo
 
 // bf16 operand map.  K-major operand [rows][contraction contiguous]: box {64, tile rows};
 // MN-major operand [contraction rows][M or N contiguous]: box {64, 64}.
-static int make_map(CUtensorMap* map, const Operand& op, long long mn_extent, long long kc, int tile_rows, int batch_in, int batch_out) {
+int make_map(CUtensorMap* map, const Operand& op, long long mn_extent, long long kc, int tile_rows, int batch_in, int batch_out) {
   if (!strides_ok(op.ptr, 2, op.ld, batch_in, op.s_in, batch_out, op.s_out))
     return fail(HAPX_ERR_EXTENT, "gemm: operand base, row pitch and batch strides must be multiples of 16 bytes (8 bf16 elements)");
   if (op.mn_major)
@@ -1182,6 +1058,15 @@ static int launch2(const Operand& A, const Operand& B, const Operand& Dop, Param
     HAPX_CUDA(cudaGetLastError());
     count_launch();
   }
+  return HAPX_OK;
+}
+
+// The device word the tensor-core kernels report a timed-out wait into (read by hapx_gemm_status).
+int error_word(unsigned** out, int* sm_count) {
+  DeviceState* dev = nullptr;
+  if (int e = device_state(&dev)) return e;
+  *out = dev->error;
+  if (sm_count) *sm_count = dev->sm_count;
   return HAPX_OK;
 }
 

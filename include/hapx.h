@@ -217,12 +217,31 @@ int hapx_gemm_status(void);
  *   scores_ws  [N*H, L, Lp] fp32 scratch;   ds_ws [N*H, L, Lp] bf16 scratch (backward)
  * forward : out = softmax(Q K^T / sqrt(D) + mask) V.  causal != 0 masks keys after the query
  *           (the -inf upper-triangular mask of models.py:72); mask = optional additive [L, L] fp32.
- * backward: dqkv [L, N, 3E] from dout [L, N, E].  Attention dropout is not applied (p = 0).
+ * backward: dqkv [L, N, 3E] from dout [L, N, E].  No dropout on this path (head dimensions other
+ * than 64 without dropout; for D = 64 see the fused entry points below).
  * Limits: L <= 1024, D % 8 == 0. */
 int hapx_attention_forward(void* out, void* probs, void* scores_ws, const void* qkv, int64_t L, int64_t N, int64_t H,
                            int64_t D, int causal, const float* mask, hapx_stream stream);
 int hapx_attention_backward(void* dqkv, void* dscores_ws, void* ds_ws, const void* dout, const void* probs,
                             const void* qkv, int64_t L, int64_t N, int64_t H, int64_t D, hapx_stream stream);
+
+/* Fused form of the same attention core for head dimension D = 64 (every benchmark configuration):
+ * one kernel computes S = Q K^T in tensor memory, the online softmax, the dropout on the
+ * probabilities (dropout_p of the attention node, hap.rs:1257, 1307, 1319; 0.1 in config.py:33) and
+ * O = P V, so nothing of size L x L is written to memory; only lse2 [N*H, L] fp32 (the rows'
+ * log-sum-exp in the log2 domain) is kept for backward.  backward recomputes the probabilities per
+ * tile and regenerates the dropout mask from (generator state, call_id) - see the dropout section -
+ * so it must run in the same iteration (before the next hapx_rng_advance) with the same call_id,
+ * causal flag and mask.  delta_ws: N*H*L floats of scratch.  out is the forward's output.
+ * Deterministic: no atomics, every output element is written by one thread block.
+ * hapx_attention_dropout_mask writes the keep mask [N*H, L, L] as bytes (for tests). */
+int hapx_attention_fused_forward(void* out, float* lse2, const void* qkv, int64_t L, int64_t N, int64_t H, int64_t D,
+                                 int causal, const float* mask, double dropout_p, uint64_t call_id, hapx_stream stream);
+int hapx_attention_fused_backward(void* dqkv, float* delta_ws, const void* dout, const void* out, const float* lse2,
+                                  const void* qkv, int64_t L, int64_t N, int64_t H, int64_t D, int causal, const float* mask,
+                                  double dropout_p, uint64_t call_id, hapx_stream stream);
+int hapx_attention_dropout_mask(unsigned char* mask, int64_t L, int64_t N, int64_t H, double dropout_p, uint64_t call_id,
+                                hapx_stream stream);
 
 /* ---- dropout ---------------------------------------------------------------------------------
  * Replaces the torch.nn.functional.dropout(input, p) nodes the planner emits (hap.rs:1446-1464;

@@ -16,8 +16,10 @@ import math
 import torch
 
 
-def attention_core(qkv: torch.Tensor, num_heads: int, mask=None) -> torch.Tensor:
-    """qkv (L, N, 3E) -> (L, N, E) in float64."""
+def attention_core(qkv: torch.Tensor, num_heads: int, mask=None, keep=None, dropout_p: float = 0.0) -> torch.Tensor:
+    """qkv (L, N, 3E) -> (L, N, E) in float64.  ``keep`` (N, H, L, L), 0/1: the dropout mask on the
+    probabilities; kept entries are scaled by 1 / (1 - dropout_p) as ``F.dropout`` does inside
+    ``multi_head_attention_forward``."""
     L, n, e3 = qkv.shape
     E = e3 // 3
     d = E // num_heads
@@ -26,6 +28,8 @@ def attention_core(qkv: torch.Tensor, num_heads: int, mask=None) -> torch.Tensor
     if mask is not None:
         s = s + mask.double()
     p = torch.softmax(s, dim=-1)
+    if keep is not None:
+        p = p * keep.double() / (1.0 - dropout_p)
     return (p @ v).permute(2, 0, 1, 3).reshape(L, n, E)
 
 

@@ -68,8 +68,15 @@ def test_multi_head_attention_forward_drop_in():
                                                   out_proj_bias=out_b.to(DEV), attn_mask=mask.to(DEV))
     assert weights is None
     close(got, want, "mha", tol=2e-2)
+    # head dimension 64 has the fused kernels with dropout; other head dimensions refuse it
+    dropped, _ = A.multi_head_attention_forward(xd, xd, xd, E, H, in_w.to(DEV), in_b.to(DEV), dropout_p=0.1, out_proj_weight=out_w.to(DEV),
+                                                out_proj_bias=out_b.to(DEV))
+    assert dropped.shape == got.shape and not torch.equal(dropped, got)
+    same, _ = A.multi_head_attention_forward(xd, xd, xd, E, H, in_w.to(DEV), in_b.to(DEV), dropout_p=0.1, out_proj_weight=out_w.to(DEV),
+                                             out_proj_bias=out_b.to(DEV), training=False, attn_mask=mask.to(DEV))
+    assert torch.equal(same, got)
     with pytest.raises(NotImplementedError):
-        A.multi_head_attention_forward(xd, xd, xd, E, H, in_w.to(DEV), in_b.to(DEV), dropout_p=0.1, out_proj_weight=out_w.to(DEV),
+        A.multi_head_attention_forward(xd, xd, xd, E, 8, in_w.to(DEV), in_b.to(DEV), dropout_p=0.1, out_proj_weight=out_w.to(DEV),
                                        out_proj_bias=out_b.to(DEV))
 
 
