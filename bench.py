@@ -1092,6 +1092,14 @@ def run_ops(args):
             qkv.grad = None
             A.attention(qkv, H, mask).backward(go)
 
+        def ours_dropout():
+            qkv.grad = None
+            A.attention(qkv, H, mask, dropout_p=0.1).backward(go)
+
+        def ours_fwd():
+            with torch.no_grad():
+                A.attention(qkv, H, mask)
+
         def ref():
             qkv.grad = None
             q, k, v = (t.reshape(L, n * H, D).transpose(0, 1) for t in qkv.split(E, dim=2))
@@ -1099,8 +1107,13 @@ def run_ops(args):
             o.transpose(0, 1).reshape(L, n, E).backward(go)
 
         flops = 3.5 * 4.0 * n * H * L * L * D * (0.5 if causal else 1.0)     # fwd 2 GEMMs + bwd 5 GEMMs (2.5x fwd)
-        t, tr = timeit(ours), timeit(ref)
-        rows.append({"op": name + " fwd+bwd", "shape": f"L={L} N={n} H={H} D={D}", "ms": t, "torch_ms": tr, "tflops": flops / t / 1e9})
+        t, tr = timeit(graphed(ours)), timeit(ref)
+        td, tf = timeit(graphed(ours_dropout)), timeit(graphed(ours_fwd))
+        # bytes that must move: qkv read + out written (forward); qkv, out, dout read + dqkv written (backward)
+        io = (L * n * 3 * E + L * n * E + 2 * L * n * 3 * E + 2 * L * n * E) * 2
+        rows.append({"op": name + " fwd+bwd", "shape": f"L={L} N={n} H={H} D={D}", "ms": t, "torch_ms": tr, "tflops": flops / t / 1e9,
+                     "dropout_0.1_ms": td, "fwd_only_ms": tf, "gbs": io / t / 1e6, "frac_of_hbm_peak": io / t / 1e6 / float(measured_peaks()[0]["hbm_gbs"]),
+                     "eager_ms": timeit(ours)})
     b, s, e, c, d, h = 16, 512, 32, 20, 1024, 4096
     x = torch.randn(b, s, d, device=dev, generator=g).to(torch.bfloat16)
     disp = (torch.rand(b, s, e, c, device=dev, generator=g) < 0.003).to(torch.bfloat16)

@@ -112,6 +112,60 @@ __device__ __forceinline__ void store_row64(__nv_bfloat16* dst, const float (&v)
   }
 }
 
+// ---- per-chunk math (32 columns of one row, all in registers, no branches) ------------------------------
+// PARTIAL: columns after `lim` (relative to the chunk) take no part (causal diagonal, ragged end, rows past L).
+// mrow: optional additive mask row, already offset to the chunk's first column (general masks only).
+template <bool PARTIAL>
+__device__ __forceinline__ float chunk_score(unsigned raw, float scale2, int e, int lim, const float* mrow) {
+  float x = __uint_as_float(raw) * scale2;
+  if (mrow) x = fmaf(mrow[e], kLog2e, x);
+  if (PARTIAL) x = (e <= lim) ? x : -INFINITY;
+  return x;
+}
+template <bool PARTIAL>
+__device__ __forceinline__ float chunk_max(const unsigned (&v)[32], float scale2, int lim, const float* mrow, float mx) {
+  float m0 = mx, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+  for (int e = 0; e < 32; e += 4) {
+    m0 = fmaxf(m0, chunk_score<PARTIAL>(v[e], scale2, e, lim, mrow));
+    m1 = fmaxf(m1, chunk_score<PARTIAL>(v[e + 1], scale2, e + 1, lim, mrow));
+    m2 = fmaxf(m2, chunk_score<PARTIAL>(v[e + 2], scale2, e + 2, lim, mrow));
+    m3 = fmaxf(m3, chunk_score<PARTIAL>(v[e + 3], scale2, e + 3, lim, mrow));
+  }
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+// exp2(score - shift) of the chunk; returns the sum of the (undropped) values.
+template <bool PARTIAL>
+__device__ __forceinline__ float chunk_exp(const unsigned (&v)[32], float scale2, float shift, int lim, const float* mrow, float (&pe)[32]) {
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+  for (int e = 0; e < 32; e += 4) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float x;
+      if (mrow) {
+        x = chunk_score<PARTIAL>(v[e + u], scale2, e + u, lim, mrow) - shift;
+      } else {
+        x = fmaf(__uint_as_float(v[e + u]), scale2, -shift);
+        if (PARTIAL) x = (e + u <= lim) ? x : -INFINITY;
+      }
+      pe[e + u] = ex2(x);
+    }
+    s0 += pe[e]; s1 += pe[e + 1]; s2 += pe[e + 2]; s3 += pe[e + 3];
+  }
+  return (s0 + s1) + (s2 + s3);
+}
+
+__device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const float (&v)[32]) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    uint4 pk;
+    pk.x = pack_bf16(v[8 * g], v[8 * g + 1]); pk.y = pack_bf16(v[8 * g + 2], v[8 * g + 3]);
+    pk.z = pack_bf16(v[8 * g + 4], v[8 * g + 5]); pk.w = pack_bf16(v[8 * g + 6], v[8 * g + 7]);
+    reinterpret_cast<uint4*>(dst)[g] = pk;
+  }
+}
+
 // A ring of 16 KiB tiles filled by TMA in load order; slot and phase follow from the load's number.
 struct Ring {
   unsigned base, full0, empty0;   // shared-memory addresses: slot 0, full barrier 0, empty barrier 0
@@ -275,23 +329,20 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params
         // for the whole warp, by the last key that ANY of its 32 rows may see
         const int wq0 = i * BT + q4 * 32;
         const int wlast = wq0 < p.L ? (causal ? min(wq0 + 31, p.L - 1) : p.L - 1) : -1;
+        // the smallest `last` of the warp's rows decides, for the whole warp, whether a chunk needs per-element limits
+        const int wmin_last = (wq0 + 31 < p.L) ? (causal ? wq0 : p.L - 1) : -1;
         // pass 1 over the scores in tensor memory: the row maximum
         float mx = m;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
-          if (k0 + 32 * c > wlast) break;
+          const int c0 = k0 + 32 * c;
+          if (c0 > wlast) break;
           unsigned v[32];
           tmem_ld_32x32(tS + lane_off + 32u * c, v);
           tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int col = k0 + 32 * c + e;
-            if (col <= last) {
-              float x = __uint_as_float(v[e]) * p.scale2;
-              if (mrow) x = fmaf(mrow[col], kLog2e, x);
-              mx = fmaxf(mx, x);
-            }
-          }
+          const float* mr = mrow ? mrow + c0 : nullptr;
+          if (c0 + 31 > wmin_last) mx = chunk_max<true>(v, p.scale2, last - c0, mr, mx);
+          else mx = chunk_max<false>(v, p.scale2, 31, mr, mx);
         }
         const float m_use = (mx == -INFINITY) ? 0.f : mx;
         const float alpha = (m == -INFINITY) ? 0.f : ex2(m - m_use);
@@ -299,27 +350,22 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params
         float sum = 0.f;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
+          const int c0 = k0 + 32 * c;
           float pr[32];
-          if (k0 + 32 * c > wlast) {
+          if (c0 > wlast) {
 #pragma unroll
             for (int e = 0; e < 32; ++e) pr[e] = 0.f;
           } else {
             unsigned v[32];
             tmem_ld_32x32(tS + lane_off + 32u * c, v);
             tmem_ld_wait();
-            unsigned keep = 0xffffffffu;
-            if (p.drop_threshold) keep = keep32(key, p.drop_threshold, rg0, k0 + 32 * c);
+            const float* mr = mrow ? mrow + c0 : nullptr;
+            if (c0 + 31 > wmin_last) sum += chunk_exp<true>(v, p.scale2, m_use, last - c0, mr, pr);
+            else sum += chunk_exp<false>(v, p.scale2, m_use, 31, mr, pr);
+            if (p.drop_threshold) {
+              const unsigned keep = keep32(key, p.drop_threshold, rg0, c0);
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              const int col = k0 + 32 * c + e;
-              float pe = 0.f;
-              if (col <= last) {
-                float x = __uint_as_float(v[e]) * p.scale2;
-                if (mrow) x = fmaf(mrow[col], kLog2e, x);
-                pe = ex2(x - m_use);
-              }
-              sum += pe;
-              pr[e] = (keep >> e) & 1u ? pe : 0.f;
+              for (int e = 0; e < 32; ++e) pr[e] = (keep >> e) & 1u ? pr[e] : 0.f;
             }
           }
           store_prob_columns(sP_gen, r, c, pr);
@@ -372,10 +418,12 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params
 // Shared memory: 2 outer tiles | 2 stages x 2 inner tiles | Pd | dS.  Tensor memory (512 columns): S [0,128),
 // dPd [128,256), accumulators [256,320) and [320,384).
 constexpr int kBwdStages = 2;
+constexpr int kBwdThreads = 320;            // TMA warp, MMA warp, 8 math warps: two per tensor-memory lane quarter, each
+constexpr int kBwdMath = 256;               // taking half of the columns of its 32 rows (no row reductions are needed here)
 constexpr unsigned kBwdSmem = 1024 + kTileBytes * (2 + 2 * kBwdStages) + 2 * kProbBytes + 256;
 
 template <bool KEY_MAJOR>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attention_backward_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO, const Params p) {
   extern __shared__ unsigned char smem_raw[];
   const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -395,8 +443,8 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap tmQKV, const __gri
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    mbar_init(out_full, 1); mbar_init(out_empty, 1); mbar_init(s_full, 1); mbar_init(s_empty, 128); mbar_init(p_full, 128);
-    mbar_init(p_empty, 1); mbar_init(acc_full, 1); mbar_init(acc_empty, 128);
+    mbar_init(out_full, 1); mbar_init(out_empty, 1); mbar_init(s_full, 1); mbar_init(s_empty, kBwdMath); mbar_init(p_full, kBwdMath);
+    mbar_init(p_empty, 1); mbar_init(acc_full, 1); mbar_init(acc_empty, kBwdMath);
     for (int s = 0; s < kBwdStages; ++s) { mbar_init(in_full0 + 8u * s, 1); mbar_init(in_empty0 + 8u * s, 1); }
     fence_barrier_init();
     prefetch_tensormap(&tmQKV);
@@ -515,7 +563,8 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap tmQKV, const __gri
       if (!ok) atomicCAS(p.error, 0u, 22u);
     }
   } else {
-    const int q4 = warp & 3;
+    const int q4 = warp & 3;                       // tensor-memory lane quarter of this warp
+    const int half = (warp - 2) >> 2;              // which 64 of the tile's 128 columns this warp takes
     const int r = q4 * 32 + lane;
     const unsigned lane_off = (unsigned)(q4 * 32) << 16;
     unsigned n_out = 0, n_in = 0;
@@ -538,14 +587,18 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap tmQKV, const __gri
         const float* mrow = (use_mask && row_ok) ? p.mask + (long long)q * p.L : nullptr;
         const unsigned long long rg0 = ((unsigned long long)bh * (unsigned long long)p.L + (unsigned long long)q) * row_groups;
         const int last = row_ok ? (causal ? min(q, p.L - 1) : p.L - 1) : -1;
-        const int wq0 = i * BT + q4 * 32;          // warp-wide decision for the warp-wide tcgen05.ld (see the forward kernel)
+        // warp-wide decisions for the warp-wide tcgen05.ld (see the forward kernel)
+        const int wq0 = i * BT + q4 * 32;
         const int wlast = wq0 < p.L ? (causal ? min(wq0 + 31, p.L - 1) : p.L - 1) : -1;
+        const int wmin_last = (wq0 + 31 < p.L) ? (causal ? wq0 : p.L - 1) : -1;
         if (!mbar_wait(s_full, n_in & 1u) || !mbar_wait(p_empty, (n_in & 1u) ^ 1u)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = 2 * half + cc;
+          const int c0 = k0 + 32 * c;
           float pd[32], ds[32];
-          if (k0 + 32 * c > wlast) {
+          if (c0 > wlast) {
 #pragma unroll
             for (int e = 0; e < 32; ++e) { pd[e] = 0.f; ds[e] = 0.f; }
           } else {
@@ -553,20 +606,20 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap tmQKV, const __gri
             tmem_ld_32x32(tS + lane_off + 32u * c, sv);
             tmem_ld_32x32(tDP + lane_off + 32u * c, gv);
             tmem_ld_wait();
-            unsigned keep = 0xffffffffu;
-            if (p.drop_threshold) keep = keep32(key, p.drop_threshold, rg0, k0 + 32 * c);
+            const float* mr = mrow ? mrow + c0 : nullptr;
+            if (c0 + 31 > wmin_last) chunk_exp<true>(sv, p.scale2, lse, last - c0, mr, pd);
+            else chunk_exp<false>(sv, p.scale2, lse, 31, mr, pd);
+            if (p.drop_threshold) {
+              const unsigned keep = keep32(key, p.drop_threshold, rg0, c0);
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              const int col = k0 + 32 * c + e;
-              float pe = 0.f;
-              if (col <= last) {
-                float x = __uint_as_float(sv[e]) * p.scale2;
-                if (mrow) x = fmaf(mrow[col], kLog2e, x);
-                pe = ex2(x - lse);
+              for (int e = 0; e < 32; ++e) {
+                const float kd = (keep >> e) & 1u ? p.drop_scale : 0.f;
+                ds[e] = pd[e] * p.scale * fmaf(__uint_as_float(gv[e]), kd, -dl);
+                pd[e] *= kd;
               }
-              const float kd = (keep >> e) & 1u ? p.drop_scale : 0.f;
-              pd[e] = pe * kd;
-              ds[e] = pe * (__uint_as_float(gv[e]) * kd - dl) * p.scale;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) ds[e] = pd[e] * p.scale * (__uint_as_float(gv[e]) - dl);
             }
           }
           if (KEY_MAJOR) store_prob_columns(sP_gen, r, c, pd);
@@ -579,28 +632,26 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap tmQKV, const __gri
         ++n_in;
       }
       if (!ok) break;
-      // epilogue: this thread's row of the accumulators (a key row, or a query row)
+      // epilogue: 32 of the 64 columns of this thread's row of the accumulators (a key row, or a query row)
       if (!mbar_wait(acc_full, n_out & 1u)) { ok = false; break; }
       tc_fence_after();
       const int row = o * BT + r;
-      float v[64];
-      unsigned a0[32], a1[32];
-      tmem_ld_32x32(tA0 + lane_off, a0);
-      tmem_ld_32x32(tA0 + lane_off + 32u, a1);
+      unsigned a0[32];
+      float v[32];
+      tmem_ld_32x32(tA0 + lane_off + 32u * half, a0);
       tmem_ld_wait();
 #pragma unroll
-      for (int d = 0; d < 32; ++d) { v[d] = __uint_as_float(a0[d]); v[32 + d] = __uint_as_float(a1[d]); }
-      __nv_bfloat16* grow = p.dqkv + ((long long)row * p.N + b) * (3LL * p.E) + h * HD;
+      for (int d = 0; d < 32; ++d) v[d] = __uint_as_float(a0[d]);
+      __nv_bfloat16* grow = p.dqkv + ((long long)row * p.N + b) * (3LL * p.E) + h * HD + 32 * half;
       if (KEY_MAJOR) {
-        if (row < p.L) store_row64(grow + 2 * p.E, v, 1.f);          // dV
-        tmem_ld_32x32(tA1 + lane_off, a0);
-        tmem_ld_32x32(tA1 + lane_off + 32u, a1);
+        if (row < p.L) store_row32(grow + 2 * p.E, v);               // dV
+        tmem_ld_32x32(tA1 + lane_off + 32u * half, a0);
         tmem_ld_wait();
 #pragma unroll
-        for (int d = 0; d < 32; ++d) { v[d] = __uint_as_float(a0[d]); v[32 + d] = __uint_as_float(a1[d]); }
-        if (row < p.L) store_row64(grow + p.E, v, 1.f);              // dK
+        for (int d = 0; d < 32; ++d) v[d] = __uint_as_float(a0[d]);
+        if (row < p.L) store_row32(grow + p.E, v);                   // dK
       } else {
-        if (row < p.L) store_row64(grow, v, 1.f);                    // dQ
+        if (row < p.L) store_row32(grow, v);                         // dQ
       }
       tc_fence_before();
       mbar_arrive(acc_empty);
@@ -617,23 +668,33 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap tmQKV, const __gri
   }
 }
 
-// delta[bh][l] = sum_d dO[l, b, h*64 + d] * O[l, b, h*64 + d]: one warp per (l, b, h).
+// delta[bh][l] = sum_d dO[l, b, h*64 + d] * O[l, b, h*64 + d]: eight threads per (l, b, h), one 16-byte load of each
+// tensor per thread.
 __global__ void __launch_bounds__(256) attention_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out,
                                                               float* __restrict__ delta, int L, int N, int H) {
-  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   const long long total = (long long)L * N * H;
-  if (w >= total) return;
-  const int lane = threadIdx.x & 31;
-  const int h = (int)(w % H);
-  const long long lb = w / H;                 // l * N + b
-  const int b = (int)(lb % N), l = (int)(lb / N);
-  const long long off = lb * (long long)(H * HD) + h * HD + 2 * lane;
-  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(dout + off), o = *reinterpret_cast<const __nv_bfloat162*>(out + off);
-  const float2 fa = __bfloat1622float2(a), fo = __bfloat1622float2(o);
-  float s = fa.x * fo.x + fa.y * fo.y;
+  const long long w = ((long long)blockIdx.x * 256 + threadIdx.x) >> 3;     // (l * N + b) * H + h
+  const int part = threadIdx.x & 7;
+  float s = 0.f;
+  int h = 0;
+  long long lb = 0;
+  if (w < total) {
+    h = (int)(w % H);
+    lb = w / H;
+    const long long off = w * HD + 8 * part;                                // rows of dout / out are contiguous over (l, b, h, d)
+    const uint4 a = *reinterpret_cast<const uint4*>(dout + off), o = *reinterpret_cast<const uint4*>(out + off);
+    const unsigned aw[4] = {a.x, a.y, a.z, a.w}, ow[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
-  for (int k = 16; k > 0; k >>= 1) s += __shfl_xor_sync(0xffffffffu, s, k);
-  if (lane == 0) delta[((long long)b * H + h) * L + l] = s;
+    for (int k = 0; k < 4; ++k)
+      s += __uint_as_float(aw[k] << 16) * __uint_as_float(ow[k] << 16) + __uint_as_float(aw[k] & 0xffff0000u) * __uint_as_float(ow[k] & 0xffff0000u);
+  }
+  s += __shfl_xor_sync(0xffffffffu, s, 4);
+  s += __shfl_xor_sync(0xffffffffu, s, 2);
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  if (w < total && part == 0) {
+    const int b = (int)(lb % N), l = (int)(lb / N);
+    delta[((long long)b * H + h) * L + l] = s;
+  }
 }
 
 // Keep mask of the dropout on the probabilities, as bytes [N*H][L][L] (for tests).
@@ -758,8 +819,8 @@ int hapx_attention_fused_backward(void* dqkv, float* delta_ws, const void* dout,
   p.units = (int)(N * H * p.nt);
   const long long E = H * fattn::HD;
   {
-    const long long warps = L * N * H;
-    fattn::attention_delta_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(dout),
+    const long long rows = L * N * H;      // 8 threads each
+    fattn::attention_delta_kernel<<<(unsigned)((rows + 31) / 32), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(dout),
                                                                                  static_cast<const __nv_bfloat16*>(out), delta_ws, (int)L, (int)N, (int)H);
     HAPX_CUDA(cudaGetLastError());
     count_launch();
@@ -778,9 +839,9 @@ int hapx_attention_fused_backward(void* dqkv, float* delta_ws, const void* dout,
     }
   }
   const int grid = std::max(1, std::min(p.units, sms));
-  fattn::attention_backward_kernel<true><<<grid, fattn::kThreads, fattn::kBwdSmem, stream>>>(tmQKV, tmDO, p);
+  fattn::attention_backward_kernel<true><<<grid, fattn::kBwdThreads, fattn::kBwdSmem, stream>>>(tmQKV, tmDO, p);
   HAPX_CUDA(cudaGetLastError());
-  fattn::attention_backward_kernel<false><<<grid, fattn::kThreads, fattn::kBwdSmem, stream>>>(tmQKV, tmDO, p);
+  fattn::attention_backward_kernel<false><<<grid, fattn::kBwdThreads, fattn::kBwdSmem, stream>>>(tmQKV, tmDO, p);
   HAPX_CUDA(cudaGetLastError());
   count_launch(2);
   return HAPX_OK;
