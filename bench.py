@@ -895,17 +895,21 @@ def lm_step(args, job, kind, plan, use_graph, dropout_p):
     model = model.to(torch.bfloat16).to(dev)
     n_params = sum(p.numel() for p in model.parameters())
     hap_b200.dropout.manual_seed(39 + rank)
+    def program(r):
+        graph = emit(model, r)
+        if not args.lm_no_fuse:
+            hap_b200.fxpass.fuse_elementwise(graph)     # dropout + residual add, activation + dropout: one pass each
+        return torch.fx.GraphModule(model, graph)
+
     if W == 1:
         comm = hap_b200.single_comm(dev, stage_bytes=256 << 20, heap_bytes=(320 << 20) + 2 * n_params)
         hap_b200.collectives.set_default_comm(comm)
-        graph = emit(model, 0)
-        worker = ProcessWorker(torch.fx.GraphModule(model, graph), comm=comm)
+        worker = ProcessWorker(program(0), comm=comm)
     else:
         comm = hap_b200.init_process_comm(stage_bytes=256 << 20, heap_bytes=(320 << 20) + 2 * n_params)
         hap_b200.collectives.set_default_comm(comm)
-        graph = emit(model, rank)
         # the reference sums the partial losses with dist.reduce (worker.py:63-64); here through the package's all_reduce
-        worker = ProcessWorker(torch.fx.GraphModule(model, graph),
+        worker = ProcessWorker(program(rank),
                                reduce_loss=lambda t: comm.all_reduce([t.reshape(1).float()])[0], comm=comm)
     step = worker.step
     tok_h, tgt_h = in_h[0].pin_memory(), in_h[1].pin_memory()
@@ -1247,6 +1251,7 @@ def main():
     ap.add_argument("--lm-batch", type=int, default=0, help="samples per GPU (0: the configuration's 32 / 64 / 16)")
     ap.add_argument("--lm-layers", type=int, default=0, help="0: the configuration's 12 / 12 / 8")
     ap.add_argument("--lm-plan", default="dp_zero", choices=["dp", "dp_zero"])
+    ap.add_argument("--lm-no-fuse", action="store_true", help="run the program as emitted, without the elementwise fusion pass")
     ap.add_argument("--lm-graph", action="store_true", help="capture the training step into a CUDA graph")
     ap.add_argument("--gemm-tokens", type=int, default=8192)
     ap.add_argument("--gemm-layers", default="", help="comma-separated layer names to restrict the gemm workload to")

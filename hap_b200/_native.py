@@ -58,8 +58,9 @@ SIGNATURES = {
     "hapx_gemm_status": (_int, []),
     "hapx_attention_forward": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp]),
     "hapx_attention_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
-    "hapx_attention_fused_forward": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _dbl, _u64, _vp]),
-    "hapx_attention_fused_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _dbl, _u64, _vp]),
+    "hapx_attention_classify_mask": (_int, [_vp, _i64, _vp, _vp]),
+    "hapx_attention_fused_forward": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp, _dbl, _u64, _vp]),
+    "hapx_attention_fused_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp, _dbl, _u64, _vp]),
     "hapx_attention_dropout_mask": (_int, [_vp, _i64, _i64, _i64, _dbl, _u64, _vp]),
     "hapx_grad_sqnorm": (_int, [_int, _pp, _pi64, _int, _vp, _int, _vp]),
     "hapx_clip_adam_apply": (_int, [_int, _pp, _pp, _pp, _pp, _pi64, _int, _dbl, _dbl, _dbl, _dbl, _dbl, _dbl, _vp, _int, _vp]),
@@ -72,6 +73,9 @@ SIGNATURES = {
     "hapx_rng_advance": (_int, [_vp]),
     "hapx_dropout": (_int, [_vp, _vp, _int, _i64, _dbl, _u64, _vp]),
     "hapx_dropout_mask": (_int, [_vp, _i64, _dbl, _u64, _vp]),
+    "hapx_dropout_add": (_int, [_vp, _vp, _vp, _int, _i64, _dbl, _u64, _vp]),
+    "hapx_act_dropout": (_int, [_vp, _vp, _int, _i64, _int, _dbl, _u64, _vp]),
+    "hapx_act_dropout_backward": (_int, [_vp, _vp, _vp, _int, _i64, _int, _dbl, _u64, _vp]),
     "hapx_local_all_reduce_noalloc": (_int, [_int, _pp, _pp, _int, _int, _dbl, _i64, _vp]),
     "hapx_local_all_reduce_noalloc_status": (_int, []),
     "hapx_debug_host_walk": (_int, [_int, _int, _int, _int, _i64, _i64, _i64, _int, _pi64, _pi64, _pp,

@@ -13,6 +13,7 @@ backward recomputes them), and on batched GEMMs plus softmax kernels for other h
 """
 from __future__ import annotations
 
+import weakref
 from typing import Optional
 
 import torch
@@ -25,24 +26,42 @@ from .linear import linear
 FUSED_HEAD_DIM = 64
 
 
+# One program hands the same mask tensor to every layer (the language model builds it once per forward,
+# models.py:72): its float32 form and the device word that says "this is just the causal mask" are made
+# once per tensor (and per in-place version of it) and reused by all layers, forward and backward.
+_mask_cache = {}      # id(mask tensor) -> (weak reference to it, its version, float32 form, flag word)
+
+
 def _classify_mask(mask: Optional[torch.Tensor], L: int):
-    """(causal flag, additive fp32 mask or None).  A mask tensor is always applied as an additive
-    (L, L) fp32 term inside the softmax kernel (-inf entries mask, as with the reference's LM mask,
-    ``models.py:72``); no value of it is inspected on the host, so nothing synchronises.  The string
-    ``"causal"`` selects the built-in causal masking without a tensor."""
+    """(causal flag, additive fp32 mask or None, device flag word or None).  A mask tensor is applied as
+    an additive (L, L) fp32 term inside the kernels (-inf entries mask, as with the reference's LM mask,
+    ``models.py:72``); no value of it is inspected on the host, so nothing synchronises: a small kernel
+    leaves a device word that tells the attention kernels whether the tensor is exactly the causal
+    mask.  The string ``"causal"`` selects the built-in causal masking without a tensor."""
     if mask is None:
-        return 0, None
+        return 0, None, None
     if isinstance(mask, str):
         if mask != "causal":
             raise ValueError(f"attention: unknown mask {mask!r}")
-        return 1, None
+        return 1, None, None
+    hit = _mask_cache.get(id(mask))
+    if hit is not None and hit[0]() is mask and hit[1] == mask._version:
+        return 0, hit[2], hit[3]
     if mask.dtype == torch.bool:
         add = torch.zeros(mask.shape, dtype=torch.float32, device=mask.device).masked_fill_(mask, float("-inf"))
     else:
         add = mask.float()
     if add.shape != (L, L):
         raise ValueError(f"attention: attn_mask must be ({L}, {L}), got {tuple(add.shape)}")
-    return 0, add.contiguous()
+    add = add.contiguous()
+    flag = None
+    if add.is_cuda:
+        flag = torch.empty(1, dtype=torch.int32, device=add.device)
+        with _on_device(add.device):
+            N.check(N.lib.hapx_attention_classify_mask(add.data_ptr(), L, flag.data_ptr(), _stream(add.device)))
+    key = id(mask)
+    _mask_cache[key] = (weakref.ref(mask, lambda _ref, key=key: _mask_cache.pop(key, None)), mask._version, add, flag)
+    return 0, add, flag
 
 
 class _Attention(torch.autograd.Function):
@@ -82,7 +101,7 @@ class _FusedAttention(torch.autograd.Function):
     """The fused kernels (head dimension 64): saves qkv, the output and one float per row."""
 
     @staticmethod
-    def forward(ctx, qkv, num_heads, causal, mask, dropout_p, call_id):
+    def forward(ctx, qkv, num_heads, causal, mask, mask_flag, dropout_p, call_id):
         L, n, e3 = qkv.shape
         E = e3 // 3
         qkv = qkv.contiguous()
@@ -90,15 +109,16 @@ class _FusedAttention(torch.autograd.Function):
         lse2 = torch.empty((n * num_heads, L), dtype=torch.float32, device=qkv.device)
         with _on_device(qkv.device):
             N.check(N.lib.hapx_attention_fused_forward(out.data_ptr(), lse2.data_ptr(), qkv.data_ptr(), L, n, num_heads, FUSED_HEAD_DIM,
-                                                       int(causal), mask.data_ptr() if mask is not None else None, float(dropout_p),
+                                                       int(causal), mask.data_ptr() if mask is not None else None,
+                                                       mask_flag.data_ptr() if mask_flag is not None else None, float(dropout_p),
                                                        int(call_id), _stream(qkv.device)))
-        ctx.save_for_backward(qkv, out, lse2, mask)
+        ctx.save_for_backward(qkv, out, lse2, mask, mask_flag)
         ctx.meta = (L, n, num_heads, int(causal), float(dropout_p), int(call_id))
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        qkv, out, lse2, mask = ctx.saved_tensors
+        qkv, out, lse2, mask, mask_flag = ctx.saved_tensors
         L, n, H, causal, dropout_p, call_id = ctx.meta
         dout = dout.contiguous()
         dqkv = torch.empty_like(qkv)
@@ -106,9 +126,10 @@ class _FusedAttention(torch.autograd.Function):
         with _on_device(qkv.device):
             N.check(N.lib.hapx_attention_fused_backward(dqkv.data_ptr(), delta.data_ptr(), dout.data_ptr(), out.data_ptr(), lse2.data_ptr(),
                                                         qkv.data_ptr(), L, n, H, FUSED_HEAD_DIM, causal,
-                                                        mask.data_ptr() if mask is not None else None, dropout_p, call_id,
+                                                        mask.data_ptr() if mask is not None else None,
+                                                        mask_flag.data_ptr() if mask_flag is not None else None, dropout_p, call_id,
                                                         _stream(qkv.device)))
-        return dqkv, None, None, None, None, None
+        return dqkv, None, None, None, None, None, None
 
 
 def attention_keep_mask(L: int, n: int, num_heads: int, dropout_p: float, call_id: int, device=None) -> torch.Tensor:
@@ -130,12 +151,12 @@ def attention(qkv: torch.Tensor, num_heads: int, attn_mask: Optional[torch.Tenso
         raise TypeError(f"attention: bfloat16 only, got {qkv.dtype}")
     if qkv.dim() != 3 or qkv.shape[2] % (3 * num_heads):
         raise ValueError("attention: qkv must be (L, N, 3 * num_heads * head_dim)")
-    causal, mask = _classify_mask(attn_mask, qkv.shape[0])
+    causal, mask, mask_flag = _classify_mask(attn_mask, qkv.shape[0])
     if not 0.0 <= dropout_p < 1.0:
         raise ValueError(f"attention: dropout_p must be in [0, 1), got {dropout_p}")
     if qkv.shape[2] // (3 * num_heads) == FUSED_HEAD_DIM and qkv.shape[1] > 0:
         call_id = _dropout.new_call_id() if dropout_p > 0.0 else 0
-        return _FusedAttention.apply(qkv, num_heads, causal, mask, dropout_p, call_id)
+        return _FusedAttention.apply(qkv, num_heads, causal, mask, mask_flag, dropout_p, call_id)
     if dropout_p > 0.0:
         raise NotImplementedError("attention: dropout on the probabilities needs head dimension 64 (the fused kernels)")
     return _Attention.apply(qkv, num_heads, causal, mask)

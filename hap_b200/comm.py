@@ -84,6 +84,9 @@ class Comm:
         w, nl, fr = C.c_int(), C.c_int(), C.c_int()
         N.check(N.lib.hapx_comm_world(self._h, C.byref(w), C.byref(nl), C.byref(fr)))
         self.world, self.n_local, self.first_rank = w.value, nl.value, fr.value
+        # A world of ONE rank: all_gather, reduce_scatter (unscaled), all_reduce (unscaled) and all_to_all are the
+        # identity, so the tensor-level methods hand the input back instead of launching a copy.
+        self._alone = self.world == 1
         self._heap_views: List[Optional[torch.Tensor]] = [None] * self.n_local
         self._heap_cursor = [0] * self.n_local
         self.debug_sync = os.environ.get("HAPX_DEBUG_SYNC", "0") == "1"
@@ -205,6 +208,8 @@ class Comm:
                 raise ValueError(f"all_gather: rank {r} holds extent {t.shape[dim]} on dim {dim}, sharding length is {lengths[r]}")
             if t.dtype != ref.dtype or t.shape[:dim] != ref.shape[:dim] or t.shape[dim + 1:] != ref.shape[dim + 1:]:
                 raise ValueError("all_gather: shards disagree in dtype or non-sharded extents")
+        if self._alone and out is None:
+            return shards                      # a world of one: the shard is the whole tensor
         full = list(ref.shape)
         full[dim] = sum(lengths)
         outs = list(out) if out is not None else [torch.empty(full, dtype=ref.dtype, device=t.device) for t in shards]
@@ -230,6 +235,8 @@ class Comm:
             if t.shape != ref.shape or t.dtype != ref.dtype:
                 raise ValueError("reduce_scatter: inputs disagree in shape or dtype")
         out_dtype = out_dtype or ref.dtype
+        if self._alone and scale == 1.0 and out_dtype == ref.dtype:
+            return inputs                      # a world of one: nothing to add, nothing to cut
         outs = []
         for r in self.ranks():
             shape = list(ref.shape)
@@ -252,6 +259,8 @@ class Comm:
             if t.shape != ref.shape or t.dtype != ref.dtype:
                 raise ValueError("all_reduce: inputs disagree in shape or dtype")
         out_dtype = out_dtype or ref.dtype
+        if self._alone and scale == 1.0 and out_dtype == ref.dtype:
+            return inputs
         if inplace:
             if out_dtype != ref.dtype:
                 raise ValueError("all_reduce: in-place needs out_dtype == input dtype")
@@ -275,6 +284,8 @@ class Comm:
         if split_dim == cat_dim:
             raise ValueError("all_to_all: split_dim and cat_dim must differ")
         d1, d2 = min(split_dim, cat_dim), max(split_dim, cat_dim)
+        if self._alone and all(t.shape[split_dim] == split_lengths[0] and t.shape[cat_dim] == cat_lengths[0] for t in inputs):
+            return inputs
         outs = []
         for r, t in zip(self.ranks(), inputs):
             if t.shape[split_dim] != sum(split_lengths):

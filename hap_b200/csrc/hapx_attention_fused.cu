@@ -710,15 +710,18 @@ __global__ void __launch_bounds__(256) attention_mask_kernel(unsigned char* __re
   }
 }
 
-__global__ void __launch_bounds__(1024) classify_mask_kernel(const float* __restrict__ mask, int L, unsigned* flag) {
+// *flag stays non-zero when mask[q][k] is 0 for k <= q and -inf for k > q (the language-model mask).  The host
+// sets the word to all ones before the launch; any block that finds a deviating entry clears it.
+__global__ void __launch_bounds__(256) classify_mask_kernel(const float* __restrict__ mask, int L, unsigned* flag) {
   int ok = 1;
-  for (long long e = threadIdx.x; e < (long long)L * L; e += blockDim.x) {
+  const long long n = (long long)L * L;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (long long)gridDim.x * blockDim.x) {
     const int q = (int)(e / L), k = (int)(e - (long long)q * L);
     const float v = mask[e];
     ok &= (k <= q) ? (v == 0.f) : (v == -INFINITY);
   }
   ok = __syncthreads_and(ok);
-  if (threadIdx.x == 0) *flag = ok ? 1u : 0u;
+  if (threadIdx.x == 0 && !ok) atomicAnd(flag, 0u);
 }
 
 // ---- host side ----------------------------------------------------------------------------------------
@@ -734,8 +737,8 @@ static int check(long long L, long long N, long long H, long long D, double p) {
   return HAPX_OK;
 }
 
-static int fill(Params& p, long long L, long long N, long long H, int causal, const float* mask, double dropout_p, uint64_t call_id,
-                cudaStream_t stream, int* sm_count) {
+static int fill(Params& p, long long L, long long N, long long H, int causal, const float* mask, const unsigned* mask_flag, double dropout_p,
+                uint64_t call_id, int* sm_count) {
   p = Params();
   p.L = (int)L; p.N = (int)N; p.H = (int)H; p.E = (int)(H * HD);
   p.nt = (int)((L + BT - 1) / BT);
@@ -752,14 +755,7 @@ static int fill(Params& p, long long L, long long N, long long H, int causal, co
     if (int e = rng_state(&st)) return e;
     p.rng = st;
   }
-  if (mask && !causal) {     // let the device find out whether the mask tensor is just the causal mask; no host sync
-    unsigned* flag = nullptr;
-    if (int e = gemm::scratch_flag(&flag)) return e;
-    classify_mask_kernel<<<1, 1024, 0, stream>>>(mask, (int)L, flag);
-    HAPX_CUDA(cudaGetLastError());
-    count_launch();
-    p.mask_is_causal = flag;
-  }
+  p.mask_is_causal = (mask && !causal) ? mask_flag : nullptr;
   return HAPX_OK;
 }
 
@@ -771,15 +767,27 @@ using hapx::gemm::Operand;
 
 extern "C" {
 
+int hapx_attention_classify_mask(const float* mask, int64_t L, unsigned* flag, hapx_stream stream_) {
+  if (!mask || !flag || L < 1 || L > 0x7fff) return fail(HAPX_ERR_ARGUMENT, "attention_classify_mask: bad argument");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  HAPX_CUDA(cudaMemsetAsync(flag, 0xff, sizeof(unsigned), stream));
+  const long long n = L * L;
+  const int grid = (int)std::max<long long>(1, std::min<long long>((n + 1023) / 1024, 256));
+  fattn::classify_mask_kernel<<<grid, 256, 0, stream>>>(mask, (int)L, flag);
+  HAPX_CUDA(cudaGetLastError());
+  count_launch();
+  return HAPX_OK;
+}
+
 int hapx_attention_fused_forward(void* out, float* lse2, const void* qkv, int64_t L, int64_t N, int64_t H, int64_t D, int causal,
-                                 const float* mask, double dropout_p, uint64_t call_id, hapx_stream stream_) {
+                                 const float* mask, const unsigned* mask_flag, double dropout_p, uint64_t call_id, hapx_stream stream_) {
   if (int e = fattn::check(L, N, H, D, dropout_p)) return e;
   if (L == 0 || N == 0) return HAPX_OK;
   if (!out || !lse2 || !qkv) return fail(HAPX_ERR_ARGUMENT, "attention_fused_forward: null pointer");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   fattn::Params p;
   int sms = 0;
-  if (int e = fattn::fill(p, L, N, H, causal, mask, dropout_p, call_id, stream, &sms)) return e;
+  if (int e = fattn::fill(p, L, N, H, causal, mask, mask_flag, dropout_p, call_id, &sms)) return e;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.lse2 = lse2;
   p.units = (int)(N * H * p.nt);
@@ -804,15 +812,15 @@ int hapx_attention_fused_forward(void* out, float* lse2, const void* qkv, int64_
 }
 
 int hapx_attention_fused_backward(void* dqkv, float* delta_ws, const void* dout, const void* out, const float* lse2, const void* qkv,
-                                  int64_t L, int64_t N, int64_t H, int64_t D, int causal, const float* mask, double dropout_p,
-                                  uint64_t call_id, hapx_stream stream_) {
+                                  int64_t L, int64_t N, int64_t H, int64_t D, int causal, const float* mask, const unsigned* mask_flag,
+                                  double dropout_p, uint64_t call_id, hapx_stream stream_) {
   if (int e = fattn::check(L, N, H, D, dropout_p)) return e;
   if (L == 0 || N == 0) return HAPX_OK;
   if (!dqkv || !delta_ws || !dout || !out || !lse2 || !qkv) return fail(HAPX_ERR_ARGUMENT, "attention_fused_backward: null pointer");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   fattn::Params p;
   int sms = 0;
-  if (int e = fattn::fill(p, L, N, H, causal, mask, dropout_p, call_id, stream, &sms)) return e;
+  if (int e = fattn::fill(p, L, N, H, causal, mask, mask_flag, dropout_p, call_id, &sms)) return e;
   p.lse2 = const_cast<float*>(lse2);
   p.delta = delta_ws;
   p.dqkv = static_cast<__nv_bfloat16*>(dqkv);

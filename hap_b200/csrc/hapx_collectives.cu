@@ -671,6 +671,7 @@ static int gather_impl(hapx_comm* c, void* const* dst, const void* const* src, i
     P.lr[i].dst = static_cast<char*>(dst[i]);
     if (!dst[i]) return fail(HAPX_ERR_ARGUMENT, "null output pointer");
     const size_t bytes = (size_t)(outer * P.L1[r] * inner) * es;
+    if (c->world == 1) { P.self_only = 1; continue; }     // a world of one: a local copy, nothing to publish
     if (int e = publish_input(c, i, src[i], bytes, false, 0, stream, &P.lr[i].src_off)) return e;
   }
   P.seq = next_seq(c);
@@ -698,6 +699,8 @@ static int reduce_impl(hapx_comm* c, void* const* dst, const void* const* src, i
     P.lr[i].dst = static_cast<char*>(dst[i]);
     if (!dst[i] && L[r] > 0) return fail(HAPX_ERR_ARGUMENT, "null output pointer");
     const size_t bytes = (size_t)(outer * total * inner) * P.es_in;
+    // a world of one reads its own input in place (the reduce kernel assumes 16-byte aligned inputs)
+    if (c->world == 1 && (reinterpret_cast<uintptr_t>(src[i]) & 15u) == 0 && src[i] != dst[i]) { P.self_only = 1; continue; }
     if (int e = publish_input(c, i, src[i], bytes, true, stage_pos, stream, &P.lr[i].src_off)) return e;
   }
   P.seq = next_seq(c);

@@ -79,6 +79,81 @@ def dropout(input: torch.Tensor, p: float = 0.5, training: bool = True, inplace:
     return _Dropout.apply(input, float(p), new_call_id())
 
 
+_ACTS = {"relu": 1, "gelu": 2}
+
+
+class _DropoutAdd(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, p, call_id):
+        ctx.meta = (p, call_id)
+        x, residual = x.contiguous(), residual.contiguous()
+        y = torch.empty_like(x)
+        with _on_device(x.device):
+            N.check(N.lib.hapx_dropout_add(y.data_ptr(), x.data_ptr(), residual.data_ptr(), _code(x), x.numel(), float(p), call_id,
+                                           _stream(x.device)))
+        return y
+
+    @staticmethod
+    def backward(ctx, grad):
+        p, call_id = ctx.meta
+        gx = _apply(grad, p, call_id) if ctx.needs_input_grad[0] else None
+        return gx, (grad if ctx.needs_input_grad[1] else None), None, None
+
+
+class _ActDropout(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, act, p, call_id):
+        x = x.contiguous()
+        y = torch.empty_like(x)
+        with _on_device(x.device):
+            N.check(N.lib.hapx_act_dropout(y.data_ptr(), x.data_ptr(), _code(x), x.numel(), act, float(p), call_id, _stream(x.device)))
+        ctx.save_for_backward(y if act == 1 else x)     # relu: the output tells active-and-kept; gelu: needs its input
+        ctx.meta = (act, p, call_id)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad):
+        (saved,) = ctx.saved_tensors
+        act, p, call_id = ctx.meta
+        grad = grad.contiguous()
+        dx = torch.empty_like(grad)
+        with _on_device(grad.device):
+            N.check(N.lib.hapx_act_dropout_backward(dx.data_ptr(), grad.data_ptr(), saved.data_ptr(), _code(grad), grad.numel(), act,
+                                                    float(p), call_id, _stream(grad.device)))
+        return dx, None, None, None
+
+
+def _code(t: torch.Tensor) -> int:
+    return N.BF16 if t.dtype == torch.bfloat16 else N.F32
+
+
+def _check(t: torch.Tensor, what: str, p: float) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{what}: hap_b200 has no CPU path; tensor is on {t.device}")
+    if t.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError(f"{what}: bfloat16 or float32 only, got {t.dtype}")
+    if not 0.0 <= p < 1.0:
+        raise ValueError(f"{what}: p must be in [0, 1), got {p}")
+
+
+def dropout_add(x: torch.Tensor, residual: torch.Tensor, p: float, training: bool = True) -> torch.Tensor:
+    """``residual + dropout(x, p)`` in one pass: the two residual connections of an encoder layer
+    (``x + dropout1(sa(x))``, ``x + dropout2(ff(x))``)."""
+    _check(x, "dropout_add", p)
+    if residual.shape != x.shape or residual.dtype != x.dtype or residual.device != x.device:
+        raise ValueError("dropout_add: x and residual must agree in shape, dtype and device")
+    p = float(p) if training else 0.0
+    return _DropoutAdd.apply(x, residual, p, new_call_id() if p > 0.0 else 0)
+
+
+def act_dropout(x: torch.Tensor, act: str, p: float, training: bool = True) -> torch.Tensor:
+    """``dropout(act(x), p)`` in one pass (``act``: ``"relu"`` or ``"gelu"``): the FFN's
+    ``dropout(activation(linear1(x)))``.  With p == 0 it is the bare activation."""
+    _check(x, "act_dropout", p)
+    p = float(p) if training else 0.0
+    return _ActDropout.apply(x, _ACTS[act], p, new_call_id() if p > 0.0 else 0)
+
+
 def keep_mask(n: int, p: float, call_id: int, device=None) -> torch.Tensor:
     """The keep mask (uint8, n elements) that call ``call_id`` draws in the current iteration."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)

@@ -66,6 +66,80 @@ def retarget_tensor_ops(graph: torch.fx.Graph, fold_loss: bool = True) -> Dict[s
     return changed
 
 
+def fuse_elementwise(graph: torch.fx.Graph) -> Dict[str, int]:
+    """Fold the elementwise neighbours of the dropout sites into single-pass kernels; rewrites ``graph``
+    in place and returns how many nodes of each kind were folded.
+
+    * ``operator.add(a, dropout(b, p))`` (either order; the dropout feeds nothing else)
+      -> :func:`hap_b200.dropout.dropout_add` ``(b, a, p)``
+    * ``dropout(relu(x), p)`` / ``dropout(gelu(x), p)`` (the activation feeds nothing else)
+      -> :func:`hap_b200.dropout.act_dropout` ``(x, act, p)``
+    * a remaining ``relu(x)`` / ``gelu(x)`` (erf form) -> ``act_dropout(x, act, 0.0)``: the bare activation
+      on the package's kernel, whose backward needs only the activation's output (relu).
+
+    Run it after :func:`retarget_tensor_ops`; it recognises torch's ``F.dropout`` / ``F.relu`` /
+    ``F.gelu`` as well as this package's ``dropout``.  The arithmetic is unchanged: each fused kernel
+    rounds once where the separate kernels rounded after every op, and draws its mask from the same
+    generator (the call ids of the remaining sites shift, as after any change of the program)."""
+    import operator
+    from .dropout import act_dropout, dropout, dropout_add
+
+    def is_dropout(n):
+        return isinstance(n, torch.fx.Node) and n.op == "call_function" and _is(n.target, F.dropout, dropout)
+
+    def dropout_args(n):
+        x = n.args[0] if n.args else n.kwargs["input"]
+        p = n.args[1] if len(n.args) > 1 else n.kwargs.get("p", 0.5)
+        training = n.args[2] if len(n.args) > 2 else n.kwargs.get("training", True)
+        return x, p, training
+
+    def act_of(n):
+        if not (isinstance(n, torch.fx.Node) and n.op == "call_function"):
+            return None
+        if _is(n.target, F.relu, torch.relu):
+            return "relu"
+        if _is(n.target, F.gelu) and n.kwargs.get("approximate", "none") == "none" and len(n.args) == 1:
+            return "gelu"
+        return None
+
+    changed = {"dropout_add": 0, "act_dropout": 0, "activation": 0}
+    for node in list(graph.nodes):
+        if node.op != "call_function":
+            continue
+        if _is(node.target, operator.add) and len(node.args) == 2 and not node.kwargs:
+            a, b = node.args
+            drop, other = (b, a) if is_dropout(b) else ((a, b) if is_dropout(a) else (None, None))
+            if drop is not None and len(drop.users) == 1 and isinstance(other, torch.fx.Node):
+                x, p, training = dropout_args(drop)
+                if isinstance(p, (int, float)) and training is True:
+                    with graph.inserting_before(node):
+                        new = graph.call_function(dropout_add, (x, other, float(p)))
+                    node.replace_all_uses_with(new)
+                    graph.erase_node(node)
+                    graph.erase_node(drop)
+                    changed["dropout_add"] += 1
+        elif is_dropout(node):
+            x, p, training = dropout_args(node)
+            act = act_of(x)
+            if act is not None and len(x.users) == 1 and isinstance(p, (int, float)) and training is True:
+                with graph.inserting_before(node):
+                    new = graph.call_function(act_dropout, (x.args[0], act, float(p)))
+                node.replace_all_uses_with(new)
+                graph.erase_node(node)
+                graph.erase_node(x)
+                changed["act_dropout"] += 1
+    for node in list(graph.nodes):
+        act = act_of(node)
+        if act is not None:
+            with graph.inserting_before(node):
+                new = graph.call_function(act_dropout, (node.args[0], act, 0.0))
+            node.replace_all_uses_with(new)
+            graph.erase_node(node)
+            changed["activation"] += 1
+    graph.lint()
+    return changed
+
+
 def _peel(node, method: str):
     """If ``node`` is ``x.<method>(...)`` return ``x`` else ``node`` itself."""
     if isinstance(node, torch.fx.Node) and node.op == "call_method" and node.target == method:

@@ -38,6 +38,8 @@ def _program_has_dropout(module) -> bool:
         name = getattr(n.target, "__name__", "")
         if name == "dropout" or (name == "multi_head_attention_forward" and float(n.kwargs.get("dropout_p", 0.0) or 0.0) > 0.0):
             return True
+        if name in ("dropout_add", "act_dropout") and float(n.args[2]) > 0.0:
+            return True
     return False
 
 

@@ -234,12 +234,19 @@ int hapx_attention_backward(void* dqkv, void* dscores_ws, void* ds_ws, const voi
  * so it must run in the same iteration (before the next hapx_rng_advance) with the same call_id,
  * causal flag and mask.  delta_ws: N*H*L floats of scratch.  out is the forward's output.
  * Deterministic: no atomics, every output element is written by one thread block.
+ * mask_flag (optional, with a mask tensor): a device word written by hapx_attention_classify_mask,
+ * non-zero when the mask tensor is exactly the causal mask (0 on and below the diagonal, -inf
+ * above, as models.py:72 builds it); the kernels then skip the key tiles the causal rule excludes
+ * and never read the tensor.  The word is read on the device, so nothing synchronises with the host;
+ * classify a mask tensor once and pass the word to every layer's forward and backward.
  * hapx_attention_dropout_mask writes the keep mask [N*H, L, L] as bytes (for tests). */
+int hapx_attention_classify_mask(const float* mask, int64_t L, unsigned* flag, hapx_stream stream);
 int hapx_attention_fused_forward(void* out, float* lse2, const void* qkv, int64_t L, int64_t N, int64_t H, int64_t D,
-                                 int causal, const float* mask, double dropout_p, uint64_t call_id, hapx_stream stream);
+                                 int causal, const float* mask, const unsigned* mask_flag, double dropout_p, uint64_t call_id,
+                                 hapx_stream stream);
 int hapx_attention_fused_backward(void* dqkv, float* delta_ws, const void* dout, const void* out, const float* lse2,
                                   const void* qkv, int64_t L, int64_t N, int64_t H, int64_t D, int causal, const float* mask,
-                                  double dropout_p, uint64_t call_id, hapx_stream stream);
+                                  const unsigned* mask_flag, double dropout_p, uint64_t call_id, hapx_stream stream);
 int hapx_attention_dropout_mask(unsigned char* mask, int64_t L, int64_t N, int64_t H, double dropout_p, uint64_t call_id,
                                 hapx_stream stream);
 
@@ -261,6 +268,19 @@ int hapx_rng_seed(uint64_t seed, hapx_stream stream);
 int hapx_rng_advance(hapx_stream stream);
 int hapx_dropout(void* y, const void* x, int dtype, int64_t n, double p, uint64_t call_id, hapx_stream stream);
 int hapx_dropout_mask(unsigned char* mask, int64_t n, double p, uint64_t call_id, hapx_stream stream);
+/* The same dropout fused with its neighbours in the reference's encoder layers (one pass over memory
+ * instead of two or three; p = 0 is allowed and gives the bare operation):
+ *   hapx_dropout_add : y = residual + dropout(x)            x + dropout1(sa(x)), x + dropout2(ff(x))
+ *   hapx_act_dropout : y = dropout(act(x))                  dropout(activation(linear1(x)));  act 1 = relu, 2 = gelu (erf)
+ * backward of dropout_add w.r.t. x is hapx_dropout on the incoming gradient (w.r.t. residual: the
+ * identity); backward of act_dropout is hapx_act_dropout_backward with `saved` = the forward's OUTPUT
+ * for relu (an element is non-zero iff it was active and kept: no mask is regenerated) and the
+ * forward's INPUT for gelu. */
+int hapx_dropout_add(void* y, const void* x, const void* residual, int dtype, int64_t n, double p, uint64_t call_id,
+                     hapx_stream stream);
+int hapx_act_dropout(void* y, const void* x, int dtype, int64_t n, int act, double p, uint64_t call_id, hapx_stream stream);
+int hapx_act_dropout_backward(void* dx, const void* dy, const void* saved, int dtype, int64_t n, int act, double p,
+                              uint64_t call_id, hapx_stream stream);
 
 /* all_reduce that allocates nothing.  No counterpart in the reference.
  * Same values as hapx_all_reduce on a local (single-device) communicator of `world` virtual

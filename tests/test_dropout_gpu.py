@@ -88,3 +88,51 @@ def test_eval_mode_and_p_zero_are_the_identity_and_bad_inputs_raise():
         D.dropout(x.cpu(), 0.1)
     with pytest.raises(TypeError):
         D.dropout(x.half(), 0.1)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n,p", [(4099, 0.1), (1 << 18, 0.3), (64, 0.0)])
+def test_dropout_add_equals_the_separate_ops_given_the_mask(dtype, n, p):
+    D.manual_seed(5, DEV)
+    D.advance(DEV)
+    g = torch.Generator().manual_seed(n)
+    x = torch.randn(n, generator=g).to(dtype).to(DEV).requires_grad_(True)
+    r = torch.randn(n, generator=g).to(dtype).to(DEV).requires_grad_(True)
+    y = D.dropout_add(x, r, p)
+    mask = D.keep_mask(n, p, D._next_call_id, DEV).bool() if p > 0 else torch.ones(n, dtype=torch.bool, device=DEV)
+    scale = 1.0 / (1.0 - p)
+    # the kernel computes residual + x * scale as ONE fused multiply-add in float32: evaluate it exactly in float64
+    # (the float32 scale factor included) and round once to float32, then to the tensor's dtype
+    scale32 = float(torch.tensor(scale, dtype=torch.float32))
+    want = (r.detach().double() + torch.where(mask, x.detach().double() * scale32, torch.zeros((), device=DEV, dtype=torch.float64)))
+    want = want.float().to(dtype)
+    assert torch.equal(y.detach(), want)
+    gy = torch.randn(n, generator=g).to(dtype).to(DEV)
+    y.backward(gy)
+    assert torch.equal(r.grad, gy)
+    assert torch.equal(x.grad, torch.where(mask, gy.float() * scale, torch.zeros((), device=DEV)).to(dtype))
+
+
+@pytest.mark.parametrize("act", ["relu", "gelu"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n,p", [(4099, 0.1), (1 << 18, 0.25), (96, 0.0)])
+def test_act_dropout_equals_the_separate_ops_given_the_mask(act, dtype, n, p):
+    D.manual_seed(6, DEV)
+    D.advance(DEV)
+    g = torch.Generator().manual_seed(n + 1)
+    x = torch.randn(n, generator=g).to(dtype).to(DEV).requires_grad_(True)
+    y = D.act_dropout(x, act, p)
+    mask = D.keep_mask(n, p, D._next_call_id, DEV).bool() if p > 0 else torch.ones(n, dtype=torch.bool, device=DEV)
+    scale = 1.0 / (1.0 - p)
+    ref_in = x.detach().double().requires_grad_(True)
+    fn = torch.relu if act == "relu" else torch.nn.functional.gelu
+    ref = fn(ref_in) * mask.double() * scale
+    gy = torch.randn(n, generator=g).to(dtype).to(DEV)
+    y.backward(gy)
+    ref.backward(gy.double())
+    tol = dict(rtol=1e-2, atol=1e-2) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(y.detach().double(), ref.detach(), **tol)
+    torch.testing.assert_close(x.grad.double(), ref_in.grad, **tol)
+    if act == "relu":       # exact: one rounding of max(x, 0) * scale, and the gradient passes exactly where the output is non-zero
+        assert torch.equal(y.detach(), (torch.relu(x.detach().float()) * mask * scale).to(dtype))
+        assert torch.equal(x.grad, torch.where(y.detach() != 0, gy.float() * scale, torch.zeros((), device=DEV)).to(dtype))

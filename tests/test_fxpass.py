@@ -79,3 +79,35 @@ def test_rewritten_program_matches_the_natively_emitted_one():
         comm.check()
     finally:
         comm.destroy()
+
+
+def test_elementwise_fusion_folds_the_dropout_sites():
+    import operator
+    from hap_b200 import fxpass
+    from hap_b200 import plan as P
+    from hap_b200.dropout import act_dropout, dropout_add
+    nl = C.LM_SMALL["nlayers"]
+    model = C.lm_model()
+    graph = P.emit_lm(copy.deepcopy(model), "dp_zero", C.RATIOS, 0, C.LM_BATCH, C.lm_cpu_namespace(), dropout_p=0.1)
+    assert fxpass.fuse_elementwise(graph) == {"dropout_add": 2 * nl, "act_dropout": nl, "activation": 0}
+    targets = [n.target for n in graph.nodes if n.op == "call_function"]
+    assert F.dropout not in targets and F.relu not in targets
+    assert targets.count(dropout_add) == 2 * nl and targets.count(act_dropout) == nl
+    for n in graph.nodes:
+        if n.op == "call_function" and n.target is act_dropout:
+            assert n.args[1] == "relu" and n.args[2] == 0.1
+    # without dropout only the activations are left to replace
+    graph = P.emit_lm(copy.deepcopy(model), "dp", C.RATIOS, 0, C.LM_BATCH, C.lm_cpu_namespace())
+    assert fxpass.fuse_elementwise(graph) == {"dropout_add": 0, "act_dropout": 0, "activation": nl}
+    vit = C.vit_model()
+    graph = P.emit_vit(copy.deepcopy(vit), "dp", C.RATIOS, 0, C.LM_BATCH, C.lm_cpu_namespace(), dropout_p=0.2)
+    changed = fxpass.fuse_elementwise(graph)
+    assert changed == {"dropout_add": 2 * C.VIT_SMALL["nlayers"], "act_dropout": C.VIT_SMALL["nlayers"], "activation": 0}
+    assert all(n.args[1] == "gelu" for n in graph.nodes if n.op == "call_function" and n.target is act_dropout)
+    # a dropout whose result is used twice is left alone
+    g = torch.fx.Graph()
+    x, y = g.placeholder("x"), g.placeholder("y")
+    d = g.call_function(F.dropout, (x, 0.1))
+    s1 = g.call_function(operator.add, (y, d))
+    g.output(g.call_function(operator.add, (s1, d)))
+    assert fxpass.fuse_elementwise(g)["dropout_add"] == 0
