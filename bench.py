@@ -899,6 +899,8 @@ def lm_step(args, job, kind, plan, use_graph, dropout_p):
         graph = emit(model, r)
         if not args.lm_no_fuse:
             hap_b200.fxpass.fuse_elementwise(graph)     # dropout + residual add, activation + dropout: one pass each
+        if W > 1 and not args.lm_no_prefetch:
+            hap_b200.fxpass.prefetch_parameter_gathers(graph)   # parameter gathers early, on the side stream
         return torch.fx.GraphModule(model, graph)
 
     if W == 1:
@@ -1251,6 +1253,7 @@ def main():
     ap.add_argument("--lm-batch", type=int, default=0, help="samples per GPU (0: the configuration's 32 / 64 / 16)")
     ap.add_argument("--lm-layers", type=int, default=0, help="0: the configuration's 12 / 12 / 8")
     ap.add_argument("--lm-plan", default="dp_zero", choices=["dp", "dp_zero"])
+    ap.add_argument("--lm-no-prefetch", action="store_true", help="gather sharded parameters where they are used, on the main stream")
     ap.add_argument("--lm-no-fuse", action="store_true", help="run the program as emitted, without the elementwise fusion pass")
     ap.add_argument("--lm-graph", action="store_true", help="capture the training step into a CUDA graph")
     ap.add_argument("--gemm-tokens", type=int, default=8192)

@@ -163,6 +163,43 @@ def replicate(tensor):
     return _Replicate.apply(tensor)
 
 
+class PendingGather:
+    """An all_gather that was issued on the communicator's side stream: its result and the event
+    that marks its completion.  :func:`all_gather_wait` turns it into the tensor."""
+
+    __slots__ = ("tensor", "event")
+
+    def __init__(self, tensor, event):
+        self.tensor, self.event = tensor, event
+
+
+def all_gather_start(tensor, dim, sharding_lengths, rank):
+    """:func:`all_gather` issued on the communicator's side stream, so that it overlaps with whatever
+    the current stream does next.  For gathers whose input is ready early - the ZeRO-style sharded
+    parameters of a program (``hap.rs:2527-2555``), which only change in the optimizer step.  The
+    backward pass (the uneven reduce_scatter of the gradient) then runs on that side stream as well,
+    because autograd runs a node's backward on its forward's stream, and overlaps with the rest of
+    the backward pass.  Returns a :class:`PendingGather`; :func:`all_gather_wait` makes the current
+    stream wait for it.  Collectives stay ordered among themselves (one in flight per communicator)."""
+    comm = get_default_comm()
+    side = comm.side_stream()
+    cur = torch.cuda.current_stream(tensor.device)
+    side.wait_stream(cur)
+    with torch.cuda.stream(side):
+        out = _AllGather.apply(tensor, dim, sharding_lengths, rank, N.MODE_PADDING)
+        event = torch.cuda.Event()
+        event.record(side)
+    return PendingGather(out, event)
+
+
+def all_gather_wait(pending):
+    """The gathered tensor of :func:`all_gather_start`, usable on the current stream."""
+    cur = torch.cuda.current_stream(pending.tensor.device)
+    cur.wait_event(pending.event)
+    pending.tensor.record_stream(cur)
+    return pending.tensor
+
+
 NAMES = ("all_gather", "all_gather_by_group_call", "all_reduce", "reduce_scatter",
          "reduce_scatter_by_group_call", "dynamic_slice", "all_to_all", "replicate")
 

@@ -90,6 +90,7 @@ class Comm:
         self._heap_views: List[Optional[torch.Tensor]] = [None] * self.n_local
         self._heap_cursor = [0] * self.n_local
         self.debug_sync = os.environ.get("HAPX_DEBUG_SYNC", "0") == "1"
+        self._side_stream: Optional[torch.cuda.Stream] = None
 
     # ---- lifecycle -------------------------------------------------------------------
     def destroy(self, group=None) -> None:
@@ -129,6 +130,13 @@ class Comm:
 
     def set_stream_ordering(self, on: bool) -> None:
         N.check(N.lib.hapx_comm_set_stream_ordering(self._h, int(bool(on))))
+
+    def side_stream(self) -> torch.cuda.Stream:
+        """A second stream for collectives that should overlap with the current stream's work (calls on
+        different streams are ordered against each other by the library with an event)."""
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(self.device)
+        return self._side_stream
 
     def set_max_ctas(self, ctas: int) -> None:
         N.check(N.lib.hapx_comm_set_max_ctas(self._h, int(ctas)))

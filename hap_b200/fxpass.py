@@ -66,6 +66,53 @@ def retarget_tensor_ops(graph: torch.fx.Graph, fold_loss: bool = True) -> Dict[s
     return changed
 
 
+def prefetch_parameter_gathers(graph: torch.fx.Graph) -> int:
+    """Issue the all_gathers of sharded PARAMETERS early and on the communicator's side stream.
+
+    The planner gathers a ZeRO-style sharded parameter right where it is used (``hap.rs:2527-2555``), so a
+    step pays one short, latency-bound collective in front of every projection.  A parameter does not
+    change between the optimizer steps, so its gather can start at the top of the program: every node
+    ``all_gather(get_attr(p), dim, L, rank)`` (either entry point) becomes
+    ``collectives.all_gather_start(...)`` at the top of the graph plus ``collectives.all_gather_wait(...)``
+    where the gather stood.  The gathers then run next to the layers before their use, and their backward
+    reduce_scatters next to the remaining backward pass.  Values are unchanged; the gathered weights live
+    from the top of the step instead of from their first use (autograd keeps them until backward anyway).
+    Returns the number of gathers moved."""
+    from . import collectives
+
+    moved = 0
+    anchor = None
+    for node in graph.nodes:
+        if node.op == "placeholder":
+            anchor = node
+    for node in list(graph.nodes):
+        if node.op != "call_function" or getattr(node.target, "__name__", "") not in ("all_gather", "all_gather_by_group_call"):
+            continue
+        if (getattr(node.target, "__module__", "") or "").split(".")[-1] != "collectives":
+            continue
+        src = node.args[0]
+        if not (isinstance(src, torch.fx.Node) and src.op == "get_attr"):
+            continue
+        if anchor is None:
+            with graph.inserting_before(next(iter(graph.nodes))):
+                attr = graph.get_attr(src.target)
+        else:
+            with graph.inserting_after(anchor):
+                attr = graph.get_attr(src.target)
+        with graph.inserting_after(attr):
+            start = graph.call_function(collectives.all_gather_start, (attr,) + tuple(node.args[1:]))
+        anchor = start
+        with graph.inserting_before(node):
+            done = graph.call_function(collectives.all_gather_wait, (start,))
+        node.replace_all_uses_with(done)
+        graph.erase_node(node)
+        if not src.users:
+            graph.erase_node(src)
+        moved += 1
+    graph.lint()
+    return moved
+
+
 def fuse_elementwise(graph: torch.fx.Graph) -> Dict[str, int]:
     """Fold the elementwise neighbours of the dropout sites into single-pass kernels; rewrites ``graph``
     in place and returns how many nodes of each kind were folded.

@@ -144,10 +144,12 @@ class ProcessWorker:
         self.module = module
         self.clip = clip
         self.lr = lr
-        # clip by the local-shard norm + Adam as multi-tensor kernels without a host round trip
-        self.optimizer = self._make_optimizer(list(module.parameters()), lr, clip)
         self.reduce_loss = reduce_loss
         self.comm = comm
+        if comm is not None and comm.world > 1:
+            self._move_gathered_parameters_into_heap()
+        # clip by the local-shard norm + Adam as multi-tensor kernels without a host round trip
+        self.optimizer = self._make_optimizer(list(module.parameters()), lr, clip)
         self.uses_dropout = _program_has_dropout(module)
         self._buckets = []          # (flat tensor in the heap, [parameters])
         if comm is not None:
@@ -158,6 +160,35 @@ class ProcessWorker:
 
     def _optimizer_step(self) -> None:
         self.optimizer.step()
+
+    def _join_side_stream(self) -> None:
+        """Gradients of parameters whose gather ran on the communicator's side stream are produced there
+        (autograd runs a backward node on its forward's stream): the step tail waits for that stream."""
+        from . import collectives
+        comm = self.comm if self.comm is not None else (collectives.get_default_comm() if collectives.has_default_comm() else None)
+        if comm is not None and comm._side_stream is not None:
+            torch.cuda.current_stream(comm.device).wait_stream(comm._side_stream)
+
+    def _move_gathered_parameters_into_heap(self) -> None:
+        """Parameters that the program all-gathers (ZeRO-style shards, ``hap.rs:2527-2555``) are re-homed in
+        the peer-visible heap, so the gather kernels read them in place on every step instead of copying
+        them into the staging area first."""
+        names = []
+        for n in self.module.graph.nodes:
+            if n.op == "call_function" and getattr(n.target, "__name__", "") in ("all_gather", "all_gather_by_group_call", "all_gather_start") \
+                    and isinstance(n.args[0], torch.fx.Node) and n.args[0].op == "get_attr":
+                names.append(n.args[0].target)
+        params = dict(self.module.named_parameters())
+        for name in dict.fromkeys(names):
+            p = params.get(name)
+            if p is None or not p.is_cuda:
+                continue
+            try:
+                home = self.comm.symm_empty(tuple(p.shape), p.dtype)
+            except MemoryError:
+                return                  # the heap is full: the remaining parameters are staged as before
+            home.copy_(p.data)
+            p.data = home
 
     def _build_buckets(self) -> None:
         names = [n.args[0].target for n in self.module.graph.nodes
@@ -202,8 +233,6 @@ class ProcessWorker:
         from . import collectives
         comm = self.comm if self.comm is not None else (collectives.get_default_comm() if collectives.has_default_comm() else None)
         static_in = [t.clone() for t in example_inputs]
-        if comm is not None:
-            comm.set_stream_ordering(False)     # no event may be recorded into the graph and waited on outside it
         try:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
@@ -212,6 +241,10 @@ class ProcessWorker:
                     self.step(*static_in)
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
+            if comm is not None:
+                # calls on different streams stay ordered by an event inside the capture; forget the event of the
+                # eager calls so far, which must not be waited on from a capturing stream
+                comm.set_stream_ordering(True)
             graph = torch.cuda.CUDAGraph()
             before = N.lib.hapx_launch_count()
             calls_before = comm.calls_issued() if comm is not None else 0
@@ -220,7 +253,7 @@ class ProcessWorker:
             calls = (comm.calls_issued() - calls_before) if comm is not None else 0
         finally:
             if comm is not None:
-                comm.set_stream_ordering(True)
+                comm.set_stream_ordering(True)      # and forget the captured event: eager calls must not wait on it
         if comm is not None and comm.world > 1 and calls < 2:
             raise RuntimeError("ProcessWorker.capture: an iteration with fewer than two collectives cannot be replayed safely "
                                "(its flag words would repeat from one replay to the next)")
@@ -254,9 +287,11 @@ class ProcessWorker:
                 loss.backward()
             finally:
                 collectives.defer_replicate(False)
+            self._join_side_stream()
             for flat, _ in self._buckets:
                 self.comm.all_reduce([flat], inplace=True)
         else:
             loss.backward()
+        self._join_side_stream()
         self._optimizer_step()
         return total

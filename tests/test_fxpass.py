@@ -111,3 +111,26 @@ def test_elementwise_fusion_folds_the_dropout_sites():
     s1 = g.call_function(operator.add, (y, d))
     g.output(g.call_function(operator.add, (s1, d)))
     assert fxpass.fuse_elementwise(g)["dropout_add"] == 0
+
+
+def test_parameter_gathers_are_hoisted():
+    from hap_b200 import collectives, fxpass
+    from hap_b200 import plan as P
+    nl = C.LM_SMALL["nlayers"]
+    model = C.lm_model()
+    ns = C.lm_cpu_namespace()
+    ns.collectives = collectives            # the pass looks for this package's (or the reference's) collectives module
+    graph = P.emit_lm(copy.deepcopy(model), "dp_zero", C.RATIOS, 0, C.LM_BATCH, ns)
+    gathers = sum(1 for n in graph.nodes if n.op == "call_function" and n.target is collectives.all_gather)
+    assert gathers == 6 * nl + 2
+    assert fxpass.prefetch_parameter_gathers(graph) == gathers
+    nodes = list(graph.nodes)
+    starts = [i for i, n in enumerate(nodes) if n.op == "call_function" and n.target is collectives.all_gather_start]
+    waits = [i for i, n in enumerate(nodes) if n.op == "call_function" and n.target is collectives.all_gather_wait]
+    first_compute = min(i for i, n in enumerate(nodes) if n.op in ("call_function", "call_method")
+                        and n.target not in (collectives.all_gather_start,))
+    assert len(starts) == len(waits) == gathers and max(starts) < first_compute
+    assert not any(n.op == "call_function" and n.target is collectives.all_gather for n in nodes)
+    # program order of the gathers is kept (all ranks must issue the same sequence of collectives)
+    order = [nodes[i].args[0].target for i in starts]
+    assert order == [nodes[w].args[0].args[0].target for w in waits]

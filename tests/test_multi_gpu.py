@@ -162,6 +162,26 @@ def _spmd_worker(rank, world, store):
     assert got2 == got
     for (name, pa), (_, pb) in zip(worker.module.named_parameters(), bucketed.module.named_parameters()):
         assert torch.equal(pa, pb), name
+    # the same program with its parameter gathers issued early on the side stream (and the elementwise ops fused),
+    # eagerly and replayed from a CUDA graph: the same bits again
+    from hap_b200 import fxpass
+    m3 = copy.deepcopy(model).to(dev)
+    g3 = P.emit_lm(m3, "dp_zero", ratios, rank, C.LM_BATCH)
+    assert fxpass.prefetch_parameter_gathers(g3) > 0
+    fxpass.fuse_elementwise(g3)
+    overlapped = ProcessWorker(torch.fx.GraphModule(m3, g3), reduce_loss=reduce, comm=comm)
+    got3 = float(overlapped.step(tok.to(dev), tgt.to(dev)))
+    assert got3 == got, (got3, got)
+    theirs = dict(overlapped.module.named_parameters())      # the pass reorders the module's parameters: compare by name
+    for name, pa in worker.module.named_parameters():
+        assert torch.equal(pa, theirs[name]), name
+    second = float(worker.step(tok.to(dev), tgt.to(dev)))
+    replay = overlapped.capture(tok.to(dev), tgt.to(dev), warmup=1)         # the warm-up is the second step
+    third = float(worker.step(tok.to(dev), tgt.to(dev)))
+    torch.cuda.synchronize()
+    dist.barrier()
+    # capture itself does not execute: the replay below is the overlapped worker's third step
+    assert abs(float(replay(tok.to(dev), tgt.to(dev))) - third) <= 1e-2 * abs(third) and second > third * 0.5
     comm.check()
     hap_b200.linear_ops.gemm_status()
     dist.barrier()
