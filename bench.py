@@ -590,6 +590,41 @@ def run_sweep(args):
             ts = t.tolist()
         return statistics.median(ts), min(ts)
 
+    def graphed_ms(fn, inner, reps):
+        """Device time per call with the host out of the way: `inner` calls recorded into a CUDA graph and replayed."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream().wait_stream(side)
+        sync()
+        comm.set_stream_ordering(True)          # forget the event of the eager calls: it must not be waited on while capturing
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(max(2, inner)):
+                fn()
+        comm.set_stream_ordering(True)
+        sync()
+        for _ in range(2):
+            graph.replay()
+        sync()
+        ts = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if dist is not None:
+                dist.barrier()
+            a.record()
+            graph.replay()
+            b.record()
+            b.synchronize()
+            ts.append(a.elapsed_time(b) / max(2, inner))
+        if dist is not None:
+            t = torch.tensor(ts, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ts = t.tolist()
+        del graph
+        return statistics.median(ts)
+
     rows = []
     sizes = [1 << k for k in range(10, 31, 2) if (1 << k) <= max_bytes]
     for dtype, dname, es in ((torch.float32, "f32", 4), (torch.bfloat16, "bf16", 2)):
@@ -631,12 +666,27 @@ def run_sweep(args):
                 m = [[L[j] * LC[r] * es for j in range(W)] for r in range(W)]          # bytes r -> j
                 alg_a2a = max(max(sum(m[r][j] for j in range(W) if j != r), sum(m[i][r] for i in range(W) if i != r)) for r in range(W))
                 cases.append(("all_to_all", lambda: comm.all_to_all(a2a_in, 0, 1, L, LC), S * (W - 1) / W, alg_a2a))
+            # the same calls on ordinary torch tensors: every call first copies its input into the staging area
+            staged = {}
+            if S <= (64 << 20) and dtype == torch.float32:
+                t_sh = [s_.clone() for s_ in shards]
+                t_fu = [f_.clone() for f_ in fulls]
+                staged = {"all_gather": lambda: comm.all_gather(t_sh, 0, L, N.MODE_PADDING, out=out),
+                          "reduce_scatter": lambda: comm.reduce_scatter(t_fu, 0, L, N.MODE_PADDING),
+                          "all_reduce": lambda: comm.all_reduce(t_fu, scale=1.0 / W)}
             for name, fn, bus, alg in cases:
                 med, best = timed(fn, reps, inner=inner)
                 row = {"op": name, "dtype": dname, "bytes": S, "world": W, "ms_median": med, "ms_min": best, "calls_per_timing": inner,
                        "busbw_GBps": bus / (med * 1e-3) / 1e9, "alg_GBps": alg / (med * 1e-3) / 1e9}
+                if S <= (256 << 20):
+                    row["graph_ms"] = graphed_ms(fn, inner, max(5, reps // 2))
+                    row["graph_alg_GBps"] = alg / (row["graph_ms"] * 1e-3) / 1e9
+                if name in staged:
+                    row["staged_ms"], _ = timed(staged[name], max(5, reps // 2), warm=2, inner=inner)
                 if not emulated:
                     row["frac_nvlink_900"] = row["alg_GBps"] / NVLINK_NOMINAL_GBS
+                    if "graph_ms" in row:
+                        row["graph_frac_nvlink_900"] = row["graph_alg_GBps"] / NVLINK_NOMINAL_GBS
                     if dtype == torch.float32 or name == "all_reduce":      # the reference's buffers are fp32-only
                         ref = {"all_gather": lambda: gp.all_gather(shards[0], 0, L, rank),
                                "all_gather_by_group_call": lambda: gp.all_gather_by_group_call(shards[0], 0, L, rank),
@@ -650,7 +700,8 @@ def run_sweep(args):
                 rows.append(row)
                 if rank == 0:
                     _print_sweep_row(row)
-            del out, shards, fulls, cases
+            del out, shards, fulls, cases, staged
+            t_sh = t_fu = None
             a2a_in = None
             torch.cuda.empty_cache()
     # Secondary sweep in the reference's own convention (profiler.py:85-104, plot_collective_by_group_call.py:15-23):
@@ -709,6 +760,12 @@ def _print_sweep_row(r):
     extra = ""
     if "frac_nvlink_900" in r:
         extra = f" nvlink {100 * r['frac_nvlink_900']:5.1f}%"
+    if "graph_ms" in r:
+        extra += f"  graph {r['graph_ms']:8.4f} ms"
+        if "graph_frac_nvlink_900" in r:
+            extra += f" ({100 * r['graph_frac_nvlink_900']:5.1f}%)"
+    if "staged_ms" in r:
+        extra += f"  staged {r['staged_ms']:8.4f} ms"
     if "speedup_vs_reference_on_nccl" in r:
         extra += f"  ref/NCCL {r['reference_on_nccl_ms_median']:9.4f} ms (x{r['speedup_vs_reference_on_nccl']:.2f})"
     print(f"{r['op']:30s} {r['dtype']:4s} {r['bytes']:>11d} B  {r['ms_median']:9.4f} ms  bus {r['busbw_GBps']:8.2f} GB/s"

@@ -115,5 +115,15 @@ def ptr_array(ptrs):
     return (C.c_void_p * len(ptrs))(*[C.c_void_p(p) for p in ptrs])
 
 
+_I64_CACHE = {}
+
+
 def i64_array(vals):
-    return (C.c_int64 * len(vals))(*[int(v) for v in vals])
+    """ctypes int64 array of `vals`; sharding-length vectors repeat on every call, so small arrays are cached."""
+    key = tuple(vals)
+    arr = _I64_CACHE.get(key)
+    if arr is None:
+        arr = (C.c_int64 * len(key))(*[int(v) for v in key])
+        if len(_I64_CACHE) < 4096:
+            _I64_CACHE[key] = arr
+    return arr

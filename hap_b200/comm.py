@@ -50,6 +50,13 @@ def _stream(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+def _ptrs1(t: torch.Tensor):
+    """Pointer array of one tensor (the one-rank-per-process case) without a list in between."""
+    arr = (C.c_void_p * 1)()
+    arr[0] = t.data_ptr()
+    return arr
+
+
 class _on_device:
     """``with torch.cuda.device(d)`` costs several microseconds per use; switch only when the
     tensor's device is not the current one (never, with one process per GPU)."""
@@ -221,8 +228,9 @@ class Comm:
         full = list(ref.shape)
         full[dim] = sum(lengths)
         outs = list(out) if out is not None else [torch.empty(full, dtype=ref.dtype, device=t.device) for t in shards]
-        N.check(N.lib.hapx_all_gather(self._h, N.ptr_array([o.data_ptr() for o in outs]),
-                                      N.ptr_array([t.data_ptr() for t in shards]), dtype_code(ref.dtype),
+        one = self.n_local == 1
+        N.check(N.lib.hapx_all_gather(self._h, _ptrs1(outs[0]) if one else N.ptr_array([o.data_ptr() for o in outs]),
+                                      _ptrs1(shards[0]) if one else N.ptr_array([t.data_ptr() for t in shards]), dtype_code(ref.dtype),
                                       _prod(ref.shape[:dim]), _prod(ref.shape[dim + 1:]), N.i64_array(lengths),
                                       mode, _stream(self.device)))
         self._after()
@@ -250,8 +258,9 @@ class Comm:
             shape = list(ref.shape)
             shape[dim] = lengths[r]
             outs.append(torch.empty(shape, dtype=out_dtype, device=ref.device))
-        N.check(N.lib.hapx_reduce_scatter(self._h, N.ptr_array([o.data_ptr() for o in outs]),
-                                          N.ptr_array([t.data_ptr() for t in inputs]), dtype_code(ref.dtype),
+        one = self.n_local == 1
+        N.check(N.lib.hapx_reduce_scatter(self._h, _ptrs1(outs[0]) if one else N.ptr_array([o.data_ptr() for o in outs]),
+                                          _ptrs1(inputs[0]) if one else N.ptr_array([t.data_ptr() for t in inputs]), dtype_code(ref.dtype),
                                           dtype_code(out_dtype), float(scale), _prod(ref.shape[:dim]),
                                           _prod(ref.shape[dim + 1:]), N.i64_array(lengths), mode, _stream(self.device)))
         self._after()
@@ -275,8 +284,9 @@ class Comm:
             outs = inputs
         else:
             outs = [torch.empty(t.shape, dtype=out_dtype, device=t.device) for t in inputs]
-        N.check(N.lib.hapx_all_reduce(self._h, N.ptr_array([o.data_ptr() for o in outs]),
-                                      N.ptr_array([t.data_ptr() for t in inputs]), dtype_code(ref.dtype),
+        one = self.n_local == 1
+        N.check(N.lib.hapx_all_reduce(self._h, _ptrs1(outs[0]) if one else N.ptr_array([o.data_ptr() for o in outs]),
+                                      _ptrs1(inputs[0]) if one else N.ptr_array([t.data_ptr() for t in inputs]), dtype_code(ref.dtype),
                                       dtype_code(out_dtype), float(scale), ref.numel(), _stream(self.device)))
         self._after()
         return outs

@@ -296,10 +296,7 @@ __host__ __device__ __forceinline__ TilePos locate(const Seg* segs, int nseg, un
 }
 
 // ---- bit-exact pull copy ---------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads) pull_copy_kernel(const __grid_constant__ PullParams P) {
-  __shared__ Shared sh;
-  const LocalRank& lr = P.lr[blockIdx.y];
-  begin_collective(P, lr, sh, kCopyTile);
+__device__ __forceinline__ void copy_tiles(const PullParams& P, const LocalRank& lr, Shared& sh) {
   const unsigned lane = threadIdx.x & 31u;
   const unsigned gw = blockIdx.x * kWarps + (threadIdx.x >> 5);
   const unsigned nw = gridDim.x * kWarps;
@@ -344,6 +341,13 @@ __global__ void __launch_bounds__(kThreads) pull_copy_kernel(const __grid_consta
       }
     }
   }
+}
+
+__global__ void __launch_bounds__(kThreads) pull_copy_kernel(const __grid_constant__ PullParams P) {
+  __shared__ Shared sh;
+  const LocalRank& lr = P.lr[blockIdx.y];
+  begin_collective(P, lr, sh, kCopyTile);
+  copy_tiles(P, lr, sh);
   end_collective(P, lr, sh);
 }
 
@@ -413,11 +417,8 @@ __device__ __forceinline__ void store_values(char* d, const float (&f)[K]) {
 }
 
 template <typename InT, typename OutT>
-__global__ void __launch_bounds__(kThreads) pull_reduce_kernel(const __grid_constant__ PullParams P) {
-  __shared__ Shared sh;
+__device__ __forceinline__ void reduce_tiles(const PullParams& P, const LocalRank& lr, Shared& sh) {
   constexpr int K = Num<InT>::K;
-  const LocalRank& lr = P.lr[blockIdx.y];
-  begin_collective(P, lr, sh, kRedTile);
   const unsigned lane = threadIdx.x & 31u;
   const unsigned gw = blockIdx.x * kWarps + (threadIdx.x >> 5);
   const unsigned nw = gridDim.x * kWarps;
@@ -491,7 +492,62 @@ __global__ void __launch_bounds__(kThreads) pull_reduce_kernel(const __grid_cons
       }
     }
   }
+}
+
+template <typename InT, typename OutT>
+__global__ void __launch_bounds__(kThreads) pull_reduce_kernel(const __grid_constant__ PullParams P) {
+  __shared__ Shared sh;
+  const LocalRank& lr = P.lr[blockIdx.y];
+  begin_collective(P, lr, sh, kRedTile);
+  reduce_tiles<InT, OutT>(P, lr, sh);
   end_collective(P, lr, sh);
+}
+
+// ---- all_reduce in one launch -----------------------------------------------------------------
+// R: the reduce of an even split (rank r sums slice r of every input into a peer-visible buffer `mid` at
+// the same heap offset on every rank); G: the gather of the reduced slices.  Between the two, the CTA that
+// finishes a rank's reduce last tells every peer that the slice is complete; a rank gathers once all slices
+// are.  Because a peer announces its slice only after it has read every input, the gather may write into the
+// buffer the input came from (in-place all_reduce).
+template <typename InT, typename OutT>
+__global__ void __launch_bounds__(kThreads) pull_allreduce_kernel(const __grid_constant__ PullParams R, const __grid_constant__ PullParams G) {
+  __shared__ Shared sh;
+  const LocalRank& lr = R.lr[blockIdx.y];
+  const int tid = threadIdx.x, rank = lr.rank;
+  Ctrl* my = reinterpret_cast<Ctrl*>(R.heap[rank]);
+  begin_collective(R, lr, sh, kRedTile);
+  reduce_tiles<InT, OutT>(R, lr, sh);
+  // publish this rank's slice when its last CTA has finished reducing
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence_system();
+    sh.last = (atomicAdd(&my->cta_phase, 1u) == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (sh.last) {
+    if (tid < R.world) st_release_sys(&reinterpret_cast<Ctrl*>(R.heap[tid])->ready[rank], (unsigned long long)R.seq);
+    if (tid == 0) my->cta_phase = 0;
+  }
+  // wait for every rank's slice, then rebuild the segment table for the gather
+  if (tid < R.world) {
+    unsigned long long v;
+    if (!sh.abort && !wait_flag(&my->ready[tid], 0, R.seq, R.timeout_ns, &v)) {
+      sh.abort = 1;
+      report_timeout(my, R.seq, tid, R.host_status);
+    }
+    sh.base[tid] = G.heap[tid] + G.lr[blockIdx.y].src_off;
+    build_seg(G, rank, tid, kCopyTile, sh.segs[tid]);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    unsigned acc = 0;
+    for (int i = 0; i < G.world; ++i) { sh.segs[i].tile_begin = acc; acc += sh.segs[i].n_tiles; }
+    sh.nseg = G.world;
+    sh.total_tiles = sh.abort ? 0u : acc;
+  }
+  __syncthreads();
+  copy_tiles(G, G.lr[blockIdx.y], sh);
+  end_collective(R, lr, sh);
 }
 
 // ---- local helper: copy an input into the staging area ------------------------------------
@@ -516,6 +572,22 @@ static PullKernel reduce_kernel_for(int in_dtype, int out_dtype) {
     if (out_dtype == HAPX_F32) return pull_reduce_kernel<INT, float>;               \
     if (out_dtype == HAPX_BF16) return pull_reduce_kernel<INT, __nv_bfloat16>;      \
     if (out_dtype == HAPX_F16) return pull_reduce_kernel<INT, __half>;              \
+  }
+  HAPX_PICK(HAPX_F32, float)
+  HAPX_PICK(HAPX_BF16, __nv_bfloat16)
+  HAPX_PICK(HAPX_F16, __half)
+#undef HAPX_PICK
+  return nullptr;
+}
+
+typedef void (*AllReduceKernel)(const PullParams, const PullParams);
+
+static AllReduceKernel allreduce_kernel_for(int in_dtype, int out_dtype) {
+#define HAPX_PICK(IN, INT)                                                             \
+  if (in_dtype == IN) {                                                                \
+    if (out_dtype == HAPX_F32) return pull_allreduce_kernel<INT, float>;               \
+    if (out_dtype == HAPX_BF16) return pull_allreduce_kernel<INT, __nv_bfloat16>;      \
+    if (out_dtype == HAPX_F16) return pull_allreduce_kernel<INT, __half>;              \
   }
   HAPX_PICK(HAPX_F32, float)
   HAPX_PICK(HAPX_BF16, __nv_bfloat16)
@@ -621,6 +693,58 @@ static int launch_pull(hapx_comm* c, PullKernel kernel, PullParams& P, int tile_
     HAPX_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), grid, block, args, 0, stream));
   } else {
     kernel<<<grid, block, 0, stream>>>(P);
+    HAPX_CUDA(cudaGetLastError());
+  }
+  count_launch();
+  return HAPX_OK;
+}
+
+static int count_tiles(const PullParams& P, int tile_bytes, unsigned long long* max_tiles) {
+  const bool one_seg = (P.op == OP_SLICE || P.op == OP_UNSLICE || P.op == OP_REDUCE);
+  for (int i = 0; i < P.n_local; ++i) {
+    unsigned long long tiles = 0;
+    for (int p = 0; p < (one_seg ? 1 : P.world); ++p) {
+      Seg s;
+      build_seg(P, P.lr[i].rank, one_seg ? P.lr[i].rank : p, tile_bytes, s);
+      if (s.rows64 >= (1ull << 32) || s.tiles64 >= (1ull << 32)) return fail(HAPX_ERR_EXTENT, "tensor too large for 32-bit tile indices");
+      tiles += s.tiles64;
+    }
+    if (tiles >= (1ull << 32)) return fail(HAPX_ERR_EXTENT, "tensor too large for 32-bit tile indices");
+    *max_tiles = std::max(*max_tiles, tiles);
+  }
+  return HAPX_OK;
+}
+
+// Launch of the fused all_reduce: one wave of CTAs (they wait on each other's ranks in the middle of the kernel).
+static int launch_allreduce(hapx_comm* c, AllReduceKernel kernel, PullParams& R, PullParams& G, cudaStream_t stream) {
+  unsigned long long max_tiles = 0;
+  if (int e = count_tiles(R, kRedTile, &max_tiles)) return e;
+  if (int e = count_tiles(G, kCopyTile, &max_tiles)) return e;
+  int per_sm = 0;
+  {
+    static std::mutex mu;
+    static std::map<const void*, int> cache;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(reinterpret_cast<const void*>(kernel));
+    if (it == cache.end()) {
+      HAPX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0));
+      cache[reinterpret_cast<const void*>(kernel)] = per_sm;
+    } else {
+      per_sm = it->second;
+    }
+  }
+  if (per_sm < 1) return fail(HAPX_ERR_CUDA, "kernel does not fit on an SM");
+  long long cap = (long long)c->sm_count * per_sm;
+  if (c->local_mode) cap = std::max<long long>(1, cap / c->world);
+  if (c->max_ctas > 0) cap = std::min<long long>(cap, c->max_ctas);
+  const long long need = (long long)((max_tiles + kWarps - 1) / kWarps);
+  const int grid_x = (int)std::max<long long>(1, std::min(need, cap));
+  dim3 grid(grid_x, R.n_local), block(kThreads);
+  if (c->local_mode && R.n_local > 1) {
+    void* args[] = {&R, &G};
+    HAPX_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), grid, block, args, 0, stream));
+  } else {
+    kernel<<<grid, block, 0, stream>>>(R, G);
     HAPX_CUDA(cudaGetLastError());
   }
   count_launch();
@@ -804,10 +928,8 @@ int hapx_all_reduce(hapx_comm* c, void* const* dst, const void* const* src, int 
   if (mid_bytes > c->stage_bytes) return fail(HAPX_ERR_STAGING, "all_reduce: staging area too small for the reduced slice");
   const size_t mid_pos = c->stage_bytes - mid_bytes;
   void* mid[HAPX_MAX_WORLD];
-  const void* mid_c[HAPX_MAX_WORLD];
   for (int i = 0; i < c->n_local; ++i) {
     mid[i] = c->heap[c->first_rank + i] + kCtrlBytes + mid_pos;
-    mid_c[i] = mid[i];
     // a staged input must not run into the reduced slice
     const char* s = static_cast<const char*>(src[i]);
     const int r = c->first_rank + i;
@@ -815,8 +937,33 @@ int hapx_all_reduce(hapx_comm* c, void* const* dst, const void* const* src, int 
     if (!in_heap && in_bytes > mid_pos)
       return fail(HAPX_ERR_STAGING, "all_reduce: input of " + std::to_string(in_bytes) + " bytes is outside the peer-visible heap and does not fit the staging area");
   }
-  if (int e = reduce_impl(c, mid, src, in_dtype, out_dtype, scale, 1, 1, L, Pfx, total, 0, stream)) return e;
-  return gather_impl(c, dst, mid_c, es_out, 1, 1, lengths, stream);
+  // one launch: reduce the own slice into `mid`, announce it, gather every rank's slice
+  AllReduceKernel kernel = allreduce_kernel_for(in_dtype, out_dtype);
+  PullParams R, G;
+  init_params(c, R, OP_REDUCE, es_in, es_out);
+  R.A = 1; R.C = 1; R.scale = (float)scale;
+  for (int i = 0; i < HAPX_MAX_WORLD; ++i) { R.L1[i] = L[i]; R.P1[i] = Pfx[i]; }
+  R.tot1 = total;
+  init_params(c, G, OP_GATHER, es_out, es_out);
+  G.A = 1; G.C = 1;
+  fill_prefix(lengths, W, G.L1, G.P1, &G.tot1);
+  CallScope scope{c, stream};
+  if (int e = scope.enter()) return e;
+  for (int i = 0; i < c->n_local; ++i) {
+    const int r = c->first_rank + i;
+    R.lr[i].rank = r;
+    R.lr[i].src = static_cast<const char*>(src[i]);
+    R.lr[i].dst = static_cast<char*>(mid[i]);
+    if (!dst[i]) return fail(HAPX_ERR_ARGUMENT, "null output pointer");
+    if (int e = publish_input(c, i, src[i], in_bytes, true, 0, stream, &R.lr[i].src_off)) return e;
+    G.lr[i].rank = r;
+    G.lr[i].src = static_cast<const char*>(mid[i]);
+    G.lr[i].dst = static_cast<char*>(dst[i]);
+    G.lr[i].src_off = kCtrlBytes + mid_pos;
+  }
+  R.seq = G.seq = next_seq(c);
+  if (int e = launch_allreduce(c, kernel, R, G, stream)) return e;
+  return scope.leave();
 }
 
 int hapx_all_to_all(hapx_comm* c, void* const* dst, const void* const* src, int dtype, int64_t a, int64_t b, int64_t cc,

@@ -29,7 +29,9 @@ constexpr size_t kCtrlBytes = 4096;
 struct Ctrl {
   unsigned long long start[HAPX_MAX_WORLD];  // peer p writes (seq<<40 | offset of its input in its heap)
   unsigned long long done[HAPX_MAX_WORLD];   // peer p writes seq when it has finished reading this rank
+  unsigned long long ready[HAPX_MAX_WORLD];  // all_reduce: peer p writes seq when its reduced slice is complete (and it has read all inputs)
   unsigned int cta_done;                     // CTAs of the running kernel that have finished
+  unsigned int cta_phase;                    // all_reduce: CTAs that have finished reducing
   unsigned int status;                       // 0, or a hapx_status code left by a kernel (as a positive number)
   unsigned long long status_info;            // (seq<<32 | peer) of the wait that ran out
 };
