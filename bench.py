@@ -956,6 +956,8 @@ def lm_step(args, job, kind, plan, use_graph, dropout_p):
         graph = emit(model, r)
         if not args.lm_no_fuse:
             hap_b200.fxpass.fuse_elementwise(graph)     # dropout + residual add, activation + dropout: one pass each
+        if kind == "moe" and not args.lm_no_fuse:
+            hap_b200.fxpass.sparsify_moe(graph)         # dispatch / combine as row gathers instead of dense one-hot contractions
         if W > 1 and not args.lm_no_prefetch:
             hap_b200.fxpass.prefetch_parameter_gathers(graph)   # parameter gathers early, on the side stream
         return torch.fx.GraphModule(model, graph)

@@ -56,6 +56,10 @@ SIGNATURES = {
     "hapx_linear_wgrad": (_int, [_vp, _vp, _vp, _vp, _int, _int, _i64, _i64, _i64, _vp]),
     "hapx_gemm_batched": (_int, [_vp, _vp, _vp, _int, _int, _int] + [_i64] * 14 + [_vp]),
     "hapx_gemm_status": (_int, []),
+    "hapx_moe_index": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "hapx_moe_rows_from_tokens": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
+    "hapx_moe_tokens_from_rows": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
+    "hapx_moe_weight_grad": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "hapx_attention_forward": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp]),
     "hapx_attention_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "hapx_attention_classify_mask": (_int, [_vp, _i64, _vp, _vp]),

@@ -15,7 +15,7 @@ CSRC = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(CSRC)
 ROOT = os.path.dirname(PKG)
 LIB = os.path.join(PKG, "libhapx.so")
-SOURCES = ["hapx_comm.cu", "hapx_collectives.cu", "hapx_gemm_sm100.cu", "hapx_attention.cu", "hapx_attention_fused.cu", "hapx_sgemm.cu", "hapx_optim.cu", "hapx_loss.cu", "hapx_norm.cu", "hapx_dropout.cu", "hapx_sharding.cpp"]
+SOURCES = ["hapx_comm.cu", "hapx_collectives.cu", "hapx_gemm_sm100.cu", "hapx_attention.cu", "hapx_attention_fused.cu", "hapx_sgemm.cu", "hapx_optim.cu", "hapx_loss.cu", "hapx_norm.cu", "hapx_dropout.cu", "hapx_moe.cu", "hapx_sharding.cpp"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

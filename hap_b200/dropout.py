@@ -43,8 +43,28 @@ def advance(device=None) -> None:
     _next_call_id = 0
 
 
+def _dense(*tensors):
+    """The tensors as they are when they share one dense, non-overlapping layout (a permuted view of contiguous
+    memory counts: an elementwise kernel can then walk the storage, and ``empty_like`` keeps the strides, so the
+    layout of, say, expert-major activations survives the op); contiguous copies otherwise."""
+    first = tensors[0]
+    span = sum((n - 1) * st for n, st in zip(first.shape, first.stride())) + 1 if first.numel() else 0
+    if span == first.numel() and all(t.stride() == first.stride() and t.shape == first.shape for t in tensors[1:]) \
+            and torch.empty_like(first).stride() == first.stride():
+        return tensors
+    return tuple(t.contiguous() for t in tensors)
+
+
+def _in_layout(t: torch.Tensor, strides) -> torch.Tensor:
+    """``t`` with exactly these strides (a copy when it has others).  The mask of an element is looked up by
+    its position in memory, so a backward pass must see the gradient in the layout the forward pass used."""
+    if t.stride() == tuple(strides):
+        return t
+    return torch.empty_strided(t.shape, strides, dtype=t.dtype, device=t.device).copy_(t)
+
+
 def _apply(x: torch.Tensor, p: float, call_id: int, out: torch.Tensor = None) -> torch.Tensor:
-    x = x.contiguous()
+    (x,) = _dense(x)
     y = torch.empty_like(x) if out is None else out
     code = N.BF16 if x.dtype == torch.bfloat16 else N.F32
     with _on_device(x.device):
@@ -55,13 +75,14 @@ def _apply(x: torch.Tensor, p: float, call_id: int, out: torch.Tensor = None) ->
 class _Dropout(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, p, call_id):
-        ctx.meta = (p, call_id)
-        return _apply(x, p, call_id)
+        y = _apply(x, p, call_id)
+        ctx.meta = (p, call_id, y.stride())
+        return y
 
     @staticmethod
     def backward(ctx, grad):
-        p, call_id = ctx.meta
-        return _apply(grad, p, call_id), None, None
+        p, call_id, strides = ctx.meta
+        return _apply(_in_layout(grad, strides), p, call_id), None, None
 
 
 def dropout(input: torch.Tensor, p: float = 0.5, training: bool = True, inplace: bool = False) -> torch.Tensor:
@@ -85,9 +106,9 @@ _ACTS = {"relu": 1, "gelu": 2}
 class _DropoutAdd(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, residual, p, call_id):
-        ctx.meta = (p, call_id)
-        x, residual = x.contiguous(), residual.contiguous()
+        x, residual = _dense(x, residual)
         y = torch.empty_like(x)
+        ctx.meta = (p, call_id, y.stride())
         with _on_device(x.device):
             N.check(N.lib.hapx_dropout_add(y.data_ptr(), x.data_ptr(), residual.data_ptr(), _code(x), x.numel(), float(p), call_id,
                                            _stream(x.device)))
@@ -95,15 +116,15 @@ class _DropoutAdd(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad):
-        p, call_id = ctx.meta
-        gx = _apply(grad, p, call_id) if ctx.needs_input_grad[0] else None
+        p, call_id, strides = ctx.meta
+        gx = _apply(_in_layout(grad, strides), p, call_id) if ctx.needs_input_grad[0] else None
         return gx, (grad if ctx.needs_input_grad[1] else None), None, None
 
 
 class _ActDropout(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, act, p, call_id):
-        x = x.contiguous()
+        (x,) = _dense(x)
         y = torch.empty_like(x)
         with _on_device(x.device):
             N.check(N.lib.hapx_act_dropout(y.data_ptr(), x.data_ptr(), _code(x), x.numel(), act, float(p), call_id, _stream(x.device)))
@@ -115,7 +136,7 @@ class _ActDropout(torch.autograd.Function):
     def backward(ctx, grad):
         (saved,) = ctx.saved_tensors
         act, p, call_id = ctx.meta
-        grad = grad.contiguous()
+        grad = _in_layout(grad, saved.stride())       # the layout the forward pass walked
         dx = torch.empty_like(grad)
         with _on_device(grad.device):
             N.check(N.lib.hapx_act_dropout_backward(dx.data_ptr(), grad.data_ptr(), saved.data_ptr(), _code(grad), grad.numel(), act,

@@ -148,6 +148,119 @@ class _Combine(torch.autograd.Function):           # "becd,bsec->bsd"
         return deo, dcomb
 
 
+# ---- sparse dispatch / combine ---------------------------------------------------------------------
+# The dispatch and combine tensors of a gating function hold at most one token per (expert, capacity)
+# slot and at most two slots per token (models.py:477-502), so the two einsums that use them are row
+# gathers.  :func:`sparse_dispatch` / :func:`sparse_combine` compute the same values as
+# ``einsum("bsd,bsec->becd", x, dispatch)`` / ``einsum("becd,bsec->bsd", expert_out, combine)`` for such
+# tensors; :func:`hap_b200.fxpass.sparsify_moe` puts them in place of the einsum nodes whose second
+# operand comes straight out of a gating function.
+def _moe_index(dense: torch.Tensor):
+    b, s, e, c = dense.shape
+    dense = dense.contiguous()
+    dev = dense.device
+    slot_token = torch.empty((b, e * c), dtype=torch.int32, device=dev)
+    slot_weight = torch.empty((b, e * c), dtype=torch.float32, device=dev)
+    token_slot = torch.empty((b, s, 2), dtype=torch.int32, device=dev)
+    token_weight = torch.empty((b, s, 2), dtype=torch.float32, device=dev)
+    with _on_device(dev):
+        N.check(N.lib.hapx_moe_index(dense.data_ptr(), slot_token.data_ptr(), slot_weight.data_ptr(), token_slot.data_ptr(),
+                                     token_weight.data_ptr(), b, s, e * c, _stream(dev)))
+    return slot_token, slot_weight, token_slot, token_weight
+
+
+def _rows_from_tokens(x, slot_token, slot_weight, ec):
+    b, s, d = x.shape
+    x = x.contiguous()
+    rows = torch.empty((b, ec, d), dtype=x.dtype, device=x.device)
+    with _on_device(x.device):
+        N.check(N.lib.hapx_moe_rows_from_tokens(rows.data_ptr(), x.data_ptr(), slot_token.data_ptr(),
+                                                slot_weight.data_ptr() if slot_weight is not None else None, b, s, ec, d, _stream(x.device)))
+    return rows
+
+
+def _tokens_from_rows(rows, token_slot, token_weight, s):
+    b, ec, d = rows.shape
+    rows = rows.contiguous()
+    y = torch.empty((b, s, d), dtype=rows.dtype, device=rows.device)
+    with _on_device(rows.device):
+        N.check(N.lib.hapx_moe_tokens_from_rows(y.data_ptr(), rows.data_ptr(), token_slot.data_ptr(),
+                                                token_weight.data_ptr() if token_weight is not None else None, b, s, ec, d, _stream(rows.device)))
+    return y
+
+
+def _check_sparse(a: torch.Tensor, dense: torch.Tensor, what: str) -> None:
+    for t in (a, dense):
+        if not t.is_cuda:
+            raise RuntimeError(f"{what}: hap_b200 has no CPU path; tensor is on {t.device}")
+        if t.dtype != torch.bfloat16:
+            raise TypeError(f"{what}: bfloat16 only, got {t.dtype}")
+    if a.shape[-1] % 8:
+        raise ValueError(f"{what}: the model dimension must be a multiple of 8")
+
+
+class _SparseDispatch(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, disp):
+        b, s, e, c = disp.shape
+        slot_token, slot_weight, token_slot, token_weight = _moe_index(disp)
+        ctx.save_for_backward(token_slot, token_weight)
+        ctx.meta = (s, e, c)
+        return _rows_from_tokens(x, slot_token, slot_weight, e * c).view(b, e, c, x.shape[2])
+
+    @staticmethod
+    def backward(ctx, g):
+        token_slot, token_weight = ctx.saved_tensors
+        s, e, c = ctx.meta
+        b, d = g.shape[0], g.shape[3]
+        if ctx.needs_input_grad[1]:
+            raise NotImplementedError("sparse_dispatch: the dispatch tensor is a constant of the gating function ((combine > 0), models.py:500)")
+        dx = _tokens_from_rows(g.contiguous().view(b, e * c, d), token_slot, token_weight, s) if ctx.needs_input_grad[0] else None
+        return dx, None
+
+
+class _SparseCombine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, eo, comb):
+        b, e, c, d = eo.shape
+        s = comb.shape[1]
+        slot_token, slot_weight, token_slot, token_weight = _moe_index(comb)
+        eo = eo.contiguous()
+        ctx.save_for_backward(eo, slot_token, slot_weight, token_slot)
+        ctx.meta = (s, e, c)
+        return _tokens_from_rows(eo.view(b, e * c, d), token_slot, token_weight, s)
+
+    @staticmethod
+    def backward(ctx, g):
+        eo, slot_token, slot_weight, token_slot = ctx.saved_tensors
+        s, e, c = ctx.meta
+        b, d = eo.shape[0], eo.shape[3]
+        g = g.contiguous()
+        deo = dcomb = None
+        if ctx.needs_input_grad[0]:
+            deo = _rows_from_tokens(g, slot_token, slot_weight, e * c).view(b, e, c, d)
+        if ctx.needs_input_grad[1]:
+            dcomb = torch.empty((b, s, e, c), dtype=g.dtype, device=g.device)
+            with _on_device(g.device):
+                N.check(N.lib.hapx_moe_weight_grad(dcomb.data_ptr(), eo.data_ptr(), g.data_ptr(), token_slot.data_ptr(), b, s, e * c, d,
+                                                   _stream(g.device)))
+        return deo, dcomb
+
+
+def sparse_dispatch(x: torch.Tensor, dispatch: torch.Tensor) -> torch.Tensor:
+    """``einsum("bsd,bsec->becd", x, dispatch)`` for a gating function's dispatch tensor, as a row gather."""
+    _check_sparse(x, dispatch, "sparse_dispatch")
+    return _SparseDispatch.apply(x, dispatch)
+
+
+def sparse_combine(expert_out: torch.Tensor, combine: torch.Tensor) -> torch.Tensor:
+    """``einsum("becd,bsec->bsd", expert_out, combine)`` for a gating function's combine tensor, as a weighted
+    gather of at most two rows per token.  The gradient w.r.t. ``combine`` is produced at the positions
+    where ``combine`` is non-zero - the only ones a gating function's backward reads."""
+    _check_sparse(expert_out, combine, "sparse_combine")
+    return _SparseCombine.apply(expert_out, combine)
+
+
 def einsum(code: str, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """``torch.einsum(code, a, b)`` for the four MoE contractions of the reference."""
     code = code.replace(" ", "")

@@ -113,6 +113,43 @@ def prefetch_parameter_gathers(graph: torch.fx.Graph) -> int:
     return moved
 
 
+GATING_FUNCTIONS = ("top2_gating", "top_2_gating", "_top_2_gating", "switch_gating", "_switch_gating")
+
+
+def sparsify_moe(graph: torch.fx.Graph) -> int:
+    """Replace the dense dispatch / combine einsums of the MoE layers by row gathers.
+
+    ``einsum("bsd,bsec->becd", x, D)`` and ``einsum("becd,bsec->bsd", y, C)`` (``models.py:356, 364``; emitted at
+    ``hap.rs:2266-2276``) are rewritten to :func:`hap_b200.einsum.sparse_dispatch` / ``sparse_combine`` when D / C
+    is ``getitem(g, 0)`` / ``getitem(g, 1)`` of a call of one of the reference's gating functions
+    (``models.py:441-502``, matched by name), whose outputs hold at most one token per slot and at most two
+    slots per token.  Einsums fed by anything else are left on the dense kernels.  Returns the number of
+    nodes rewritten."""
+    import operator
+    from .einsum import einsum, sparse_combine, sparse_dispatch
+
+    def from_gating(n, index):
+        if not (isinstance(n, torch.fx.Node) and n.op == "call_function" and _is(n.target, operator.getitem)):
+            return False
+        src, idx = n.args
+        return (idx == index and isinstance(src, torch.fx.Node) and src.op == "call_function"
+                and getattr(src.target, "__name__", "") in GATING_FUNCTIONS)
+
+    changed = 0
+    for node in list(graph.nodes):
+        if node.op != "call_function" or not _is(node.target, torch.einsum, einsum) or len(node.args) != 3:
+            continue
+        code = node.args[0].replace(" ", "") if isinstance(node.args[0], str) else None
+        if code == "bsd,bsec->becd" and from_gating(node.args[2], 0):
+            node.target, node.args = sparse_dispatch, (node.args[1], node.args[2])
+            changed += 1
+        elif code == "becd,bsec->bsd" and from_gating(node.args[2], 1):
+            node.target, node.args = sparse_combine, (node.args[1], node.args[2])
+            changed += 1
+    graph.lint()
+    return changed
+
+
 def fuse_elementwise(graph: torch.fx.Graph) -> Dict[str, int]:
     """Fold the elementwise neighbours of the dropout sites into single-pass kernels; rewrites ``graph``
     in place and returns how many nodes of each kind were folded.

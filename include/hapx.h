@@ -208,6 +208,29 @@ int hapx_gemm_batched(void* d, const void* a, const void* b, int out_dtype, int 
  * bounded barrier wait ran out. */
 int hapx_gemm_status(void);
 
+/* Sparse form of the two einsums that move tokens into expert slots and back ("bsd,bsec->becd" and
+ * "becd,bsec->bsd", models.py:353-366) for dense (batch, seq, expert * capacity) tensors as the gating
+ * functions build them (models.py:477-502): every slot of a batch entry holds at most one token, every
+ * token sits in at most two slots.  bfloat16 data, row width D a multiple of 8.
+ *   hapx_moe_index: one pass over dense [B, S, EC]: slot_token [B, EC] (-1 = empty) and slot_weight
+ *       [B, EC]; token_slot [B, S, 2] (-1 = unused) and token_weight [B, S, 2].
+ *   hapx_moe_rows_from_tokens: rows[b, slot, :] = slot_weight * x[b, slot_token, :] (0 for an empty
+ *       slot; slot_weight null = 1).  The dispatch einsum; the gradient of the combine einsum w.r.t.
+ *       the expert outputs (x = the output gradient).
+ *   hapx_moe_tokens_from_rows: y[b, s, :] = sum_k token_weight_k * rows[b, token_slot_k, :]
+ *       (token_weight null = 1).  The combine einsum; the gradient of the dispatch einsum w.r.t. x.
+ *   hapx_moe_weight_grad: d_dense [B, S, EC] = 0 except d_dense[b, s, slot_k(s)] =
+ *       <rows[b, slot_k(s), :], dy[b, s, :]>: the gradient of the combine weights at the positions the
+ *       gating function reads it back from. */
+int hapx_moe_index(const void* dense, int32_t* slot_token, float* slot_weight, int32_t* token_slot, float* token_weight,
+                   int64_t B, int64_t S, int64_t EC, hapx_stream stream);
+int hapx_moe_rows_from_tokens(void* rows, const void* x, const int32_t* slot_token, const float* slot_weight, int64_t B,
+                              int64_t S, int64_t EC, int64_t D, hapx_stream stream);
+int hapx_moe_tokens_from_rows(void* y, const void* rows, const int32_t* token_slot, const float* token_weight, int64_t B,
+                              int64_t S, int64_t EC, int64_t D, hapx_stream stream);
+int hapx_moe_weight_grad(void* d_dense, const void* rows, const void* dy, const int32_t* token_slot, int64_t B, int64_t S,
+                         int64_t EC, int64_t D, hapx_stream stream);
+
 /* ---- multi-head self-attention on a batch shard ---------------------------------------------
  * Replace the attention core of F.multi_head_attention_forward as emitted at hap.rs:1297-1329
  * (query = key = value, packed in-projection, no bias_k/bias_v, no key padding mask; only the

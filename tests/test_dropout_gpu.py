@@ -136,3 +136,31 @@ def test_act_dropout_equals_the_separate_ops_given_the_mask(act, dtype, n, p):
     if act == "relu":       # exact: one rounding of max(x, 0) * scale, and the gradient passes exactly where the output is non-zero
         assert torch.equal(y.detach(), (torch.relu(x.detach().float()) * mask * scale).to(dtype))
         assert torch.equal(x.grad, torch.where(y.detach() != 0, gy.float() * scale, torch.zeros((), device=DEV)).to(dtype))
+
+
+@pytest.mark.parametrize("act", ["relu", "gelu"])
+def test_permuted_views_keep_their_layout_and_their_mask(act):
+    """A dense permuted view (the expert-major activations of the MoE layers) goes through without a copy,
+    comes out with the same strides, and the backward pass applies the forward's mask whatever layout the
+    incoming gradient has."""
+    D.manual_seed(8, DEV)
+    D.advance(DEV)
+    base = torch.randn(6, 4, 5, 16, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).to(DEV)
+    x = base.permute(1, 0, 2, 3).requires_grad_(True)            # (b, e, c, h) view of (e, b, c, h) memory
+    y = D.act_dropout(x, act, 0.25)
+    call_id = D._next_call_id
+    assert y.stride() == x.stride()
+    y2 = D.act_dropout(x.detach().contiguous().requires_grad_(True), act, 0.0)      # the bare activation, other layout
+    kept = (y.detach() != 0) | (y2.detach() == 0)
+    torch.testing.assert_close(torch.where(y.detach() != 0, y.detach().float() * 0.75, y2.detach().float()), y2.detach().float(), rtol=1e-2, atol=1e-2)
+    g = torch.randn(4, 6, 5, 16, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).to(DEV)     # contiguous gradient
+    y.backward(g)
+    dropped = (y.detach() == 0) & (y2.detach() != 0)
+    assert float(x.grad[dropped].abs().max()) == 0.0 if bool(dropped.any()) else True
+    z = D.dropout(x.detach().requires_grad_(True), 0.5)
+    zid = D._next_call_id
+    assert z.stride() == x.stride()
+    xin = x.detach().requires_grad_(True)
+    z = D.dropout(xin, 0.5)
+    z.backward(torch.ones(4, 6, 5, 16, dtype=torch.bfloat16, device=DEV))
+    assert torch.equal(xin.grad != 0, z.detach() != 0) or bool((xin.detach() == 0).any())

@@ -83,3 +83,38 @@ def test_moe_block_chain_matches_oracle():
 def test_unsupported_code_raises():
     with pytest.raises(NotImplementedError):
         einsum("ab,bc->ac", torch.ones(8, 8, device=DEV, dtype=torch.bfloat16), torch.ones(8, 8, device=DEV, dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("b,s,e,c,d", [(2, 64, 4, 20, 64), (3, 96, 32, 20, 1024), (1, 17, 5, 6, 8)])
+def test_sparse_dispatch_and_combine_equal_the_dense_einsums(b, s, e, c, d):
+    """Gating-shaped dispatch / combine tensors (at most one token per slot, two slots per token) through the
+    gather kernels against float64 einsums; dispatch is exact (a pure row move)."""
+    from hap_b200.einsum import sparse_combine, sparse_dispatch
+    from hap_b200.plan import top2_gating
+    g = torch.Generator().manual_seed(b * 1000 + s)
+    x = torch.randn(b, s, d, generator=g).to(torch.bfloat16)
+    gate_w = (torch.randn(d, e, generator=g) * d ** -0.5).to(torch.bfloat16)
+    disp, comb = top2_gating(x, gate_w, e, c)
+    assert int((disp.sum(dim=1) > 1).sum()) == 0 and int((disp.flatten(2).sum(dim=2) > 2).sum()) == 0
+    xd = x.to(DEV).requires_grad_(True)
+    got = sparse_dispatch(xd, disp.to(DEV))
+    want = torch.einsum("bsd,bsec->becd", x.double(), disp.double())
+    assert torch.equal(got.detach().cpu().double(), want)
+    w1 = torch.randn(b, e, c, d, generator=g).to(torch.bfloat16)
+    got.backward(w1.to(DEV))
+    want_dx = torch.einsum("becd,bsec->bsd", w1.double(), disp.double())
+    torch.testing.assert_close(xd.grad.cpu().double(), want_dx, rtol=1e-2, atol=1e-2)
+    eo = torch.randn(b, e, c, d, generator=g).to(torch.bfloat16)
+    eod, combd = eo.to(DEV).requires_grad_(True), comb.to(DEV).requires_grad_(True)
+    y = sparse_combine(eod, combd)
+    ref_eo, ref_comb = eo.double().requires_grad_(True), comb.double().requires_grad_(True)
+    ref = torch.einsum("becd,bsec->bsd", ref_eo, ref_comb)
+    torch.testing.assert_close(y.detach().cpu().double(), ref.detach(), rtol=1e-2, atol=1e-2)
+    gy = torch.randn(b, s, d, generator=g).to(torch.bfloat16)
+    y.backward(gy.to(DEV))
+    ref.backward(gy.double())
+    torch.testing.assert_close(eod.grad.cpu().double(), ref_eo.grad, rtol=1e-2, atol=1e-2)
+    # the gradient of the combine weights where the gating function reads it: at the non-zero positions
+    nz = comb != 0
+    torch.testing.assert_close(combd.grad.cpu().double()[nz], ref_comb.grad[nz], rtol=2e-2, atol=2e-2 * float(ref_comb.grad[nz].abs().max()))
+    assert float(combd.grad.cpu()[~nz].abs().max()) == 0.0

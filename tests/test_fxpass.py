@@ -134,3 +134,21 @@ def test_parameter_gathers_are_hoisted():
     # program order of the gathers is kept (all ranks must issue the same sequence of collectives)
     order = [nodes[i].args[0].target for i in starts]
     assert order == [nodes[w].args[0].args[0].target for w in waits]
+
+
+def test_moe_einsums_fed_by_a_gating_function_become_gathers():
+    from hap_b200 import fxpass
+    from hap_b200 import plan as P
+    from hap_b200.einsum import sparse_combine, sparse_dispatch
+    moe = C.moe_model()
+    g = P.emit_moe(copy.deepcopy(moe), C.RATIOS, 0, C.LM_BATCH, C.moe_cpu_namespace())
+    nl = C.MOE_SMALL["nlayers"]
+    assert fxpass.sparsify_moe(g) == 2 * nl
+    targets = [n.target for n in g.nodes if n.op == "call_function"]
+    assert targets.count(sparse_dispatch) == nl and targets.count(sparse_combine) == nl
+    assert targets.count(torch.einsum) == 2 * nl          # the two expert contractions stay dense
+    # an einsum whose second operand is not a gating output is left alone
+    g2 = torch.fx.Graph()
+    x, d = g2.placeholder("x"), g2.placeholder("d")
+    g2.output(g2.call_function(torch.einsum, ("bsd,bsec->becd", x, d)))
+    assert fxpass.sparsify_moe(g2) == 0

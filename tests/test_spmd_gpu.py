@@ -321,3 +321,37 @@ def test_full_width_single_layer_step_matches_cpu_replay(kind):
         hap_b200.linear_ops.gemm_status()
     finally:
         comm.destroy()
+
+
+def test_moe_step_with_sparse_dispatch_follows_the_dense_program():
+    """The expert-parallel program after fxpass.sparsify_moe (dispatch / combine as row gathers) and
+    fxpass.fuse_elementwise must walk the same loss trajectory as the program as emitted."""
+    import copy
+    from hap_b200 import fxpass
+    from hap_b200 import plan as P
+    model = C.moe_model(torch.bfloat16)
+    tok, tgt = C.lm_batch()
+
+    def modules(rewrite):
+        mods = []
+        for r in range(2):
+            m = copy.deepcopy(model).to(DEV)
+            g = P.emit_moe(m, C.RATIOS, r, C.LM_BATCH)
+            if rewrite:
+                assert fxpass.sparsify_moe(g) == 2 * C.MOE_SMALL["nlayers"]
+                fxpass.fuse_elementwise(g)
+            mods.append(torch.fx.GraphModule(m, g))
+        return mods
+
+    comm = hap_b200.local_comm(2, DEV, stage_bytes=16 << 20, heap_bytes=32 << 20)
+    try:
+        dense = LockstepWorld(modules(False), hap_b200.LocalCollectives(comm))
+        sparse = LockstepWorld(modules(True), hap_b200.LocalCollectives(comm))
+        feed = [(tok.to(DEV), tgt.to(DEV))] * 2
+        for it in range(3):
+            a, b = float(dense.step(feed)), float(sparse.step(feed))
+            assert abs(a - b) <= 1e-2 * abs(a), (it, a, b)
+        comm.check()
+        hap_b200.linear_ops.gemm_status()
+    finally:
+        comm.destroy()
