@@ -1311,7 +1311,7 @@ def main():
     ap.add_argument("--lm-model", default="lm", choices=["lm", "vit", "moe"], help="which program the lm workload steps")
     ap.add_argument("--lm-batch", type=int, default=0, help="samples per GPU (0: the configuration's 32 / 64 / 16)")
     ap.add_argument("--lm-layers", type=int, default=0, help="0: the configuration's 12 / 12 / 8")
-    ap.add_argument("--lm-plan", default="dp_zero", choices=["dp", "dp_zero"])
+    ap.add_argument("--lm-plan", default="dp_zero", choices=["dp", "dp_zero", "tp"])
     ap.add_argument("--lm-no-prefetch", action="store_true", help="gather sharded parameters where they are used, on the main stream")
     ap.add_argument("--lm-no-fuse", action="store_true", help="run the program as emitted, without the elementwise fusion pass")
     ap.add_argument("--lm-graph", action="store_true", help="capture the training step into a CUDA graph")

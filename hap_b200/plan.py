@@ -191,7 +191,9 @@ def _lm_forward(m, tokens, targets, ns, emit, ratios, rank, plan, dropout_p=0.0)
                 obj = getattr(obj, part)
             return obj
         node = emit.get_attr(name)
-        if plan == "dp_zero" and shardable:
+        if name in getattr(m, "_column_parallel", ()):
+            return node                  # column-parallel weight or bias: the in-place shard itself (hap.rs:2591-2593)
+        if plan in ("dp_zero", "tp") and shardable and name in m._full_extent:
             # ZeRO-style: the parameter lives sharded on dim 0 and is gathered where it is used
             # (hap.rs:2527-2555); backward of the gather is the uneven reduce_scatter of its gradient
             full = m._full_extent[name]
@@ -216,9 +218,23 @@ def _lm_forward(m, tokens, targets, ns, emit, ratios, rank, plan, dropout_p=0.0)
                    out_proj_bias=param(f"l{i}_out_b"), attn_mask=mask)
         x = call(operator.add, x, drop(call(operator.getitem, att, 0)))
         h = call(_ln(ns), x, (E,), param(f"l{i}_ln2_w"), param(f"l{i}_ln2_b"))
-        h = call(linear, h, param(f"l{i}_w1", True), param(f"l{i}_b1", True))
-        h = drop(call(F.relu, h))
-        h = call(linear, h, param(f"l{i}_w2", True), param(f"l{i}_b2"))
+        if plan == "tp":
+            # the FFN column-parallel (hap.rs:2807-2816): every rank multiplies the WHOLE batch by its rows of the
+            # weight, so the batch shards are gathered first (re-sharding batch -> replicated, hap.rs:2631-2653),
+            # the output columns are gathered on the last dimension before the activation (an activation's output
+            # is not communicatable, hap.rs:1102, 1432), and the own batch shard is cut out again at the end
+            lb, l_ffn, l_e = m._tp_lengths
+            h = emit.call_function(col.all_gather, (h, 1, lb, rank))                                   # (S, B, E)
+            z = call(linear, h, param(f"l{i}_w1"), param(f"l{i}_b1"))                                  # (S, B, ffn_r)
+            z = emit.call_function(col.all_gather, (z, 2, l_ffn, rank))                                # (S, B, ffn)
+            z = drop(call(F.relu, z))
+            o = call(linear, z, param(f"l{i}_w2"), param(f"l{i}_b2"))                                  # (S, B, E_r)
+            o = emit.call_function(col.all_gather, (o, 2, l_e, rank))                                  # (S, B, E)
+            h = emit.call_function(col.dynamic_slice, (o, 1, lb, rank))                                # (S, B_r, E)
+        else:
+            h = call(linear, h, param(f"l{i}_w1", True), param(f"l{i}_b1", True))
+            h = drop(call(F.relu, h))
+            h = call(linear, h, param(f"l{i}_w2", True), param(f"l{i}_b2"))
         x = call(operator.add, x, drop(h))
     x = call(_ln(ns), x, (E,), param("lnf_w"), param("lnf_b"))
     logits = call(linear, x, param("dec_w", True), param("dec_b", True))  # (S, B, V)
@@ -237,12 +253,18 @@ def emit_lm(model: TransformerLM, plan: str, ratios: Sequence[float], rank: int,
     ``"dp_zero"`` - as above, but attention and FFN weights, the first FFN bias and the decoder live
                     sharded on dim 0 by ``ratios`` (cut in place on the module) and are all-gathered
                     at their use; their gradients come back through the uneven reduce_scatter.
+    ``"tp"``      - hybrid: attention data parallel on the batch shards (the attention node is only ever batch-
+                    sharded, ``hap.rs:2903-2926``) with ZeRO-style projection weights as in ``"dp_zero"``; the FFN
+                    column-parallel (``hap.rs:2807-2816``): ``w1``/``b1``/``w2``/``b2`` sharded on dim 0 for good,
+                    the batch gathered in front of it, the output columns gathered on the LAST dimension
+                    (strided shards of 154 ... 676 columns under the r8 ratios) and the own batch shard cut out
+                    afterwards; the decoder ZeRO-style.
     ``dropout_p`` > 0 adds the reference's dropout (``config.py:33``): on the attention probabilities
     (the attention node's ``dropout_p``, ``hap.rs:1257, 1307``) and as ``F.dropout`` nodes after the
     attention block, the FFN activation and the FFN.
     """
     ns = ns or default_namespace()
-    if plan not in ("dp", "dp_zero"):
+    if plan not in ("dp", "dp_zero", "tp"):
         raise ValueError(f"unknown plan {plan!r}")
     g = torch.fx.Graph()
     tokens, targets = g.placeholder("tokens"), g.placeholder("targets")
@@ -250,8 +272,18 @@ def emit_lm(model: TransformerLM, plan: str, ratios: Sequence[float], rank: int,
     tok_r = g.call_function(operator.getitem, (g.call_method("split", (tokens, lb, 0)), rank))
     tgt_r = g.call_function(operator.getitem, (g.call_method("split", (targets, lb, 0)), rank))
     model._full_extent = {}
-    if plan == "dp_zero":
-        names = [n for i in range(model.nlayers) for n in (f"l{i}_in_w", f"l{i}_in_b", f"l{i}_out_w", f"l{i}_w1", f"l{i}_b1", f"l{i}_w2")]
+    model._column_parallel = set()
+    if plan == "tp":
+        d_ffn = model.l0_w1.shape[0]
+        model._tp_lengths = (lb, sharding_round(d_ffn, ratios), sharding_round(model.d_model, ratios))
+        for i in range(model.nlayers):
+            for n, extent in ((f"l{i}_w1", d_ffn), (f"l{i}_b1", d_ffn), (f"l{i}_w2", model.d_model), (f"l{i}_b2", model.d_model)):
+                shard_parameter_(model, n, sharding_round(extent, ratios), 0, rank)
+                model._column_parallel.add(n)
+    if plan in ("dp_zero", "tp"):
+        names = [n for i in range(model.nlayers) for n in (f"l{i}_in_w", f"l{i}_in_b", f"l{i}_out_w")]
+        if plan == "dp_zero":
+            names += [n for i in range(model.nlayers) for n in (f"l{i}_w1", f"l{i}_b1", f"l{i}_w2")]
         names += ["dec_w", "dec_b"]
         for n in names:
             full = getattr(model, n).shape[0]
@@ -371,6 +403,7 @@ def emit_vit(model: ViT, plan: str, ratios: Sequence[float], rank: int, batch: i
     img_r = g.call_function(operator.getitem, (g.call_method("split", (images, lb, 0)), rank))
     lab_r = g.call_function(operator.getitem, (g.call_method("split", (labels, lb, 0)), rank))
     model._full_extent = {}
+    model._column_parallel = set()
     if plan == "dp_zero":
         names = [n for i in range(model.nlayers) for n in (f"l{i}_in_w", f"l{i}_in_b", f"l{i}_out_w", f"l{i}_w1", f"l{i}_b1", f"l{i}_w2")]
         names += ["patch_w", "head_w", "head_b"]

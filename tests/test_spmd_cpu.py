@@ -85,7 +85,7 @@ def test_two_gloo_processes_match_the_lockstep_replay(plan):
                 torch.testing.assert_close(got["params"][name], p.detach(), rtol=1e-5, atol=1e-6)
 
 
-@pytest.mark.parametrize("plan", ["dp", "dp_zero"])
+@pytest.mark.parametrize("plan", ["dp", "dp_zero", "tp"])
 def test_language_model_programs_reproduce_the_unsharded_model(plan):
     """Transformer LM (pre-LN, causal MHA, summed NLL): data parallel, and data parallel with
     ZeRO-style dim-0 sharded weights gathered at use (hap.rs:2527-2555)."""
@@ -109,7 +109,11 @@ def test_language_model_programs_reproduce_the_unsharded_model(plan):
                 g = torch.split(g, sharding_round(g.shape[0], C.RATIOS), dim=0)[r]
                 n_sharded += 1
             torch.testing.assert_close(p.grad, g, rtol=1e-3, atol=1e-4)
-    assert (n_sharded > 0) == (plan == "dp_zero")
+    assert (n_sharded > 0) == (plan in ("dp_zero", "tp"))
+    if plan == "tp":      # the FFN is column-parallel: gathers on the last dimension and on the batch dimension, a slice back
+        names = [getattr(n.target, "__name__", "") for n in world.modules[0].graph.nodes if n.op == "call_function"]
+        nl = C.LM_SMALL["nlayers"]
+        assert names.count("dynamic_slice") == nl and names.count("all_gather") == 3 * nl + 3 * nl + 2
 
 
 @pytest.mark.parametrize("plan", ["dp", "dp_zero"])

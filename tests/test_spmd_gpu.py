@@ -78,7 +78,7 @@ def test_training_step_matches_cpu_replay(plan, dtype, tol):
         comm.destroy()
 
 
-@pytest.mark.parametrize("plan", ["dp", "dp_zero"])
+@pytest.mark.parametrize("plan", ["dp", "dp_zero", "tp"])
 def test_language_model_step_matches_cpu_replay(plan):
     """Transformer LM step in bf16: package linear + attention + collectives on the GPU (2 virtual
     ranks) against the same fx programs replayed on the CPU in bf16 with torch's own ops."""
@@ -267,10 +267,10 @@ def _full_width_case(kind):
     torch.manual_seed(39)
     g = torch.Generator().manual_seed(2024)
     B = 8
-    if kind == "lm":
+    if kind in ("lm", "lm_tp"):
         model = P.TransformerLM(nlayers=1)
         inputs = (torch.randint(0, 33278, (B, 256), generator=g), torch.randint(0, 33278, (B, 256), generator=g))
-        emit = lambda m, r, ns: P.emit_lm(m, "dp_zero", C.RATIOS, r, B, ns)
+        emit = lambda m, r, ns: P.emit_lm(m, "tp" if kind == "lm_tp" else "dp_zero", C.RATIOS, r, B, ns)
         cpu_ns = C.lm_cpu_namespace()
     elif kind == "vit":
         model = P.ViT(nlayers=1)
@@ -294,7 +294,7 @@ def _full_width_case(kind):
     return modules, cpu_ns, inputs
 
 
-@pytest.mark.parametrize("kind", ["lm", "vit", "moe"])
+@pytest.mark.parametrize("kind", ["lm", "lm_tp", "vit", "moe"])
 def test_full_width_single_layer_step_matches_cpu_replay(kind):
     modules, cpu_ns, inputs = _full_width_case(kind)
     cpu = CpuLockstepWorld(modules(cpu_ns, "cpu", torch.float32), OracleCollectives())
