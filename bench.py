@@ -643,7 +643,7 @@ def run_sweep(args):
                 shards.append(sh)
                 fulls.append(fu)
             out = [torch.empty(ROWS, cols, dtype=dtype, device=dev) for _ in ranks]
-            reps = 20 if S <= (256 << 20) else 5
+            reps = (20 if S <= (256 << 20) else 5) if not args.sweep_quick else (8 if S <= (256 << 20) else 3)
             inner = 10 if S <= (64 << 20) else 2
             s_r = [L[r] * cols * es for r in range(W)]
             alg_ag = max(max(s_r[r] * (W - 1), S - s_r[r]) for r in range(W))
@@ -709,7 +709,7 @@ def run_sweep(args):
     # from the even split to 0.95 and the rest shared evenly.
     cols = 4096
     for max_ratio in [1.0 / W, 0.25, 0.5, 0.75, 0.95]:
-        if max_ratio < 1.0 / W - 1e-9:
+        if max_ratio < 1.0 / W - 1e-9 or args.sweep_quick:
             continue
         raw = [max_ratio] + [(1.0 - max_ratio) / (W - 1)] * (W - 1)
         LS = hap_b200.sharding_round(cols, [x / sum(raw) for x in raw])
@@ -1305,6 +1305,7 @@ def main():
     ap.add_argument("--no-spmd-step", action="store_true", help="default run: skip the Transformer-LM training step")
     ap.add_argument("--lm-dropout", type=float, default=0.1, help="dropout of the lm workload (the reference trains with 0.1)")
     ap.add_argument("--sweep", action="store_true", help="size sweep instead of the single JSON line")
+    ap.add_argument("--sweep-quick", action="store_true", help="fewer repetitions per size and no dim-1 skew sweep")
     ap.add_argument("--sweep-out", default="", help="write the sweep's rows to this JSON file")
     ap.add_argument("--sweep-max-mib", type=int, default=1024)
     ap.add_argument("--workload", default="collectives", choices=["collectives", "gemm", "lm", "ops"])

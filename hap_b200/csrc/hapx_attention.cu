@@ -7,7 +7,6 @@
 // of the tensor maps.  The contractions run on the batched tcgen05 GEMM (hapx_gemm_sm100.cu):
 //
 //   forward : S = Q K^T (fp32)  ->  P = softmax(scale * S + mask) (bf16, kept for backward)  ->  O = P V
-//             (for 128 < L <= 256 the softmax is the epilogue of the S GEMM: scores stay in tensor memory)
 //   backward: dV = P^T dO;  dP = dO V^T (fp32);  dS = scale * P * (dP - rowsum(dP * P));  dQ = dS K;  dK = dS^T Q
 //
 // The softmax kernels keep one row per warp in registers (L <= 1024).
@@ -157,18 +156,6 @@ __global__ void __launch_bounds__(256) softmax_bwd_kernel(const __nv_bfloat16* _
   }
 }
 
-// flag = 1 when mask[q][k] is 0 for k <= q and -inf for k > q (the language-model mask), else 0.
-__global__ void __launch_bounds__(1024) classify_mask_kernel(const float* __restrict__ mask, int L, unsigned* flag) {
-  int ok = 1;
-  for (long long e = threadIdx.x; e < (long long)L * L; e += blockDim.x) {
-    const int q = (int)(e / L), k = (int)(e - (long long)q * L);
-    const float v = mask[e];
-    ok &= (k <= q) ? (v == 0.f) : (v == -INFINITY);
-  }
-  ok = __syncthreads_and(ok);
-  if (threadIdx.x == 0) *flag = ok ? 1u : 0u;
-}
-
 static int check(long long L, long long N, long long H, long long D) {
   if (L < 0 || N < 0 || H < 1 || D < 1) return fail(HAPX_ERR_EXTENT, "attention: negative extent");
   if (L > 32 * kMaxPerLane) return fail(HAPX_ERR_EXTENT, "attention: sequence length above 1024 is not supported");
@@ -197,23 +184,6 @@ int hapx_attention_forward(void* out, void* probs, void* scores_ws, const void* 
   const Operand Vmn{base + 2 * E, true, row_qkv, D, 3 * E};
   const Operand S{scores_ws, false, Lp, L * Lp, H * L * Lp}, P{probs, false, Lp, L * Lp, H * L * Lp};
   const Operand O{out, false, N * E, D, E};
-  // Optional (HAPX_FUSED_SOFTMAX=1): when the whole score row fits one accumulator tile the softmax can
-  // run in the score GEMM's epilogue, so the fp32 scores never leave tensor memory.  Measured on the
-  // Transformer-LM shapes it is slower than the separate kernel (four epilogue warps per SM do all the
-  // exponentials: 160 us against 105 + 40 us per layer), so it is off by default.
-  static const bool fused = std::getenv("HAPX_FUSED_SOFTMAX") != nullptr;
-  if (fused && L > 128 && L <= 256) {
-    unsigned* flag = nullptr;
-    if (mask) {  // let the device find out whether the mask tensor is just the causal mask; no host sync
-      if (int e = gemm::scratch_flag(&flag)) return e;
-      attn::classify_mask_kernel<<<1, 1024, 0, stream>>>(mask, (int)L, flag);
-      HAPX_CUDA(cudaGetLastError());
-      count_launch();
-    }
-    const gemm::RowSoftmax sm{1.0f / sqrtf((float)D), causal, mask, flag};
-    if (int e = gemm::gemm_bf16(P, 0, Q, K, nullptr, 0, L, L, D, (int)H, (int)N, stream, &sm)) return e;
-    return gemm::gemm_bf16(O, 0, P, Vmn, nullptr, 0, L, D, L, (int)H, (int)N, stream);
-  }
   // S[b] = Q[b] K[b]^T   (fp32)
   if (int e = gemm::gemm_bf16(S, 1, Q, K, nullptr, 0, L, L, D, (int)H, (int)N, stream)) return e;
   const long long rows = N * H * L;

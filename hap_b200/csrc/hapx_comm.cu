@@ -33,10 +33,6 @@ static int check_sizes(int world, size_t heap_bytes, size_t stage_bytes) {
 }
 
 static int common_init(hapx_comm* c) {
-  if (const char* e = std::getenv("HAPX_TILE_STREAMS_LOG2")) {  // tuning knob, 0..10
-    int v = std::atoi(e);
-    if (v >= 0 && v <= 10) c->order_log2 = v;
-  }
   if (const char* e = std::getenv("HAPX_TIMEOUT_MS")) {  // default bound of the device-side waits on peers
     long v = std::atol(e);
     if (v >= 1 && v <= 0x7fffffffL) c->timeout_ms = (int)v;

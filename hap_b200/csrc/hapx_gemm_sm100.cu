@@ -60,11 +60,6 @@ struct Params {
   int batch, batch_in;
   long long d_stride_in, d_stride_out;
   int a_shared_out, b_shared_out;   // operand does not depend on b_out (e.g. expert weights): its maps get coordinate 0
-  // row-softmax epilogue (attention scores that fit one column tile): D = softmax(scale * acc + mask)
-  int softmax, sm_causal;
-  float sm_scale;
-  const float* sm_mask;             // additive [M][N] fp32 or null
-  const unsigned* sm_mask_is_causal; // device word: non-zero when sm_mask is exactly the causal mask (then it is not read)
 };
 
 using namespace tc;   // PTX wrappers (hapx_tc.h)
@@ -284,103 +279,6 @@ __device__ __forceinline__ void drain_tile(const Params& p, const CUtensorMap* t
   }
 }
 
-
-// Epilogue for attention scores whose whole row lies in this tile (N <= BN): the thread that owns
-// row q reads the accumulator row twice from tensor memory - first for the running maximum and the
-// sum of exponentials, then to write exp(x - max) / sum as bf16 through the staging tile and a bulk
-// tensor store - so the fp32 scores never touch HBM.  x = scale * acc + mask[q][col]; columns
-// after q are dropped when `sm_causal` is set.
-template <int BN>
-__device__ __forceinline__ void drain_tile_softmax(const Params& p, const CUtensorMap* tmD, unsigned char* stage_gen,
-                                                   unsigned stage_u32, unsigned t_row, int m0, int bi, int bo, int q, int lane,
-                                                   int& buf) {
-  const int row = m0 + q * 32 + lane;          // query index inside this (batch, head) matrix
-  const float k = p.sm_scale * 1.4426950408889634f;   // exp(x) = exp2(x * log2 e)
-  const bool mask_causal = p.sm_mask_is_causal != nullptr && *p.sm_mask_is_causal != 0u;
-  const float* mrow = (p.sm_mask != nullptr && !mask_causal && row < p.M) ? p.sm_mask + (long long)row * p.N : nullptr;
-  const int last = (p.sm_causal || mask_causal) ? min(row, p.N - 1) : p.N - 1;   // last column that takes part
-  // three sweeps over the accumulator row in tensor memory (cheap to re-read): maximum, sum of
-  // exponentials, normalised output - one exponential per element in each of the last two
-  float mx = -INFINITY, sum = 0.f;
-#pragma unroll 1
-  for (int c0 = 0; c0 < BN; c0 += 32) {
-    if (c0 >= p.N) break;
-    unsigned r[32];
-    tmem_ld_32x32(t_row + (unsigned)c0, r);
-    tmem_ld_wait();
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const int col = c0 + j;
-      if (col <= last && row < p.M) {
-        float x = __uint_as_float(r[j]) * k;
-        if (mrow) x += mrow[col] * 1.4426950408889634f;
-        mx = fmaxf(mx, x);
-      }
-    }
-  }
-  if (mx == -INFINITY) mx = 0.f;               // nothing takes part: all outputs become 0
-#pragma unroll 1
-  for (int c0 = 0; c0 < BN; c0 += 32) {
-    if (c0 >= p.N) break;
-    unsigned r[32];
-    tmem_ld_32x32(t_row + (unsigned)c0, r);
-    tmem_ld_wait();
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const int col = c0 + j;
-      if (col <= last && row < p.M) {
-        float x = __uint_as_float(r[j]) * k;
-        if (mrow) x += mrow[col] * 1.4426950408889634f;
-        sum += exp2f(x - mx);
-      }
-    }
-  }
-  const float inv = (sum > 0.f) ? 1.f / sum : 0.f;
-  unsigned char* warp_gen = stage_gen + q * (2 * kWarpTileBytes);
-  const unsigned warp_u32 = stage_u32 + q * (2 * kWarpTileBytes);
-  const int sw = lane & 7;
-#pragma unroll 1
-  for (int c0 = 0; c0 < BN; c0 += 64) {
-    if (c0 >= p.N) break;
-    unsigned r0[32], r1[32];
-    tmem_ld_32x32(t_row + (unsigned)c0, r0);
-    tmem_ld_32x32(t_row + (unsigned)(c0 + 32), r1);
-    tmem_ld_wait();
-    if (lane == 0) bulk_wait_read_1();
-    __syncwarp();
-    unsigned char* tile = warp_gen + buf * kWarpTileBytes + lane * 128;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const unsigned* src = (j < 4) ? r0 : r1;
-      const int b = (j & 3) * 8, cb = c0 + j * 8;
-      float v[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const int col = cb + e;
-        float x = 0.f;
-        if (col <= last && row < p.M) {
-          float t = __uint_as_float(src[b + e]) * k;
-          if (mrow) t += mrow[col] * 1.4426950408889634f;
-          x = exp2f(t - mx) * inv;
-        }
-        v[e] = x;
-      }
-      __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
-      __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]), h3 = __floats2bfloat162_rn(v[6], v[7]);
-      uint4 pk;
-      pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
-      pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
-      *reinterpret_cast<uint4*>(tile + ((j ^ sw) << 4)) = pk;
-    }
-    fence_proxy_async();
-    __syncwarp();
-    if (lane == 0) {
-      tma_store_4d(tmD, warp_u32 + buf * kWarpTileBytes, c0, m0 + q * 32, bi, bo);
-      bulk_commit_group();
-    }
-    buf ^= 1;
-  }
-}
 
 template <int BN, bool A_MN, bool B_MN>
 struct Cfg {
@@ -621,7 +519,7 @@ struct Cfg2 {
                                     ((unsigned)(BN >> 3) << 17) | ((unsigned)((2 * BM) >> 4) << 24);
 };
 
-template <int BN, bool A_MN, bool B_MN, bool SOFTMAX>
+template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmD, const Params p) {
@@ -759,8 +657,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (!ok) break;
       tc_fence_after();
       const unsigned t_row = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(acc * BN);
-      if constexpr (SOFTMAX) drain_tile_softmax<BN>(p, &tmD, store_gen, store_u32, t_row, m0, bi, bo, q, lane, store_buf);
-      else if (p.fast_drain) drain_fast_any<BN>(p, &tmD, store_gen, store_u32, t_row, m0, n0, bi, bo, q, lane, store_buf);
+      if (p.fast_drain) drain_fast_any<BN>(p, &tmD, store_gen, store_u32, t_row, m0, n0, bi, bo, q, lane, store_buf);
       else drain_tile<BN>(p, &tmD, p.tma_store != 0, store_gen, store_u32, bias_tile, t_row, m0, n0, bi, bo, q, lane, et, store_buf);
       tc_fence_before();
       mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));   // tell the leader this thread has drained its rows
@@ -880,8 +777,7 @@ static int device_state(DeviceState** out) {
 // The barrier-free epilogue applies when D goes out through bulk tensor stores, there is no
 // activation, and a bias can be fetched in aligned groups of 8.
 static bool fast_drain_ok(const Params& p) {
-  static const bool off = std::getenv("HAPX_GEMM_SLOW_DRAIN") != nullptr;
-  if (off || !p.tma_store || p.epilogue != EPI_NONE || p.softmax) return false;
+  if (!p.tma_store || p.epilogue != EPI_NONE) return false;
   if (p.bias && ((reinterpret_cast<uintptr_t>(p.bias) & 15u) != 0 || (p.N & 7) != 0)) return false;
   return true;
 }
@@ -973,10 +869,10 @@ static int workspace(int device, cudaStream_t stream, size_t bytes, float** out)
   return HAPX_OK;
 }
 
-template <int BN, bool A_MN, bool B_MN, bool SOFTMAX = false>
+template <int BN, bool A_MN, bool B_MN>
 static int launch2(const Operand& A, const Operand& B, const Operand& Dop, Params& p, cudaStream_t stream, const DeviceState& dev) {
   using C = Cfg2<BN, A_MN, B_MN>;
-  auto kernel = gemm2_bf16_kernel<BN, A_MN, B_MN, SOFTMAX>;
+  auto kernel = gemm2_bf16_kernel<BN, A_MN, B_MN>;
   const int sm_count = dev.sm_count;
   static int max_clusters_of[64] = {};      // per device: function attributes and occupancy belong to one
   int max_clusters = 0;
@@ -1014,8 +910,7 @@ static int launch2(const Operand& A, const Operand& B, const Operand& Dop, Param
   // an SM pair) + 3 for the ramp, and for a split the partial tiles written and read back at about
   // 4 TB/s plus the second launch.
   const int tiles = p.m_tiles * p.n_tiles;
-  static const bool split_model = std::getenv("HAPX_GEMM_NO_SPLITK") == nullptr;
-  if (split_model && !SOFTMAX && p.batch == 1 && p.k_blocks >= 16 && (p.N & 3) == 0) {
+  if (p.batch == 1 && p.k_blocks >= 16 && (p.N & 3) == 0) {
     auto waves = [&](long long units) { return (double)((units + max_clusters - 1) / max_clusters); };
     const double out_bytes = (double)p.M * p.N * (p.out_f32 ? 4.0 : 2.0), partial_bytes = (double)p.M * p.N * 4.0;
     int best = 1;
@@ -1041,7 +936,6 @@ static int launch2(const Operand& A, const Operand& B, const Operand& Dop, Param
   if (int e = make_out_map(&tmD, &p.tma_store, p.D, p.N, out_rows, p.ldd, p.out_f32, p.batch_in, Dop.s_in, batch_out, Dop.s_out)) return e;
   p.fast_drain = fast_drain_ok(p);
   if (p.splits > 1 && !p.tma_store) return fail(HAPX_ERR_EXTENT, "gemm: split-K needs an output width that is a multiple of 4");
-  if (p.softmax && !p.tma_store) return fail(HAPX_ERR_EXTENT, "gemm: the row-softmax epilogue needs a 16-byte aligned output pitch");
   if (int e = make_map(&tmA, A, p.M, p.Kc, BM, p.batch_in, p.a_shared_out ? 1 : batch_out)) return e;
   if (int e = make_map(&tmB, B, p.N, p.Kc, C::BN / 2, p.batch_in, p.b_shared_out ? 1 : batch_out)) return e;
   const long long units = (long long)tiles * p.splits * p.batch;
@@ -1070,17 +964,9 @@ int error_word(unsigned** out, int* sm_count) {
   return HAPX_OK;
 }
 
-// A device word the attention code uses for its "mask is causal" flag (stream-ordered reuse).
-int scratch_flag(unsigned** out) {
-  DeviceState* dev = nullptr;
-  if (int e = device_state(&dev)) return e;
-  *out = dev->error + 1;
-  return HAPX_OK;
-}
-
 // D[b] = A[b] * B[b]^T for b in [0, batch): M x N outputs, contraction length Kc.
 int gemm_bf16(const Operand& Dop, int out_f32, const Operand& A, const Operand& B, const void* bias, int epilogue,
-              long long M, long long N, long long Kc, int batch_in, int batch_out, cudaStream_t stream, const RowSoftmax* softmax) {
+              long long M, long long N, long long Kc, int batch_in, int batch_out, cudaStream_t stream) {
   if (M < 0 || N < 0 || Kc < 0 || batch_in < 1 || batch_out < 1) return fail(HAPX_ERR_EXTENT, "gemm: bad extent");
   if (M == 0 || N == 0) return HAPX_OK;
   if (Kc == 0) {  // an empty contraction (e.g. the weight gradient of a rank that holds no samples): D = 0
@@ -1097,21 +983,12 @@ int gemm_bf16(const Operand& Dop, int out_f32, const Operand& A, const Operand& 
   p.out_f32 = out_f32;
   p.error = dev->error;
   p.batch = batch_in * batch_out; p.batch_in = batch_in; p.d_stride_in = Dop.s_in; p.d_stride_out = Dop.s_out;
-  if (softmax) {
-    // only the pair kernel carries the softmax epilogue, and the row must fit one column tile
-    if (!(M > BM && N > 64 && N <= 256) || out_f32 || A.mn_major || B.mn_major)
-      return fail(HAPX_ERR_ARGUMENT, "gemm: row-softmax epilogue needs 128 < M, 64 < N <= 256, bf16 output, K-major operands");
-    p.softmax = 1; p.sm_causal = softmax->causal; p.sm_scale = softmax->scale; p.sm_mask = softmax->mask;
-    p.sm_mask_is_causal = softmax->mask_is_causal;
-  }
   p.a_shared_out = (batch_out > 1 && A.s_out == 0) ? 1 : 0;
   p.b_shared_out = (batch_out > 1 && B.s_out == 0) ? 1 : 0;
   const bool a_mn = A.mn_major, b_mn = B.mn_major;
   // SM pairs (256 x 256 tiles, half the B traffic per SM) whenever there is more than one row tile
-  static const bool pair_kernel = std::getenv("HAPX_GEMM_SINGLE_CTA") == nullptr;
-  if (pair_kernel && M > BM && N > 64) {
+  if (M > BM && N > 64) {
     // (256 x 128 pair tiles were measured too: slower than 256 x 256 even where they fill the waves better)
-    if (softmax) return launch2<256, false, false, true>(A, B, Dop, p, stream, *dev);   // the only variant that carries the softmax epilogue
     if (!a_mn && !b_mn) return launch2<256, false, false>(A, B, Dop, p, stream, *dev);
     if (!a_mn && b_mn) return launch2<256, false, true>(A, B, Dop, p, stream, *dev);
     if (a_mn && b_mn) return launch2<256, true, true>(A, B, Dop, p, stream, *dev);

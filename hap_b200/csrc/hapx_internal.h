@@ -56,18 +56,9 @@ struct Operand {
   bool mn_major;
   long long ld, s_in, s_out;
 };
-// Optional epilogue: D = softmax over each row of (scale * acc + mask), written as bf16.
-struct RowSoftmax {
-  float scale;
-  int causal;          // drop columns after the row index
-  const float* mask;   // additive [M][N] fp32, or null
-  const unsigned* mask_is_causal;  // optional device word: non-zero when `mask` equals the causal mask
-};
-int scratch_flag(unsigned** out);
 // D[b] = A[b] * B[b]^T (+ bias, activation) on the tensor cores; see hapx_gemm_sm100.cu.
 int gemm_bf16(const Operand& D, int out_f32, const Operand& A, const Operand& B, const void* bias, int epilogue,
-              long long M, long long N, long long Kc, int batch_in, int batch_out, cudaStream_t stream,
-              const RowSoftmax* softmax = nullptr);
+              long long M, long long N, long long Kc, int batch_in, int batch_out, cudaStream_t stream);
 }  // namespace gemm
 
 }  // namespace hapx
