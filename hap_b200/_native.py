@@ -43,6 +43,7 @@ SIGNATURES = {
     "hapx_comm_set_timeout_ms": (_int, [_vp, _int]),
     "hapx_comm_set_max_ctas": (_int, [_vp, _int]),
     "hapx_comm_set_stream_ordering": (_int, [_vp, _int]),
+    "hapx_comm_set_fused_all_reduce": (_int, [_vp, _int]),
     "hapx_comm_check": (_int, [_vp]),
     "hapx_comm_get": (_int, [_vp, _int, _sz, _vp, _sz, _vp]),
     "hapx_all_gather": (_int, [_vp, _pp, _pp, _int, _i64, _i64, _pi64, _int, _vp]),

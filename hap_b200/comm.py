@@ -145,6 +145,10 @@ class Comm:
             self._side_stream = torch.cuda.Stream(self.device)
         return self._side_stream
 
+    def set_fused_all_reduce(self, mode: Optional[bool]) -> None:
+        """Force the one-launch (True) or two-launch (False) form of large all_reduces; None = the default."""
+        N.check(N.lib.hapx_comm_set_fused_all_reduce(self._h, -1 if mode is None else int(bool(mode))))
+
     def set_max_ctas(self, ctas: int) -> None:
         N.check(N.lib.hapx_comm_set_max_ctas(self._h, int(ctas)))
 

@@ -937,6 +937,14 @@ int hapx_all_reduce(hapx_comm* c, void* const* dst, const void* const* src, int 
     if (!in_heap && in_bytes > mid_pos)
       return fail(HAPX_ERR_STAGING, "all_reduce: input of " + std::to_string(in_bytes) + " bytes is outside the peer-visible heap and does not fit the staging area");
   }
+  if (c->fused_all_reduce == 0 || (c->fused_all_reduce < 0 && c->local_mode)) {
+    // single-device emulation: all virtual ranks share the GPU, so there is no launch or flag latency to save and the
+    // two phases run best as two launches, each with its own grid
+    const void* mid_c[HAPX_MAX_WORLD];
+    for (int i = 0; i < c->n_local; ++i) mid_c[i] = mid[i];
+    if (int e = reduce_impl(c, mid, src, in_dtype, out_dtype, scale, 1, 1, L, Pfx, total, 0, stream)) return e;
+    return gather_impl(c, dst, mid_c, es_out, 1, 1, lengths, stream);
+  }
   // one launch: reduce the own slice into `mid`, announce it, gather every rank's slice
   AllReduceKernel kernel = allreduce_kernel_for(in_dtype, out_dtype);
   PullParams R, G;

@@ -224,6 +224,12 @@ int hapx_comm_set_max_ctas(hapx_comm* c, int ctas) {
   return HAPX_OK;
 }
 
+int hapx_comm_set_fused_all_reduce(hapx_comm* c, int mode) {
+  if (!c || mode < -1 || mode > 1) return fail(HAPX_ERR_ARGUMENT, "bad argument");
+  c->fused_all_reduce = mode;
+  return HAPX_OK;
+}
+
 int hapx_comm_set_stream_ordering(hapx_comm* c, int on) {
   if (!c) return fail(HAPX_ERR_ARGUMENT, "null communicator");
   c->stream_ordering = on != 0;

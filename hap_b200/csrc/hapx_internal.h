@@ -78,6 +78,7 @@ struct hapx_comm {
   unsigned* host_status = nullptr;      // host address
   unsigned* host_status_dev = nullptr;  // the same word as the device sees it
   int max_ctas = 0;
+  int fused_all_reduce = -1;        // large all_reduce as one launch: -1 = yes between processes, no in single-device emulation; 0 / 1 force it
   int order_log2 = 6;               // copy kernels interleave 64 tile streams (see pull_copy_kernel)
   int sm_count = 0;
   cudaEvent_t last_done = nullptr;

@@ -116,6 +116,10 @@ int hapx_comm_poll(hapx_comm* c);
 int hapx_comm_calls_issued(hapx_comm* c, int64_t* calls);
 /* Cap the CTAs per rank that a collective launches (0 = one full wave). */
 int hapx_comm_set_max_ctas(hapx_comm* c, int ctas);
+/* all_reduce above 256 KiB runs as ONE launch (reduce the own slice, announce it, gather all slices) between
+ * processes and as two launches (reduce, then gather) in the single-device emulation, where there is no launch
+ * or flag latency to save.  mode 1 / 0 forces the one-launch / two-launch form, -1 restores the default. */
+int hapx_comm_set_fused_all_reduce(hapx_comm* c, int mode);
 /* Calls issued on different streams are ordered with an event by default.  Turn that off
  * (on = 0) while the caller captures its stream into a CUDA graph and keeps all calls on that one
  * stream: event records / waits against streams outside the capture would invalidate it. */

@@ -214,6 +214,28 @@ def test_all_reduce_sizes_and_in_place(n, dtype):
         assert torch.equal(same[r], got[r])
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_all_reduce_one_launch_form(world, dtype):
+    """The one-launch all_reduce (reduce own slice, announce, gather) is the default between processes; the
+    emulated communicator runs it when forced, as a cooperative launch over all virtual ranks."""
+    comm = comm_for(world)
+    comm.set_fused_all_reduce(True)
+    try:
+        for n in (65537, 300001, (1 << 20) + 5, (1 << 22)):
+            xs = [gen((n,), 911 + r, dtype) for r in range(world)]
+            want = cm.all_reduce(xs)[0]
+            got = comm.all_reduce(gpu(xs))
+            bufs = gpu(xs)
+            same = comm.all_reduce(bufs, inplace=True)
+            comm.check()
+            for r in range(world):
+                torch.testing.assert_close(got[r].cpu(), want, **TOL[dtype])
+                assert torch.equal(same[r], got[r])
+    finally:
+        comm.set_fused_all_reduce(None)
+
+
 def test_all_to_all_against_oracle():
     for world, sl, cl in ((4, [4, 3, 2, 1], [1, 2, 3, 4]), (4, [5, 0, 5, 0], [0, 2, 0, 8]), (2, [3, 2], [1, 4]),
                           (8, [7, 6, 5, 4, 3, 3, 2, 2], [56, 46, 39, 33, 28, 23, 18, 13])):
