@@ -161,7 +161,7 @@ def collective_config(W, size_mib, emulated):
             "world": W, "sharding_lengths": hap_b200.sharding_round(ROWS, ratios_for(W)), "ratios": "r8 (first W renormalised)",
             "ranks": ("8 virtual ranks on ONE GPU (an emulation of the 8-GPU exchange, one cooperative launch per collective, HBM bound): "
                       "not a point of a scaling curve") if emulated else "one process per GPU, peer loads over NVLink",
-            "inputs": "resident in the peer-visible heap", "l2": "inputs larger than L2 (126 MB)",
+            "inputs": "resident in the peer-visible heap (so is the all_reduce output)", "l2": "inputs larger than L2 (126 MB)",
             "cpu_arm": "the reference arm and cpu_baseline time a bounded sample of this workload (a smaller tensor, see cpu_baseline.sample)"}
 
 
@@ -228,7 +228,7 @@ def run_collective_bench(args, job):
     W = 8 if emulated else n_gpus
     L = hap_b200.sharding_round(ROWS, ratios_for(W))
     stage = (S + S // W + (64 << 20) + 255) // 256 * 256     # staged input + the reduced slice of all_reduce
-    heap = stage + S + (max(L) * cols * es) + (64 << 20)
+    heap = stage + 2 * S + (max(L) * cols * es) + (64 << 20)
 
     if emulated:
         comm = hap_b200.local_comm(W, dev, heap_bytes=heap, stage_bytes=stage)
@@ -249,6 +249,9 @@ def run_collective_bench(args, job):
         shards.append(sh)
         fulls.append(fu)
     ag_out = [torch.empty(ROWS, cols, dtype=dtype, device=dev) for _ in ranks]
+    # the all_reduce result goes to a second heap tensor: with every output peer-visible the slice owners write
+    # their sums straight into all outputs (torch.distributed's all_reduce, which the reference calls, is in place)
+    ar_out = [comm.symm_empty((ROWS, cols), dtype, i) for i in range(nl)]
     barrier = job.barrier
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
@@ -259,7 +262,7 @@ def run_collective_bench(args, job):
         if marks: marks[1].record()
         rs = comm.reduce_scatter(fulls, 0, L)
         if marks: marks[2].record()
-        ar = comm.all_reduce(fulls, scale=1.0 / W)
+        ar = comm.all_reduce(fulls, scale=1.0 / W, out=ar_out)
         if marks:
             marks[3].record()
             events.append(marks)
@@ -550,7 +553,7 @@ def run_sweep(args):
     L = hap_b200.sharding_round(ROWS, ratios_for(W))
     max_bytes = args.sweep_max_mib << 20
     stage = (max_bytes // W + (64 << 20) + 255) // 256 * 256      # all_reduce keeps its reduced slice there
-    heap = stage + max_bytes + max(L) * (max_bytes // ROWS) + int(max_bytes * max(ratios_for(W)) * 1.05) + (64 << 20)
+    heap = stage + 2 * max_bytes + max(L) * (max_bytes // ROWS) + int(max_bytes * max(ratios_for(W)) * 1.05) + (64 << 20)
     if emulated:
         comm = hap_b200.local_comm(W, dev, heap_bytes=heap, stage_bytes=stage)
         dist = None
@@ -643,6 +646,7 @@ def run_sweep(args):
                 shards.append(sh)
                 fulls.append(fu)
             out = [torch.empty(ROWS, cols, dtype=dtype, device=dev) for _ in ranks]
+            ar_heap = [comm.symm_empty((ROWS, cols), dtype, i) for i in range(len(ranks))]
             reps = (20 if S <= (256 << 20) else 5) if not args.sweep_quick else (8 if S <= (256 << 20) else 3)
             inner = 10 if S <= (64 << 20) else 2
             s_r = [L[r] * cols * es for r in range(W)]
@@ -653,6 +657,8 @@ def run_sweep(args):
                 ("reduce_scatter", lambda: comm.reduce_scatter(fulls, 0, L, N.MODE_PADDING), S * (W - 1) / W, alg_ag),
                 ("reduce_scatter_by_group_call", lambda: comm.reduce_scatter(fulls, 0, L, N.MODE_GROUP_CALL), S * (W - 1) / W, alg_ag),
                 ("all_reduce", lambda: comm.all_reduce(fulls, scale=1.0 / W), 2 * S * (W - 1) / W, 2 * S * (W - 1) / W),
+                # output in the peer-visible heap as well: slice owners write the sums into every rank's output
+                ("all_reduce_heap_output", lambda: comm.all_reduce(fulls, scale=1.0 / W, out=ar_heap), 2 * S * (W - 1) / W, 2 * S * (W - 1) / W),
             ]
             if cols >= W:
                 # uneven all_to_all in the reference profiler's convention (profiler.py:106-117): the (256, C) tensor is
@@ -687,12 +693,13 @@ def run_sweep(args):
                     row["frac_nvlink_900"] = row["alg_GBps"] / NVLINK_NOMINAL_GBS
                     if "graph_ms" in row:
                         row["graph_frac_nvlink_900"] = row["graph_alg_GBps"] / NVLINK_NOMINAL_GBS
-                    if dtype == torch.float32 or name == "all_reduce":      # the reference's buffers are fp32-only
+                    if dtype == torch.float32 or name.startswith("all_reduce"):      # the reference's buffers are fp32-only
                         ref = {"all_gather": lambda: gp.all_gather(shards[0], 0, L, rank),
                                "all_gather_by_group_call": lambda: gp.all_gather_by_group_call(shards[0], 0, L, rank),
                                "reduce_scatter": lambda: gp.reduce_scatter(fulls[0], 0, L, rank),
                                "reduce_scatter_by_group_call": lambda: gp.reduce_scatter_by_group_call(fulls[0], 0, L, rank),
                                "all_reduce": lambda: gp.all_reduce(fulls[0]),
+                               "all_reduce_heap_output": lambda: gp.all_reduce(fulls[0]),
                                "all_to_all": lambda: gp.all_to_all(a2a_in[0], 0, 1, L, LC, rank)}[name]
                         rmed, rbest = timed(ref, max(3, reps // 2), warm=2, inner=inner)
                         row["reference_on_nccl_ms_median"] = rmed
@@ -1214,6 +1221,60 @@ def run_ops(args):
         nbytes = 5 * rows_ * E_ * 2            # forward: x in, y out; backward: x, dy in, dx out
         rows.append({"op": "layer_norm fwd+bwd", "shape": f"rows={rows_} E={E_} bf16", "ms": t, "torch_ms": tr, "tflops": 0.0,
                      "gbs": nbytes / t / 1e6, "frac_of_hbm_peak": nbytes / t / 1e6 / peak_gbs, "eager_ms": t_eager})
+    if "dropout" in parts:
+        # F.dropout and its fusions with the neighbouring elementwise ops of an encoder layer, forward + backward,
+        # on the activations of one Transformer-LM layer (8192 tokens x 768 after attention / FFN, x 3072 inside the FFN)
+        from hap_b200 import dropout as DR
+        F_ = torch.nn.functional
+        for label, width, ours_fn, ref_fn, passes in (
+                ("dropout", 768, lambda x_, r_: DR.dropout(x_, 0.1), lambda x_, r_: F_.dropout(x_, 0.1), 4),
+                ("x + dropout(y)", 768, lambda x_, r_: DR.dropout_add(x_, r_, 0.1), lambda x_, r_: r_ + F_.dropout(x_, 0.1), 5),
+                ("dropout(relu(x))", 3072, lambda x_, r_: DR.act_dropout(x_, "relu", 0.1), lambda x_, r_: F_.dropout(F_.relu(x_), 0.1), 5),
+                ("dropout(gelu(x))", 3072, lambda x_, r_: DR.act_dropout(x_, "gelu", 0.1), lambda x_, r_: F_.dropout(F_.gelu(x_), 0.1), 5)):
+            xd = torch.randn(8192, width, device=dev, generator=g).to(torch.bfloat16).requires_grad_(True)
+            rd = torch.randn(8192, width, device=dev, generator=g).to(torch.bfloat16)
+            gd = torch.randn(8192, width, device=dev, generator=g).to(torch.bfloat16)
+
+            def step_of(fn):
+                def run():
+                    xd.grad = None
+                    fn(xd, rd).backward(gd)
+                return run
+
+            t_eager = timeit(step_of(ours_fn))
+            t, tr = timeit(graphed(step_of(ours_fn))), timeit(graphed(step_of(ref_fn)))
+            # forward reads x (and the residual) and writes y; backward reads dy (and x or y for an activation) and writes dx
+            nbytes = passes * 8192 * width * 2
+            rows.append({"op": label + " fwd+bwd", "shape": f"rows=8192 E={width} bf16 p=0.1", "ms": t, "torch_ms": tr, "tflops": 0.0,
+                         "gbs": nbytes / t / 1e6, "frac_of_hbm_peak": nbytes / t / 1e6 / peak_gbs, "eager_ms": t_eager})
+    if "moe" in parts:
+        # dispatch / combine of one MoE layer as row gathers (top-2 gating, 32 experts, capacity 20) against the
+        # dense one-hot contractions torch runs for the same einsums; forward + backward
+        from hap_b200 import plan as P_
+        from hap_b200.einsum import sparse_dispatch, sparse_combine
+        bm, sm, em, cm, dm = 16, 512, 32, 20, 1024
+        xm = torch.randn(bm, sm, dm, device=dev, generator=g).to(torch.bfloat16).requires_grad_(True)
+        gate_w = (torch.randn(dm, em, device=dev, generator=g) * dm ** -0.5).to(torch.bfloat16)
+        with torch.no_grad():
+            disp_m, comb_m = P_.top2_gating(xm.detach(), gate_w, em, cm)
+        disp_m, comb_m = disp_m.to(torch.bfloat16), comb_m.to(torch.bfloat16).requires_grad_(True)
+        gm = torch.randn(bm, sm, dm, device=dev, generator=g).to(torch.bfloat16)
+
+        def moe_step(dispatch_fn, combine_fn):
+            def run():
+                xm.grad = comb_m.grad = None
+                combine_fn(dispatch_fn(xm, disp_m), comb_m).backward(gm)
+            return run
+
+        ours_m = moe_step(sparse_dispatch, sparse_combine)
+        ref_m = moe_step(lambda a_, b_: torch.einsum("bsd,bsec->becd", a_, b_), lambda a_, b_: torch.einsum("becd,bsec->bsd", a_, b_))
+        t_eager = timeit(ours_m)
+        t, tr = timeit(graphed(ours_m)), timeit(graphed(ref_m))
+        # rows of 2 KiB: dispatch reads <= e*c rows per sequence and writes e*c; combine reads them and writes s rows; same
+        # again for the gradients; plus the dense dispatch / combine tensors read once each to build the index
+        nbytes = 2 * (2 * bm * em * cm * dm * 2 + 2 * bm * sm * dm * 2) + 2 * bm * sm * em * cm * 2
+        rows.append({"op": "MoE dispatch + combine fwd+bwd (row gathers)", "shape": f"b={bm} s={sm} e={em} c={cm} d={dm}", "ms": t, "torch_ms": tr,
+                     "tflops": 0.0, "gbs": nbytes / t / 1e6, "frac_of_hbm_peak": nbytes / t / 1e6 / peak_gbs, "eager_ms": t_eager})
     if "loss" in parts:
         # log_softmax + summed nll_loss forward + backward on the LM head's logits (8192 tokens x 33280, bf16)
         from hap_b200.loss import nll_log_softmax_sum
@@ -1318,7 +1379,7 @@ def main():
     ap.add_argument("--lm-graph", action="store_true", help="capture the training step into a CUDA graph")
     ap.add_argument("--gemm-tokens", type=int, default=8192)
     ap.add_argument("--gemm-layers", default="", help="comma-separated layer names to restrict the gemm workload to")
-    ap.add_argument("--ops", default="attention,einsum,norm,loss,tail", help="parts of the ops workload to run")
+    ap.add_argument("--ops", default="attention,einsum,norm,dropout,moe,loss,tail", help="parts of the ops workload to run")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

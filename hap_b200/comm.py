@@ -145,9 +145,12 @@ class Comm:
             self._side_stream = torch.cuda.Stream(self.device)
         return self._side_stream
 
-    def set_fused_all_reduce(self, mode: Optional[bool]) -> None:
-        """Force the one-launch (True) or two-launch (False) form of large all_reduces; None = the default."""
-        N.check(N.lib.hapx_comm_set_fused_all_reduce(self._h, -1 if mode is None else int(bool(mode))))
+    def set_fused_all_reduce(self, mode) -> None:
+        """Form of large all_reduces: False = two launches, True = one launch, ``"push"`` = one launch that writes the
+        sums straight into the peers' outputs when all of them lie in the heap; None = the default (``"push"``
+        between processes, two launches in the single-device emulation).  Same setting on every rank."""
+        code = {None: -1, False: 0, True: 1, "push": 2}[mode]
+        N.check(N.lib.hapx_comm_set_fused_all_reduce(self._h, code))
 
     def set_max_ctas(self, ctas: int) -> None:
         N.check(N.lib.hapx_comm_set_max_ctas(self._h, int(ctas)))
@@ -271,7 +274,7 @@ class Comm:
         return outs
 
     def all_reduce(self, inputs: Sequence[torch.Tensor], scale: float = 1.0, out_dtype: Optional[torch.dtype] = None,
-                   inplace: bool = False) -> List[torch.Tensor]:
+                   inplace: bool = False, out: Optional[Sequence[torch.Tensor]] = None) -> List[torch.Tensor]:
         inputs = self._lists(inputs, "all_reduce")
         ref = inputs[0]
         if ref.dtype not in _REDUCIBLE:
@@ -280,12 +283,17 @@ class Comm:
             if t.shape != ref.shape or t.dtype != ref.dtype:
                 raise ValueError("all_reduce: inputs disagree in shape or dtype")
         out_dtype = out_dtype or ref.dtype
-        if self._alone and scale == 1.0 and out_dtype == ref.dtype:
+        if self._alone and scale == 1.0 and out_dtype == ref.dtype and out is None:
             return inputs
         if inplace:
             if out_dtype != ref.dtype:
                 raise ValueError("all_reduce: in-place needs out_dtype == input dtype")
             outs = inputs
+        elif out is not None:
+            outs = self._lists(out, "all_reduce")
+            for o, t in zip(outs, inputs):
+                if o.shape != t.shape or o.dtype != out_dtype or not o.is_contiguous():
+                    raise ValueError("all_reduce: out must be contiguous tensors of the inputs' shape and the output dtype")
         else:
             outs = [torch.empty(t.shape, dtype=out_dtype, device=t.device) for t in inputs]
         one = self.n_local == 1

@@ -49,12 +49,15 @@ struct LocalRank {
   const char* src;
   char* dst;
   unsigned long long src_off;  // where peers find this rank's input inside its heap
+  unsigned long long dst_off;  // all_reduce: where peers may write this rank's output inside its heap (kNoOffset: they may not)
 };
+constexpr unsigned long long kNoOffset = (1ull << 40) - 1;
 
 struct PullParams {
   int op, world, n_local, es_in, es_out;
   int self_only;    // no peers involved: skip the flag protocol
   int split_first;  // OP_EXCHANGE: split dim comes before cat dim
+  int push;         // all_reduce: results may be written straight into the peers' outputs when every output lies in a heap
   int order_log2;   // copy kernels visit tiles in 2^order_log2 interleaved streams (0 = in order)
   unsigned seq;
   unsigned long long timeout_ns;
@@ -416,8 +419,11 @@ __device__ __forceinline__ void store_values(char* d, const float (&f)[K]) {
   }
 }
 
-template <typename InT, typename OutT>
-__device__ __forceinline__ void reduce_tiles(const PullParams& P, const LocalRank& lr, Shared& sh) {
+// PUSH: the sums go to every rank's output (`push_dst[q]` + the slice's place in the whole tensor) instead of
+// this rank's compact slice buffer.
+template <typename InT, typename OutT, bool PUSH = false>
+__device__ __forceinline__ void reduce_tiles(const PullParams& P, const LocalRank& lr, Shared& sh, char* const* push_dst = nullptr,
+                                             long long push_off_b = 0) {
   constexpr int K = Num<InT>::K;
   const unsigned lane = threadIdx.x & 31u;
   const unsigned gw = blockIdx.x * kWarps + (threadIdx.x >> 5);
@@ -477,7 +483,12 @@ __device__ __forceinline__ void reduce_tiles(const PullParams& P, const LocalRan
       if (full[u]) {
 #pragma unroll
         for (int i = 0; i < K; ++i) acc[u][i] *= scale;
-        store_values<OutT, K>(drow + (rel / (long long)sizeof(InT)) * (long long)sizeof(OutT), acc[u]);
+        const long long out_b = (rel / (long long)sizeof(InT)) * (long long)sizeof(OutT);
+        if constexpr (PUSH) {
+          for (int q = 0; q < W; ++q) store_values<OutT, K>(push_dst[q] + push_off_b + tp.dst_row_b + out_b, acc[u]);
+        } else {
+          store_values<OutT, K>(drow + out_b, acc[u]);
+        }
       } else {
         const long long lo = rel < 0 ? 0 : rel;
         const long long hi = (rel + 16 < run_b) ? rel + 16 : run_b;
@@ -487,7 +498,12 @@ __device__ __forceinline__ void reduce_tiles(const PullParams& P, const LocalRan
             const float x = Num<InT>::load(sh.base[p] + tp.src_row_b + b);
             a = (p == 0) ? x : a + x;
           }
-          Num<OutT>::store(drow + (b / (long long)sizeof(InT)) * (long long)sizeof(OutT), a * scale);
+          const long long out_b = (b / (long long)sizeof(InT)) * (long long)sizeof(OutT);
+          if constexpr (PUSH) {
+            for (int q = 0; q < W; ++q) Num<OutT>::store(push_dst[q] + push_off_b + tp.dst_row_b + out_b, a * scale);
+          } else {
+            Num<OutT>::store(drow + out_b, a * scale);
+          }
         }
       }
     }
@@ -512,10 +528,57 @@ __global__ void __launch_bounds__(kThreads) pull_reduce_kernel(const __grid_cons
 template <typename InT, typename OutT>
 __global__ void __launch_bounds__(kThreads) pull_allreduce_kernel(const __grid_constant__ PullParams R, const __grid_constant__ PullParams G) {
   __shared__ Shared sh;
+  __shared__ char* push_dst[HAPX_MAX_WORLD];
+  __shared__ int push_ok;
   const LocalRank& lr = R.lr[blockIdx.y];
   const int tid = threadIdx.x, rank = lr.rank;
   Ctrl* my = reinterpret_cast<Ctrl*>(R.heap[rank]);
   begin_collective(R, lr, sh, kRedTile);
+  if (R.push) {
+    // Every rank tells the others where its OUTPUT lies in its heap (or that it does not).  If all outputs are
+    // reachable, the owner of a slice writes its sums straight into every output: each byte crosses the links
+    // once per direction (read as input, written as result), there is no intermediate slice and no second phase.
+    if (tid == 0) push_ok = 1;
+    __syncthreads();
+    if (tid < R.world) {
+      const int p = tid;
+      unsigned long long off = lr.dst_off;
+      if (p != rank) {
+        if (blockIdx.x == 0)
+          st_release_sys(&reinterpret_cast<Ctrl*>(R.heap[p])->dst_start[rank], ((unsigned long long)R.seq << 40) | lr.dst_off);
+        unsigned long long v = 0;
+        if (!sh.abort && wait_flag(&my->dst_start[p], 40, R.seq, R.timeout_ns, &v)) {
+          off = v & kNoOffset;
+        } else if (!sh.abort) {
+          sh.abort = 1;
+          report_timeout(my, R.seq, p, R.host_status);
+        }
+      }
+      if (off == kNoOffset) push_ok = 0;
+      push_dst[p] = R.heap[p] + off;
+    }
+    __syncthreads();
+    if (tid == 0 && sh.abort) sh.total_tiles = 0;
+    __syncthreads();
+    if (push_ok) {
+      reduce_tiles<InT, OutT, true>(R, lr, sh, push_dst, R.P1[rank] * R.C * (long long)sizeof(OutT));
+      __threadfence_system();                      // this thread's writes into the peers before the CTA is counted
+      __syncthreads();
+      if (tid == 0) sh.last = (atomicAdd(&my->cta_phase, 1u) == gridDim.x - 1);
+      __syncthreads();
+      if (!sh.last) return;
+      // the slice is complete in every output, and every input of it has been read: tell everybody (and wait for
+      // their slices: then this rank's output is whole and nobody reads its input any more)
+      if (tid == 0) { __threadfence_system(); my->cta_phase = 0; }
+      __syncthreads();
+      if (tid < R.world) {
+        st_release_sys(&reinterpret_cast<Ctrl*>(R.heap[tid])->ready[rank], (unsigned long long)R.seq);
+        unsigned long long v;
+        if (!sh.abort && !wait_flag(&my->ready[tid], 0, R.seq, R.timeout_ns, &v)) report_timeout(my, R.seq, tid, R.host_status);
+      }
+      return;
+    }
+  }
   reduce_tiles<InT, OutT>(R, lr, sh);
   // publish this rank's slice when its last CTA has finished reducing
   __syncthreads();
@@ -968,6 +1031,15 @@ int hapx_all_reduce(hapx_comm* c, void* const* dst, const void* const* src, int 
     G.lr[i].src = static_cast<const char*>(mid[i]);
     G.lr[i].dst = static_cast<char*>(dst[i]);
     G.lr[i].src_off = kCtrlBytes + mid_pos;
+  }
+  // Outputs that lie in the peer-visible heap can be written by the slice owners directly; whether all of them
+  // do is settled between the ranks inside the kernel (a rank only knows its own).
+  R.push = (c->fused_all_reduce == 2 || c->fused_all_reduce < 0) && (in_bytes % 16 == 0) && (((size_t)n * es_out) % 16 == 0);
+  for (int i = 0; i < c->n_local; ++i) {
+    const int r = c->first_rank + i;
+    const char* d = static_cast<const char*>(dst[i]);
+    const bool reachable = d >= c->heap[r] + kCtrlBytes && d + (size_t)n * es_out <= c->heap[r] + c->heap_bytes && ((uintptr_t)d & 15u) == 0;
+    R.lr[i].dst_off = reachable ? (unsigned long long)(d - c->heap[r]) : kNoOffset;
   }
   R.seq = G.seq = next_seq(c);
   if (int e = launch_allreduce(c, kernel, R, G, stream)) return e;

@@ -225,7 +225,7 @@ int hapx_comm_set_max_ctas(hapx_comm* c, int ctas) {
 }
 
 int hapx_comm_set_fused_all_reduce(hapx_comm* c, int mode) {
-  if (!c || mode < -1 || mode > 1) return fail(HAPX_ERR_ARGUMENT, "bad argument");
+  if (!c || mode < -1 || mode > 2) return fail(HAPX_ERR_ARGUMENT, "bad argument");
   c->fused_all_reduce = mode;
   return HAPX_OK;
 }

@@ -30,6 +30,7 @@ struct Ctrl {
   unsigned long long start[HAPX_MAX_WORLD];  // peer p writes (seq<<40 | offset of its input in its heap)
   unsigned long long done[HAPX_MAX_WORLD];   // peer p writes seq when it has finished reading this rank
   unsigned long long ready[HAPX_MAX_WORLD];  // all_reduce: peer p writes seq when its reduced slice is complete (and it has read all inputs)
+  unsigned long long dst_start[HAPX_MAX_WORLD];  // all_reduce: peer p writes (seq<<40 | offset of its OUTPUT in its heap), all ones = not in the heap
   unsigned int cta_done;                     // CTAs of the running kernel that have finished
   unsigned int cta_phase;                    // all_reduce: CTAs that have finished reducing
   unsigned int status;                       // 0, or a hapx_status code left by a kernel (as a positive number)
@@ -78,7 +79,7 @@ struct hapx_comm {
   unsigned* host_status = nullptr;      // host address
   unsigned* host_status_dev = nullptr;  // the same word as the device sees it
   int max_ctas = 0;
-  int fused_all_reduce = -1;        // large all_reduce as one launch: -1 = yes between processes, no in single-device emulation; 0 / 1 force it
+  int fused_all_reduce = -1;        // large all_reduce: 0 two launches, 1 one launch (pull), 2 one launch that may write results into the peers; -1 = 2 between processes, 0 in single-device emulation
   int order_log2 = 6;               // copy kernels interleave 64 tile streams (see pull_copy_kernel)
   int sm_count = 0;
   cudaEvent_t last_done = nullptr;

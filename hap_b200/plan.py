@@ -178,6 +178,32 @@ class TransformerLM(torch.nn.Module):
         return _lm_forward(self, tokens, targets, ns, None, None, None, "none")
 
 
+def _column_parallel_ffn(m, i, h, activation, emit, col, call, linear, param, drop, rank):
+    """The FFN of layer ``i`` column-parallel (hap.rs:2807-2816): every rank multiplies the WHOLE batch by its
+    rows of the weight, so the batch shards are gathered first (re-sharding batch -> replicated,
+    hap.rs:2631-2653), the output columns are gathered on the last dimension before the activation (an
+    activation's output is not communicatable, hap.rs:1102, 1432), and the own batch shard is cut out again
+    at the end.  ``h`` is (L, B_r, E); so is the result."""
+    lb, l_ffn, l_e = m._tp_lengths
+    h = emit.call_function(col.all_gather, (h, 1, lb, rank))                                   # (L, B, E)
+    z = call(linear, h, param(f"l{i}_w1"), param(f"l{i}_b1"))                                  # (L, B, ffn_r)
+    z = emit.call_function(col.all_gather, (z, 2, l_ffn, rank))                                # (L, B, ffn)
+    z = drop(call(activation, z))
+    o = call(linear, z, param(f"l{i}_w2"), param(f"l{i}_b2"))                                  # (L, B, E_r)
+    o = emit.call_function(col.all_gather, (o, 2, l_e, rank))                                  # (L, B, E)
+    return emit.call_function(col.dynamic_slice, (o, 1, lb, rank))                             # (L, B_r, E)
+
+
+def _shard_column_parallel_ffn_(model, ratios, rank, lb):
+    """Cut the FFN weights and biases of every layer on dim 0 for good (plan ``"tp"``)."""
+    d_ffn = model.l0_w1.shape[0]
+    model._tp_lengths = (lb, sharding_round(d_ffn, ratios), sharding_round(model.d_model, ratios))
+    for i in range(model.nlayers):
+        for n, extent in ((f"l{i}_w1", d_ffn), (f"l{i}_b1", d_ffn), (f"l{i}_w2", model.d_model), (f"l{i}_b2", model.d_model)):
+            shard_parameter_(model, n, sharding_round(extent, ratios), 0, rank)
+            model._column_parallel.add(n)
+
+
 def _lm_forward(m, tokens, targets, ns, emit, ratios, rank, plan, dropout_p=0.0):
     """The model's forward written once; `emit` (an fx graph) turns parameter reads and collectives
     into nodes, otherwise it runs eagerly on the unsharded module."""
@@ -219,18 +245,7 @@ def _lm_forward(m, tokens, targets, ns, emit, ratios, rank, plan, dropout_p=0.0)
         x = call(operator.add, x, drop(call(operator.getitem, att, 0)))
         h = call(_ln(ns), x, (E,), param(f"l{i}_ln2_w"), param(f"l{i}_ln2_b"))
         if plan == "tp":
-            # the FFN column-parallel (hap.rs:2807-2816): every rank multiplies the WHOLE batch by its rows of the
-            # weight, so the batch shards are gathered first (re-sharding batch -> replicated, hap.rs:2631-2653),
-            # the output columns are gathered on the last dimension before the activation (an activation's output
-            # is not communicatable, hap.rs:1102, 1432), and the own batch shard is cut out again at the end
-            lb, l_ffn, l_e = m._tp_lengths
-            h = emit.call_function(col.all_gather, (h, 1, lb, rank))                                   # (S, B, E)
-            z = call(linear, h, param(f"l{i}_w1"), param(f"l{i}_b1"))                                  # (S, B, ffn_r)
-            z = emit.call_function(col.all_gather, (z, 2, l_ffn, rank))                                # (S, B, ffn)
-            z = drop(call(F.relu, z))
-            o = call(linear, z, param(f"l{i}_w2"), param(f"l{i}_b2"))                                  # (S, B, E_r)
-            o = emit.call_function(col.all_gather, (o, 2, l_e, rank))                                  # (S, B, E)
-            h = emit.call_function(col.dynamic_slice, (o, 1, lb, rank))                                # (S, B_r, E)
+            h = _column_parallel_ffn(m, i, h, F.relu, emit, col, call, linear, param, drop, rank)
         else:
             h = call(linear, h, param(f"l{i}_w1", True), param(f"l{i}_b1", True))
             h = drop(call(F.relu, h))
@@ -274,12 +289,7 @@ def emit_lm(model: TransformerLM, plan: str, ratios: Sequence[float], rank: int,
     model._full_extent = {}
     model._column_parallel = set()
     if plan == "tp":
-        d_ffn = model.l0_w1.shape[0]
-        model._tp_lengths = (lb, sharding_round(d_ffn, ratios), sharding_round(model.d_model, ratios))
-        for i in range(model.nlayers):
-            for n, extent in ((f"l{i}_w1", d_ffn), (f"l{i}_b1", d_ffn), (f"l{i}_w2", model.d_model), (f"l{i}_b2", model.d_model)):
-                shard_parameter_(model, n, sharding_round(extent, ratios), 0, rank)
-                model._column_parallel.add(n)
+        _shard_column_parallel_ffn_(model, ratios, rank, lb)
     if plan in ("dp_zero", "tp"):
         names = [n for i in range(model.nlayers) for n in (f"l{i}_in_w", f"l{i}_in_b", f"l{i}_out_w")]
         if plan == "dp_zero":
@@ -354,7 +364,9 @@ def _vit_forward(m, images, labels, ns, emit, ratios, rank, plan, dropout_p=0.0)
         if emit is None:
             return getattr(m, name)
         node = emit.get_attr(name)
-        if plan == "dp_zero" and shardable:
+        if name in m._column_parallel:
+            return node                  # column-parallel weight or bias: the in-place shard itself
+        if plan in ("dp_zero", "tp") and shardable and name in m._full_extent:
             return emit.call_function(col.all_gather, (node, 0, sharding_round(m._full_extent[name], ratios), rank))
         return emit.call_function(col.replicate, (node,))
 
@@ -379,9 +391,12 @@ def _vit_forward(m, images, labels, ns, emit, ratios, rank, plan, dropout_p=0.0)
                    out_proj_bias=param(f"l{i}_out_b"), attn_mask=None)
         x = call(operator.add, x, drop(call(operator.getitem, att, 0)))
         h = call(_ln(ns), x, (E,), param(f"l{i}_ln2_w"), param(f"l{i}_ln2_b"))
-        h = call(linear, h, param(f"l{i}_w1", True), param(f"l{i}_b1", True))
-        h = drop(call(F.gelu, h))
-        h = call(linear, h, param(f"l{i}_w2", True), param(f"l{i}_b2"))
+        if plan == "tp":
+            h = _column_parallel_ffn(m, i, h, F.gelu, emit, col, call, linear, param, drop, rank)
+        else:
+            h = call(linear, h, param(f"l{i}_w1", True), param(f"l{i}_b1", True))
+            h = drop(call(F.gelu, h))
+            h = call(linear, h, param(f"l{i}_w2", True), param(f"l{i}_b2"))
         x = call(operator.add, x, drop(h))
     x = call(operator.getitem, x, 0)                                        # the class token: (B, E)
     x = call(_ln(ns), x, (E,), param("lnf_w"), param("lnf_b"))
@@ -393,9 +408,10 @@ def emit_vit(model: ViT, plan: str, ratios: Sequence[float], rank: int, batch: i
              dropout_p: float = 0.0) -> torch.fx.Graph:
     """fx graph of the ViT training forward for one rank; plans as in :func:`emit_lm` (``"dp"``:
     images and labels batch-sharded by ``ratios``, parameters replicated; ``"dp_zero"``: projection
-    weights additionally sharded on dim 0 and all-gathered at their use)."""
+    weights additionally sharded on dim 0 and all-gathered at their use; ``"tp"``: the MLP of every block
+    column-parallel, everything else as in ``"dp_zero"``)."""
     ns = ns or default_namespace()
-    if plan not in ("dp", "dp_zero"):
+    if plan not in ("dp", "dp_zero", "tp"):
         raise ValueError(f"unknown plan {plan!r}")
     g = torch.fx.Graph()
     images, labels = g.placeholder("images"), g.placeholder("labels")
@@ -404,8 +420,12 @@ def emit_vit(model: ViT, plan: str, ratios: Sequence[float], rank: int, batch: i
     lab_r = g.call_function(operator.getitem, (g.call_method("split", (labels, lb, 0)), rank))
     model._full_extent = {}
     model._column_parallel = set()
-    if plan == "dp_zero":
-        names = [n for i in range(model.nlayers) for n in (f"l{i}_in_w", f"l{i}_in_b", f"l{i}_out_w", f"l{i}_w1", f"l{i}_b1", f"l{i}_w2")]
+    if plan == "tp":
+        _shard_column_parallel_ffn_(model, ratios, rank, lb)
+    if plan in ("dp_zero", "tp"):
+        names = [n for i in range(model.nlayers) for n in (f"l{i}_in_w", f"l{i}_in_b", f"l{i}_out_w")]
+        if plan == "dp_zero":
+            names += [n for i in range(model.nlayers) for n in (f"l{i}_w1", f"l{i}_b1", f"l{i}_w2")]
         names += ["patch_w", "head_w", "head_b"]
         for n in names:
             full = getattr(model, n).shape[0]

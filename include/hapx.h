@@ -116,9 +116,15 @@ int hapx_comm_poll(hapx_comm* c);
 int hapx_comm_calls_issued(hapx_comm* c, int64_t* calls);
 /* Cap the CTAs per rank that a collective launches (0 = one full wave). */
 int hapx_comm_set_max_ctas(hapx_comm* c, int ctas);
-/* all_reduce above 256 KiB runs as ONE launch (reduce the own slice, announce it, gather all slices) between
- * processes and as two launches (reduce, then gather) in the single-device emulation, where there is no launch
- * or flag latency to save.  mode 1 / 0 forces the one-launch / two-launch form, -1 restores the default. */
+/* Forms of all_reduce above 256 KiB:
+ *   0  two launches: every rank reduces its slice of an even split into a peer-visible buffer, then all gather;
+ *   1  the same in ONE launch (reduce the own slice, announce it, gather all slices);
+ *   2  one launch in which the owner of a slice writes its sums straight into every rank's output when every
+ *      output lies in its rank's peer-visible heap and the byte count is a multiple of 16 (the in-place all_reduce
+ *      of a heap-resident gradient bucket): each byte crosses the links once per direction and there is no second
+ *      phase.  The ranks settle inside the kernel whether all outputs qualify; if not, the launch proceeds as form 1.
+ *  -1  the default: 2 between processes, 0 in the single-device emulation (no launch or flag latency to save there).
+ * Every rank of a communicator must use the same setting. */
 int hapx_comm_set_fused_all_reduce(hapx_comm* c, int mode);
 /* Calls issued on different streams are ordered with an event by default.  Turn that off
  * (on = 0) while the caller captures its stream into a CUDA graph and keeps all calls on that one

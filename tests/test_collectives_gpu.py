@@ -236,6 +236,51 @@ def test_all_reduce_one_launch_form(world, dtype):
         comm.set_fused_all_reduce(None)
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_all_reduce_written_into_the_peers_outputs(world, dtype):
+    """Form 2: when every output lies in its rank's heap the slice owners write the sums straight into all outputs
+    (in place on heap tensors, and into separate heap tensors); if one output is an ordinary tensor the same
+    launch falls back to reduce + gather.  All three against the oracle, bit-identical across ranks."""
+    n = (1 << 20) + 64
+    comm = hap_b200.local_comm(world, DEV, stage_bytes=8 << 20, heap_bytes=(8 << 20) + 3 * n * 4 + (1 << 20))
+    try:
+        comm.set_fused_all_reduce("push")
+        xs = [gen((n,), 1311 + r, dtype) for r in range(world)]
+        want = cm.rank_sum(xs, 0.25, dtype)
+        src = [comm.symm_empty((n,), dtype, i) for i in range(world)]
+        dst = [comm.symm_empty((n,), dtype, i) for i in range(world)]
+        for s_, x in zip(src, xs):
+            s_.copy_(x.to(DEV))
+        got = comm.all_reduce(src, scale=0.25, out=dst)                       # heap -> heap
+        comm.check()
+        for r in range(world):
+            assert got[r].data_ptr() == dst[r].data_ptr()
+            torch.testing.assert_close(got[r].cpu(), want, **TOL[dtype])
+            assert torch.equal(got[r], got[0])
+            torch.testing.assert_close(src[r].cpu(), xs[r])                    # inputs untouched
+        mixed = list(dst)
+        mixed[world - 1] = torch.empty(n, dtype=dtype, device=DEV)             # one ordinary output: reduce + gather
+        for d in dst:
+            d.zero_()
+        got = comm.all_reduce(src, scale=0.25, out=mixed)
+        comm.check()
+        for r in range(world):
+            torch.testing.assert_close(got[r].cpu(), want, **TOL[dtype])
+        same = comm.all_reduce(src, scale=0.25, inplace=True)                 # in place on heap tensors
+        comm.check()
+        for r in range(world):
+            assert same[r].data_ptr() == src[r].data_ptr()
+            torch.testing.assert_close(same[r].cpu(), want, **TOL[dtype])
+            assert torch.equal(same[r], same[0])
+        ordinary = comm.all_reduce(gpu(xs), scale=0.25)                       # staged inputs, ordinary outputs
+        comm.check()
+        for r in range(world):
+            torch.testing.assert_close(ordinary[r].cpu(), want, **TOL[dtype])
+    finally:
+        comm.destroy()
+
+
 def test_all_to_all_against_oracle():
     for world, sl, cl in ((4, [4, 3, 2, 1], [1, 2, 3, 4]), (4, [5, 0, 5, 0], [0, 2, 0, 8]), (2, [3, 2], [1, 4]),
                           (8, [7, 6, 5, 4, 3, 3, 2, 2], [56, 46, 39, 33, 28, 23, 18, 13])):

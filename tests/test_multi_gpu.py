@@ -97,6 +97,27 @@ def _worker(rank, world, store):
     assert torch.equal(hap_b200.comm.dynamic_slice(full, 0, L, rank), shard)
     back = comm.reduce_scatter([full], 0, L, scale=1.0 / world)[0]
     torch.testing.assert_close(back, shard, rtol=1e-6, atol=1e-6)
+    # all_reduce of heap-resident tensors: the slice owners write the sums straight into every rank's output
+    # (out of place into a heap tensor, then in place), bit-identical on all ranks; an ordinary output on one rank
+    # makes the same launch fall back to reduce + gather
+    for dtype in (torch.float32, torch.bfloat16):
+        n = (3 << 20) + 64
+        src = comm.symm_empty((n,), dtype)
+        dst = comm.symm_empty((n,), dtype)
+        x = gen((n,), 9000 + rank, dtype)
+        src.copy_(x.to(dev))
+        want = cm.rank_sum(everyone(x), 1.0 / world, dtype)
+        got = comm.all_reduce([src], scale=1.0 / world, out=[dst])[0]
+        assert got.data_ptr() == dst.data_ptr()
+        torch.testing.assert_close(got.cpu(), want, **tol[dtype])
+        assert all(torch.equal(g, got.cpu()) for g in everyone(got))
+        odd = torch.empty(n, dtype=dtype, device=dev) if rank == world - 1 else dst.zero_()
+        got = comm.all_reduce([src], scale=1.0 / world, out=[odd])[0]
+        torch.testing.assert_close(got.cpu(), want, **tol[dtype])
+        got = comm.all_reduce([src], scale=1.0 / world, inplace=True)[0]
+        assert got.data_ptr() == src.data_ptr()
+        torch.testing.assert_close(got.cpu(), want, **tol[dtype])
+        assert all(torch.equal(g, got.cpu()) for g in everyone(got))
     comm.check()
     dist.barrier()
     comm.destroy()

@@ -116,7 +116,7 @@ def test_language_model_programs_reproduce_the_unsharded_model(plan):
         assert names.count("dynamic_slice") == nl and names.count("all_gather") == 3 * nl + 3 * nl + 2
 
 
-@pytest.mark.parametrize("plan", ["dp", "dp_zero"])
+@pytest.mark.parametrize("plan", ["dp", "dp_zero", "tp"])
 def test_vit_programs_reproduce_the_unsharded_model(plan):
     """ViT (patch embedding as a linear map of flattened patches, class token, unmasked MHA, GELU MLP,
     summed NLL over the class token), ratios [.6,.4]; also checked against a convolutional patch
@@ -149,7 +149,11 @@ def test_vit_programs_reproduce_the_unsharded_model(plan):
                 g = torch.split(g, sharding_round(g.shape[0], C.RATIOS), dim=0)[r]
                 n_sharded += 1
             torch.testing.assert_close(p.grad, g, rtol=1e-3, atol=1e-4)
-    assert (n_sharded > 0) == (plan == "dp_zero")
+    assert (n_sharded > 0) == (plan in ("dp_zero", "tp"))
+    if plan == "tp":      # the MLP is column-parallel, as in the language model's tp plan
+        names = [getattr(n.target, "__name__", "") for n in world.modules[0].graph.nodes if n.op == "call_function"]
+        nl = C.VIT_SMALL["nlayers"]
+        assert names.count("dynamic_slice") == nl and names.count("all_gather") == 3 * nl + 3 * nl + 3
 
 
 def test_expert_parallel_moe_program_reproduces_the_unsharded_model():

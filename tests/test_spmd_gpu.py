@@ -107,7 +107,7 @@ def test_language_model_step_matches_cpu_replay(plan):
         comm.destroy()
 
 
-@pytest.mark.parametrize("plan", ["dp", "dp_zero"])
+@pytest.mark.parametrize("plan", ["dp", "dp_zero", "tp"])
 def test_vit_step_matches_cpu_replay(plan):
     """ViT step in bf16 with the heterogeneous ratios [.3,.25,.2,.25] on 4 virtual ranks: patch
     embedding, unmasked attention with an odd sequence length (17), GELU MLP and the class-token
@@ -272,10 +272,10 @@ def _full_width_case(kind):
         inputs = (torch.randint(0, 33278, (B, 256), generator=g), torch.randint(0, 33278, (B, 256), generator=g))
         emit = lambda m, r, ns: P.emit_lm(m, "tp" if kind == "lm_tp" else "dp_zero", C.RATIOS, r, B, ns)
         cpu_ns = C.lm_cpu_namespace()
-    elif kind == "vit":
+    elif kind in ("vit", "vit_tp"):
         model = P.ViT(nlayers=1)
         inputs = (torch.randn(B, 3, 224, 224, generator=g), torch.randint(0, 1000, (B,), generator=g))
-        emit = lambda m, r, ns: P.emit_vit(m, "dp_zero", C.RATIOS, r, B, ns)
+        emit = lambda m, r, ns: P.emit_vit(m, "tp" if kind == "vit_tp" else "dp_zero", C.RATIOS, r, B, ns)
         cpu_ns = C.lm_cpu_namespace()
     else:
         model = P.MoETransformerLM(nlayers=1)
@@ -294,7 +294,7 @@ def _full_width_case(kind):
     return modules, cpu_ns, inputs
 
 
-@pytest.mark.parametrize("kind", ["lm", "lm_tp", "vit", "moe"])
+@pytest.mark.parametrize("kind", ["lm", "lm_tp", "vit", "vit_tp", "moe"])
 def test_full_width_single_layer_step_matches_cpu_replay(kind):
     modules, cpu_ns, inputs = _full_width_case(kind)
     cpu = CpuLockstepWorld(modules(cpu_ns, "cpu", torch.float32), OracleCollectives())
