@@ -963,6 +963,8 @@ def lm_step(args, job, kind, plan, use_graph, dropout_p):
         graph = emit(model, r)
         if not args.lm_no_fuse:
             hap_b200.fxpass.fuse_elementwise(graph)     # dropout + residual add, activation + dropout: one pass each
+        if not args.lm_no_fuse:
+            hap_b200.fxpass.fuse_residual_norm(graph)   # pre-LN blocks: the residual gradient joins inside the norm's backward kernel
         if kind == "moe" and not args.lm_no_fuse:
             hap_b200.fxpass.sparsify_moe(graph)         # dispatch / combine as row gathers instead of dense one-hot contractions
         if W > 1 and not args.lm_no_prefetch:

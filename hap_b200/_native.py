@@ -74,6 +74,7 @@ SIGNATURES = {
     "hapx_layer_norm_forward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _dbl, _vp]),
     "hapx_layer_norm_backward_blocks": (_int, [_i64, _i64]),
     "hapx_layer_norm_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _vp]),
+    "hapx_layer_norm_backward_add": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _vp]),
     "hapx_rng_seed": (_int, [_u64, _vp]),
     "hapx_rng_advance": (_int, [_vp]),
     "hapx_dropout": (_int, [_vp, _vp, _int, _i64, _dbl, _u64, _vp]),

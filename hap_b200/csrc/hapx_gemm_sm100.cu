@@ -54,6 +54,8 @@ struct Params {
   int splits;             // > 1: the contraction is cut into `splits` ranges of kb_per_split slices, each
   int kb_per_split;       //      writing an fp32 partial tile to rows [split * m_pad, ...) of the workspace
   int m_pad;
+  int tail_begin;         // pair kernel: tiles [tail_begin, m_tiles * n_tiles) are worked on as two half-width units each, so that
+                          // the last, partly filled round of tiles takes half as long (only without batching and split-K)
   // batched operation: `batch` independent GEMMs; batch index b = b_out * batch_in + b_in and every
   // tensor map carries (b_in, b_out) as its 3rd and 4th coordinate.  Element strides of D for the
   // direct-store path:
@@ -124,9 +126,9 @@ __device__ __forceinline__ void stage_columns(const unsigned (&r)[32], unsigned 
 // (with a bias the width is a multiple of 8 for either output type).
 template <int BN, bool OUT_F32, bool BIAS>
 __device__ __forceinline__ void drain_fast(const Params& p, const CUtensorMap* tmD, unsigned char* stage_gen, unsigned stage_u32,
-                                           unsigned t_row, int m0, int n0, int bi, int bo, int q, int lane, int& buf) {
+                                           unsigned t_row, int m0, int n0, int bi, int bo, int q, int lane, int& buf, int width = BN) {
   constexpr int PIECES = OUT_F32 ? 1 : 2;          // 32-column groups per 128-byte staging row
-  constexpr int GROUPS = BN / 32;
+  const int GROUPS = width / 32;
   unsigned char* warp_gen = stage_gen + q * (2 * kWarpTileBytes);
   const unsigned warp_u32 = stage_u32 + q * (2 * kWarpTileBytes);
   const int sw = lane & 7;
@@ -163,13 +165,13 @@ __device__ __forceinline__ void drain_fast(const Params& p, const CUtensorMap* t
 
 template <int BN>
 __device__ __forceinline__ void drain_fast_any(const Params& p, const CUtensorMap* tmD, unsigned char* stage_gen, unsigned stage_u32,
-                                               unsigned t_row, int m0, int n0, int bi, int bo, int q, int lane, int& buf) {
+                                               unsigned t_row, int m0, int n0, int bi, int bo, int q, int lane, int& buf, int width = BN) {
   if (p.out_f32) {
-    if (p.bias) drain_fast<BN, true, true>(p, tmD, stage_gen, stage_u32, t_row, m0, n0, bi, bo, q, lane, buf);
-    else drain_fast<BN, true, false>(p, tmD, stage_gen, stage_u32, t_row, m0, n0, bi, bo, q, lane, buf);
+    if (p.bias) drain_fast<BN, true, true>(p, tmD, stage_gen, stage_u32, t_row, m0, n0, bi, bo, q, lane, buf, width);
+    else drain_fast<BN, true, false>(p, tmD, stage_gen, stage_u32, t_row, m0, n0, bi, bo, q, lane, buf, width);
   } else {
-    if (p.bias) drain_fast<BN, false, true>(p, tmD, stage_gen, stage_u32, t_row, m0, n0, bi, bo, q, lane, buf);
-    else drain_fast<BN, false, false>(p, tmD, stage_gen, stage_u32, t_row, m0, n0, bi, bo, q, lane, buf);
+    if (p.bias) drain_fast<BN, false, true>(p, tmD, stage_gen, stage_u32, t_row, m0, n0, bi, bo, q, lane, buf, width);
+    else drain_fast<BN, false, false>(p, tmD, stage_gen, stage_u32, t_row, m0, n0, bi, bo, q, lane, buf, width);
   }
 }
 
@@ -522,7 +524,7 @@ struct Cfg2 {
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const __grid_constant__ CUtensorMap tmD, const Params p) {
+                  const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmD, const Params p) {
   using C = Cfg2<BN, A_MN, B_MN>;
   extern __shared__ unsigned char smem_raw[];
   const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -543,7 +545,18 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const unsigned cta = cluster_ctarank();            // 0 = leader
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int tiles_per_batch = p.m_tiles * p.n_tiles;
-  const int total_tiles = tiles_per_batch * p.splits * p.batch;   // work units: (batch, 256-row tile, column tile, contraction range); splits > 1 only without batching
+  // work units: (batch, 256-row tile, column tile, contraction range); splits > 1 only without batching.  Tiles from
+  // p.tail_begin on (only without batching and split-K) are two units each, one per half of the tile's columns: the
+  // last round of tiles, which fills only part of the SM pairs, then takes half as long.
+  const int tail_tiles = tiles_per_batch - p.tail_begin;
+  const int total_tiles = tiles_per_batch * p.splits * p.batch + tail_tiles;
+  // unit -> (tile of its batch entry, first column inside the tile, columns): full tiles first, then the half-width units
+  auto unit_tile = [&](int bt_tile, int& col_off, int& width) {
+    if (bt_tile < p.tail_begin || tail_tiles == 0) { col_off = 0; width = BN; return bt_tile; }
+    const int u = bt_tile - p.tail_begin;
+    col_off = (u & 1) * (BN / 2); width = BN / 2;
+    return p.tail_begin + (u >> 1);
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -565,37 +578,51 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   if (warp == 0) {
     // ---------------- TMA producer (one per CTA) ----------------
     if (lane == 0) {
+      struct UnitPos { int m0, n0, bi, boA, boB, width, kb_begin, kb_end; bool valid; };
+      auto decode = [&](int unit) {
+        UnitPos u;
+        u.valid = unit < total_tiles;
+        if (!u.valid) return u;
+        const int bt = unit / p.splits, sp = unit - bt * p.splits;
+        const int per_b = tiles_per_batch + tail_tiles;
+        const int b = bt / per_b;
+        int col_off;
+        const int tile = unit_tile(bt - b * per_b, col_off, u.width);
+        const int bo = b / p.batch_in;
+        u.bi = b - bo * p.batch_in;
+        u.boA = p.a_shared_out ? 0 : bo; u.boB = p.b_shared_out ? 0 : bo;
+        u.m0 = (tile % p.m_tiles) * (2 * BM) + (int)cta * BM;
+        u.n0 = (tile / p.m_tiles) * BN + col_off + (int)cta * (u.width / 2);
+        u.kb_begin = sp * p.kb_per_split; u.kb_end = min(u.kb_begin + p.kb_per_split, p.k_blocks);
+        return u;
+      };
       int stage = 0;
       unsigned phase = 0;
       bool ok = true;
-      for (int unit = pair; unit < total_tiles && ok; unit += n_pairs) {
-        const int bt = unit / p.splits, sp = unit - bt * p.splits;
-        const int b = bt / tiles_per_batch, tile = bt - b * tiles_per_batch;
-        const int bo = b / p.batch_in, bi = b - bo * p.batch_in;
-        const int boA = p.a_shared_out ? 0 : bo, boB = p.b_shared_out ? 0 : bo;
-        const int m0 = (tile % p.m_tiles) * (2 * BM) + (int)cta * BM;
-        const int n0 = (tile / p.m_tiles) * BN + (int)cta * (BN / 2);
-        const int kb_begin = sp * p.kb_per_split, kb_end = min(kb_begin + p.kb_per_split, p.k_blocks);
-        for (int kb = kb_begin; kb < kb_end; ++kb) {
+      UnitPos cur = decode(pair);
+      for (int unit = pair; cur.valid && ok; unit += n_pairs) {
+        const UnitPos nxt = decode(unit + n_pairs);
+        const unsigned tx_bytes = 2 * (C::A_BYTES + (cur.width == BN ? C::B_BYTES : C::B_BYTES / 2));
+        for (int kb = cur.kb_begin; kb < cur.kb_end; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u)) { ok = false; break; }
           const unsigned sa = base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
           const unsigned leader_full = map_to_cta(full_bar(stage), 0);
-          if (cta == 0) mbar_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);   // bytes of both CTAs
+          if (cta == 0) mbar_expect_tx(full_bar(stage), tx_bytes);   // bytes of both CTAs
           const int k0 = kb * BK;
           if (!A_MN) {
-            tma_load_4d_pair(sa, &tmA, k0, m0, bi, boA, leader_full);
+            tma_load_4d_pair(sa, &tmA, k0, cur.m0, cur.bi, cur.boA, leader_full);
           } else {
 #pragma unroll
-            for (int i = 0; i < BM / 64; ++i) tma_load_4d_pair(sa + i * 8192u, &tmA, m0 + 64 * i, k0, bi, boA, leader_full);
+            for (int i = 0; i < BM / 64; ++i) tma_load_4d_pair(sa + i * 8192u, &tmA, cur.m0 + 64 * i, k0, cur.bi, cur.boA, leader_full);
           }
           if (!B_MN) {
-            tma_load_4d_pair(sb, &tmB, k0, n0, bi, boB, leader_full);
+            tma_load_4d_pair(sb, cur.width == BN ? &tmB : &tmBh, k0, cur.n0, cur.bi, cur.boB, leader_full);   // BN/2 (or BN/4) rows of B per CTA
           } else {
-#pragma unroll
-            for (int i = 0; i < BN / 128; ++i) tma_load_4d_pair(sb + i * 8192u, &tmB, n0 + 64 * i, k0, bi, boB, leader_full);   // BN/2 columns per CTA
+            for (int i = 0; i < cur.width / 128; ++i) tma_load_4d_pair(sb + i * 8192u, &tmB, cur.n0 + 64 * i, k0, cur.bi, cur.boB, leader_full);   // width/2 columns per CTA
           }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
+        cur = nxt;
       }
       if (!ok) atomicCAS(p.error, 0u, 1u);
     }
@@ -608,6 +635,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       for (int unit = pair; unit < total_tiles && ok; unit += n_pairs) {
         const int sp = unit % p.splits;
         const int kb_begin = sp * p.kb_per_split, kb_end = min(kb_begin + p.kb_per_split, p.k_blocks);
+        int col_off, width;
+        {
+          const int bt = unit / p.splits, per_b = tiles_per_batch + tail_tiles;
+          unit_tile(bt - (bt / per_b) * per_b, col_off, width);
+        }
+        // the instruction descriptor's N field follows the unit's width
+        const unsigned idesc = (C::IDESC & ~(0x3fu << 17)) | ((unsigned)(width >> 3) << 17);
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u)) { ok = false; break; }
         tc_fence_after();
         const unsigned d_tmem = tmem_base + (unsigned)(acc * BN);
@@ -619,7 +653,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const unsigned long long da = A_MN ? make_desc(sa + k * 2048u, 8192u, 1024u) : make_desc(sa + k * 32u, 16u, 1024u);
             const unsigned long long db = B_MN ? make_desc(sb + k * 2048u, 8192u, 1024u) : make_desc(sb + k * 32u, 16u, 1024u);
-            umma2_bf16(d_tmem, da, db, C::IDESC, (kb != kb_begin || k != 0) ? 1u : 0u);
+            umma2_bf16(d_tmem, da, db, idesc, (kb != kb_begin || k != 0) ? 1u : 0u);
           }
           umma2_commit_both(empty_bar(stage));
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
@@ -640,10 +674,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     int store_buf = 0;
     for (int unit = pair; unit < total_tiles && ok; unit += n_pairs) {
       const int bt = unit / p.splits, sp = unit - bt * p.splits;
-      const int b = bt / tiles_per_batch, tile = bt - b * tiles_per_batch;
+      const int per_b = tiles_per_batch + tail_tiles;
+      const int b = bt / per_b;
+      int col_off, width;
+      const int tile = unit_tile(bt - b * per_b, col_off, width);
       const int bo = b / p.batch_in, bi = b - bo * p.batch_in;
       // with split-K the partial tile goes to the workspace, whose rows are [split][m_pad]
-      const int m0 = (tile % p.m_tiles) * (2 * BM) + (int)cta * BM + sp * p.m_pad, n0 = (tile / p.m_tiles) * BN;
+      const int m0 = (tile % p.m_tiles) * (2 * BM) + (int)cta * BM + sp * p.m_pad, n0 = (tile / p.m_tiles) * BN + col_off;
       if (!p.fast_drain) {
         asm volatile("bar.sync 1, 128;" ::: "memory");
         for (int j = et; j < BN; j += kEpilogueThreads) {
@@ -657,7 +694,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (!ok) break;
       tc_fence_after();
       const unsigned t_row = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(acc * BN);
-      if (p.fast_drain) drain_fast_any<BN>(p, &tmD, store_gen, store_u32, t_row, m0, n0, bi, bo, q, lane, store_buf);
+      if (p.fast_drain) drain_fast_any<BN>(p, &tmD, store_gen, store_u32, t_row, m0, n0, bi, bo, q, lane, store_buf, width);
       else drain_tile<BN>(p, &tmD, p.tma_store != 0, store_gen, store_u32, bias_tile, t_row, m0, n0, bi, bo, q, lane, et, store_buf);
       tc_fence_before();
       mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));   // tell the leader this thread has drained its rows
@@ -930,7 +967,7 @@ static int launch2(const Operand& A, const Operand& B, const Operand& Dop, Param
     if (int e = workspace(dev.index, stream, (size_t)p.splits * p.m_pad * p.N * sizeof(float), &ws)) return e;
     p.D = ws; p.ldd = p.N; p.out_f32 = 1; p.bias = nullptr; p.epilogue = EPI_NONE;
   }
-  CUtensorMap tmA, tmB, tmD;
+  CUtensorMap tmA, tmB, tmBh, tmD;
   const int batch_out = p.batch / p.batch_in;
   const long long out_rows = p.splits > 1 ? (long long)p.splits * p.m_pad : p.M;
   if (int e = make_out_map(&tmD, &p.tma_store, p.D, p.N, out_rows, p.ldd, p.out_f32, p.batch_in, Dop.s_in, batch_out, Dop.s_out)) return e;
@@ -938,11 +975,19 @@ static int launch2(const Operand& A, const Operand& B, const Operand& Dop, Param
   if (p.splits > 1 && !p.tma_store) return fail(HAPX_ERR_EXTENT, "gemm: split-K needs an output width that is a multiple of 4");
   if (int e = make_map(&tmA, A, p.M, p.Kc, BM, p.batch_in, p.a_shared_out ? 1 : batch_out)) return e;
   if (int e = make_map(&tmB, B, p.N, p.Kc, C::BN / 2, p.batch_in, p.b_shared_out ? 1 : batch_out)) return e;
-  const long long units = (long long)tiles * p.splits * p.batch;
+  if (int e = make_map(&tmBh, B, p.N, p.Kc, C::BN / 4, p.batch_in, p.b_shared_out ? 1 : batch_out)) return e;
+  // A last round that fills at most half of the SM pairs is run as half-width units (no partial sums, no second
+  // launch): 96 tiles on 74 pairs take 1.5 tile times instead of 2.
+  p.tail_begin = tiles;
+  if (p.splits == 1 && p.batch == 1 && p.fast_drain && tiles > max_clusters) {
+    const int rest = tiles % max_clusters;
+    if (rest > 0 && 2 * rest <= max_clusters) p.tail_begin = tiles - rest;
+  }
+  const long long units = (long long)tiles * p.splits * p.batch + (tiles - p.tail_begin);
   if (units > 0x7fffffff) return fail(HAPX_ERR_EXTENT, "gemm: too many tiles");
   const int pairs = (int)std::max<long long>(1, std::min<long long>(units, max_clusters));
   cfg.gridDim = dim3(2 * pairs);
-  HAPX_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmD, p));
+  HAPX_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmBh, tmD, p));
   count_launch();
   if (p.splits > 1) {
     const long long total = (long long)user.M * (user.N / 4);

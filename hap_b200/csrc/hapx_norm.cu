@@ -134,12 +134,14 @@ __global__ void __launch_bounds__(kThreads) layer_norm_forward_kernel(const T* _
   }
 }
 
-// dx = rstd * (dy*gamma - mean(dy*gamma) - xhat * mean(dy*gamma*xhat));  partial[b][0][e] += dy*xhat, partial[b][1][e] += dy
-template <typename T, int NV>
+// dx = rstd * (dy*gamma - mean(dy*gamma) - xhat * mean(dy*gamma*xhat)) [+ add];  partial[b][0][e] += dy*xhat, partial[b][1][e] += dy
+// `add` (may be null): a second gradient of x - the one that arrives through the residual connection around the
+// normalised branch of a pre-LN block - added here instead of by a separate kernel.
+template <typename T, int NV, bool ADD>
 __global__ void __launch_bounds__(kThreads, (NV <= 3 ? 3 : 2)) layer_norm_backward_kernel(const T* __restrict__ x, const T* __restrict__ dy,
                                                                        const T* __restrict__ gamma, const float* __restrict__ mean_in,
-                                                                       const float* __restrict__ rstd_in, T* __restrict__ dx,
-                                                                       float* __restrict__ partial, long long rows, int E) {
+                                                                       const float* __restrict__ rstd_in, const T* __restrict__ add,
+                                                                       T* __restrict__ dx, float* __restrict__ partial, long long rows, int E) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int groups = E >> 3;
   float gam[NV][8], dg[NV][8], db[NV][8];
@@ -179,6 +181,15 @@ __global__ void __launch_bounds__(kThreads, (NV <= 3 ? 3 : 2)) layer_norm_backwa
         }
       }
     }
+    if constexpr (ADD) {
+      // no registers left to hold the residual gradient across the reductions: pull this row's lines into L2 / L1
+      // now (one request per 128-byte line), the loads at the end of the iteration then find them close by
+      if ((lane & (sizeof(T) == 2 ? 7 : 3)) == 0) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+          if (lane + 32 * v < groups) asm volatile("prefetch.global.L1 [%0];" ::"l"(add + row * E + 8 * (lane + 32 * v)));
+      }
+    }
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
@@ -203,6 +214,12 @@ __global__ void __launch_bounds__(kThreads, (NV <= 3 ? 3 : 2)) layer_norm_backwa
         float o[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) o[k] = rstd * (gy[v][k] - m1 - xh[v][k] * m2);
+        if constexpr (ADD) {
+          float r[8];
+          Row<T>::unpack(Row<T>::load(add + row * E + 8 * g), r);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) o[k] += r[k];
+        }
         Row<T>::store8(dr + 8 * g, o);
       }
     }
@@ -271,11 +288,16 @@ static void launch_fwd(const void* x, const void* gamma, const void* beta, void*
                                                                   static_cast<const T*>(beta), static_cast<T*>(y), mean, rstd, rows, E, eps);
 }
 template <typename T, int NV>
-static void launch_bwd(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd, void* dx, float* partial,
-                       long long rows, int E, int grid, cudaStream_t stream) {
-  layer_norm_backward_kernel<T, NV><<<grid, kThreads, 0, stream>>>(static_cast<const T*>(x), static_cast<const T*>(dy),
-                                                                   static_cast<const T*>(gamma), mean, rstd, static_cast<T*>(dx), partial,
-                                                                   rows, E);
+static void launch_bwd(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd, const void* add, void* dx,
+                       float* partial, long long rows, int E, int grid, cudaStream_t stream) {
+  if (add != nullptr)
+    layer_norm_backward_kernel<T, NV, true><<<grid, kThreads, 0, stream>>>(static_cast<const T*>(x), static_cast<const T*>(dy),
+                                                                           static_cast<const T*>(gamma), mean, rstd, static_cast<const T*>(add),
+                                                                           static_cast<T*>(dx), partial, rows, E);
+  else
+    layer_norm_backward_kernel<T, NV, false><<<grid, kThreads, 0, stream>>>(static_cast<const T*>(x), static_cast<const T*>(dy),
+                                                                            static_cast<const T*>(gamma), mean, rstd, nullptr,
+                                                                            static_cast<T*>(dx), partial, rows, E);
 }
 
 static int check_common(const char* who, int dtype, int64_t rows, int64_t E) {
@@ -326,6 +348,12 @@ int hapx_layer_norm_forward(const void* x, const void* gamma, const void* beta, 
 
 int hapx_layer_norm_backward(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd, void* dx,
                              void* dgamma, void* dbeta, float* partial, int dtype, int64_t rows, int64_t E, hapx_stream stream_) {
+  return hapx_layer_norm_backward_add(x, dy, gamma, mean, rstd, nullptr, dx, dgamma, dbeta, partial, dtype, rows, E, stream_);
+}
+
+int hapx_layer_norm_backward_add(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd, const void* add,
+                                 void* dx, void* dgamma, void* dbeta, float* partial, int dtype, int64_t rows, int64_t E,
+                                 hapx_stream stream_) {
   if (int e = check_common("layer_norm_backward", dtype, rows, E)) return e;
   if (!partial) return fail(HAPX_ERR_ARGUMENT, "layer_norm_backward: null partials buffer");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -336,11 +364,11 @@ int hapx_layer_norm_backward(const void* x, const void* dy, const void* gamma, c
     const int nv = (int)((E / 8 + 31) / 32);
 #define HAPX_LN_BWD(T)                                                                                       \
   switch (nv) {                                                                                              \
-    case 1: launch_bwd<T, 1>(x, dy, gamma, mean, rstd, dx, partial, rows, (int)E, grid, stream); break;      \
-    case 2: launch_bwd<T, 2>(x, dy, gamma, mean, rstd, dx, partial, rows, (int)E, grid, stream); break;      \
-    case 3: launch_bwd<T, 3>(x, dy, gamma, mean, rstd, dx, partial, rows, (int)E, grid, stream); break;      \
-    case 4: launch_bwd<T, 4>(x, dy, gamma, mean, rstd, dx, partial, rows, (int)E, grid, stream); break;      \
-    default: launch_bwd<T, 8>(x, dy, gamma, mean, rstd, dx, partial, rows, (int)E, grid, stream); break;     \
+    case 1: launch_bwd<T, 1>(x, dy, gamma, mean, rstd, add, dx, partial, rows, (int)E, grid, stream); break;      \
+    case 2: launch_bwd<T, 2>(x, dy, gamma, mean, rstd, add, dx, partial, rows, (int)E, grid, stream); break;      \
+    case 3: launch_bwd<T, 3>(x, dy, gamma, mean, rstd, add, dx, partial, rows, (int)E, grid, stream); break;      \
+    case 4: launch_bwd<T, 4>(x, dy, gamma, mean, rstd, add, dx, partial, rows, (int)E, grid, stream); break;      \
+    default: launch_bwd<T, 8>(x, dy, gamma, mean, rstd, add, dx, partial, rows, (int)E, grid, stream); break;     \
   }
     if (dtype == HAPX_BF16) { HAPX_LN_BWD(__nv_bfloat16) } else { HAPX_LN_BWD(float) }
 #undef HAPX_LN_BWD

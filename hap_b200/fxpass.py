@@ -224,6 +224,34 @@ def fuse_elementwise(graph: torch.fx.Graph) -> Dict[str, int]:
     return changed
 
 
+def fuse_residual_norm(graph: torch.fx.Graph) -> int:
+    """Pre-LN residual blocks, ``x_new = x + f(layer_norm(x))``: ``x`` feeds the normalisation and the residual
+    addition, so autograd adds two gradients of ``x`` with a kernel of its own in every block.  Rewrites
+    ``h = layer_norm(x, ...)`` into ``x_res, h = layer_norm_fork(x, ...)`` and hands ``x_res`` to the other
+    users of ``x``; the two gradients then meet inside the normalisation's backward kernel.  Applies to this
+    package's ``layer_norm`` nodes whose input has exactly one other user; returns the number rewritten."""
+    import operator
+    from .norm import layer_norm, layer_norm_fork
+    changed = 0
+    for node in list(graph.nodes):
+        if node.op != "call_function" or not _is(node.target, layer_norm):
+            continue
+        x = node.args[0] if node.args else node.kwargs.get("input")
+        if not isinstance(x, torch.fx.Node) or len(x.users) != 2:
+            continue
+        other = next(u for u in x.users if u is not node)
+        with graph.inserting_before(node):
+            fork = graph.call_function(layer_norm_fork, node.args, node.kwargs)
+            x_res = graph.call_function(operator.getitem, (fork, 0))
+            h = graph.call_function(operator.getitem, (fork, 1))
+        other.replace_input_with(x, x_res)
+        node.replace_all_uses_with(h)
+        graph.erase_node(node)
+        changed += 1
+    graph.lint()
+    return changed
+
+
 def _peel(node, method: str):
     """If ``node`` is ``x.<method>(...)`` return ``x`` else ``node`` itself."""
     if isinstance(node, torch.fx.Node) and node.op == "call_method" and node.target == method:

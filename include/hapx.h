@@ -396,6 +396,12 @@ int hapx_layer_norm_backward_blocks(int64_t rows, int64_t E);
 int hapx_layer_norm_backward(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd, void* dx,
                              void* dgamma, void* dbeta, float* partial, int dtype, int64_t rows, int64_t E,
                              hapx_stream stream);
+/* The same with a second gradient of x added to dx in the same pass (`add`: rows x E of the data type, or
+ * NULL): the gradient that reaches x through the residual connection around the normalised branch of a
+ * pre-LN block, which autograd would otherwise add with a kernel of its own. */
+int hapx_layer_norm_backward_add(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd, const void* add,
+                                 void* dx, void* dgamma, void* dbeta, float* partial, int dtype, int64_t rows, int64_t E,
+                                 hapx_stream stream);
 
 /* ---- diagnostics ----------------------------------------------------------------
  * No counterpart in the reference.  Walks the kernels' tiling of ONE rank's pull over

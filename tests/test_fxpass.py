@@ -113,6 +113,31 @@ def test_elementwise_fusion_folds_the_dropout_sites():
     assert fxpass.fuse_elementwise(g)["dropout_add"] == 0
 
 
+def test_residual_norms_are_forked():
+    """x + f(layer_norm(x)): the normalisation hands x through, so the residual user reads the fork's first result."""
+    import operator
+    from hap_b200 import fxpass
+    from hap_b200 import plan as P
+    from hap_b200.norm import layer_norm, layer_norm_fork
+    nl = C.LM_SMALL["nlayers"]
+    for p_drop in (0.0, 0.1):
+        graph = P.emit_lm(copy.deepcopy(C.lm_model()), "dp_zero", C.RATIOS, 0, C.LM_BATCH, P.default_namespace(), dropout_p=p_drop)
+        fxpass.fuse_elementwise(graph)
+        assert fxpass.fuse_residual_norm(graph) == 2 * nl
+        targets = [n.target for n in graph.nodes if n.op == "call_function"]
+        assert targets.count(layer_norm_fork) == 2 * nl and targets.count(layer_norm) == 1      # the final norm has no residual
+        for n in graph.nodes:
+            if n.op == "call_function" and n.target is layer_norm_fork:
+                parts = {u.args[1]: u for u in n.users}
+                assert set(parts) == {0, 1} and all(u.target is operator.getitem for u in n.users)
+                assert len(parts[0].users) == 1 and len(n.args[0].users) == 1               # x now feeds the fork only
+    vit = P.emit_vit(copy.deepcopy(C.vit_model()), "dp", C.RATIOS, 0, C.LM_BATCH, P.default_namespace(), dropout_p=0.1)
+    assert fxpass.fuse_residual_norm(vit) == 2 * C.VIT_SMALL["nlayers"]
+    # the post-LN MoE blocks normalise the sum itself: nothing to fork
+    moe = P.emit_moe(copy.deepcopy(C.moe_model()), C.RATIOS, 0, C.LM_BATCH, P.default_namespace())
+    assert fxpass.fuse_residual_norm(moe) == 0
+
+
 def test_parameter_gathers_are_hoisted():
     from hap_b200 import collectives, fxpass
     from hap_b200 import plan as P

@@ -63,3 +63,36 @@ def test_layer_norm_is_deterministic_and_handles_leading_dimensions():
     # shapes the kernels do not cover go to torch's implementation
     odd = torch.randn(4, 10, device=dev)
     torch.testing.assert_close(layer_norm(odd, (10,), torch.ones(10, device=dev), None), F.layer_norm(odd, (10,), torch.ones(10, device=dev)))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(256, 8, 768), (197, 3, 768), (40, 1024), (9, 2, 64)])
+def test_layer_norm_fork_adds_the_residual_gradient_in_the_same_kernel(dtype, shape):
+    """(x, layer_norm(x)) for the pre-LN residual pattern: same values as layer_norm, and the gradient of x is the
+    normalisation's gradient plus the residual path's, in float64 from the same rounded inputs."""
+    from hap_b200.norm import layer_norm, layer_norm_fork
+    dev = torch.device("cuda:0")
+    E = shape[-1]
+    g = torch.Generator().manual_seed(sum(shape))
+    x = (torch.randn(*shape, generator=g) * 2 + 0.5).to(dtype)
+    w = (torch.rand(E, generator=g) + 0.5).to(dtype)
+    b = torch.randn(E, generator=g).to(dtype)
+    dres, dy = torch.randn(*shape, generator=g).to(dtype), torch.randn(*shape, generator=g).to(dtype)
+    xr, wr, br = x.double().requires_grad_(True), w.double().requires_grad_(True), b.double().requires_grad_(True)
+    (F.layer_norm(xr, (E,), wr, br, 1e-5) * dy.double()).sum().backward()
+    want_dx = xr.grad + dres.double()
+    xg, wg, bg = x.to(dev).requires_grad_(True), w.to(dev).requires_grad_(True), b.to(dev).requires_grad_(True)
+    x_res, h = layer_norm_fork(xg, (E,), wg, bg, 1e-5)
+    assert x_res.data_ptr() == xg.data_ptr() and torch.equal(h, layer_norm(xg.detach(), (E,), wg.detach(), bg.detach(), 1e-5))
+    ((x_res * dres.to(dev)).sum() + (h * dy.to(dev)).sum()).backward()
+    rtol, atol = (1e-5, 2e-5) if dtype == torch.float32 else (2 ** -7, 2 ** -6)
+    torch.testing.assert_close(xg.grad.cpu().double(), want_dx, rtol=rtol, atol=atol)
+    for got, ref in ((wg.grad, wr.grad), (bg.grad, br.grad)):
+        assert float((got.cpu().double() - ref).abs().max()) <= (1e-5 if dtype == torch.float32 else 2 ** -7) * max(float(ref.abs().max()), 1.0)
+    # only one of the two results used
+    for use in (0, 1):
+        xg2 = x.to(dev).requires_grad_(True)
+        out = layer_norm_fork(xg2, (E,), wg, bg, 1e-5)[use]
+        (out * dy.to(dev)).sum().backward()
+        want = dy.double() if use == 0 else xr.grad
+        torch.testing.assert_close(xg2.grad.cpu().double(), want, rtol=rtol, atol=atol)

@@ -355,3 +355,51 @@ def test_moe_step_with_sparse_dispatch_follows_the_dense_program():
         hap_b200.linear_ops.gemm_status()
     finally:
         comm.destroy()
+
+
+@pytest.mark.parametrize("kind", ["lm", "vit"])
+def test_step_with_forked_residual_norms_follows_the_program_as_emitted(kind):
+    """fxpass.fuse_residual_norm only moves an addition into the normalisation's backward kernel: the pre-LN
+    programs give the same gradients (one bf16 rounding apart) and walk the same loss trajectory."""
+    import copy
+    from hap_b200 import fxpass
+    from hap_b200 import plan as P
+    if kind == "lm":
+        model, feed1 = C.lm_model(torch.bfloat16), C.lm_batch()
+        emit, nl = (lambda m, r: P.emit_lm(m, "dp_zero", C.RATIOS, r, C.LM_BATCH)), C.LM_SMALL["nlayers"]
+    else:
+        model, feed1 = C.vit_model(torch.bfloat16), C.vit_batch(torch.bfloat16)
+        emit, nl = (lambda m, r: P.emit_vit(m, "dp_zero", C.RATIOS, r, C.LM_BATCH)), C.VIT_SMALL["nlayers"]
+
+    def modules(rewrite):
+        mods = []
+        for r in range(2):
+            m = copy.deepcopy(model).to(DEV)
+            g = emit(m, r)
+            if rewrite:
+                assert fxpass.fuse_residual_norm(g) == 2 * nl
+            mods.append(torch.fx.GraphModule(m, g))
+        return mods
+
+    comm = hap_b200.local_comm(2, DEV, stage_bytes=16 << 20, heap_bytes=32 << 20)
+    try:
+        plain = LockstepWorld(modules(False), hap_b200.LocalCollectives(comm))
+        forked = LockstepWorld(modules(True), hap_b200.LocalCollectives(comm))
+        feed = [tuple(t.to(DEV) for t in feed1)] * 2
+        # first the gradients of one backward pass (before Adam's sign-like first steps amplify rounding differences) ...
+        la, lb = plain.forward(feed), forked.forward(feed)
+        torch.stack(la).sum().backward()
+        torch.stack(lb).sum().backward()
+        for r in range(2):
+            assert abs(float(la[r]) - float(lb[r])) <= 1e-3 * abs(float(la[r]))
+            for (name, pa), (_, pb) in zip(plain.modules[r].named_parameters(), forked.modules[r].named_parameters()):
+                d = (pa.grad.float() - pb.grad.float()).norm()
+                assert float(d) <= 3e-2 * float(pa.grad.float().norm()) + 1e-3, (name, float(d), float(pa.grad.float().norm()))
+        # ... then the loss trajectory of whole steps
+        for it in range(3):
+            a, b = float(plain.step(feed)), float(forked.step(feed))
+            assert abs(a - b) <= 1e-2 * abs(a), (it, a, b)
+        comm.check()
+        hap_b200.linear_ops.gemm_status()
+    finally:
+        comm.destroy()
