@@ -34,20 +34,49 @@ enum Mode {
   M_GELU_DROP_BWD = 5  // y = a * k * gelu'(b)           a = dy, b = the forward's INPUT
 };
 
-__device__ __forceinline__ float gelu_f(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752f)); }
+// Phi(v) = 0.5 (1 + erf(v / sqrt 2)) and the density's exponential e^{-v^2/2}.  FAST (16-bit tensors): erf by the
+// rational approximation 7.1.26 of Abramowitz & Stegun, 1 - (a1 t + ... + a5 t^5) e^{-z^2} with t = 1 / (1 + p z),
+// absolute error 1.5e-7 - far below a bfloat16 rounding - which shares its exponential with the density: one ex2, one
+// rcp and a handful of FMAs where erff() spends several dozen instructions (the GELU passes were bound by them).
+template <bool FAST>
+__device__ __forceinline__ void normal_cdf(float v, float& cdf, float& e) {
+  if constexpr (FAST) {
+    const float z = fabsf(v) * 0.70710678118654752f;
+    e = __expf(-z * z);
+    const float t = __fdividef(1.f, fmaf(0.3275911f, z, 1.f));
+    float poly = fmaf(1.061405429f, t, -1.453152027f);
+    poly = fmaf(poly, t, 1.421413741f);
+    poly = fmaf(poly, t, -0.284496736f);
+    poly = fmaf(poly, t, 0.254829592f);
+    const float tail = 0.5f * poly * t * e;          // 0.5 (1 - erf z)
+    cdf = v >= 0.f ? 1.f - tail : tail;
+  } else {
+    cdf = 0.5f * (1.f + erff(v * 0.70710678118654752f));
+    e = __expf(-0.5f * v * v);
+  }
+}
+template <bool FAST>
+__device__ __forceinline__ float gelu_f(float v) {
+  float cdf, e;
+  normal_cdf<FAST>(v, cdf, e);
+  return v * cdf;
+}
+template <bool FAST>
 __device__ __forceinline__ float gelu_grad_f(float v) {
-  return 0.5f * (1.f + erff(v * 0.70710678118654752f)) + v * 0.3989422804014327f * __expf(-0.5f * v * v);
+  float cdf, e;
+  normal_cdf<FAST>(v, cdf, e);
+  return fmaf(v * 0.3989422804014327f, e, cdf);
 }
 
-template <int MODE>
+template <int MODE, bool FAST>
 __device__ __forceinline__ float fused_value(float a, float b, float k, float scale) {
   switch (MODE) {
     case M_DROP: return a * k;
     case M_DROP_ADD: return fmaf(a, k, b);
     case M_RELU_DROP: return fmaxf(a, 0.f) * k;
-    case M_GELU_DROP: return gelu_f(a) * k;
+    case M_GELU_DROP: return gelu_f<FAST>(a) * k;
     case M_RELU_DROP_BWD: return b != 0.f ? a * scale : 0.f;
-    default: return a * k * gelu_grad_f(b);
+    default: return a * k * gelu_grad_f<FAST>(b);
   }
 }
 
@@ -99,11 +128,11 @@ __global__ void __launch_bounds__(256) dropout_kernel(const T* __restrict__ a, c
       Vec8<T>::load(a + e0, fa);
       if (TWO) Vec8<T>::load(b + e0, fb);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) fy[i] = fused_value<MODE>(fa[i], TWO ? fb[i] : 0.f, (keep >> i) & 1u ? scale : 0.f, scale);
+      for (int i = 0; i < 8; ++i) fy[i] = fused_value<MODE, sizeof(T) == 2>(fa[i], TWO ? fb[i] : 0.f, (keep >> i) & 1u ? scale : 0.f, scale);
       Vec8<T>::store(y + e0, fy);
     } else {
       for (int i = 0; i < 8 && e0 + i < n; ++i)
-        y[e0 + i] = (T)fused_value<MODE>((float)a[e0 + i], TWO ? (float)b[e0 + i] : 0.f, (keep >> i) & 1u ? scale : 0.f, scale);
+        y[e0 + i] = (T)fused_value<MODE, sizeof(T) == 2>((float)a[e0 + i], TWO ? (float)b[e0 + i] : 0.f, (keep >> i) & 1u ? scale : 0.f, scale);
     }
   }
 }
