@@ -156,6 +156,50 @@ __device__ __forceinline__ float chunk_exp(const unsigned (&v)[32], float scale2
   return (s0 + s1) + (s2 + s3);
 }
 
+// The same for 16 columns (the backward pass, whose sixteen math warps each take 32 columns in two steps).
+template <bool PARTIAL>
+__device__ __forceinline__ void chunk_exp16(const unsigned (&v)[16], float scale2, float shift, int lim, const float* mrow, float (&pe)[16]) {
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    float x;
+    if (mrow) {
+      x = chunk_score<PARTIAL>(v[e], scale2, e, lim, mrow) - shift;
+    } else {
+      x = fmaf(__uint_as_float(v[e]), scale2, -shift);
+      if (PARTIAL) x = (e <= lim) ? x : -INFINITY;
+    }
+    pe[e] = ex2(x);
+  }
+}
+// Store 16 consecutive columns [16c, 16c+16) of row `row` into the swizzled [2 chunks][128 rows][64 columns] tile.
+__device__ __forceinline__ void store_prob_columns16(unsigned char* tile, int row, int c, const float (&v)[16]) {
+  unsigned char* base = tile + (c >> 2) * (BT * 128) + row * 128;
+  const int sw = row & 7;
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    uint4 pk;
+    pk.x = pack_bf16(v[8 * g], v[8 * g + 1]); pk.y = pack_bf16(v[8 * g + 2], v[8 * g + 3]);
+    pk.z = pack_bf16(v[8 * g + 4], v[8 * g + 5]); pk.w = pack_bf16(v[8 * g + 6], v[8 * g + 7]);
+    *reinterpret_cast<uint4*>(base + ((((c & 3) * 2 + g) ^ sw) << 4)) = pk;
+  }
+}
+__device__ __forceinline__ unsigned keep16(const rng::Key& key, unsigned threshold, unsigned long long row_groups0, int col0) {
+  unsigned bits = 0;
+#pragma unroll
+  for (int g = 0; g < 2; ++g)
+    bits |= rng::keep_bits(rng::philox(key, row_groups0 + (unsigned)((col0 >> 3) + g)), threshold) << (8 * g);
+  return bits;
+}
+__device__ __forceinline__ void store_row16(__nv_bfloat16* dst, const float (&v)[16]) {
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    uint4 pk;
+    pk.x = pack_bf16(v[8 * g], v[8 * g + 1]); pk.y = pack_bf16(v[8 * g + 2], v[8 * g + 3]);
+    pk.z = pack_bf16(v[8 * g + 4], v[8 * g + 5]); pk.w = pack_bf16(v[8 * g + 6], v[8 * g + 7]);
+    reinterpret_cast<uint4*>(dst)[g] = pk;
+  }
+}
+
 __device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const float (&v)[32]) {
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
@@ -418,8 +462,8 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params
 // Shared memory: 2 outer tiles | 2 stages x 2 inner tiles | Pd | dS.  Tensor memory (512 columns): S [0,128),
 // dPd [128,256), accumulators [256,320) and [320,384).
 constexpr int kBwdStages = 2;
-constexpr int kBwdThreads = 320;            // TMA warp, MMA warp, 8 math warps: two per tensor-memory lane quarter, each
-constexpr int kBwdMath = 256;               // taking half of the columns of its 32 rows (no row reductions are needed here)
+constexpr int kBwdThreads = 576;            // TMA warp, MMA warp, 16 math warps: four per tensor-memory lane quarter, each
+constexpr int kBwdMath = 512;               // taking a quarter of the columns of its 32 rows (no row reductions are needed here)
 constexpr unsigned kBwdSmem = 1024 + kTileBytes * (2 + 2 * kBwdStages) + 2 * kProbBytes + 256;
 
 template <bool KEY_MAJOR>
@@ -564,7 +608,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap tmQKV, const __gri
     }
   } else {
     const int q4 = warp & 3;                       // tensor-memory lane quarter of this warp
-    const int half = (warp - 2) >> 2;              // which 64 of the tile's 128 columns this warp takes
+    const int part = (warp - 2) >> 2;              // which 32 of the tile's 128 columns this warp takes
     const int r = q4 * 32 + lane;
     const unsigned lane_off = (unsigned)(q4 * 32) << 16;
     unsigned n_out = 0, n_in = 0;
@@ -595,35 +639,35 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap tmQKV, const __gri
         tc_fence_after();
 #pragma unroll 1
         for (int cc = 0; cc < 2; ++cc) {
-          const int c = 2 * half + cc;
-          const int c0 = k0 + 32 * c;
-          float pd[32], ds[32];
+          const int c = 2 * part + cc;               // group of 16 columns of the tile
+          const int c0 = k0 + 16 * c;
+          float pd[16], ds[16];
           if (c0 > wlast) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) { pd[e] = 0.f; ds[e] = 0.f; }
+            for (int e = 0; e < 16; ++e) { pd[e] = 0.f; ds[e] = 0.f; }
           } else {
-            unsigned sv[32], gv[32];
-            tmem_ld_32x32(tS + lane_off + 32u * c, sv);
-            tmem_ld_32x32(tDP + lane_off + 32u * c, gv);
+            unsigned sv[16], gv[16];
+            tmem_ld_32x16(tS + lane_off + 16u * c, sv);
+            tmem_ld_32x16(tDP + lane_off + 16u * c, gv);
             tmem_ld_wait();
             const float* mr = mrow ? mrow + c0 : nullptr;
-            if (c0 + 31 > wmin_last) chunk_exp<true>(sv, p.scale2, lse, last - c0, mr, pd);
-            else chunk_exp<false>(sv, p.scale2, lse, 31, mr, pd);
+            if (c0 + 15 > wmin_last) chunk_exp16<true>(sv, p.scale2, lse, last - c0, mr, pd);
+            else chunk_exp16<false>(sv, p.scale2, lse, 15, mr, pd);
             if (p.drop_threshold) {
-              const unsigned keep = keep32(key, p.drop_threshold, rg0, c0);
+              const unsigned keep = keep16(key, p.drop_threshold, rg0, c0);
 #pragma unroll
-              for (int e = 0; e < 32; ++e) {
+              for (int e = 0; e < 16; ++e) {
                 const float kd = (keep >> e) & 1u ? p.drop_scale : 0.f;
                 ds[e] = pd[e] * p.scale * fmaf(__uint_as_float(gv[e]), kd, -dl);
                 pd[e] *= kd;
               }
             } else {
 #pragma unroll
-              for (int e = 0; e < 32; ++e) ds[e] = pd[e] * p.scale * (__uint_as_float(gv[e]) - dl);
+              for (int e = 0; e < 16; ++e) ds[e] = pd[e] * p.scale * (__uint_as_float(gv[e]) - dl);
             }
           }
-          if (KEY_MAJOR) store_prob_columns(sP_gen, r, c, pd);
-          store_prob_columns(sdS_gen, r, c, ds);
+          if (KEY_MAJOR) store_prob_columns16(sP_gen, r, c, pd);
+          store_prob_columns16(sdS_gen, r, c, ds);
         }
         tc_fence_before();
         mbar_arrive(s_empty);
@@ -632,26 +676,26 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap tmQKV, const __gri
         ++n_in;
       }
       if (!ok) break;
-      // epilogue: 32 of the 64 columns of this thread's row of the accumulators (a key row, or a query row)
+      // epilogue: 16 of the 64 columns of this thread's row of the accumulators (a key row, or a query row)
       if (!mbar_wait(acc_full, n_out & 1u)) { ok = false; break; }
       tc_fence_after();
       const int row = o * BT + r;
-      unsigned a0[32];
-      float v[32];
-      tmem_ld_32x32(tA0 + lane_off + 32u * half, a0);
+      unsigned a0[16];
+      float v[16];
+      tmem_ld_32x16(tA0 + lane_off + 16u * part, a0);
       tmem_ld_wait();
 #pragma unroll
-      for (int d = 0; d < 32; ++d) v[d] = __uint_as_float(a0[d]);
-      __nv_bfloat16* grow = p.dqkv + ((long long)row * p.N + b) * (3LL * p.E) + h * HD + 32 * half;
+      for (int d = 0; d < 16; ++d) v[d] = __uint_as_float(a0[d]);
+      __nv_bfloat16* grow = p.dqkv + ((long long)row * p.N + b) * (3LL * p.E) + h * HD + 16 * part;
       if (KEY_MAJOR) {
-        if (row < p.L) store_row32(grow + 2 * p.E, v);               // dV
-        tmem_ld_32x32(tA1 + lane_off + 32u * half, a0);
+        if (row < p.L) store_row16(grow + 2 * p.E, v);               // dV
+        tmem_ld_32x16(tA1 + lane_off + 16u * part, a0);
         tmem_ld_wait();
 #pragma unroll
-        for (int d = 0; d < 32; ++d) v[d] = __uint_as_float(a0[d]);
-        if (row < p.L) store_row32(grow + p.E, v);                   // dK
+        for (int d = 0; d < 16; ++d) v[d] = __uint_as_float(a0[d]);
+        if (row < p.L) store_row16(grow + p.E, v);                   // dK
       } else {
-        if (row < p.L) store_row32(grow, v);                         // dQ
+        if (row < p.L) store_row16(grow, v);                         // dQ
       }
       tc_fence_before();
       mbar_arrive(acc_empty);
