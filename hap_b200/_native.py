@@ -61,6 +61,9 @@ SIGNATURES = {
     "hapx_moe_rows_from_tokens": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "hapx_moe_tokens_from_rows": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "hapx_moe_weight_grad": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
+    "hapx_moe_rows_from_tokens_strided": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp]),
+    "hapx_moe_tokens_from_rows_strided": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp]),
+    "hapx_moe_weight_grad_strided": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp]),
     "hapx_attention_forward": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp]),
     "hapx_attention_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "hapx_attention_classify_mask": (_int, [_vp, _i64, _vp, _vp]),

@@ -305,17 +305,18 @@ class Comm:
 
     def all_to_all(self, inputs: Sequence[torch.Tensor], split_dim: int, cat_dim: int,
                    split_lengths: Sequence[int], cat_lengths: Sequence[int]) -> List[torch.Tensor]:
-        inputs = self._lists(inputs, "all_to_all")
         split_lengths = self._lengths(split_lengths, "all_to_all")
         cat_lengths = self._lengths(cat_lengths, "all_to_all")
-        ref = inputs[0]
-        nd = ref.dim()
+        nd = inputs[0].dim()
         split_dim, cat_dim = split_dim % nd, cat_dim % nd
         if split_dim == cat_dim:
             raise ValueError("all_to_all: split_dim and cat_dim must differ")
+        if self._alone and len(inputs) == 1 and inputs[0].is_cuda and \
+                inputs[0].shape[split_dim] == split_lengths[0] and inputs[0].shape[cat_dim] == cat_lengths[0]:
+            return list(inputs)                # a world of one: the tensor as it is, whatever its memory layout
+        inputs = self._lists(inputs, "all_to_all")
+        ref = inputs[0]
         d1, d2 = min(split_dim, cat_dim), max(split_dim, cat_dim)
-        if self._alone and all(t.shape[split_dim] == split_lengths[0] and t.shape[cat_dim] == cat_lengths[0] for t in inputs):
-            return inputs
         outs = []
         for r, t in zip(self.ranks(), inputs):
             if t.shape[split_dim] != sum(split_lengths):

@@ -169,23 +169,54 @@ def _moe_index(dense: torch.Tensor):
     return slot_token, slot_weight, token_slot, token_weight
 
 
-def _rows_from_tokens(x, slot_token, slot_weight, ec):
+def _token_view(t: torch.Tensor) -> torch.Tensor:
+    """A (b, s, d) token tensor the kernels can address in place: rows contiguous, both strides multiples of 8
+    elements (any dense permutation of (b, s) qualifies, e.g. a view of sequence-major memory); a copy otherwise."""
+    if t.stride(2) == 1 and t.stride(0) % 8 == 0 and t.stride(1) % 8 == 0 and t.data_ptr() % 16 == 0:
+        return t
+    return t.contiguous()
+
+
+def _rows_view(rows: torch.Tensor):
+    """(tensor, capacity flag) for a (b, e, c, d) row tensor: 0 for batch-major memory, c for expert-major memory
+    (a permuted view of a contiguous (e, b, c, d) tensor - what the expert GEMMs produce); a copy otherwise."""
+    if rows.is_contiguous():
+        return rows, 0
+    if rows.permute(1, 0, 2, 3).is_contiguous():
+        return rows, rows.shape[2]
+    return rows.contiguous(), 0
+
+
+def _new_rows(b, e, c, d, like: torch.Tensor, expert_major: bool) -> torch.Tensor:
+    if expert_major:
+        return torch.empty((e, b, c, d), dtype=like.dtype, device=like.device).permute(1, 0, 2, 3)
+    return torch.empty((b, e, c, d), dtype=like.dtype, device=like.device)
+
+
+def _rows_from_tokens(x, slot_token, slot_weight, e, c, expert_major=False):
     b, s, d = x.shape
-    x = x.contiguous()
-    rows = torch.empty((b, ec, d), dtype=x.dtype, device=x.device)
+    x = _token_view(x)
+    rows = _new_rows(b, e, c, d, x, expert_major)
     with _on_device(x.device):
-        N.check(N.lib.hapx_moe_rows_from_tokens(rows.data_ptr(), x.data_ptr(), slot_token.data_ptr(),
-                                                slot_weight.data_ptr() if slot_weight is not None else None, b, s, ec, d, _stream(x.device)))
+        N.check(N.lib.hapx_moe_rows_from_tokens_strided(rows.data_ptr(), x.data_ptr(), slot_token.data_ptr(),
+                                                        slot_weight.data_ptr() if slot_weight is not None else None, b, s, e * c, d,
+                                                        x.stride(0), x.stride(1), c if expert_major else 0, _stream(x.device)))
     return rows
 
 
-def _tokens_from_rows(rows, token_slot, token_weight, s):
-    b, ec, d = rows.shape
-    rows = rows.contiguous()
-    y = torch.empty((b, s, d), dtype=rows.dtype, device=rows.device)
+def _tokens_from_rows(rows, token_slot, token_weight, s, sequence_major=False):
+    """rows: (b, e, c, d) in either memory layout; the (b, s, d) result is a view of sequence-major memory when
+    asked (so that a gradient comes out in the layout of the tensor it belongs to)."""
+    b, e, c, d = rows.shape
+    rows, cap = _rows_view(rows)
+    if sequence_major:
+        y = torch.empty((s, b, d), dtype=rows.dtype, device=rows.device).permute(1, 0, 2)
+    else:
+        y = torch.empty((b, s, d), dtype=rows.dtype, device=rows.device)
     with _on_device(rows.device):
-        N.check(N.lib.hapx_moe_tokens_from_rows(y.data_ptr(), rows.data_ptr(), token_slot.data_ptr(),
-                                                token_weight.data_ptr() if token_weight is not None else None, b, s, ec, d, _stream(rows.device)))
+        N.check(N.lib.hapx_moe_tokens_from_rows_strided(y.data_ptr(), rows.data_ptr(), token_slot.data_ptr(),
+                                                        token_weight.data_ptr() if token_weight is not None else None, b, s, e * c, d,
+                                                        y.stride(0), y.stride(1), cap, _stream(rows.device)))
     return y
 
 
@@ -201,22 +232,24 @@ def _check_sparse(a: torch.Tensor, dense: torch.Tensor, what: str) -> None:
 
 class _SparseDispatch(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, disp):
+    def forward(ctx, x, disp, expert_major):
         b, s, e, c = disp.shape
         slot_token, slot_weight, token_slot, token_weight = _moe_index(disp)
         ctx.save_for_backward(token_slot, token_weight)
         ctx.meta = (s, e, c)
-        return _rows_from_tokens(x, slot_token, slot_weight, e * c).view(b, e, c, x.shape[2])
+        ctx.x_sequence_major = (not x.is_contiguous()) and x.permute(1, 0, 2).is_contiguous()
+        return _rows_from_tokens(x, slot_token, slot_weight, e, c, expert_major)
 
     @staticmethod
     def backward(ctx, g):
         token_slot, token_weight = ctx.saved_tensors
         s, e, c = ctx.meta
-        b, d = g.shape[0], g.shape[3]
         if ctx.needs_input_grad[1]:
             raise NotImplementedError("sparse_dispatch: the dispatch tensor is a constant of the gating function ((combine > 0), models.py:500)")
-        dx = _tokens_from_rows(g.contiguous().view(b, e * c, d), token_slot, token_weight, s) if ctx.needs_input_grad[0] else None
-        return dx, None
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = _tokens_from_rows(g, token_slot, token_weight, s, ctx.x_sequence_major)
+        return dx, None, None
 
 
 class _SparseCombine(torch.autograd.Function):
@@ -225,32 +258,34 @@ class _SparseCombine(torch.autograd.Function):
         b, e, c, d = eo.shape
         s = comb.shape[1]
         slot_token, slot_weight, token_slot, token_weight = _moe_index(comb)
-        eo = eo.contiguous()
+        eo, cap = _rows_view(eo)
         ctx.save_for_backward(eo, slot_token, slot_weight, token_slot)
-        ctx.meta = (s, e, c)
-        return _tokens_from_rows(eo.view(b, e * c, d), token_slot, token_weight, s)
+        ctx.meta = (s, e, c, cap)
+        return _tokens_from_rows(eo, token_slot, token_weight, s)
 
     @staticmethod
     def backward(ctx, g):
         eo, slot_token, slot_weight, token_slot = ctx.saved_tensors
-        s, e, c = ctx.meta
+        s, e, c, cap = ctx.meta
         b, d = eo.shape[0], eo.shape[3]
-        g = g.contiguous()
+        g = _token_view(g)
         deo = dcomb = None
         if ctx.needs_input_grad[0]:
-            deo = _rows_from_tokens(g, slot_token, slot_weight, e * c).view(b, e, c, d)
+            deo = _rows_from_tokens(g, slot_token, slot_weight, e, c, expert_major=cap != 0)     # in the layout of the rows it belongs to
         if ctx.needs_input_grad[1]:
             dcomb = torch.empty((b, s, e, c), dtype=g.dtype, device=g.device)
             with _on_device(g.device):
-                N.check(N.lib.hapx_moe_weight_grad(dcomb.data_ptr(), eo.data_ptr(), g.data_ptr(), token_slot.data_ptr(), b, s, e * c, d,
-                                                   _stream(g.device)))
+                N.check(N.lib.hapx_moe_weight_grad_strided(dcomb.data_ptr(), eo.data_ptr(), g.data_ptr(), token_slot.data_ptr(), b, s, e * c, d,
+                                                           g.stride(0), g.stride(1), cap, _stream(g.device)))
         return deo, dcomb
 
 
-def sparse_dispatch(x: torch.Tensor, dispatch: torch.Tensor) -> torch.Tensor:
-    """``einsum("bsd,bsec->becd", x, dispatch)`` for a gating function's dispatch tensor, as a row gather."""
+def sparse_dispatch(x: torch.Tensor, dispatch: torch.Tensor, expert_major: bool = False) -> torch.Tensor:
+    """``einsum("bsd,bsec->becd", x, dispatch)`` for a gating function's dispatch tensor, as a row gather.
+    ``expert_major``: return the (b, e, c, d) result as a view of (e, b, c, d) memory, the layout the expert GEMMs
+    read - for when they consume it directly (no all_to_all in between)."""
     _check_sparse(x, dispatch, "sparse_dispatch")
-    return _SparseDispatch.apply(x, dispatch)
+    return _SparseDispatch.apply(x, dispatch, bool(expert_major))
 
 
 def sparse_combine(expert_out: torch.Tensor, combine: torch.Tensor) -> torch.Tensor:

@@ -123,8 +123,9 @@ def sparsify_moe(graph: torch.fx.Graph) -> int:
     ``hap.rs:2266-2276``) are rewritten to :func:`hap_b200.einsum.sparse_dispatch` / ``sparse_combine`` when D / C
     is ``getitem(g, 0)`` / ``getitem(g, 1)`` of a call of one of the reference's gating functions
     (``models.py:441-502``, matched by name), whose outputs hold at most one token per slot and at most two
-    slots per token.  Einsums fed by anything else are left on the dense kernels.  Returns the number of
-    nodes rewritten."""
+    slots per token.  Einsums fed by anything else are left on the dense kernels.  A dispatch whose rows feed
+    the expert contractions directly (single-rank programs) writes them in the experts' memory layout.  Returns
+    the number of nodes rewritten."""
     import operator
     from .einsum import einsum, sparse_combine, sparse_dispatch
 
@@ -141,7 +142,13 @@ def sparsify_moe(graph: torch.fx.Graph) -> int:
             continue
         code = node.args[0].replace(" ", "") if isinstance(node.args[0], str) else None
         if code == "bsd,bsec->becd" and from_gating(node.args[2], 0):
-            node.target, node.args = sparse_dispatch, (node.args[1], node.args[2])
+            # the rows go straight into the expert GEMMs' layout unless a real all_to_all (more than one rank in
+            # its length lists) stands between the gather and the experts
+            def exchanges(u):
+                return (u.op == "call_function" and getattr(u.target, "__name__", "") == "all_to_all"
+                        and any(isinstance(a, (list, tuple)) and len(a) > 1 for a in u.args))
+            expert_major = not any(exchanges(u) for u in node.users)
+            node.target, node.args = sparse_dispatch, (node.args[1], node.args[2], expert_major)
             changed += 1
         elif code == "becd,bsec->bsd" and from_gating(node.args[2], 1):
             node.target, node.args = sparse_combine, (node.args[1], node.args[2])

@@ -440,6 +440,16 @@ def emit_vit(model: ViT, plan: str, ratios: Sequence[float], rank: int, batch: i
 # ---------------------------------------------------------------------------------------------
 # MoE Transformer (expert-parallel configuration)
 # ---------------------------------------------------------------------------------------------
+_LOWER_ONES = {}
+
+
+def _lower_ones(n: int, device) -> torch.Tensor:
+    key = (n, str(device))
+    if key not in _LOWER_ONES:
+        _LOWER_ONES[key] = torch.ones(n, n, dtype=torch.float32, device=device).tril()
+    return _LOWER_ONES[key]
+
+
 def top2_gating(x, gate_weight, n_expert: int, capacity: int):
     """Top-2 gating with a fixed per-expert capacity; reproduces the reference's fx-wrapped
     ``top_2_gating`` (``models.py:477-502``) entry for entry: softmax gate, two best experts per
@@ -451,18 +461,25 @@ def top2_gating(x, gate_weight, n_expert: int, capacity: int):
     Plain torch ops: the planner treats this function as an opaque leaf (``hap.rs:2169``)."""
     gates = torch.softmax(torch.matmul(x, gate_weight).float(), dim=2)                   # (b, s, e)
     top_p, top_i = torch.topk(gates, 2, dim=2)                                           # (b, s, 2)
-    chosen = F.one_hot(top_i, n_expert)                                                  # (b, s, 2, e)
+    chosen = F.one_hot(top_i, n_expert).to(torch.float32)                                # (b, s, 2, e)
     first, second = chosen[:, :, 0, :], chosen[:, :, 1, :]
-    slot1 = torch.cumsum(first, dim=1) * first                                           # 1-based
-    slot2 = (torch.cumsum(second, dim=1) + slot1.sum(dim=1, keepdim=True)) * second
-    keep1, keep2 = (slot1 > 0) & (slot1 < capacity), (slot2 > 0) & (slot2 < capacity)
-    combine = torch.zeros(*gates.shape, capacity, dtype=gates.dtype, device=x.device)    # (b, s, e, c)
-    for keep, slot, p in ((keep1, slot1, top_p[:, :, 0]), (keep2, slot2, top_p[:, :, 1])):
-        w = (p.unsqueeze(2) * keep).unsqueeze(3)                                         # (b, s, e, 1)
-        combine = combine + w * F.one_hot((slot * keep).clamp(max=capacity - 1), capacity)
-    dispatch = (combine > 0).to(x.dtype)
-    return dispatch, combine.to(x.dtype)
-
+    # running counts along the sequence as a product with a lower-triangular matrix of ones: exact in float32
+    # (counts stay below 2^24) and an order of magnitude faster on a GPU than an int64 scan over the middle dimension
+    tri = _lower_ones(x.shape[1], x.device)
+    slot1 = torch.matmul(tri, first) * first                                             # 1-based
+    slot2 = (torch.matmul(tri, second) + slot1.sum(dim=1, keepdim=True)) * second
+    # Only the two chosen experts of a token can hold a non-zero entry, and they differ, so the (b, s, e, c) tensors
+    # are written by scattering two values per token instead of by dense one-hot arithmetic over all e * c entries
+    # (the reference's sums of `weight * one_hot(slot)` add zeros everywhere else).
+    slots = torch.stack((slot1.gather(2, top_i[:, :, 0:1]), slot2.gather(2, top_i[:, :, 1:2])), dim=2).squeeze(3)   # (b, s, 2)
+    keep = (slots > 0) & (slots < capacity)
+    index = top_i * capacity + (slots * keep).clamp(max=capacity - 1).long()             # position in (e * c)
+    weight32 = top_p * keep                                                              # (b, s, 2), zero where dropped
+    weight = weight32.to(x.dtype)
+    b, s = x.shape[0], x.shape[1]
+    combine = torch.zeros(b, s, n_expert * capacity, dtype=x.dtype, device=x.device).scatter(2, index, weight)
+    dispatch = torch.zeros(b, s, n_expert * capacity, dtype=x.dtype, device=x.device).scatter(2, index, (weight32 > 0).to(x.dtype))
+    return dispatch.view(b, s, n_expert, capacity), combine.view(b, s, n_expert, capacity)
 
 class MoETransformerLM(torch.nn.Module):
     """Post-LN MoE Transformer LM in the shape of the reference's ``Top2TransformerEncoderLayer``

@@ -240,6 +240,17 @@ int hapx_moe_tokens_from_rows(void* y, const void* rows, const int32_t* token_sl
                               int64_t S, int64_t EC, int64_t D, hapx_stream stream);
 int hapx_moe_weight_grad(void* d_dense, const void* rows, const void* dy, const int32_t* token_slot, int64_t B, int64_t S,
                          int64_t EC, int64_t D, hapx_stream stream);
+/* The same three with explicit layouts, so that no copy stands between the gathers and their neighbours:
+ * token tensors (x, y, dy) are addressed as base + b * stride_b + s * stride_s (elements, multiples of 8; rows of D
+ * contiguous elements) - e.g. a (b, s, d) view of sequence-major memory; `rows_capacity` > 0 says that the
+ * (b, e, c, d) row tensor lies in expert-major memory (e, b, c, d) with c = rows_capacity, the layout the expert
+ * GEMMs work on (0: batch-major, as above). */
+int hapx_moe_rows_from_tokens_strided(void* rows, const void* x, const int32_t* slot_token, const float* slot_weight, int64_t B, int64_t S,
+                                      int64_t EC, int64_t D, int64_t x_stride_b, int64_t x_stride_s, int64_t rows_capacity, hapx_stream stream);
+int hapx_moe_tokens_from_rows_strided(void* y, const void* rows, const int32_t* token_slot, const float* token_weight, int64_t B, int64_t S,
+                                      int64_t EC, int64_t D, int64_t y_stride_b, int64_t y_stride_s, int64_t rows_capacity, hapx_stream stream);
+int hapx_moe_weight_grad_strided(void* d_dense, const void* rows, const void* dy, const int32_t* token_slot, int64_t B, int64_t S, int64_t EC,
+                                 int64_t D, int64_t dy_stride_b, int64_t dy_stride_s, int64_t rows_capacity, hapx_stream stream);
 
 /* ---- multi-head self-attention on a batch shard ---------------------------------------------
  * Replace the attention core of F.multi_head_attention_forward as emitted at hap.rs:1297-1329

@@ -118,3 +118,35 @@ def test_sparse_dispatch_and_combine_equal_the_dense_einsums(b, s, e, c, d):
     nz = comb != 0
     torch.testing.assert_close(combd.grad.cpu().double()[nz], ref_comb.grad[nz], rtol=2e-2, atol=2e-2 * float(ref_comb.grad[nz].abs().max()))
     assert float(combd.grad.cpu()[~nz].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("b,s,e,c,d", [(3, 96, 8, 20, 256), (2, 40, 5, 6, 64)])
+def test_sparse_gathers_work_in_the_neighbours_layouts(b, s, e, c, d):
+    """No copy between the gathers and their neighbours: tokens as a (b, s, d) view of sequence-major memory, rows in
+    the expert-major memory the expert contractions use; values and gradients equal the batch-major call's, and the
+    gradients come out in the layout of the tensors they belong to."""
+    from hap_b200.einsum import sparse_combine, sparse_dispatch
+    from hap_b200.plan import top2_gating
+    g = torch.Generator().manual_seed(b * 77 + s)
+    x_sb = torch.randn(s, b, d, generator=g).to(torch.bfloat16).to(DEV)             # sequence-major memory
+    gate_w = (torch.randn(d, e, generator=g) * d ** -0.5).to(torch.bfloat16).to(DEV)
+    x_view = x_sb.transpose(0, 1).requires_grad_(True)                               # (b, s, d) view
+    x_flat = x_sb.transpose(0, 1).contiguous().requires_grad_(True)
+    disp, comb = top2_gating(x_flat.detach(), gate_w, e, c)
+    plain = sparse_dispatch(x_flat, disp)
+    major = sparse_dispatch(x_view, disp, expert_major=True)
+    assert plain.is_contiguous() and major.permute(1, 0, 2, 3).is_contiguous() and torch.equal(plain, major)
+    w = torch.randn(e, b, c, d, generator=g).to(torch.bfloat16).to(DEV).permute(1, 0, 2, 3)   # a gradient in expert-major memory
+    plain.backward(w.contiguous())
+    major.backward(w)
+    assert torch.equal(x_flat.grad, x_view.grad) and x_view.grad.stride() == x_view.stride()
+    eo_major = torch.randn(e, b, c, d, generator=g).to(torch.bfloat16).to(DEV).permute(1, 0, 2, 3).requires_grad_(True)
+    eo_plain = eo_major.detach().contiguous().requires_grad_(True)
+    comb_a, comb_b = comb.detach().requires_grad_(True), comb.detach().requires_grad_(True)
+    y_a, y_b = sparse_combine(eo_plain, comb_a), sparse_combine(eo_major, comb_b)
+    assert torch.equal(y_a, y_b)
+    gy = torch.randn(s, b, d, generator=g).to(torch.bfloat16).to(DEV).transpose(0, 1)          # sequence-major gradient
+    y_a.backward(gy.contiguous())
+    y_b.backward(gy)
+    assert torch.equal(eo_plain.grad, eo_major.grad) and eo_major.grad.permute(1, 0, 2, 3).is_contiguous()
+    assert torch.equal(comb_a.grad, comb_b.grad)
