@@ -54,6 +54,8 @@ struct Params {
   int splits;             // > 1: the contraction is cut into `splits` ranges of kb_per_split slices, each
   int kb_per_split;       //      writing an fp32 partial tile to rows [split * m_pad, ...) of the workspace
   int m_pad;
+  int a_chunked, b_chunked;  // pair kernel: the MN-major operand's map is the 5-D one (two 64-element chunks per load); for B the
+                          // 4-D map then travels in the half-width slot
   int tail_begin;         // pair kernel: tiles [tail_begin, m_tiles * n_tiles) are worked on as two half-width units each, so that
                           // the last, partly filled round of tiles takes half as long (only without batching and split-K)
   // batched operation: `batch` independent GEMMs; batch index b = b_out * batch_in + b_in and every
@@ -482,6 +484,14 @@ __device__ __forceinline__ void tma_load_4d_pair(unsigned dst, const CUtensorMap
       "l"(map), "r"(x), "r"(y), "r"(bi), "r"(bo), "r"(leader_bar)
       : "memory");
 }
+// The same through a 5-D map (64 contiguous elements, contraction row, 64-element chunk, batch_in, batch_out): one
+// instruction fetches the two adjacent 64 x 64 chunks of an MN-major operand tile that otherwise take two.
+__device__ __forceinline__ void tma_load_5d_pair(unsigned dst, const CUtensorMap* map, int row, int chunk, int bi, int bo, unsigned leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(dst),
+      "l"(map), "r"(0), "r"(row), "r"(chunk), "r"(bi), "r"(bo), "r"(leader_bar)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_alloc2(unsigned dst_smem, unsigned cols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
 }
@@ -611,14 +621,19 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const int k0 = kb * BK;
           if (!A_MN) {
             tma_load_4d_pair(sa, &tmA, k0, cur.m0, cur.bi, cur.boA, leader_full);
+          } else if (p.a_chunked) {
+            tma_load_5d_pair(sa, &tmA, k0, cur.m0 >> 6, cur.bi, cur.boA, leader_full);                         // both 64-row chunks at once
           } else {
 #pragma unroll
             for (int i = 0; i < BM / 64; ++i) tma_load_4d_pair(sa + i * 8192u, &tmA, cur.m0 + 64 * i, k0, cur.bi, cur.boA, leader_full);
           }
           if (!B_MN) {
             tma_load_4d_pair(sb, cur.width == BN ? &tmB : &tmBh, k0, cur.n0, cur.bi, cur.boB, leader_full);   // BN/2 (or BN/4) rows of B per CTA
+          } else if (p.b_chunked && cur.width == BN) {
+            tma_load_5d_pair(sb, &tmB, k0, cur.n0 >> 6, cur.bi, cur.boB, leader_full);                         // both 64-column chunks at once
           } else {
-            for (int i = 0; i < cur.width / 128; ++i) tma_load_4d_pair(sb + i * 8192u, &tmB, cur.n0 + 64 * i, k0, cur.bi, cur.boB, leader_full);   // width/2 columns per CTA
+            const CUtensorMap* m4 = p.b_chunked ? &tmBh : &tmB;
+            for (int i = 0; i < cur.width / 128; ++i) tma_load_4d_pair(sb + i * 8192u, m4, cur.n0 + 64 * i, k0, cur.bi, cur.boB, leader_full);   // width/2 columns per CTA
           }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -745,6 +760,26 @@ static int encode_map(CUtensorMap* map, const void* ptr, CUtensorMapDataType typ
   CUresult r = fn(map, type, 4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(HAPX_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  return HAPX_OK;
+}
+
+// 5-D map of an MN-major bf16 operand whose M / N extent is a multiple of 64: (64 contiguous elements, contraction row,
+// chunk of 64, batch_in, batch_out), boxes of 64 x 64 x 2 - in shared memory the two chunks lie 8 KiB apart, exactly as two
+// separate 64 x 64 loads leave them.
+static int encode_chunked_map(CUtensorMap* map, const void* ptr, long long mn_extent, long long kc, long long ld, int batch_in, long long s_in,
+                              int batch_out, long long s_out) {
+  typedef CUresult (*Fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                         const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  Fn fn = reinterpret_cast<Fn>(encode_fn());
+  if (!fn) return fail(HAPX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const long long bs_in = (batch_in > 1 ? s_in : ld) * 2, bs_out = (batch_out > 1 ? s_out : ld) * 2;
+  cuuint64_t dims[5] = {64, (cuuint64_t)kc, (cuuint64_t)(mn_extent / 64), (cuuint64_t)batch_in, (cuuint64_t)batch_out};
+  cuuint64_t strides[4] = {(cuuint64_t)(ld * 2), 128, (cuuint64_t)bs_in, (cuuint64_t)bs_out};
+  cuuint32_t box[5] = {64, 64, 2, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(HAPX_ERR_CUDA, "cuTensorMapEncodeTiled (5-D) failed with code " + std::to_string((int)r));
   return HAPX_OK;
 }
 
@@ -975,7 +1010,14 @@ static int launch2(const Operand& A, const Operand& B, const Operand& Dop, Param
   if (p.splits > 1 && !p.tma_store) return fail(HAPX_ERR_EXTENT, "gemm: split-K needs an output width that is a multiple of 4");
   if (int e = make_map(&tmA, A, p.M, p.Kc, BM, p.batch_in, p.a_shared_out ? 1 : batch_out)) return e;
   if (int e = make_map(&tmB, B, p.N, p.Kc, C::BN / 2, p.batch_in, p.b_shared_out ? 1 : batch_out)) return e;
-  if (int e = make_map(&tmBh, B, p.N, p.Kc, C::BN / 4, p.batch_in, p.b_shared_out ? 1 : batch_out)) return e;
+  if (int e = make_map(&tmBh, B, p.N, p.Kc, C::BN / 4, p.batch_in, p.b_shared_out ? 1 : batch_out)) return e;   // MN-major: the same 64 x 64 boxes
+  // MN-major operands whose extent is a whole number of 64-element chunks: one load per stage instead of two
+  p.a_chunked = (A_MN && p.M % 64 == 0) ? 1 : 0;
+  p.b_chunked = (B_MN && p.N % 64 == 0) ? 1 : 0;
+  if (p.a_chunked)
+    if (int e = encode_chunked_map(&tmA, A.ptr, p.M, p.Kc, A.ld, p.batch_in, A.s_in, p.a_shared_out ? 1 : batch_out, A.s_out)) return e;
+  if (p.b_chunked)
+    if (int e = encode_chunked_map(&tmB, B.ptr, p.N, p.Kc, B.ld, p.batch_in, B.s_in, p.b_shared_out ? 1 : batch_out, B.s_out)) return e;
   // A last round that fills at most half of the SM pairs is run as half-width units (no partial sums, no second
   // launch): 96 tiles on 74 pairs take 1.5 tile times instead of 2.
   p.tail_begin = tiles;
