@@ -317,29 +317,63 @@ def run_collective_bench(args, job):
     host_out = [torch.empty(L[r], cols).pin_memory() for r in ranks]
     lc = hap_b200.LocalCollectives(comm) if emulated else None
 
-    def e2e_step():
-        d_sh = [torch.empty(L[r], cols, device=dev).copy_(h, non_blocking=True) for r, h in zip(ranks, host_shards)]
-        d_fu = [torch.empty(ROWS, cols, device=dev).copy_(host_full, non_blocking=True) for _ in ranks]
+    # Every step uploads its inputs from pinned host memory and brings the reduce_scatter result back.  The copies run
+    # on streams of their own: the upload of step k + 1 and the download of step k - 1 overlap with the collectives of
+    # step k (PCIe is full duplex), as a caller that feeds the library from the host would arrange it.
+    up_s, down_s, cur_s = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+    slots = [{"sh": [torch.empty(L[r], cols, device=dev) for r in ranks], "fu": [torch.empty(ROWS, cols, device=dev) for _ in ranks],
+              "up": torch.cuda.Event(), "free": torch.cuda.Event()} for _ in range(2)]
+
+    def upload(k):
+        slot = slots[k % 2]
+        with torch.cuda.stream(up_s):
+            up_s.wait_event(slot["free"])                 # the collectives that last read this slot are done
+            for d, h in zip(slot["sh"], host_shards):
+                d.copy_(h, non_blocking=True)
+            for d in slot["fu"]:
+                d.copy_(host_full, non_blocking=True)
+            slot["up"].record(up_s)
+
+    def e2e_step(k, last):
+        slot = slots[k % 2]
+        if not last:
+            upload(k + 1)
+        cur_s.wait_event(slot["up"])
         if emulated:
-            lc.all_gather(d_sh, 0, L)
-            rs = lc.reduce_scatter(d_fu, 0, L)
-            lc.all_reduce(d_fu)
+            lc.all_gather(slot["sh"], 0, L)
+            rs = lc.reduce_scatter(slot["fu"], 0, L)
+            lc.all_reduce(slot["fu"])
         else:
             col = hap_b200.collectives
-            col.all_gather(d_sh[0], 0, L, rank)
-            rs = [col.reduce_scatter(d_fu[0], 0, L, rank)]
-            col.all_reduce(d_fu[0])
-        for o, h in zip(rs, host_out):
-            h.copy_(o, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+            col.all_gather(slot["sh"][0], 0, L, rank)
+            rs = [col.reduce_scatter(slot["fu"][0], 0, L, rank)]
+            col.all_reduce(slot["fu"][0])
+        slot["free"].record(cur_s)
+        done = torch.cuda.Event()
+        done.record(cur_s)
+        with torch.cuda.stream(down_s):
+            down_s.wait_event(done)
+            for o, h in zip(rs, host_out):
+                o.record_stream(down_s)
+                h.copy_(o, non_blocking=True)
 
-    e2e_step()
+    def e2e_run(n):
+        for sl in slots:
+            sl["free"].record(cur_s)
+        upload(0)
+        for k in range(n):
+            e2e_step(k, k == n - 1)
+        cur_s.wait_stream(down_s)                         # the last result has reached the host
+        cur_s.wait_stream(up_s)
+
+    e2e_run(1)
+    torch.cuda.synchronize()
     barrier()
     b0, b1 = ev(), ev()
     b0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
+    e2e_run(e2e_steps)
     b1.record()
+    torch.cuda.synchronize()
     barrier()
     e2e_ms = job.max_over_ranks(b0.elapsed_time(b1)) / e2e_steps
     comm.check()
@@ -350,7 +384,8 @@ def run_collective_bench(args, job):
     e2e = {"value": bus_bytes(S, W) / (e2e_ms * 1e-3) / 1e9 * n_gpus, "unit": "GB/s", "h2d_bytes_per_step": int(h2d),
            "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms, "steps": e2e_steps,
            "api": "hap_b200.LocalCollectives" if emulated else "hap_b200.collectives (drop-in)",
-           "note": "ordinary torch tensors: every call also pays the copy into the staging area"}
+           "note": "ordinary torch tensors: every call also pays the copy into the staging area",
+           "pipeline": "uploads and downloads on their own streams: the next step's upload and the previous step's download overlap with this step's collectives"}
 
     # ---- roofline of the dominant kernel -----------------------------------------------------------
     peaks, peak_kind = measured_peaks()

@@ -277,6 +277,15 @@ def test_all_reduce_written_into_the_peers_outputs(world, dtype):
         comm.check()
         for r in range(world):
             torch.testing.assert_close(ordinary[r].cpu(), want, **TOL[dtype])
+        # a byte count that is not a multiple of 16: heap tensors all the same, but the launch reduces and gathers
+        m = n - 3
+        odd_src = [s_[:m] for s_ in src]
+        for s_, x in zip(odd_src, xs):
+            s_.copy_(x[:m].to(DEV))
+        odd = comm.all_reduce(odd_src, scale=0.25, out=[d[:m] for d in dst])
+        comm.check()
+        for r in range(world):
+            torch.testing.assert_close(odd[r].cpu(), cm.rank_sum([x[:m] for x in xs], 0.25, dtype), **TOL[dtype])
     finally:
         comm.destroy()
 
