@@ -254,14 +254,14 @@ class _SparseDispatch(torch.autograd.Function):
 
 class _SparseCombine(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, eo, comb):
+    def forward(ctx, eo, comb, sequence_major):
         b, e, c, d = eo.shape
         s = comb.shape[1]
         slot_token, slot_weight, token_slot, token_weight = _moe_index(comb)
         eo, cap = _rows_view(eo)
         ctx.save_for_backward(eo, slot_token, slot_weight, token_slot)
         ctx.meta = (s, e, c, cap)
-        return _tokens_from_rows(eo, token_slot, token_weight, s)
+        return _tokens_from_rows(eo, token_slot, token_weight, s, sequence_major)
 
     @staticmethod
     def backward(ctx, g):
@@ -277,7 +277,7 @@ class _SparseCombine(torch.autograd.Function):
             with _on_device(g.device):
                 N.check(N.lib.hapx_moe_weight_grad_strided(dcomb.data_ptr(), eo.data_ptr(), g.data_ptr(), token_slot.data_ptr(), b, s, e * c, d,
                                                            g.stride(0), g.stride(1), cap, _stream(g.device)))
-        return deo, dcomb
+        return deo, dcomb, None
 
 
 def sparse_dispatch(x: torch.Tensor, dispatch: torch.Tensor, expert_major: bool = False) -> torch.Tensor:
@@ -288,12 +288,13 @@ def sparse_dispatch(x: torch.Tensor, dispatch: torch.Tensor, expert_major: bool 
     return _SparseDispatch.apply(x, dispatch, bool(expert_major))
 
 
-def sparse_combine(expert_out: torch.Tensor, combine: torch.Tensor) -> torch.Tensor:
+def sparse_combine(expert_out: torch.Tensor, combine: torch.Tensor, sequence_major: bool = False) -> torch.Tensor:
     """``einsum("becd,bsec->bsd", expert_out, combine)`` for a gating function's combine tensor, as a weighted
     gather of at most two rows per token.  The gradient w.r.t. ``combine`` is produced at the positions
-    where ``combine`` is non-zero - the only ones a gating function's backward reads."""
+    where ``combine`` is non-zero - the only ones a gating function's backward reads.  ``sequence_major``: return
+    the (b, s, d) result as a view of (s, b, d) memory - for a program that transposes it right away."""
     _check_sparse(expert_out, combine, "sparse_combine")
-    return _SparseCombine.apply(expert_out, combine)
+    return _SparseCombine.apply(expert_out, combine, bool(sequence_major))
 
 
 def einsum(code: str, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:

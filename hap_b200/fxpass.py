@@ -151,7 +151,11 @@ def sparsify_moe(graph: torch.fx.Graph) -> int:
             node.target, node.args = sparse_dispatch, (node.args[1], node.args[2], expert_major)
             changed += 1
         elif code == "becd,bsec->bsd" and from_gating(node.args[2], 1):
-            node.target, node.args = sparse_combine, (node.args[1], node.args[2])
+            # a result that is only ever read through transpose(0, 1) is written in that memory order
+            users = list(node.users)
+            swapped = len(users) == 1 and users[0].op == "call_method" and users[0].target == "transpose" and \
+                tuple(users[0].args[1:]) in ((0, 1), (1, 0))
+            node.target, node.args = sparse_combine, (node.args[1], node.args[2], swapped)
             changed += 1
     graph.lint()
     return changed

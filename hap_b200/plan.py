@@ -459,15 +459,24 @@ def top2_gating(x, gate_weight, n_expert: int, capacity: int):
     A slot number must stay below ``capacity`` (slot 0 is never used); combine weight = the raw gate
     probability.  Returns (dispatch, combine), both (batch, seq, n_expert, capacity) in x's dtype.
     Plain torch ops: the planner treats this function as an opaque leaf (``hap.rs:2169``)."""
-    gates = torch.softmax(torch.matmul(x, gate_weight).float(), dim=2)                   # (b, s, e)
+    if not x.is_contiguous() and x.transpose(0, 1).is_contiguous():     # a (b, s, d) view of sequence-first memory:
+        logits = torch.matmul(x.transpose(0, 1), gate_weight).transpose(0, 1)   # multiply in memory order, no copy of x
+    else:
+        logits = torch.matmul(x, gate_weight)
+    gates = torch.softmax(logits.float(), dim=2)                                          # (b, s, e)
     top_p, top_i = torch.topk(gates, 2, dim=2)                                           # (b, s, 2)
     chosen = F.one_hot(top_i, n_expert).to(torch.float32)                                # (b, s, 2, e)
     first, second = chosen[:, :, 0, :], chosen[:, :, 1, :]
     # running counts along the sequence as a product with a lower-triangular matrix of ones: exact in float32
     # (counts stay below 2^24) and an order of magnitude faster on a GPU than an int64 scan over the middle dimension
     tri = _lower_ones(x.shape[1], x.device)
-    slot1 = torch.matmul(tri, first) * first                                             # 1-based
-    slot2 = (torch.matmul(tri, second) + slot1.sum(dim=1, keepdim=True)) * second
+    counts = torch.matmul(tri, chosen.flatten(2))                                        # (b, s, 2 e): both choices in one product
+    count1, count2 = counts[:, :, :n_expert], counts[:, :, n_expert:]
+    slot1 = count1 * first                                                               # 1-based
+    # the reference shifts an expert's second-choice slots by the SUM of its first-choice slot numbers; those are
+    # 1 ... n for n first choices, i.e. n (n + 1) / 2 with n the last running count (exact in float32)
+    n1 = count1[:, -1:, :]
+    slot2 = (count2 + n1 * (n1 + 1.0) * 0.5) * second
     # Only the two chosen experts of a token can hold a non-zero entry, and they differ, so the (b, s, e, c) tensors
     # are written by scattering two values per token instead of by dense one-hot arithmetic over all e * c entries
     # (the reference's sums of `weight * one_hot(slot)` add zeros everywhere else).
@@ -491,7 +500,7 @@ class MoETransformerLM(torch.nn.Module):
         self.vocab, self.d_model, self.nheads, self.nlayers, self.seqlen = vocab, d_model, nheads, nlayers, seqlen
         self.n_expert, self.capacity = n_expert, capacity
         self.embed = torch.nn.Embedding(vocab, d_model)
-        self.pos = torch.nn.Parameter(torch.randn(1, seqlen, d_model) * 0.02)
+        self.pos = torch.nn.Parameter((torch.randn(1, seqlen, d_model) * 0.02).transpose(0, 1).contiguous())   # (s, 1, d)
         P_ = lambda *shape, scale=1.0: torch.nn.Parameter(torch.randn(*shape) * scale)
         for i in range(nlayers):
             self.register_parameter(f"l{i}_in_w", P_(3 * d_model, d_model, scale=d_model ** -0.5))
@@ -527,17 +536,19 @@ def _moe_forward(m, tokens, targets, ns, emit, ratios, rank, batch, dropout_p=0.
     method = (lambda obj, name, *a: getattr(obj, name)(*a)) if emit is None else (lambda obj, name, *a: emit.call_method(name, (obj, *a)))
 
     drop = _dropout_of(ns, call, dropout_p)      # the Top-2 layer drops only after its attention block (models.py:346-351)
-    x = call(operator.add, call(F.embedding, tokens, param("embed.weight")), param("pos"))          # (b, s, E)
+    # sequence-first activations (s, b, E), as in the language model: contiguous in the (L, N, E) layout the attention
+    # handler wants (hap.rs:1284-1287); the gating function and the dispatch see the (b, s, E) view of the same memory
+    x = call(operator.add, call(F.embedding, method(tokens, "transpose", 0, 1), param("embed.weight")), param("pos"))
     for i in range(m.nlayers):
-        h = method(x, "transpose", 0, 1)                                                               # (s, b, E)
-        att = call(mha, query=h, key=h, value=h, embed_dim_to_check=E, num_heads=H, in_proj_weight=param(f"l{i}_in_w"),
+        att = call(mha, query=x, key=x, value=x, embed_dim_to_check=E, num_heads=H, in_proj_weight=param(f"l{i}_in_w"),
                    in_proj_bias=param(f"l{i}_in_b"), bias_k=None, bias_v=None, add_zero_attn=False, dropout_p=float(dropout_p),
                    out_proj_weight=param(f"l{i}_out_w"), out_proj_bias=param(f"l{i}_out_b"))
-        a = drop(method(call(operator.getitem, att, 0), "transpose", 0, 1))
+        a = drop(call(operator.getitem, att, 0))
         x = call(_ln(ns), call(operator.add, x, a), (E,), param(f"l{i}_ln1_w"), param(f"l{i}_ln1_b"))
-        gated = call(top2_gating, x, param(f"l{i}_gate"), ne, cap)
+        xb = method(x, "transpose", 0, 1)                                                              # (b_r, s, E)
+        gated = call(top2_gating, xb, param(f"l{i}_gate"), ne, cap)
         dispatch, combine = call(operator.getitem, gated, 0), call(operator.getitem, gated, 1)
-        ein = call(einsum, "bsd,bsec->becd", x, dispatch)                                              # (b_r, e, c, d)
+        ein = call(einsum, "bsd,bsec->becd", xb, dispatch)                                             # (b_r, e, c, d)
         if emit is not None:   # batch-sharded -> expert-sharded (hap.rs:2713-2744: all_to_all(x, split=j, cat=i, ...))
             le, lb = sharding_round(ne, ratios), sharding_round(batch, ratios)
             ein = emit.call_function(col.all_to_all, (ein, 1, 0, le, lb, rank))                       # (b, e_r, c, d)
@@ -545,10 +556,10 @@ def _moe_forward(m, tokens, targets, ns, emit, ratios, rank, batch, dropout_p=0.
         eo = call(einsum, "ehd,bech->becd", param(f"l{i}_w2", True), hid)
         if emit is not None:
             eo = emit.call_function(col.all_to_all, (eo, 0, 1, lb, le, rank))                         # (b_r, e, c, d)
-        y = call(einsum, "becd,bsec->bsd", eo, combine)
+        y = method(call(einsum, "becd,bsec->bsd", eo, combine), "transpose", 0, 1)                     # (s, b_r, d)
         x = call(_ln(ns), call(operator.add, x, y), (E,), param(f"l{i}_ln2_w"), param(f"l{i}_ln2_b"))
-    logits = call(linear, x, param("dec_w"), param("dec_b"))
-    return _summed_nll(ns, call, method, logits, targets, m.vocab)
+    logits = call(linear, x, param("dec_w"), param("dec_b"))                                           # (s, b_r, V)
+    return _summed_nll(ns, call, method, logits, method(targets, "transpose", 0, 1), m.vocab)
 
 
 def emit_moe(model: MoETransformerLM, ratios: Sequence[float], rank: int, batch: int, ns=None,
