@@ -152,7 +152,7 @@ class ProcessWorker:
         self.optimizer = self._make_optimizer(list(module.parameters()), lr, clip)
         self.uses_dropout = _program_has_dropout(module)
         self._buckets = []          # (flat tensor in the heap, [parameters])
-        if comm is not None:
+        if comm is not None and comm.world > 1:       # a world of one reduces nothing: gradients stay where autograd leaves them
             self._build_buckets()
 
     def _make_optimizer(self, params, lr, clip):
