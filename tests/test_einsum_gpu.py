@@ -150,3 +150,6 @@ def test_sparse_gathers_work_in_the_neighbours_layouts(b, s, e, c, d):
     y_b.backward(gy)
     assert torch.equal(eo_plain.grad, eo_major.grad) and eo_major.grad.permute(1, 0, 2, 3).is_contiguous()
     assert torch.equal(comb_a.grad, comb_b.grad)
+    # the combine written in sequence-major order, for a program that transposes it right away
+    y_c = sparse_combine(eo_major.detach(), comb.detach(), sequence_major=True)
+    assert y_c.transpose(0, 1).is_contiguous() and torch.equal(y_c, y_a.detach())

@@ -172,6 +172,17 @@ def test_moe_einsums_fed_by_a_gating_function_become_gathers():
     targets = [n.target for n in g.nodes if n.op == "call_function"]
     assert targets.count(sparse_dispatch) == nl and targets.count(sparse_combine) == nl
     assert targets.count(torch.einsum) == 2 * nl          # the two expert contractions stay dense
+    # two ranks: a real all_to_all follows the dispatch, so its rows stay batch-major; the combine's result is only read
+    # through transpose(0, 1), so it is written in that order
+    for n in g.nodes:
+        if n.op == "call_function" and n.target is sparse_dispatch:
+            assert n.args[2] is False
+        if n.op == "call_function" and n.target is sparse_combine:
+            assert n.args[2] is True
+    # one rank: the rows go straight to the expert contractions, in their memory layout
+    g1 = P.emit_moe(copy.deepcopy(moe), [1.0], 0, C.LM_BATCH, C.moe_cpu_namespace())
+    assert fxpass.sparsify_moe(g1) == 2 * nl
+    assert all(n.args[2] is True for n in g1.nodes if n.op == "call_function" and n.target is sparse_dispatch)
     # an einsum whose second operand is not a gating output is left alone
     g2 = torch.fx.Graph()
     x, d = g2.placeholder("x"), g2.placeholder("d")
