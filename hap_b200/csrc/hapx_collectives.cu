@@ -1035,6 +1035,10 @@ int hapx_all_reduce(hapx_comm* c, void* const* dst, const void* const* src, int 
   // Outputs that lie in the peer-visible heap can be written by the slice owners directly; whether all of them
   // do is settled between the ranks inside the kernel (a rank only knows its own).
   R.push = (c->fused_all_reduce == 2 || c->fused_all_reduce < 0) && (in_bytes % 16 == 0) && (((size_t)n * es_out) % 16 == 0);
+  // Measured on 8 GPUs: writing into seven peers at once wins up to 64 MiB (1.1 - 2.1 x NCCL) and loses above 128 MiB
+  // (1 GiB: 3.14 ms against 3.00 ms for reduce + gather); on 2 and 4 GPUs it is never slower.  Unless forced, wide
+  // communicators therefore keep reduce + gather for the largest tensors (a rule of n and W only: every rank agrees).
+  if (c->fused_all_reduce < 0 && W > 4 && in_bytes > ((size_t)128 << 20)) R.push = 0;
   for (int i = 0; i < c->n_local; ++i) {
     const int r = c->first_rank + i;
     const char* d = static_cast<const char*>(dst[i]);

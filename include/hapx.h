@@ -123,7 +123,8 @@ int hapx_comm_set_max_ctas(hapx_comm* c, int ctas);
  *      output lies in its rank's peer-visible heap and the byte count is a multiple of 16 (the in-place all_reduce
  *      of a heap-resident gradient bucket): each byte crosses the links once per direction and there is no second
  *      phase.  The ranks settle inside the kernel whether all outputs qualify; if not, the launch proceeds as form 1.
- *  -1  the default: 2 between processes, 0 in the single-device emulation (no launch or flag latency to save there).
+ *  -1  the default: 2 between processes (1 for tensors above 128 MiB on more than 4 GPUs, where writing into seven
+ *      peers at once measured slower), 0 in the single-device emulation (no launch or flag latency to save there).
  * Every rank of a communicator must use the same setting. */
 int hapx_comm_set_fused_all_reduce(hapx_comm* c, int mode);
 /* Calls issued on different streams are ordered with an event by default.  Turn that off
