@@ -75,6 +75,7 @@ SIGNATURES = {
     "hapx_nll_logsoftmax_forward": (_int, [_vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _vp]),
     "hapx_nll_logsoftmax_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _vp]),
     "hapx_layer_norm_forward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _dbl, _vp]),
+    "hapx_embedding_backward": (_int, [_vp, _vp, _vp, _int, _i64, _i64, _i64, _vp]),
     "hapx_layer_norm_backward_blocks": (_int, [_i64, _i64]),
     "hapx_layer_norm_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _vp]),
     "hapx_layer_norm_backward_add": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _vp]),

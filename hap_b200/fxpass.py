@@ -30,17 +30,19 @@ def retarget_tensor_ops(graph: torch.fx.Graph, fold_loss: bool = True) -> Dict[s
     * ``torch.einsum`` with one of the four MoE codes -> :func:`hap_b200.einsum`
     * ``F.layer_norm`` -> :func:`hap_b200.layer_norm`
     * ``F.dropout`` (``hap.rs:1446-1464``) -> :func:`hap_b200.dropout.dropout`
+    * ``F.embedding`` -> :func:`hap_b200.embedding.embedding` (torch's forward, this package's backward kernel)
     * ``nll_loss(log_softmax(x[.float()], -1)[.reshape(-1, V)], y[.reshape(-1)], reduction='sum')``
       -> :func:`hap_b200.nll_log_softmax_sum` ``(x, y)`` when the intermediate nodes have no other user.
     """
     from .attention import multi_head_attention_forward
     from .dropout import dropout
     from .einsum import CODES as SUPPORTED_CODES, einsum
+    from .embedding import embedding
     from .linear import linear
     from .loss import nll_log_softmax_sum
     from .norm import layer_norm
 
-    changed = {"linear": 0, "multi_head_attention_forward": 0, "einsum": 0, "layer_norm": 0, "dropout": 0, "loss": 0}
+    changed = {"linear": 0, "multi_head_attention_forward": 0, "einsum": 0, "layer_norm": 0, "dropout": 0, "embedding": 0, "loss": 0}
     for node in list(graph.nodes):
         if node.op != "call_function":
             continue
@@ -60,6 +62,9 @@ def retarget_tensor_ops(graph: torch.fx.Graph, fold_loss: bool = True) -> Dict[s
         elif _is(t, F.dropout):
             node.target = dropout
             changed["dropout"] += 1
+        elif _is(t, F.embedding):
+            node.target = embedding
+            changed["embedding"] += 1
         elif fold_loss and _is(t, F.nll_loss) and _fold_loss(graph, node, nll_log_softmax_sum):
             changed["loss"] += 1
     graph.lint()

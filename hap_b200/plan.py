@@ -42,6 +42,11 @@ class MLP(torch.nn.Module):
         return F.mse_loss(self.fc2(F.gelu(self.fc1(x))), y, reduction="sum")
 
 
+def _emb(ns):
+    """embedding of the namespace (torch's forward, this package's backward kernel by default), else torch's."""
+    return getattr(ns, "embedding", None) or F.embedding
+
+
 def _ln(ns):
     """layer_norm of the namespace (this package's kernels by default), else torch's."""
     return getattr(ns, "layer_norm", None) or F.layer_norm
@@ -63,11 +68,12 @@ def default_namespace() -> SimpleNamespace:
     from .attention import multi_head_attention_forward
     from .dropout import dropout
     from .einsum import einsum
+    from .embedding import embedding
     from .linear import linear
     from .loss import nll_log_softmax_sum
     from .norm import layer_norm
     return SimpleNamespace(collectives=collectives, linear=linear, mha=multi_head_attention_forward, einsum=einsum,
-                           nll=nll_log_softmax_sum, layer_norm=layer_norm, dropout=dropout)
+                           nll=nll_log_softmax_sum, layer_norm=layer_norm, dropout=dropout, embedding=embedding)
 
 
 def _dropout_of(ns, call, p):
@@ -232,7 +238,7 @@ def _lm_forward(m, tokens, targets, ns, emit, ratios, rank, plan, dropout_p=0.0)
     drop = _dropout_of(ns, call, dropout_p)
     # look the tokens up in (S, B) order: the activations are then contiguous in the (L, N, E) layout the
     # attention handler wants (hap.rs:1284-1287) instead of a transposed view that every layer_norm copies
-    x = call(F.embedding, method(tokens, "transpose", 0, 1), param("embed.weight"))   # (S, B, E)
+    x = call(_emb(ns), method(tokens, "transpose", 0, 1), param("embed.weight"))   # (S, B, E)
     x = call(operator.add, x, param("pos"))
     S = m.seqlen
     mask = call(torch.triu, call(torch.full, (S, S), float("-inf"), device=_device_of(m), dtype=m.pos.dtype), 1)
@@ -538,7 +544,7 @@ def _moe_forward(m, tokens, targets, ns, emit, ratios, rank, batch, dropout_p=0.
     drop = _dropout_of(ns, call, dropout_p)      # the Top-2 layer drops only after its attention block (models.py:346-351)
     # sequence-first activations (s, b, E), as in the language model: contiguous in the (L, N, E) layout the attention
     # handler wants (hap.rs:1284-1287); the gating function and the dispatch see the (b, s, E) view of the same memory
-    x = call(operator.add, call(F.embedding, method(tokens, "transpose", 0, 1), param("embed.weight")), param("pos"))
+    x = call(operator.add, call(_emb(ns), method(tokens, "transpose", 0, 1), param("embed.weight")), param("pos"))
     for i in range(m.nlayers):
         att = call(mha, query=x, key=x, value=x, embed_dim_to_check=E, num_heads=H, in_proj_weight=param(f"l{i}_in_w"),
                    in_proj_bias=param(f"l{i}_in_b"), bias_k=None, bias_v=None, add_zero_attn=False, dropout_p=float(dropout_p),

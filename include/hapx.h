@@ -394,6 +394,15 @@ int hapx_nll_logsoftmax_backward(const void* logits, const int64_t* targets, con
                                  void* grad_logits, int dtype, int64_t rows, int64_t classes, int64_t pitch,
                                  int64_t grad_pitch, hapx_stream stream);
 
+/* ---- gradient of an embedding lookup ----------------------------------------------------
+ * Replaces the backward pass of the torch.nn.functional.embedding nodes (the models look their tokens up with
+ * it, models.py:66-71): dweight[v, :] = sum of grad[i, :] over the positions i with idx[i] == v, added in
+ * ascending order of position in float32 (bit-reproducible; no sort, no atomics), all other rows zero.
+ * dweight: V x E, grad: n x E of `dtype` (HAPX_F32 / HAPX_BF16), idx: n int64; E a multiple of 8 in [8, 2048],
+ * n <= 2^20 (the kernel compares every position with every other one). */
+int hapx_embedding_backward(void* dweight, const void* grad, const int64_t* idx, int dtype, int64_t n, int64_t V, int64_t E,
+                            hapx_stream stream);
+
 /* ---- layer_norm over the last dimension ---------------------------------------------
  * Replaces the torch.nn.functional.layer_norm nodes of the Transformer programs (planner
  * handler hap.rs:1637-1660; nn.LayerNorm of the reference's encoder layers, models.py:319-320).

@@ -22,7 +22,7 @@ def test_targets_are_swapped_and_the_loss_pair_is_folded():
     assert "log_softmax" in before and "nll_loss" in before
     changed = fxpass.retarget_tensor_ops(graph)
     nl = C.LM_SMALL["nlayers"]
-    assert changed == {"linear": 2 * nl + 1, "multi_head_attention_forward": nl, "einsum": 0, "layer_norm": 2 * nl + 1, "dropout": 3 * nl, "loss": 1}
+    assert changed == {"linear": 2 * nl + 1, "multi_head_attention_forward": nl, "einsum": 0, "layer_norm": 2 * nl + 1, "dropout": 3 * nl, "embedding": 1, "loss": 1}
     after = [n for n in graph.nodes if n.op == "call_function"]
     assert not any(n.target in (F.linear, F.layer_norm, F.multi_head_attention_forward, F.nll_loss, F.log_softmax, F.dropout) for n in after)
     assert all(n.kwargs["dropout_p"] == 0.1 for n in after if n.target is hap_b200.attention.multi_head_attention_forward)
