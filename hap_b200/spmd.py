@@ -203,23 +203,32 @@ class ProcessWorker:
         for dtype, ps in by_dtype.items():
             total = sum((p.numel() + 7) // 8 * 8 for p in ps)
             flat = self.comm.symm_empty((total,), dtype)
-            flat.zero_()
-            off = 0
+            flat.zero_()                  # the gaps between parameters stay zero: only parameter regions are ever written
+            off, views = 0, []
             for p in ps:
-                p.grad = flat[off:off + p.numel()].view_as(p)
+                views.append(flat[off:off + p.numel()].view_as(p))
                 off += (p.numel() + 7) // 8 * 8
-            self._buckets.append((flat, ps))
+            self._buckets.append((flat, ps, views))
 
     def zero_grad(self) -> None:
-        if not self._buckets:
-            self.optimizer.zero_grad()
-            return
-        bucketed = {id(p) for _, ps in self._buckets for p in ps}
-        for flat, _ in self._buckets:
-            flat.zero_()
+        # gradients are left where autograd puts them (no accumulation kernels into preset buffers); the replicated
+        # parameters' gradients are packed into their bucket after the backward pass, see _fill_buckets
         for p in self.module.parameters():
-            if id(p) not in bucketed:
-                p.grad = None
+            p.grad = None
+
+    def _fill_buckets(self) -> None:
+        """Copy the replicated parameters' gradients into their flat, peer-visible buckets (one multi-tensor copy per
+        bucket instead of one accumulation kernel per parameter) and make the bucket slices the gradients the
+        optimizer reads: the all_reduce that follows works in place on the bucket."""
+        for flat, ps, views in self._buckets:
+            dst = [v for p, v in zip(ps, views) if p.grad is not None]
+            src = [p.grad for p in ps if p.grad is not None]
+            if dst:
+                torch._foreach_copy_(dst, src)
+            for p, v in zip(ps, views):
+                if p.grad is None:
+                    v.zero_()             # a parameter the program did not use
+                p.grad = v
 
     def capture(self, *example_inputs, warmup: int = 3):
         """Record one whole iteration (zero_grad ... optimizer step) into a CUDA graph and return a
@@ -288,7 +297,8 @@ class ProcessWorker:
             finally:
                 collectives.defer_replicate(False)
             self._join_side_stream()
-            for flat, _ in self._buckets:
+            self._fill_buckets()
+            for flat, _, _ in self._buckets:
                 self.comm.all_reduce([flat], inplace=True)
         else:
             loss.backward()
