@@ -41,3 +41,24 @@ def test_fixture_covers_the_second_choice_offset():
     by_count = (torch.cumsum(second, 1) + first.sum(1, keepdim=True)) * second
     kept_by_count = int(((by_count > 0) & (by_count < c)).sum()) + int((((torch.cumsum(first, 1) * first) > 0) & ((torch.cumsum(first, 1) * first) < c)).sum())
     assert kept_by_count > case["dispatch_nonzero"].shape[0]
+
+
+@pytest.mark.parametrize("name", sorted(GOLDEN))
+def test_top2_gating_on_a_view_of_sequence_first_memory(name):
+    """The MoE program is sequence-first: the gating function sees a (b, s, d) view of (s, b, d) memory.  Same
+    outputs and the same gradient of the gate weights and of x as with a contiguous tensor."""
+    case = GOLDEN[name]
+    x = case["x"]
+    x_a = x.clone().requires_grad_(True)
+    w_a = case["gate_weight"].clone().requires_grad_(True)
+    base = x.transpose(0, 1).contiguous().requires_grad_(True)            # (s, b, d) memory
+    w_b = case["gate_weight"].clone().requires_grad_(True)
+    d_a, c_a = top2_gating(x_a, w_a, case["n_expert"], case["capacity"])
+    d_b, c_b = top2_gating(base.transpose(0, 1), w_b, case["n_expert"], case["capacity"])
+    assert torch.equal(d_a, d_b) and torch.equal(c_a, c_b)
+    probe = torch.randn(c_a.shape, generator=torch.Generator().manual_seed(5))
+    (c_a * probe).sum().backward()
+    (c_b * probe).sum().backward()
+    # the products sum over (b, s) in a different order: float32 rounding apart
+    torch.testing.assert_close(w_a.grad, w_b.grad, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(x_a.grad, base.grad.transpose(0, 1), rtol=1e-4, atol=1e-6)
